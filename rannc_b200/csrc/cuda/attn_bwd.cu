@@ -1,0 +1,439 @@
+// Fused multi-head attention backward on tcgen05 tensor cores (head dim 64).
+//
+// One CTA owns 128 keys of one (batch, head) and sweeps the query blocks.  Per
+// query block i it recomputes, with the keys on the TMEM lanes,
+//     St  = K_j Q_i^T          dPt = V_j dO_i^T                (TMEM, 2 x 128 cols)
+//     Pt  = exp(St*scale + bias - lse_i)      dSt = Pt * (dPt - delta_i)
+// writes Pt / dSt as 16-bit tiles into swizzled shared memory (one thread per
+// key row) and feeds them back to the tensor core:
+//     dV_j += Pt  dO_i        dK_j += dSt Q_i                  (TMEM accumulators)
+//     dQ_i  = dSt^T K_j  -- the same dSt tile read as an MN-major A operand --
+// dQ_i is drained from TMEM with vector red.global.add into an fp32 scratch
+// buffer that a last kernel converts to the 16-bit dQ.  Q_i / dO_i stream
+// through a 2-stage TMA ring.  Warps 0..3 = math, warp 4 = TMA + MMA issue.
+//
+// Takes the place of the autograd graph the reference runs for the traced
+// attention chain (src/torch/TorchDriver.cpp:642-847).
+#include "attn.h"
+#include "tc_common.cuh"
+
+namespace rb {
+
+constexpr int BQ = 128, BKEYS = 128, BD = 64;
+constexpr int TILE = 128 * 64 * 2;     // 16 KiB
+constexpr int SQ_BYTES = 128 * 128 * 2;  // 32 KiB
+constexpr int BWD_THREADS = 160;
+constexpr int BWD_TMEM_COLS = 512;
+constexpr int C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
+constexpr int BWD_SMEM = 2 * TILE /*K,V*/ + 4 * TILE /*Q,dO x2*/ + 2 * SQ_BYTES /*Pt,dSt*/ +
+                         4 * 128 * 4 /*lse,delta x2*/ + 1024 + 256;
+
+__device__ __forceinline__ void tma_load_4d_b(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
+                                              int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :
+        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
+          "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ uint32_t mix32b(uint64_t seed, uint64_t idx) {
+    uint64_t z = idx * 0x9E3779B97F4A7C15ull + seed;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return static_cast<uint32_t>(z ^ (z >> 31));
+}
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
+                 "f"(d)
+                 : "memory");
+}
+__device__ __forceinline__ void bar_sync_math() {
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+struct AttnBwdParams {
+    int B, H, S;
+    float scale, scale_log2;
+    const float* key_bias;
+    const float* lse;
+    const float* delta;
+    float* dq_accum;  // [B, S, H, 64] fp32
+    void* dK;
+    void* dV;
+    long long dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
+    uint32_t thr16;
+    float inv_keep;
+    uint64_t seed;
+    int* err;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+    attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const AttnBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint8_t* sK = smem;
+    uint8_t* sV = smem + TILE;
+    uint8_t* sQ = smem + 2 * TILE;    // [2]
+    uint8_t* sdO = smem + 4 * TILE;   // [2]
+    uint8_t* sPt = smem + 6 * TILE;
+    uint8_t* sdSt = sPt + SQ_BYTES;
+    float* s_lse = reinterpret_cast<float*>(sdSt + SQ_BYTES);  // [2][128]
+    float* s_delta = s_lse + 256;                              // [2][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 256);
+    uint64_t* kv_full = bars;
+    uint64_t* qd_full = bars + 1;  // [2]
+    uint64_t* s_full = bars + 3;
+    uint64_t* s_free = bars + 4;
+    uint64_t* pds_ready = bars + 5;
+    uint64_t* mma_done = bars + 6;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int key0 = blockIdx.x * BKEYS, h = blockIdx.y, b = blockIdx.z;
+    const int nq = (p.S + BQ - 1) / BQ;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1);
+        mbar_init(&qd_full[0], 1);
+        mbar_init(&qd_full[1], 1);
+        mbar_init(s_full, 1);
+        mbar_init(s_free, 128);
+        mbar_init(pds_ready, 128);
+        mbar_init(mma_done, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(tmem_slot, BWD_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            const uint32_t id_s = make_idesc_f16(fmt, 0, 0, 128, 128);
+            const uint32_t id_kn = make_idesc_f16(fmt, 0, 1, 128, 64);   // A K-major, B MN-major
+            const uint32_t id_nn = make_idesc_f16(fmt, 1, 1, 128, 64);   // A MN-major, B MN-major
+            auto load_qd = [&](int i) {
+                const int st = i & 1;
+                mbar_arrive_expect_tx(&qd_full[st], 2 * TILE);
+                tma_load_4d_b(sQ + st * TILE, &tmQ, &qd_full[st], 0, i * BQ, h, b);
+                tma_load_4d_b(sdO + st * TILE, &tmdO, &qd_full[st], 0, i * BQ, h, b);
+            };
+            auto issue_s = [&](int i) {
+                const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+                const uint32_t qa = smem_u32(sQ + (i & 1) * TILE), da = smem_u32(sdO + (i & 1) * TILE);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_f16(tmem + C_ST, make_smem_desc_sw128(ka + k * 32, 16, 1024),
+                             make_smem_desc_sw128(qa + k * 32, 16, 1024), id_s, k != 0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_f16(tmem + C_DPT, make_smem_desc_sw128(va + k * 32, 16, 1024),
+                             make_smem_desc_sw128(da + k * 32, 16, 1024), id_s, k != 0);
+                umma_commit(s_full);
+            };
+            mbar_arrive_expect_tx(kv_full, 2 * TILE);
+            tma_load_4d_b(sK, &tmK, kv_full, 0, key0, h, b);
+            tma_load_4d_b(sV, &tmV, kv_full, 0, key0, h, b);
+            load_qd(0);
+            if (nq > 1) load_qd(1);
+            bool ok = mbar_wait(kv_full, 0, abort_flag) && mbar_wait(&qd_full[0], 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int i = 0; i < nq && ok; ++i) {
+                if (i + 1 < nq) {
+                    ok = mbar_wait(&qd_full[(i + 1) & 1], ((i + 1) >> 1) & 1, abort_flag) &&
+                         mbar_wait(s_free, i & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(i + 1);
+                }
+                if (!mbar_wait(pds_ready, i & 1, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t pa = smem_u32(sPt), sa = smem_u32(sdSt), ka = smem_u32(sK);
+                const uint32_t qa = smem_u32(sQ + (i & 1) * TILE), da = smem_u32(sdO + (i & 1) * TILE);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t koff = (k >> 2) * (SQ_BYTES / 2) + (k & 3) * 32;
+                    umma_f16(tmem + C_DV, make_smem_desc_sw128(pa + koff, 16, 1024),
+                             make_smem_desc_sw128(da + k * 2048, 8192, 1024), id_kn, (i | k) != 0);
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t koff = (k >> 2) * (SQ_BYTES / 2) + (k & 3) * 32;
+                    umma_f16(tmem + C_DK, make_smem_desc_sw128(sa + koff, 16, 1024),
+                             make_smem_desc_sw128(qa + k * 2048, 8192, 1024), id_kn, (i | k) != 0);
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_f16(tmem + C_DQ, make_smem_desc_sw128(sa + k * 2048, SQ_BYTES / 2, 1024),
+                             make_smem_desc_sw128(ka + k * 2048, 8192, 1024), id_nn, k != 0);
+                umma_commit(mma_done);
+                if (i + 2 < nq) {
+                    if (!mbar_wait(mma_done, i & 1, abort_flag)) break;
+                    load_qd(i + 2);
+                }
+            }
+        }
+    } else {
+        const int r = threadIdx.x;  // TMEM lane: key row for St/dPt/dV/dK, query row for dQ
+        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+        const int key = key0 + r;
+        const bool key_ok = key < p.S;
+        const float kbias = (p.key_bias && key_ok)
+                                ? p.key_bias[static_cast<long long>(b) * p.S + key] * 1.4426950408889634f
+                                : 0.f;
+        const long long bh = static_cast<long long>(b) * p.H + h;
+        const uint32_t sw = r & 7;
+        uint8_t* prow = sPt + (r >> 3) * 1024 + sw * 128;
+        uint8_t* drow = sdSt + (r >> 3) * 1024 + sw * 128;
+        const uint64_t half_s = static_cast<uint64_t>((p.S + 1) / 2);
+        bool ok = true;
+
+        auto drain_dq = [&](int i) {
+            // dQ block i: lane r = query row q0 + r
+            const int q = i * BQ + r;
+            float* dst = p.dq_accum + ((static_cast<long long>(b) * p.S + q) * p.H + h) * BD;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_addr + C_DQ + c * 32, v);
+                tmem_ld_wait();
+                if (q < p.S) {
+#pragma unroll
+                    for (int g = 0; g < 8; ++g)
+                        red_add_v4(dst + c * 32 + g * 4, __uint_as_float(v[g * 4]) * p.scale,
+                                   __uint_as_float(v[g * 4 + 1]) * p.scale,
+                                   __uint_as_float(v[g * 4 + 2]) * p.scale,
+                                   __uint_as_float(v[g * 4 + 3]) * p.scale);
+                }
+            }
+        };
+
+        for (int i = 0; i < nq; ++i) {
+            const int st = i & 1;
+            const int q0 = i * BQ;
+            {
+                const int q = q0 + r;
+                s_lse[st * 128 + r] = q < p.S ? p.lse[bh * p.S + q] * 1.4426950408889634f : 0.f;
+                s_delta[st * 128 + r] = q < p.S ? p.delta[bh * p.S + q] : 0.f;
+            }
+            bar_sync_math();
+            if (!mbar_wait(s_full, i & 1, abort_flag)) {
+                ok = false;
+                break;
+            }
+            if (i > 0) {
+                if (!mbar_wait(mma_done, (i - 1) & 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                drain_dq(i - 1);
+            }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tmem + lane_addr + C_ST + c * 32, sv);
+                tmem_ld32(tmem + lane_addr + C_DPT + c * 32, dv);
+                tmem_ld_wait();
+                float pt[32], ds[32];
+#pragma unroll
+                for (int x = 0; x < 32; ++x) {
+                    const int ql = c * 32 + x;
+                    const int q = q0 + ql;
+                    float pr = 0.f;
+                    if (key_ok && q < p.S)
+                        pr = exp2f(__uint_as_float(sv[x]) * p.scale_log2 + kbias - s_lse[st * 128 + ql]);
+                    float dp = __uint_as_float(dv[x]);
+                    float pd = pr;
+                    if (p.thr16) {
+                        const uint64_t row = (static_cast<uint64_t>(bh) * p.S + q) * half_s;
+                        const uint32_t bits = mix32b(p.seed, row + (key >> 1));
+                        const uint32_t hbits = (key & 1) ? (bits >> 16) : (bits & 0xffffu);
+                        const float keep = hbits >= p.thr16 ? p.inv_keep : 0.f;
+                        pd = pr * keep;
+                        dp *= keep;
+                    }
+                    pt[x] = pd;
+                    ds[x] = pr * (dp - s_delta[st * 128 + ql]);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4 a, d;
+                    T* ea = reinterpret_cast<T*>(&a);
+                    T* ed = reinterpret_cast<T*>(&d);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                        ea[x] = from_f32<T>(pt[g * 8 + x]);
+                        ed[x] = from_f32<T>(ds[g * 8 + x]);
+                    }
+                    const int kk = c * 32 + g * 8;
+                    const uint32_t off = (kk >> 6) * (SQ_BYTES / 2) + ((((kk & 63) >> 3) ^ sw) << 4);
+                    *reinterpret_cast<uint4*>(prow + off) = a;
+                    *reinterpret_cast<uint4*>(drow + off) = d;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(s_free);
+            fence_proxy_async();
+            mbar_arrive(pds_ready);
+        }
+        if (ok && mbar_wait(mma_done, (nq - 1) & 1, abort_flag)) {
+            tc_fence_after();
+            drain_dq(nq - 1);
+            T* dk = reinterpret_cast<T*>(p.dK) + b * p.dk_sb + static_cast<long long>(key) * p.dk_ss + h * p.dk_sh;
+            T* dvp = reinterpret_cast<T*>(p.dV) + b * p.dv_sb + static_cast<long long>(key) * p.dv_ss + h * p.dv_sh;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t a[32], d[32];
+                tmem_ld32(tmem + lane_addr + C_DV + c * 32, a);
+                tmem_ld32(tmem + lane_addr + C_DK + c * 32, d);
+                tmem_ld_wait();
+                if (key_ok) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 qa, qd;
+                        T* ea = reinterpret_cast<T*>(&qa);
+                        T* ed = reinterpret_cast<T*>(&qd);
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) {
+                            ea[x] = from_f32<T>(__uint_as_float(a[g * 8 + x]));
+                            ed[x] = from_f32<T>(__uint_as_float(d[g * 8 + x]) * p.scale);
+                        }
+                        *reinterpret_cast<uint4*>(dvp + c * 32 + g * 8) = qa;
+                        *reinterpret_cast<uint4*>(dk + c * 32 + g * 8) = qd;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicExch(p.err, ERR_MBAR_TIMEOUT);
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {
+            }
+        }
+        __syncthreads();
+    }
+    if (warp == 4) {
+        tc_fence_after();
+        tmem_dealloc(tmem, BWD_TMEM_COLS);
+    }
+}
+
+// delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d]; one warp per (b,h,q), D = 64
+template <typename T>
+__global__ void attn_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO,
+                                  float* __restrict__ delta, int B, int H, int S, long long o_sb,
+                                  long long o_ss, long long o_sh, long long d_sb, long long d_ss,
+                                  long long d_sh) {
+    const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= static_cast<long long>(B) * H * S) return;
+    const int q = w % S;
+    const int h = (w / S) % H;
+    const int b = w / (static_cast<long long>(S) * H);
+    const T* o = O + b * o_sb + q * o_ss + h * o_sh + lane * 2;
+    const T* d = dO + b * d_sb + q * d_ss + h * d_sh + lane * 2;
+    float s = to_f32<T>(o[0]) * to_f32<T>(d[0]) + to_f32<T>(o[1]) * to_f32<T>(d[1]);
+#pragma unroll
+    for (int x = 16; x > 0; x >>= 1) s += __shfl_xor_sync(0xffffffffu, s, x);
+    if (lane == 0) delta[w] = s;
+}
+
+// dQ[b,q,h,:] = (T) acc[b,q,h,:]
+template <typename T>
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dQ, int B,
+                                       int H, int S, long long sb, long long ss, long long sh) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;  // 8-element group
+    const long long total = static_cast<long long>(B) * S * H * 8;
+    if (i >= total) return;
+    const int g = i & 7;
+    const long long row = i >> 3;  // (b*S + q)*H + h
+    const int h = row % H;
+    const int q = (row / H) % S;
+    const int b = row / (static_cast<long long>(H) * S);
+    const float4 a = *reinterpret_cast<const float4*>(acc + row * 64 + g * 8);
+    const float4 c = *reinterpret_cast<const float4*>(acc + row * 64 + g * 8 + 4);
+    uint4 o;
+    T* e = reinterpret_cast<T*>(&o);
+    e[0] = from_f32<T>(a.x); e[1] = from_f32<T>(a.y); e[2] = from_f32<T>(a.z); e[3] = from_f32<T>(a.w);
+    e[4] = from_f32<T>(c.x); e[5] = from_f32<T>(c.y); e[6] = from_f32<T>(c.z); e[7] = from_f32<T>(c.w);
+    *reinterpret_cast<uint4*>(dQ + b * sb + q * ss + h * sh + g * 8) = o;
+}
+
+template <typename T>
+static int launch_bwd(const RbAttnArgs& a, cudaStream_t st) {
+    CUtensorMap tq, tk, tv, tdo;
+    int rc;
+    const uint64_t D = a.D, S = a.S, H = a.H, B = a.B;
+    if ((rc = make_tmap_4d(&tq, a.Q, a.dtype, D, S, H, B, a.q_ss * 2, a.q_sh * 2, a.q_sb * 2, 64, 128))) return rc;
+    if ((rc = make_tmap_4d(&tk, a.K, a.dtype, D, S, H, B, a.k_ss * 2, a.k_sh * 2, a.k_sb * 2, 64, 128))) return rc;
+    if ((rc = make_tmap_4d(&tv, a.V, a.dtype, D, S, H, B, a.v_ss * 2, a.v_sh * 2, a.v_sb * 2, 64, 128))) return rc;
+    if ((rc = make_tmap_4d(&tdo, a.dO, a.dtype, D, S, H, B, a.do_ss * 2, a.do_sh * 2, a.do_sb * 2, 64, 128))) return rc;
+    const long long rows = static_cast<long long>(a.B) * a.H * a.S;
+    attn_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(
+        static_cast<const T*>(a.O), static_cast<const T*>(a.dO), a.delta, a.B, a.H, a.S, a.o_sb,
+        a.o_ss, a.o_sh, a.do_sb, a.do_ss, a.do_sh);
+    cudaMemsetAsync(a.dq_accum, 0, static_cast<size_t>(rows) * 64 * sizeof(float), st);
+    AttnBwdParams p;
+    p.B = a.B; p.H = a.H; p.S = a.S;
+    p.scale = a.scale;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.key_bias = a.key_bias;
+    p.lse = a.lse;
+    p.delta = a.delta;
+    p.dq_accum = a.dq_accum;
+    p.dK = a.dK; p.dV = a.dV;
+    p.dk_sb = a.dk_sb; p.dk_ss = a.dk_ss; p.dk_sh = a.dk_sh;
+    p.dv_sb = a.dv_sb; p.dv_ss = a.dv_ss; p.dv_sh = a.dv_sh;
+    p.thr16 = a.p_drop > 0.f ? static_cast<uint32_t>(a.p_drop * 65536.f + 0.5f) : 0u;
+    p.inv_keep = a.p_drop > 0.f ? 1.f / (1.f - a.p_drop) : 1.f;
+    p.seed = a.seed * 0x2545F4914F6CDD1Dull + a.offset;
+    p.err = error_word_ptr();
+    if (!p.err) return -3;
+    auto kern = attn_bwd_kernel<T>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess)
+            return -4;
+        attr_set[dev & 63] = true;
+    }
+    dim3 grid((a.S + BKEYS - 1) / BKEYS, a.H, a.B);
+    kern<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, p);
+    const long long groups = rows * 8;
+    attn_dq_convert_kernel<T><<<static_cast<unsigned>((groups + 255) / 256), 256, 0, st>>>(
+        a.dq_accum, static_cast<T*>(a.dQ), a.B, a.H, a.S, a.dq_sb, a.dq_ss, a.dq_sh);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace rb
+
+extern "C" int rb_attn_bwd(const RbAttnArgs* a, void* stream) {
+    if (a->D != 64) return -2;
+    if (a->B <= 0 || a->H <= 0 || a->S <= 0) return 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return a->dtype == 1 ? rb::launch_bwd<__nv_bfloat16>(*a, st) : rb::launch_bwd<__half>(*a, st);
+}

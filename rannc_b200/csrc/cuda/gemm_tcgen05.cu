@@ -1,0 +1,519 @@
+// Dense GEMM on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), sm_100a.
+//
+//   D[b] = epilogue( alpha * op(A[b]) * op(B[b]) )      op(A): M x K, op(B): K x N
+//
+// A is "K-major" when stored [M, K] row-major and "MN-major" when stored
+// [K, M] row-major; B is K-major when stored [N, K] (the nn.Linear weight
+// layout) and MN-major when stored [K, N].  The three GEMMs of a linear layer
+// map onto it without a transposed copy:
+//   forward  Y  = X  W^T : A = X  (K-major),  B = W  (K-major)
+//   dgrad    dX = dY W   : A = dY (K-major),  B = W  (MN-major)
+//   wgrad    dW = dY^T X : A = dY (MN-major), B = X  (MN-major)
+//
+// Structure: persistent CTAs (one per SM), 128 x 256 output tile, K step 64,
+// 4-stage TMA->smem ring, fp32 accumulators double-buffered in TMEM (2 x 256
+// columns) so the epilogue of tile i overlaps the main loop of tile i+1.
+// Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue.
+//
+// This kernel takes the place of the cuBLAS calls the reference reaches through
+// aten::linear / aten::matmul in its TorchScript interpreter
+// (src/torch/TorchDriver.cpp:566) and in src/distop/DistMatmul.cpp:97-214.
+#include "gemm_tcgen05.h"
+
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace rb {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 8;
+
+struct GemmKernelParams {
+    int M, N, K, batch;
+    int a_major, b_major;
+    int num_m_blocks, num_n_blocks, num_tiles, num_kb;
+    void* D;
+    const void* bias;
+    const void* residual;
+    const void* aux_in;
+    void* aux_out;
+    long long ldd, strideD;
+    float alpha;
+    int flags;
+    int* err;
+};
+
+__device__ __forceinline__ void tile_coords(const GemmKernelParams& p, int tile, int& mb, int& nb,
+                                            int& b) {
+    const int per_batch = p.num_m_blocks * p.num_n_blocks;
+    b = tile / per_batch;
+    int t = tile - b * per_batch;
+    const int group_sz = GROUP_M * p.num_n_blocks;
+    const int g = t / group_sz;
+    const int first_m = g * GROUP_M;
+    const int gm = min(GROUP_M, p.num_m_blocks - first_m);
+    t -= g * group_sz;
+    mb = first_m + (t % gm);
+    nb = t / gm;
+}
+
+template <typename T>
+__device__ __forceinline__ void load32(const T* ptr, bool vec_ok, int valid, float (&v)[32]) {
+    if (vec_ok) {
+        if constexpr (sizeof(T) == 2) {
+            const uint4* p4 = reinterpret_cast<const uint4*>(ptr);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 q = p4[i];
+                const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i * 8 + j] = to_f32<T>(e[j]);
+            }
+        } else {
+            const float4* p4 = reinterpret_cast<const float4*>(ptr);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float4 q = p4[i];
+                v[i * 4 + 0] = q.x;
+                v[i * 4 + 1] = q.y;
+                v[i * 4 + 2] = q.z;
+                v[i * 4 + 3] = q.w;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (j < valid) ? to_f32<T>(ptr[j]) : 0.f;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void store32(T* ptr, bool vec_ok, int valid, const float (&v)[32]) {
+    if (vec_ok) {
+        if constexpr (sizeof(T) == 2) {
+            uint4* p4 = reinterpret_cast<uint4*>(ptr);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 q;
+                T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(v[i * 8 + j]);
+                p4[i] = q;
+            }
+        } else {
+            float4* p4 = reinterpret_cast<float4*>(ptr);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                p4[i] = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < valid) ptr[j] = from_f32<T>(v[j]);
+    }
+}
+
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                        const __grid_constant__ CUtensorMap tmB, const GemmKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;                  // [STAGES]
+    uint64_t* empty = bars + STAGES;        // [STAGES]
+    uint64_t* tfull = bars + 2 * STAGES;    // [2]
+    uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 128);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 2) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer ----------------
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                int mb, nb, b;
+                tile_coords(p, tile, mb, nb, b);
+                const int m0 = mb * BM, n0 = nb * BN;
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+                    uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+                    uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+                    const int k0 = kb * BK;
+                    if (p.a_major == 0) {
+                        tma_load_3d(a_dst, &tmA, &full[stage], k0, m0, b);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c)
+                            tma_load_3d(a_dst + c * (BK * 128), &tmA, &full[stage], m0 + c * 64,
+                                        k0, b);
+                    }
+                    if (p.b_major == 0) {
+                        tma_load_3d(b_dst, &tmB, &full[stage], k0, n0, b);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)
+                            tma_load_3d(b_dst + c * (BK * 128), &tmB, &full[stage], n0 + c * 64,
+                                        k0, b);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            constexpr int fmt = (sizeof(InT) == 2 && std::is_same<InT, __nv_bfloat16>::value) ? 1 : 0;
+            const uint32_t idesc = make_idesc_f16(fmt, p.a_major, p.b_major, BM, BN);
+            // per-UMMA_K (16 elements) advance of the smem start address
+            const uint32_t a_kstep = (p.a_major == 0) ? 32u : 2048u;
+            const uint32_t b_kstep = (p.b_major == 0) ? 32u : 2048u;
+            const uint32_t a_lbo = (p.a_major == 0) ? 16u : BK * 128u;
+            const uint32_t b_lbo = (p.b_major == 0) ? 16u : BK * 128u;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.num_kb; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+                    const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t da = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
+                        const uint64_t db = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
+                        umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) umma_commit(&tfull[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may access
+        const int row_in_tile = q * 32 + lane;
+        const bool has_bias = p.flags & RB_GEMM_BIAS;
+        const bool has_res = p.flags & RB_GEMM_RESIDUAL;
+        const bool act_gelu = p.flags & RB_GEMM_GELU;
+        const bool act_dgelu = p.flags & RB_GEMM_DGELU;
+        const bool aux_out = p.flags & RB_GEMM_AUX_OUT;
+        const bool accum = p.flags & RB_GEMM_ACCUM;
+        const bool in_al = (p.ldd % 8 == 0);
+        const bool out_al = (sizeof(OutT) == 2) ? (p.ldd % 8 == 0) : (p.ldd % 4 == 0);
+        int it = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+            int mb, nb, b;
+            tile_coords(p, tile, mb, nb, b);
+            const int acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
+            tc_fence_after();
+            const int row = mb * BM + row_in_tile;
+            const bool row_ok = row < p.M;
+            const long long row_off = static_cast<long long>(b) * p.strideD +
+                                      static_cast<long long>(row) * p.ldd;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col = nb * BN + c * 32;
+                if (col >= p.N) break;
+                uint32_t r[32];
+                tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                const int valid = min(32, p.N - col);
+                const bool full_chunk = valid == 32;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                if (has_bias) {
+                    float t[32];
+                    load32(reinterpret_cast<const InT*>(p.bias) + col, full_chunk, valid, t);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += t[j];
+                }
+                if (aux_out)
+                    store32(reinterpret_cast<InT*>(p.aux_out) + row_off + col, full_chunk && in_al,
+                            valid, v);
+                if (act_gelu) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                }
+                if (act_dgelu) {
+                    float t[32];
+                    load32(reinterpret_cast<const InT*>(p.aux_in) + row_off + col,
+                           full_chunk && in_al, valid, t);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] *= gelu_erf_grad(t[j]);
+                }
+                if (has_res) {
+                    float t[32];
+                    load32(reinterpret_cast<const InT*>(p.residual) + row_off + col,
+                           full_chunk && in_al, valid, t);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += t[j];
+                }
+                OutT* dptr = reinterpret_cast<OutT*>(p.D) + row_off + col;
+                if (accum) {
+                    float t[32];
+                    load32(dptr, full_chunk && out_al, valid, t);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += t[j];
+                }
+                store32(dptr, full_chunk && out_al, valid, v);
+            }
+            tc_fence_before();
+            mbar_arrive(&tempty[acc]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicExch(p.err, ERR_MBAR_TIMEOUT);
+            // let bulk copies that may still be in flight land before the CTA's
+            // shared memory is released
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {
+            }
+        }
+        __syncthreads();
+    }
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault,
+                                             &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int make_tmap_3d(CUtensorMap* out, const void* base, int dtype_16bit_kind, uint64_t d0, uint64_t d1,
+                 uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0,
+                 uint32_t b1, int swizzle128) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -100;
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {b0, b1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMapDataType dt =
+        dtype_16bit_kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+}
+
+int make_tmap_4d(CUtensorMap* out, const void* base, int fmt, uint64_t d0, uint64_t d1, uint64_t d2,
+                 uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -100;
+    cuuint64_t dims[4] = {d0, d1, d2, d3};
+    cuuint64_t strides[3] = {s1, s2, s3};
+    cuuint32_t box[4] = {b0, b1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMapDataType dt =
+        fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = fn(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+}
+
+static __device__ int g_error_word = 0;
+
+int* error_word_ptr() {
+    // one address per device
+    static int* ptrs[64] = {nullptr};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_error_word) != cudaSuccess) return nullptr;
+        ptrs[dev] = static_cast<int*>(p);
+    }
+    return ptrs[dev];
+}
+
+int num_sms() {
+    static int n[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+    return n[dev];
+}
+
+template <typename InT, typename OutT>
+static int launch(const RbGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                  const GemmKernelParams& p, cudaStream_t stream) {
+    auto kern = gemm_tcgen05_kernel<InT, OutT>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e =
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return -static_cast<int>(e);
+        attr_set[dev & 63] = true;
+    }
+    int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
+    if (a.max_ctas > 0 && grid > a.max_ctas) grid = a.max_ctas;
+    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+}  // namespace rb
+
+extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
+    using namespace rb;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) return 0;
+    // TMA needs 16-byte aligned bases and row strides
+    if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) ||
+        (a->lda % 8) || (a->ldb % 8) || (a->batch > 1 && ((a->strideA % 8) || (a->strideB % 8))))
+        return -2;
+    CUtensorMap tmA, tmB;
+    int rc;
+    const uint64_t sA = a->batch > 1 ? a->strideA * 2 : (a->a_major == 0 ? a->M : a->K) * a->lda * 2;
+    const uint64_t sB = a->batch > 1 ? a->strideB * 2 : (a->b_major == 0 ? a->N : a->K) * a->ldb * 2;
+    if (a->a_major == 0)
+        rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->K, a->M, a->batch, a->lda * 2, sA, BK, BM, 1);
+    else
+        rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->M, a->K, a->batch, a->lda * 2, sA, 64, BK, 1);
+    if (rc) return rc;
+    if (a->b_major == 0)
+        rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->K, a->N, a->batch, a->ldb * 2, sB, BK, BN, 1);
+    else
+        rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->N, a->K, a->batch, a->ldb * 2, sB, 64, BK, 1);
+    if (rc) return rc;
+
+    GemmKernelParams p;
+    p.M = static_cast<int>(a->M);
+    p.N = static_cast<int>(a->N);
+    p.K = static_cast<int>(a->K);
+    p.batch = static_cast<int>(a->batch);
+    p.a_major = a->a_major;
+    p.b_major = a->b_major;
+    p.num_m_blocks = (p.M + BM - 1) / BM;
+    p.num_n_blocks = (p.N + BN - 1) / BN;
+    p.num_tiles = p.num_m_blocks * p.num_n_blocks * p.batch;
+    p.num_kb = (p.K + BK - 1) / BK;
+    p.D = a->D;
+    p.bias = a->bias;
+    p.residual = a->residual;
+    p.aux_in = a->aux_in;
+    p.aux_out = a->aux_out;
+    p.ldd = a->ldd;
+    p.strideD = a->strideD;
+    p.alpha = a->alpha;
+    p.flags = a->flags;
+    p.err = error_word_ptr();
+    if (!p.err) return -3;
+
+    if (a->in_dtype == 1) {
+        if (a->out_dtype == 0) return launch<__nv_bfloat16, __nv_bfloat16>(*a, tmA, tmB, p, stream);
+        return launch<__nv_bfloat16, float>(*a, tmA, tmB, p, stream);
+    } else {
+        if (a->out_dtype == 0) return launch<__half, __half>(*a, tmA, tmB, p, stream);
+        return launch<__half, float>(*a, tmA, tmB, p, stream);
+    }
+}
+
+// Reads (and clears) the device error word.  Synchronises the device.
+extern "C" int rb_read_error(int clear) {
+    int* p = rb::error_word_ptr();
+    if (!p) return -3;
+    int v = 0;
+    if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -4;
+    if (clear && v) {
+        int z = 0;
+        cudaMemcpy(p, &z, sizeof(int), cudaMemcpyHostToDevice);
+    }
+    return v;
+}

@@ -1,0 +1,55 @@
+// C ABI of the tcgen05 GEMM (see gemm_tcgen05.cu).  Called from Python through
+// ctypes with raw device pointers and the current CUDA stream.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum RbGemmFlags {
+    RB_GEMM_BIAS = 1,       // v += bias[n]            (bias in the input dtype)
+    RB_GEMM_GELU = 2,       // v = gelu(v)             (erf form)
+    RB_GEMM_DGELU = 4,      // v *= gelu'(aux_in[m,n])
+    RB_GEMM_RESIDUAL = 8,   // v += residual[m,n]
+    RB_GEMM_ACCUM = 16,     // v += D[m,n]             (gradient accumulation)
+    RB_GEMM_AUX_OUT = 32,   // aux_out[m,n] = v before the activation
+};
+
+typedef struct RbGemmArgs {
+    const void* A;
+    const void* B;
+    void* D;
+    const void* bias;
+    const void* residual;
+    const void* aux_in;
+    void* aux_out;
+    int64_t M, N, K, batch;
+    int64_t lda, ldb, ldd;              // leading dimensions, elements
+    int64_t strideA, strideB, strideD;  // batch strides, elements
+    int32_t a_major;    // 0: A stored [M,K]; 1: A stored [K,M]
+    int32_t b_major;    // 0: B stored [N,K]; 1: B stored [K,N]
+    int32_t in_dtype;   // 0 fp16, 1 bf16
+    int32_t out_dtype;  // 0 same as input, 1 fp32
+    int32_t flags;
+    int32_t max_ctas;   // 0 = one per SM
+    float alpha;
+    int32_t pad_;
+} RbGemmArgs;
+
+// returns 0 on success, <0 on a host-side error (-2: operand not 16 B aligned)
+int rb_gemm(const RbGemmArgs* args, void* stream);
+// device error word: 0 ok, 1 mbarrier wait ran out, 2 peer wait ran out
+int rb_read_error(int clear);
+
+#ifdef __cplusplus
+}
+#include <cuda.h>
+namespace rb {
+int make_tmap_3d(CUtensorMap* out, const void* base, int dtype_16bit_kind, uint64_t d0, uint64_t d1,
+                 uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0,
+                 uint32_t b1, int swizzle128);
+int* error_word_ptr();
+int num_sms();
+}  // namespace rb
+#endif

@@ -1,0 +1,68 @@
+"""ctypes access to ``_kernels.so`` (the sm_100a CUDA kernels).
+
+The library is built in-tree by :mod:`rannc_b200.build`.  When it is missing it
+is built on first use; when that is impossible the import of any kernel fails
+with an error instead of falling back to a stock PyTorch path.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent.parent
+_lock = threading.Lock()
+_lib = None
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _HERE / "_kernels.so"
+        if not path.exists():
+            from .. import build
+
+            try:
+                build.build_kernels()
+            except Exception as e:  # noqa: BLE001
+                raise KernelLibraryError(f"cannot build {path}: {e}") from e
+        try:
+            _lib = ctypes.CDLL(str(path))
+        except OSError as e:
+            raise KernelLibraryError(f"cannot load {path}: {e}") from e
+        _lib.rb_read_error.restype = ctypes.c_int
+        return _lib
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t):
+    """Device address as an int (None for a missing tensor); for ctypes.Structure fields."""
+    return None if t is None else t.data_ptr()
+
+
+def vp(t) -> ctypes.c_void_p:
+    """Device address as c_void_p; for positional arguments of a C function."""
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelLibraryError(f"{what} failed with code {rc}")
+
+
+def read_error(clear: bool = True) -> int:
+    """Device error word (synchronises): 0 ok, 1 mbarrier wait ran out, 2 peer wait ran out."""
+    return int(lib().rb_read_error(1 if clear else 0))

@@ -1,0 +1,98 @@
+"""tcgen05 GEMM wrapper (``csrc/cuda/gemm_tcgen05.cu``)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+BIAS, GELU, DGELU, RESIDUAL, ACCUM, AUX_OUT = 1, 2, 4, 8, 16, 32
+
+
+class _Args(ctypes.Structure):
+    _fields_ = [
+        ("A", ctypes.c_void_p), ("B", ctypes.c_void_p), ("D", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+        ("aux_in", ctypes.c_void_p), ("aux_out", ctypes.c_void_p),
+        ("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64), ("batch", ctypes.c_int64),
+        ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldd", ctypes.c_int64),
+        ("strideA", ctypes.c_int64), ("strideB", ctypes.c_int64), ("strideD", ctypes.c_int64),
+        ("a_major", ctypes.c_int32), ("b_major", ctypes.c_int32),
+        ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+        ("flags", ctypes.c_int32), ("max_ctas", ctypes.c_int32),
+        ("alpha", ctypes.c_float), ("pad_", ctypes.c_int32),
+    ]
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float16:
+        return 0
+    raise TypeError(f"gemm: unsupported input dtype {t.dtype}")
+
+
+def _mat(t: torch.Tensor):
+    """Returns (tensor, rows, cols, ld, batch, batch_stride) for a 2-D/3-D tensor whose last dim is contiguous."""
+    if t.dim() == 2:
+        if t.stride(1) != 1:
+            t = t.contiguous()
+        return t, t.shape[0], t.shape[1], t.stride(0), 1, 0
+    if t.dim() == 3:
+        if t.stride(2) != 1:
+            t = t.contiguous()
+        return t, t.shape[1], t.shape[2], t.stride(1), t.shape[0], t.stride(0)
+    raise ValueError("gemm operands must be 2-D or 3-D")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
+         bias=None, residual=None, aux_in=None, aux_out=None, gelu: bool = False,
+         dgelu: bool = False, out: torch.Tensor | None = None, accumulate: bool = False,
+         out_dtype: torch.dtype | None = None, alpha: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+    """``out = epilogue(alpha * op(a) @ op(b))``.
+
+    ``a`` is stored ``[M, K]`` (``trans_a=False``) or ``[K, M]`` (``trans_a=True``).
+    ``b`` is stored ``[N, K]`` (``trans_b=True``, the ``nn.Linear`` weight layout) or
+    ``[K, N]`` (``trans_b=False``).  A leading batch dimension is allowed on both.
+    """
+    a, ar, ac, lda, ba, sa = _mat(a)
+    b, br, bc, ldb, bb, sb = _mat(b)
+    M, K = (ac, ar) if trans_a else (ar, ac)
+    N, Kb = (br, bc) if trans_b else (bc, br)
+    if K != Kb:
+        raise ValueError(f"gemm: inner dimensions differ ({K} vs {Kb})")
+    batch = max(ba, bb)
+    if ba != bb and min(ba, bb) != 1:
+        raise ValueError("gemm: batch sizes differ")
+    if ba == 1 and batch > 1:
+        sa = 0
+    if bb == 1 and batch > 1:
+        sb = 0
+    odt = out_dtype or (out.dtype if out is not None else a.dtype)
+    if out is None:
+        shape = (M, N) if batch == 1 and a.dim() == 2 and b.dim() == 2 else (batch, M, N)
+        out = torch.empty(shape, dtype=odt, device=a.device)
+    ldd = out.stride(-2)
+    sd = out.stride(0) if out.dim() == 3 else 0
+    flags = 0
+    if bias is not None:
+        flags |= BIAS
+    if gelu:
+        flags |= GELU
+    if dgelu:
+        flags |= DGELU
+    if residual is not None:
+        flags |= RESIDUAL
+    if accumulate:
+        flags |= ACCUM
+    if aux_out is not None:
+        flags |= AUX_OUT
+    args = _Args(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(residual),
+        _lib.ptr(aux_in), _lib.ptr(aux_out), M, N, K, batch, lda, ldb, ldd, sa, sb, sd,
+        1 if trans_a else 0, 0 if trans_b else 1, _dt(a), 0 if odt == a.dtype else 1, flags,
+        max_ctas, float(alpha), 0)
+    rc = _lib.lib().rb_gemm(ctypes.byref(args), _lib.stream_ptr())
+    _lib.check(rc, "rb_gemm")
+    return out

@@ -1,0 +1,86 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference of the same product."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, trans_a, trans_b):
+    a32, b32 = a.float(), b.float()
+    if trans_a:
+        a32 = a32.transpose(-1, -2)
+    if trans_b:
+        b32 = b32.transpose(-1, -2)
+    return a32 @ b32
+
+
+def _check(out, ref, tol=2e-2):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"rel err {err / scale}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 264, 136), (1024, 1024, 1024), (129, 40, 72)])
+def test_gemm_layouts(dtype, trans_a, trans_b, M, N, K):
+    from rannc_b200.ops import _lib
+    from rannc_b200.ops.gemm import gemm
+
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if trans_a else (M, K), device="cuda", dtype=dtype)
+    b = torch.randn((N, K) if trans_b else (K, N), device="cuda", dtype=dtype)
+    out = gemm(a, b, trans_a=trans_a, trans_b=trans_b)
+    torch.cuda.synchronize()
+    assert _lib.read_error() == 0
+    _check(out, _ref(a, b, trans_a, trans_b))
+
+
+def test_gemm_epilogues():
+    from rannc_b200.ops.gemm import gemm
+
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 320
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out = gemm(x, w, bias=bias, gelu=True, aux_out=pre)
+    z = x.float() @ w.float().t() + bias.float()
+    _check(pre, z)
+    _check(out, torch.nn.functional.gelu(z))
+    out = gemm(x, w, bias=bias, residual=res)
+    _check(out, z + res.float())
+    # dgelu: v * gelu'(aux)
+    zz = z.clone().requires_grad_(True)
+    torch.nn.functional.gelu(zz).sum().backward()
+    out = gemm(x, w, dgelu=True, aux_in=pre)
+    _check(out, (x.float() @ w.float().t()) * zz.grad, tol=3e-2)
+    # fp32 output with accumulation
+    acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    gemm(x, w, out=acc, accumulate=True, alpha=0.5)
+    _check(acc, 0.5 * (x.float() @ w.float().t()) + 1.0)
+
+
+def test_gemm_batched():
+    from rannc_b200.ops.gemm import gemm
+
+    torch.manual_seed(2)
+    a = torch.randn(6, 200, 64, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(6, 320, 64, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, b)
+    _check(out, a.float() @ b.float().transpose(1, 2))
+    c = torch.randn(6, 64, 136, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, c, trans_b=False)
+    _check(out, a.float() @ c.float())
+
+
+def test_gemm_large_perf_shape():
+    from rannc_b200.ops.gemm import gemm
+
+    torch.manual_seed(3)
+    a = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, b)
+    _check(out, a.float() @ b.float().t())
