@@ -22,6 +22,7 @@ constexpr int XT = 256;
 
 __device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
     const float nm = fmaxf(m, m2);
+    if (nm == -INFINITY) return;  // both sides empty
     s = s * __expf(m - nm) + s2 * __expf(m2 - nm);
     m = nm;
 }

@@ -1,0 +1,161 @@
+"""trace -> profile -> partition -> deployment (the body of the reference's RaNNCModule::init,
+src/comp/RaNNCModule.cpp:160-501, steps 4-7).
+
+Planning is deterministic given the graph, the profiles and the configuration, so
+every rank can run it; the runtime lets rank 0 plan and broadcasts the msgpack
+deployment so that measured profiles (which differ slightly per rank) cannot make
+ranks disagree.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+from .. import _core
+from ..utils.config import conf
+from ..utils.log import get_logger
+
+logger = get_logger("Decomposer")
+
+
+@dataclass
+class Plan:
+    deployment: "_core.Deployment"
+    estimates: list
+    ml_nodes: int
+    dev_mem: int
+
+
+def device_memory_budget(total_bytes: int) -> int:
+    """min(total, mem_limit_gb) x (1 - mem_margin) (reference: MLPartDecomposer.cpp:15-24)."""
+    limit_gb = int(conf("mem_limit_gb"))
+    mem = total_bytes
+    if limit_gb > 0:
+        mem = min(mem, limit_gb * (1 << 30)) if mem > 0 else limit_gb * (1 << 30)
+    return int(mem * (1.0 - float(conf("mem_margin"))))
+
+
+def make_partitioning_conf(world_size: int, batch_size: int, dev_mem: int, use_amp: bool, enable_zero: bool,
+                           offload_params: bool) -> "_core.PartitioningConf":
+    c = _core.PartitioningConf()
+    dry = int(conf("partitioning_dry_run_np"))
+    c.dev_num = dry if dry > 0 else world_size
+    c.batch_size = batch_size
+    c.dev_mem = dev_mem
+    c.use_amp_master_params = use_amp
+    c.enable_zero = enable_zero
+    c.offload_params = offload_params
+    c.force_dist_matmul = bool(conf("force_dist_matmul"))
+    c.opt_param_factor = int(conf("opt_param_factor"))
+    c.min_pipeline = int(conf("min_pipeline"))
+    c.max_pipeline = int(conf("max_pipeline"))
+    c.min_pipeline_bs = int(conf("min_pipeline_bs"))
+    c.min_partition_num = int(conf("min_partition_num"))
+    c.max_partition_num = int(conf("max_partition_num"))
+    c.cfg_partition_num = int(conf("partition_num"))
+    c.cfg_replica_num = int(conf("replica_num"))
+    c.cfg_pipeline_num = int(conf("pipeline_num"))
+    c.limit_dev_num_pot = bool(conf("limit_dev_num_pot"))
+    c.limit_dev_num_more_than_bs = bool(conf("limit_dev_num_more_than_bs"))
+    c.dp_search_all = bool(conf("dp_search_all"))
+    c.do_coarsening = bool(conf("do_coarsening"))
+    c.do_uncoarsening = bool(conf("do_uncoarsening"))
+    c.coarsen_by_time = bool(conf("coarsen_by_time"))
+    c.checkpointing = bool(conf("checkpointing"))
+    c.checkpointing_no_last = bool(conf("checkpointing_no_last"))
+    c.prefer_no_checkpointing = bool(conf("prefer_no_checkpointing"))
+    link = _core.LinkModel()
+    link.p2p_bytes_per_us = float(conf("p2p_gbs")) * 1e3
+    link.allreduce_bytes_per_us = float(conf("allreduce_gbs")) * 1e3
+    c.link = link
+    return c
+
+
+def _fmt_table(estimates) -> str:
+    rows = ["Estimated profiles of subgraphs (times in us, sizes in bytes)"]
+    for e in estimates:
+        p = e.profile
+        rows.append(
+            f"  {e.name}: repl={e.repl} micro_batch={e.micro_batch} fwd={p.fwd_time} bwd={p.bwd_time} "
+            f"allreduce={e.allreduce_us:.0f} in={p.input_size} out={p.output_size} params={p.param_size} "
+            f"mem={e.total_mem} (fwd+bwd={p.param_size + p.activation_size + p.working_mem} opt={e.opt_mem} "
+            f"comm={e.comm_mem})")
+    return "\n".join(rows)
+
+
+def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: int, global_batch: int,
+         dev_total_mem: int, use_amp: bool, enable_zero: bool, offload_params: bool, dep_id: str,
+         load_deployment: Optional[str] = None) -> Plan:
+    """``ir_graph`` must already be scaled to the global batch size."""
+    dev_mem = device_memory_budget(dev_total_mem)
+    pconf = make_partitioning_conf(world_size, global_batch, dev_mem, use_amp, enable_zero, offload_params)
+
+    load_path = load_deployment or (str(conf("deployment_file")) if bool(conf("load_deployment")) else None)
+    if load_path:
+        with open(load_path, "rb") as f:
+            dep, ws, dm = _core.load_deployment(f.read())
+        # a deployment is only valid for the world size and device memory it was planned for
+        # (reference: src/graph/DeploymentSerializer.cpp:34-46)
+        if ws != pconf.dev_num:
+            raise RuntimeError(f"deployment file was made for {ws} ranks, this job has {pconf.dev_num}")
+        if dm != dev_mem:
+            raise RuntimeError(f"deployment file was made for {dm} bytes of device memory, this device has {dev_mem}")
+        logger.info("Loaded deployment from %s", load_path)
+        return Plan(dep, [], len(dep.fwd_graph_order), dev_mem)
+
+    # more stages than devices can be forced for testing: search with one virtual device per stage,
+    # the allocation then wraps around the real ranks
+    real_dev = pconf.dev_num
+    if pconf.cfg_partition_num > pconf.dev_num:
+        pconf.dev_num = pconf.cfg_partition_num
+        pconf.cfg_replica_num = 1
+        pconf.limit_dev_num_more_than_bs = False
+
+    pm = _core.ProfileModel(ir_graph, node_profiles, pconf.link)
+    decomposer = str(conf("decomposer"))
+    estimates = []
+    if decomposer == "fair_weight":
+        sol = _core.fair_weight_decompose(pm, pconf)
+        ml_nodes = len(sol.graphs)
+    else:
+        ml_file = str(conf("mlpart_results_file"))
+        if bool(conf("load_mlpart_results")) and os.path.exists(ml_file):
+            with open(ml_file, "rb") as f:
+                ml = _core.MLGraph.loads(f.read())
+        else:
+            ml = _core.ml_partition(pm, pconf)
+            if bool(conf("save_mlpart_results")):
+                with open(ml_file, "wb") as f:
+                    f.write(ml.dumps())
+        ml_nodes = len(ml.nodes)
+        logger.info("Coarsened the graph to %d blocks", ml_nodes)
+        if str(conf("dump_dp_cache")):
+            with open(str(conf("dump_dp_cache")), "wb") as f:
+                f.write(_core.dump_dp_cache(ml, ir_graph, node_profiles, pconf))
+        sol, estimates, node_json = _core.dp_staging(pm, ml, pconf)
+        if str(conf("dump_dp_node_profiles")):
+            with open(str(conf("dump_dp_node_profiles")), "w") as f:
+                f.write(node_json)
+        if bool(conf("save_alloc_solutions")):
+            path = f"{conf('alloc_solutions_file_prefix')}_s{len(sol.graphs)}_p{sol.pipeline_num}.bin"
+            with open(path, "wb") as f:
+                f.write(sol.dumps())
+        logger.info(_fmt_table(estimates))
+    dep = _core.create_deployment(ir_graph, sol, real_dev, bool(conf("alloc_repl_flat")), dep_id)
+    dep.offload_params = offload_params
+    dep.force_dist_matmul = bool(conf("force_dist_matmul"))
+    err = _core.verify_deployment(dep)
+    if err:
+        raise RuntimeError("inconsistent deployment: " + err)
+    for name in dep.fwd_graph_order:
+        logger.info("Assigned subgraph %s to rank(s) %s", name, dep.allocation[name])
+    if bool(conf("dump_graph")):
+        prefix = str(conf("dump_graph_prefix"))
+        for name, sg in dep.subgraphs.items():
+            with open(f"{prefix}_{name}.dot", "w") as f:
+                f.write(sg.to_dot())
+    if bool(conf("save_deployment")):
+        with open(str(conf("deployment_file")), "wb") as f:
+            f.write(_core.save_deployment(dep, real_dev, dev_mem))
+    return Plan(dep, list(estimates), ml_nodes, dev_mem)

@@ -1,0 +1,363 @@
+"""Autograd-aware fused operators backed by the sm_100a kernels.
+
+Each function here is what a rewritten stage graph calls in place of one or
+several ATen nodes of the exported model (``graph/rewrite.py`` does the
+rewriting).  Forward and backward both run hand-written kernels; nothing in
+here calls a library GEMM or attention.
+
+Weight gradients go straight into a parameter's fp32 ``main_grad`` buffer when
+it has one (the wgrad GEMM accumulates in its epilogue), so gradient
+accumulation over micro-batches needs no separate add and no 16-bit rounding.
+Reference counterpart: the ATen kernels run by src/torch/TorchDriver.cpp:566 and
+the per-parameter ``grad`` buffers of src/comp/ParamStorage.cpp:33-191.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels as K
+from .gemm import gemm
+
+
+# ----------------------------------------------------------------------------- RNG
+class _Rng:
+    """Counter-based dropout randomness: (seed, running offset).
+
+    A recomputed forward reproduces its masks by restoring ``offset`` to the value
+    it had when the original forward started (see ``get_state`` / ``set_state``),
+    which is what the reference achieves by stashing the CUDA RNG state
+    (src/comp/GraphConnector.cpp:395-457)."""
+
+    def __init__(self):
+        self.seed = 0x5EED
+        self.offset = 0
+
+    def next(self):
+        self.offset += 1
+        return self.seed, self.offset
+
+    def get_state(self):
+        return self.seed, self.offset
+
+    def set_state(self, st):
+        self.seed, self.offset = st
+
+
+rng = _Rng()
+
+
+def manual_seed(seed: int) -> None:
+    rng.seed = int(seed) & 0x7FFFFFFFFFFFFFFF
+    rng.offset = 0
+
+
+def _main_grad(p):
+    return getattr(p, "main_grad", None)
+
+
+def _2d(x):
+    return x.reshape(-1, x.shape[-1])
+
+
+def _kernel_ok(x) -> bool:
+    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
+
+
+def _aligned(t) -> bool:
+    return t.data_ptr() % 16 == 0 and t.shape[-1] % 8 == 0
+
+
+def _wgrad(dy2, x2, weight, mg):
+    """dW = dy2^T @ x2, into the fp32 main-grad buffer when there is one."""
+    if mg is not None:
+        gemm(dy2, x2, trans_a=True, trans_b=False, out=mg, accumulate=True)
+        return None
+    return gemm(dy2, x2, trans_a=True, trans_b=False)
+
+
+def _bgrad(dy2, bias, mg):
+    if bias is None:
+        return None
+    if mg is not None:
+        K.colsum(dy2, out=mg)
+        return None
+    return K.colsum(dy2).to(bias.dtype)
+
+
+# ----------------------------------------------------------------------------- linear
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, act):
+        x2 = _2d(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        pre = None
+        if act == "gelu":
+            pre = torch.empty(x2.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
+            y = gemm(x2, weight, bias=bias, gelu=True, aux_out=pre)
+        else:
+            y = gemm(x2, weight, bias=bias)
+        ctx.save_for_backward(x2, weight, pre)
+        ctx.has_bias = bias is not None
+        ctx.bias_ref = bias
+        ctx.w_mg = _main_grad(weight)
+        ctx.b_mg = _main_grad(bias) if bias is not None else None
+        ctx.x_shape = x.shape
+        ctx.act = act
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, pre = ctx.saved_tensors
+        dy2 = _2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if ctx.act == "gelu":
+            dy2 = K.gelu_bwd(pre, dy2)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, trans_b=False).view(ctx.x_shape)
+        dw = _wgrad(dy2, x2, weight, ctx.w_mg) if ctx.needs_input_grad[1] else None
+        db = _bgrad(dy2, ctx.bias_ref, ctx.b_mg) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None
+
+
+def linear(x, weight, bias=None, act=None):
+    """``act(x @ weight.T + bias)`` with ``act`` in (None, "gelu")."""
+    if not (_kernel_ok(x) and weight.dtype == x.dtype and _aligned(x) and _aligned(weight)):
+        y = torch.nn.functional.linear(x, weight, bias)
+        return torch.nn.functional.gelu(y) if act == "gelu" else y
+    return _Linear.apply(x, weight, bias, act)
+
+
+class _Mlp(torch.autograd.Function):
+    """y = gelu(x W1^T + b1) W2^T + b2; the GELU derivative rides in the dgrad GEMM epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2):
+        x2 = _2d(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        pre = torch.empty(x2.shape[0], w1.shape[0], dtype=x.dtype, device=x.device)
+        h = gemm(x2, w1, bias=b1, gelu=True, aux_out=pre)
+        y = gemm(h, w2, bias=b2)
+        ctx.save_for_backward(x2, w1, w2, pre, h)
+        ctx.refs = (b1, b2)
+        ctx.mgs = (_main_grad(w1), _main_grad(b1) if b1 is not None else None, _main_grad(w2),
+                   _main_grad(b2) if b2 is not None else None)
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w1, w2, pre, h = ctx.saved_tensors
+        b1, b2 = ctx.refs
+        w1_mg, b1_mg, w2_mg, b2_mg = ctx.mgs
+        dy2 = _2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dw2 = _wgrad(dy2, h, w2, w2_mg)
+        db2 = _bgrad(dy2, b2, b2_mg)
+        dpre = gemm(dy2, w2, trans_b=False, dgelu=True, aux_in=pre)
+        dw1 = _wgrad(dpre, x2, w1, w1_mg)
+        db1 = _bgrad(dpre, b1, b1_mg)
+        dx = gemm(dpre, w1, trans_b=False).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        return dx, dw1, db1, dw2, db2
+
+
+def mlp(x, w1, b1, w2, b2):
+    if not (_kernel_ok(x) and _aligned(x) and _aligned(w1) and _aligned(w2)):
+        return torch.nn.functional.linear(torch.nn.functional.gelu(torch.nn.functional.linear(x, w1, b1)), w2, b2)
+    return _Mlp.apply(x, w1, b1, w2, b2)
+
+
+# ----------------------------------------------------------------------------- layer norm
+class _DropoutAddLayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, gamma, beta, p, eps):
+        seed, offset = rng.next() if p > 0.0 else (0, 0)
+        xc = x if x.is_contiguous() else x.contiguous()
+        rc = None if residual is None else (residual if residual.is_contiguous() else residual.contiguous())
+        y, z, mean, rstd = K.ln_fwd(xc, rc, gamma, beta, eps, p, seed, offset)
+        ctx.save_for_backward(z, gamma, mean, rstd)
+        ctx.p, ctx.seed, ctx.offset = p, seed, offset
+        ctx.has_res = residual is not None
+        ctx.g_ref, ctx.b_ref = gamma, beta
+        ctx.g_mg, ctx.b_mg = _main_grad(gamma), _main_grad(beta)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        z, gamma, mean, rstd = ctx.saved_tensors
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        use_mg = ctx.g_mg is not None and ctx.b_mg is not None
+        dz, dx, dg, db = K.ln_bwd(dyc, z, gamma, mean, rstd, ctx.p, ctx.seed, ctx.offset,
+                                  dgamma=ctx.g_mg if use_mg else None, dbeta=ctx.b_mg if use_mg else None,
+                                  accumulate=use_mg)
+        if use_mg:
+            dg = db = None
+        else:
+            dg, db = dg.to(gamma.dtype), db.to(gamma.dtype)
+        return dx, (dz if ctx.has_res else None), dg, db, None, None
+
+
+def dropout_add_layer_norm(x, residual, gamma, beta, p: float = 0.0, eps: float = 1e-5, training: bool = True):
+    """``LayerNorm(dropout(x, p) + residual)`` over the last dimension."""
+    p = p if training else 0.0
+    if not (_kernel_ok(x) and K.ln_supported(x.shape[-1]) and gamma is not None and beta is not None):
+        h = torch.nn.functional.dropout(x, p, True) if p > 0 else x
+        if residual is not None:
+            h = h + residual
+        return torch.nn.functional.layer_norm(h, (x.shape[-1],), gamma, beta, eps)
+    return _DropoutAddLayerNorm.apply(x, residual, gamma, beta, float(p), float(eps))
+
+
+# ----------------------------------------------------------------------------- element-wise
+class _Dropout(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p):
+        ctx.p = p
+        ctx.seed, ctx.offset = rng.next()
+        return K.dropout(x if x.is_contiguous() else x.contiguous(), p, ctx.seed, ctx.offset)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return K.dropout(dy if dy.is_contiguous() else dy.contiguous(), ctx.p, ctx.seed, ctx.offset), None
+
+
+def dropout(x, p: float, training: bool = True):
+    if not training or p <= 0.0:
+        return x
+    if not _kernel_ok(x) or x.numel() == 0:
+        return torch.nn.functional.dropout(x, p, True)
+    return _Dropout.apply(x, float(p))
+
+
+class _Gelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x if x.is_contiguous() else x.contiguous()
+        ctx.save_for_backward(xc)
+        return K.gelu(xc)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return K.gelu_bwd(x, dy if dy.is_contiguous() else dy.contiguous())
+
+
+def gelu(x):
+    if not _kernel_ok(x):
+        return torch.nn.functional.gelu(x)
+    return _Gelu.apply(x)
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, weight, ids, padding_idx):
+        idc = ids if ids.is_contiguous() else ids.contiguous()
+        ctx.save_for_backward(idc)
+        ctx.w_ref = weight
+        ctx.w_mg = _main_grad(weight)
+        ctx.padding_idx = padding_idx
+        return K.embed_fwd(idc, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        if ctx.w_mg is not None:
+            K.embed_bwd(ids, dyc, ctx.w_mg, ctx.padding_idx)
+            return None, None, None
+        acc = torch.zeros(ctx.w_ref.shape, dtype=torch.float32, device=dy.device)
+        K.embed_bwd(ids, dyc, acc, ctx.padding_idx)
+        return acc.to(ctx.w_ref.dtype), None, None
+
+
+def embedding(weight, ids, padding_idx: int = -1):
+    if not (_kernel_ok(weight) and weight.shape[1] % 8 == 0 and ids.dtype == torch.int64):
+        return torch.nn.functional.embedding(ids, weight, None if padding_idx < 0 else padding_idx)
+    return _Embedding.apply(weight, ids, padding_idx)
+
+
+# ----------------------------------------------------------------------------- attention
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, key_bias, p, scale):
+        # q, k, v: [B, S, H, D] views
+        seed, offset = rng.next() if p > 0.0 else (0, 0)
+        o, lse = K.attn_fwd(q, k, v, key_bias, scale, p, seed, offset)
+        ctx.save_for_backward(q, k, v, o, lse, key_bias)
+        ctx.p, ctx.seed, ctx.offset, ctx.scale = p, seed, offset, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, key_bias = ctx.saved_tensors
+        B, S, H, D = q.shape
+        # one [B, S, 3, H, D] buffer so the three gradients are views a fused QKV consumer can use as is
+        dqkv = torch.empty(B, S, 3, H, D, dtype=q.dtype, device=q.device)
+        dq, dk, dv = K.attn_bwd(q, k, v, o, lse, do, key_bias, ctx.scale, ctx.p, ctx.seed, ctx.offset,
+                                dq=dqkv[:, :, 0], dk=dqkv[:, :, 1], dv=dqkv[:, :, 2])
+        return dq, dk, dv, None, None, None
+
+
+def _attn_operand_ok(t):
+    return t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:-1])
+
+
+def sdpa(q, k, v, attn_mask=None, dropout_p: float = 0.0, is_causal: bool = False, scale=None):
+    """Drop-in for ``F.scaled_dot_product_attention`` on [B, H, S, D] operands.
+
+    The fused kernel handles head dim 64, no causal mask, and an additive mask that
+    only depends on (batch, key) -- shape [B, 1, 1, S].  Anything else falls back to
+    the ATen implementation."""
+    ok = (_kernel_ok(q) and q.dim() == 4 and q.shape[-1] == 64 and not is_causal and k.shape == q.shape
+          and v.shape == q.shape)
+    key_bias = None
+    if ok and attn_mask is not None:
+        B, H, S, D = q.shape
+        if attn_mask.dtype != torch.bool and tuple(attn_mask.shape) == (B, 1, 1, S):
+            key_bias = attn_mask.reshape(B, S).float().contiguous()
+        else:
+            ok = False
+    if ok:
+        qs, ks, vs = (t.transpose(1, 2) for t in (q, k, v))  # [B, S, H, D] views
+        if not all(_attn_operand_ok(t) for t in (qs, ks, vs)):
+            qs, ks, vs = (t.contiguous() for t in (qs, ks, vs))
+        sc = float(scale) if scale is not None else q.shape[-1] ** -0.5
+        o = _Attention.apply(qs, ks, vs, key_bias, float(dropout_p), sc)
+        return o.transpose(1, 2)
+    return torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, dropout_p=dropout_p,
+                                                            is_causal=is_causal, scale=scale)
+
+
+# ----------------------------------------------------------------------------- loss
+class _SoftmaxXent(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits2d, labels, V, ignore_index, weight):
+        loss, lse, acc = K.xent_fwd(logits2d, labels, V, ignore_index, weight)
+        ctx.save_for_backward(logits2d, labels, lse, acc)
+        ctx.V, ctx.ignore_index, ctx.weight = V, ignore_index, weight
+        return loss
+
+    @staticmethod
+    def backward(ctx, gout):
+        logits2d, labels, lse, acc = ctx.saved_tensors
+        g = gout.float().contiguous()
+        # the logits are dead after the loss: their buffer receives the gradient
+        d = K.xent_bwd(logits2d, labels, lse, acc, g, ctx.V, ctx.ignore_index, ctx.weight, inplace=True)
+        return d, None, None, None, None
+
+
+def cross_entropy(logits, labels, num_classes=None, ignore_index: int = -100, weight: float = 1.0):
+    """Mean cross entropy over rows whose label is not ``ignore_index``.
+
+    ``logits`` may have more columns than ``num_classes`` (vocabulary padding): the extra
+    columns are ignored and get a zero gradient.  Returns an fp32 scalar."""
+    ld = logits.shape[-1]
+    V = int(num_classes) if num_classes is not None else ld
+    l2 = logits.reshape(-1, ld)
+    if not (_kernel_ok(l2) and l2.stride(1) == 1):
+        return torch.nn.functional.cross_entropy(l2[:, :V].float(), labels.reshape(-1), ignore_index=ignore_index) * weight
+    return _SoftmaxXent.apply(l2, labels.reshape(-1).contiguous(), V, ignore_index, float(weight))
