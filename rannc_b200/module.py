@@ -1,0 +1,499 @@
+"""``RaNNCModule``: wrap an unmodified ``nn.Module`` (+ optimizer) and train it partitioned.
+
+Public behaviour follows the reference's Python class and the C++ class behind it
+(pyrannc/__init__.py:206-593, src/comp/RaNNCModule.cpp:95-660): lazy
+initialisation on the first call (trace -> profile -> partition -> deploy),
+``__call__`` rejecting keyword arguments, parameter views restricted to this
+rank, ``clip_grad_norm``, collective ``state_dict`` / ``get_param`` /
+``get_param_grad``, ``save_deployment``, ``undeploy``, ``enable_dropout`` and the
+process-wide switches ``delay_grad_allreduce`` / ``keep_graph`` /
+``sync_params_on_init``.
+"""
+from __future__ import annotations
+
+import os
+import random
+import weakref
+from collections import OrderedDict
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _core
+from . import amp as _amp
+from .graph import planner, profiler, tracer
+from .parallel import comm
+from .parallel.param_storage import ParamStorage
+from .parallel.pipeline import PipelineRuntime
+from .parallel.stage import StageExec, build_stage_module, set_dropout
+from .utils.config import conf
+from .utils.log import get_logger
+
+logger = get_logger("RaNNCModule")
+
+_delay_grad_allreduce = False
+_keep_graph = False
+_sync_params_on_init = True
+_live_modules: "weakref.WeakSet[RaNNCModule]" = weakref.WeakSet()
+
+
+def delay_grad_allreduce(flag: bool) -> None:
+    """Skip the gradient reduction at the end of backward (gradient accumulation); call
+    ``model.allreduce_grads()`` before the optimizer step (reference: src/comp/Backward.cpp:100-107)."""
+    global _delay_grad_allreduce
+    _delay_grad_allreduce = bool(flag)
+
+
+def keep_graph(flag: bool) -> None:
+    global _keep_graph
+    _keep_graph = bool(flag)
+
+
+def sync_params_on_init(flag: bool) -> None:
+    global _sync_params_on_init
+    _sync_params_on_init = bool(flag)
+
+
+class _DistBackward(torch.autograd.Function):
+    """Autograd node that turns ``out.backward()`` into the distributed backward pass
+    (reference: RaNNCTensorBackward, src/comp/Backward.cpp:87-129)."""
+
+    @staticmethod
+    def forward(ctx, mod_ref, anchor, *outs):
+        ctx.mod_ref = mod_ref
+        ctx.n = len(outs)
+        return tuple(o.clone() if o.is_floating_point() else o for o in outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        mod = ctx.mod_ref()
+        if mod is None:
+            raise RuntimeError("the RaNNCModule of this output no longer exists")
+        mod._run_backward(grads)
+        return (None, None) + (None,) * ctx.n
+
+
+class RaNNCModule:
+    def __init__(self, model: torch.nn.Module, optimizer=None, gather_inputs: bool = True,
+                 load_deployment: Optional[str] = None, enable_apex_amp: bool = False,
+                 allreduce_amp_master_params: bool = False, enable_zero: bool = False,
+                 check_unused_values: bool = True, offload_params: bool = False):
+        comm.start()
+        if enable_zero and not enable_apex_amp:
+            # same restriction as the reference (pyrannc/__init__.py:224-225)
+            raise RuntimeError("enable_zero requires enable_apex_amp")
+        self.model = model
+        self.optimizer = optimizer
+        self.gather_inputs = gather_inputs
+        self.load_deployment = load_deployment
+        self.use_amp_master_params = enable_apex_amp
+        self.allreduce_amp_master_params = allreduce_amp_master_params
+        self.enable_zero = enable_zero
+        self.check_unused_values = check_unused_values
+        self.offload_params = offload_params
+        self.ready = False
+        self.amp_dtype = _amp.get_dtype() if enable_apex_amp else None
+        self.max_grad_norm = 0.0  # > 0: clip inside the fused optimizer step
+        ident = [f"mod_{random.getrandbits(64):016x}"]
+        self.id = comm.bcast_obj(ident[0], 0)
+        self._storage: Optional[ParamStorage] = None
+        self._runtime: Optional[PipelineRuntime] = None
+        self._traced = None
+        self._plan = None
+        self._anchor = None
+        self._used_param_names: List[str] = []
+        self._dropout = True
+        self._fused_reducer = None
+        _live_modules.add(self)
+
+    # ------------------------------------------------------------------ call
+    def __call__(self, *args, **kwargs):
+        if kwargs:
+            raise RuntimeError("RaNNCModule does not support keyword arguments")
+        dev = comm.device()
+        if dev.type == "cuda":
+            for a in args:
+                if isinstance(a, torch.Tensor) and not a.is_cuda:
+                    raise RuntimeError("All inputs to RaNNCModule must be on a CUDA device")
+        if not self.ready:
+            self._init(args)
+        outs = self._runtime.forward(args, grad_enabled=torch.is_grad_enabled())
+        if torch.is_grad_enabled():
+            outs = list(_DistBackward.apply(weakref.ref(self), self._anchor, *outs))
+        return self._pack_outputs(outs)
+
+    def _pack_outputs(self, outs):
+        spec = self._traced.out_spec
+        if spec is not None:
+            try:
+                import torch.utils._pytree as pytree
+
+                return pytree.tree_unflatten(list(outs), spec)
+            except Exception:  # noqa: BLE001
+                pass
+        return outs[0] if len(outs) == 1 else tuple(outs)
+
+    # ------------------------------------------------------------------ init
+    def _init(self, args):
+        _core.trace_enable(False)  # not during initialisation (reference: RaNNCModule.cpp:164-166)
+        rank, world = comm.get_rank(), comm.get_world_size()
+        dev = comm.device()
+        model = self.model
+        from . import dist_param as _dp
+
+        if self.use_amp_master_params:
+            for p in model.parameters():
+                if not p.is_floating_point():
+                    continue
+                if _dp.dist_param_registered(id(p)):
+                    _dp.set_dist_param_dtype(id(p), self.amp_dtype)
+                    p.data = torch.zeros(1, dtype=self.amp_dtype, device=p.device).expand(p.shape)
+                else:
+                    p.data = p.data.to(self.amp_dtype)
+            for b in model.buffers():
+                if b.is_floating_point():
+                    b.data = b.data.to(self.amp_dtype)
+
+        # global batch = sum of the local batches (reference: RaNNCModule.cpp:173-177)
+        local_bs = 0
+        for a in args:
+            if isinstance(a, torch.Tensor) and a.dim() > 0:
+                local_bs = int(a.shape[0])
+                break
+        sizes = comm.allgather_obj(local_bs)
+        if len(set(sizes)) != 1:
+            raise RuntimeError(f"every rank must pass the same local batch size, got {sizes}")
+        global_bs = sum(sizes)
+
+        logger.info("Tracing model ...")
+        pdev = next((p.device for p in model.parameters()), torch.device("cpu"))
+        targs = tuple(a.to(pdev) if isinstance(a, torch.Tensor) else a for a in args)
+        use_kernels = dev.type == "cuda" and bool(conf("fused_kernels"))
+        with torch.random.fork_rng(devices=[dev] if dev.type == "cuda" else []):
+            self._traced = tracer.trace(model, targs, use_kernels=use_kernels, name=self.id)
+        tm = self._traced
+        if tm.rewrite_stats:
+            logger.info("Fused operators: %s", str(tm.rewrite_stats))
+        if self.check_unused_values:
+            unused = [v for v in _core.find_unused_values(tm.ir)
+                      if v in tm.params or v in tm.user_inputs]
+            if unused:
+                raise RuntimeError(f"values never used by the model: {unused}; pass check_unused_values=False to "
+                                   f"ignore")
+        ir = _core.scale_graph(tm.ir, global_bs)
+
+        logger.info("Running profiler ...")
+        if bool(conf("measure_profiles")) and dev.type == "cuda":
+            node_profiles = profiler.measured_profiles(tm.gm, dev)
+        else:
+            node_profiles = profiler.analytic_profiles(tm.gm)
+        # node times were taken at the traced (local) batch: express them at the global batch
+        if global_bs != tm.trace_batch and tm.trace_batch > 0:
+            r = global_bs / tm.trace_batch
+            for k, p in node_profiles.items():
+                if p.scales_with_batch:
+                    node_profiles[k] = _core.NodeProfile(p.fwd_us * r, p.bwd_us * r, int(p.activation_bytes * r),
+                                                         int(p.working_bytes * r), True)
+
+        total_mem = 0
+        if dev.type == "cuda":
+            total_mem = torch.cuda.get_device_properties(dev).total_memory
+        dep_bytes = None
+        if rank == 0:
+            logger.info("Partitioning the model for %d device(s), global batch %d ...", world, global_bs)
+            self._plan = planner.plan(ir, node_profiles, world, global_bs, total_mem, self.use_amp_master_params,
+                                      self.enable_zero, self.offload_params, self.id, self.load_deployment)
+            dep_bytes = bytes(_core.save_deployment(self._plan.deployment, world, self._plan.dev_mem))
+        dry = int(conf("partitioning_dry_run_np"))
+        if dry > 0:
+            # plan for `dry` devices on fewer, then stop (reference: RaNNCModule.cpp:416-421)
+            comm.barrier()
+            raise SystemExit(0)
+        dep_bytes = comm.bcast_bytes(dep_bytes, 0)
+        dep, _, dev_mem = _core.load_deployment(dep_bytes)
+        self._dep = dep
+        self._dev_mem = dev_mem
+
+        # ---- deploy
+        name_to_param = OrderedDict(model.named_parameters(remove_duplicate=True))
+        name_to_buffer = OrderedDict(model.named_buffers(remove_duplicate=True))
+        self._all_param_names = list(name_to_param.keys())
+        self._param_order_by_name = {n: i for i, n in enumerate(self._all_param_names)}
+        self._global_param_order = {id(p): self._param_order_by_name[n] for n, p in name_to_param.items()}
+        self._param_meta = {n: (tuple(p.shape), p.dtype) for n, p in name_to_param.items()}
+        owner: Dict[str, set] = {n: set() for n in name_to_param}
+        buf_owner: Dict[str, set] = {n: set() for n in name_to_buffer}
+        local_stage_names = []
+        for sname in dep.fwd_graph_order:
+            sg = dep.subgraphs[sname]
+            ranks = dep.allocation[sname]
+            for pin in sg.param_input_names():
+                if pin in tm.params:
+                    owner[tm.params[pin]].update(ranks)
+                elif pin in tm.buffers:
+                    buf_owner[tm.buffers[pin]].update(ranks)
+            if rank in ranks:
+                local_stage_names.append(sname)
+        # a parameter shared by two stages of the same rank cannot be told apart by the gradient
+        # reduction (reference: ParamStorage.cpp:893-902)
+        seen: Dict[str, str] = {}
+        for sname in local_stage_names:
+            for pin in dep.subgraphs[sname].param_input_names():
+                if pin in tm.params:
+                    fq = tm.params[pin]
+                    if fq in seen and seen[fq] != sname and name_to_param[fq].requires_grad and world > 1:
+                        raise RuntimeError(f"parameter {fq} is shared by stages {seen[fq]} and {sname} on rank {rank}")
+                    seen[fq] = sname
+        unused_params = [n for n, r in owner.items() if not r]
+        for n in unused_params:
+            owner[n] = {0}
+        self._used_param_names = [n for n in name_to_param if rank in owner[n]]
+        self._used_buffer_names = [n for n in name_to_buffer if rank in buf_owner[n] or not buf_owner[n]]
+
+        # parameters sharded at construction are assembled on their owners only (collective, global order)
+        for n, p in name_to_param.items():
+            if _dp.dist_param_registered(id(p)):
+                _dp.materialize(p, rank in owner[n], dev)
+
+        opt_group_of = {}
+        if self.optimizer is not None:
+            for gi, g in enumerate(self.optimizer.param_groups):
+                for p in g["params"]:
+                    opt_group_of[id(p)] = gi
+        self._storage = ParamStorage(self.use_amp_master_params, self.enable_zero, self.allreduce_amp_master_params)
+        self._storage.sync_on_init = _sync_params_on_init
+        local_params = {n: name_to_param[n] for n in self._used_param_names}
+        self._storage.deploy(local_params, {n: sorted(r) for n, r in owner.items()}, opt_group_of, dev,
+                             self._param_order_by_name)
+        for n in self._used_buffer_names:
+            b = name_to_buffer[n]
+            b.data = b.data.to(dev)
+            ranks = sorted(buf_owner[n]) if buf_owner[n] else None
+            if _sync_params_on_init and ranks and len(ranks) > 1:
+                comm.create_groups([ranks])
+                comm.bcast(b.data, ranks[0], ranks)
+        if self.use_amp_master_params:
+            self._storage.setup_master()
+
+        stages: Dict[str, StageExec] = {}
+        for sname in local_stage_names:
+            sg = dep.subgraphs[sname]
+            gm = build_stage_module(tm.gm, sg)
+            tensors = {}
+            for pin in sg.param_input_names():
+                if pin in tm.params:
+                    tensors[pin] = name_to_param[tm.params[pin]]
+                elif pin in tm.buffers:
+                    tensors[pin] = name_to_buffer[tm.buffers[pin]]
+                elif pin in tm.constants:
+                    tensors[pin] = tm.constants[pin].to(dev)
+            st = StageExec(sname, gm, sg, tensors)
+            st.keep_graph = _keep_graph
+            stages[sname] = st
+        self._stages = stages
+        self._runtime = PipelineRuntime(dep, stages, tm.user_inputs, tm.user_outputs, global_bs, self.gather_inputs)
+        self._buffer_mutations = tm.buffer_mutations
+        self._anchor = torch.zeros((), device=dev, requires_grad=True)
+
+        if self.optimizer is not None:
+            from .opt import patch_optimizer
+
+            patch_optimizer(self, self.optimizer)
+        if self.use_amp_master_params and dev.type == "cuda" and bool(conf("fused_grad_allreduce")) and world > 1:
+            self._setup_fused_reducer()
+        self.ready = True
+        comm.barrier()
+        _core.trace_enable(bool(conf("trace_events")))
+        logger.info("RaNNCModule is ready. (rank %d: stages %s)", rank, str(local_stage_names))
+
+    def _setup_fused_reducer(self):
+        try:
+            from .parallel.fused_reduce import FusedGradReducer
+
+            self._fused_reducer = FusedGradReducer.create(self._storage, self.optimizer)
+        except Exception as e:  # noqa: BLE001
+            logger.warning("fused gradient reduction unavailable (%s); using NCCL collectives", str(e))
+            self._fused_reducer = None
+
+    # ------------------------------------------------------------------ backward
+    def _run_backward(self, grads):
+        self._runtime.backward(grads)
+        if not _delay_grad_allreduce:
+            if self.enable_zero:
+                self.allreduce_grads_zero()
+            else:
+                self.allreduce_grads()
+
+    def allreduce_grads(self):
+        if self._fused_reducer is not None and self._fused_reducer.handles_reduce:
+            self._storage.fold_model_grads()
+            self._fused_reducer.mark_ready()
+            return
+        self._storage.allreduce_grads()
+
+    def allreduce_grads_zero(self):
+        if self._fused_reducer is not None and self._fused_reducer.handles_reduce:
+            self._storage.fold_model_grads()
+            self._fused_reducer.mark_ready()
+            return
+        self._storage.allreduce_grads_zero()
+
+    def _amp_prepare_step(self):
+        """Called by the patched optimizer step.  Returns None (nothing to do), False (overflow: skip the step)
+        or a device tensor [gradient multiplier, skip flag] for the fused optimizer kernel."""
+        scaler = _amp.get_scaler()
+        scale = scaler.loss_scale() if self.use_amp_master_params else 1.0
+        need_check = self.use_amp_master_params and self.amp_dtype == torch.float16
+        if not need_check and scale == 1.0 and self.max_grad_norm <= 0.0:
+            return None
+        ss = self._storage.grad_sumsq()
+        ctrl = self._storage._ctrl
+        if ss.is_cuda:
+            from .ops import kernels as K
+
+            K.finalize_ctrl(ss, 1.0 / scale, float(self.max_grad_norm), ctrl, self._storage._norm)
+        else:
+            norm = float(ss.sqrt()) / scale
+            bad = not torch.isfinite(ss).all()
+            mul = 1.0 / scale
+            if self.max_grad_norm > 0 and not bad:
+                mul *= min(1.0, self.max_grad_norm / (norm + 1e-6))
+            ctrl[0], ctrl[1] = mul, 1.0 if bad else 0.0
+        if need_check:
+            overflow = bool(ctrl[1].item() != 0)
+            if scaler.update_scale(overflow):
+                return False
+        return ctrl
+
+    # ------------------------------------------------------------------ parameters
+    def parameters(self, recurse: bool = True):
+        for _, p in self.named_parameters():
+            yield p
+
+    def named_parameters(self, prefix: str = "", recurse: bool = True):
+        if not self.ready:
+            yield from self.model.named_parameters(prefix, recurse)
+            return
+        used = set(self._used_param_names)
+        for n, p in self.model.named_parameters(prefix, recurse):
+            base = n[len(prefix) + 1:] if prefix else n
+            if base in used:
+                yield n, p
+
+    def buffers(self, recurse: bool = True):
+        for _, b in self.named_buffers():
+            yield b
+
+    def named_buffers(self, prefix: str = "", recurse: bool = True):
+        if not self.ready:
+            yield from self.model.named_buffers(prefix, recurse)
+            return
+        used = set(self._used_buffer_names)
+        for n, b in self.model.named_buffers(prefix, recurse):
+            base = n[len(prefix) + 1:] if prefix else n
+            if base in used:
+                yield n, b
+
+    def to(self, *args, **kwargs):
+        logger.warning("to() was ignored. RaNNC places the parameters itself.")
+        return self
+
+    def cuda(self, *args, **kwargs):
+        logger.warning("cuda() was ignored. RaNNC places the parameters itself.")
+        return self
+
+    def train(self, mode: bool = True):
+        if self.ready:
+            logger.warning("train() after the first forward only toggles dropout; use enable_dropout().")
+            self.enable_dropout(mode)
+        self.model.train(mode)
+        return self
+
+    def eval(self):
+        return self.train(False)
+
+    def zero_grad(self):
+        if self._storage is not None:
+            self._storage.zero_grad()
+        else:
+            self.model.zero_grad()
+
+    def clip_grad_norm(self, max_norm: float) -> float:
+        """Global L2 norm over every rank's gradients, then scale (reference: ParamStorage.cpp:721-819)."""
+        return self._storage.clip_grad_norm(float(max_norm))
+
+    def _calc_grad_norm(self) -> float:
+        return self._storage.calc_grad_norm()
+
+    def get_param(self, name: str, amp_master_param: bool = False) -> torch.Tensor:
+        shape, dtype = self._param_meta[name]
+        return self._storage.get_param(name, shape, dtype, amp_master_param)
+
+    def get_param_grad(self, name: str, amp_master_param: bool = False) -> torch.Tensor:
+        shape, dtype = self._param_meta[name]
+        return self._storage.get_param_grad(name, shape, dtype, amp_master_param)
+
+    def state_dict(self, *args, no_hook: bool = False, sync_all_ranks: bool = True, amp_master_params: bool = True,
+                   rank0_only: bool = True, **kwargs):
+        """Collective: every rank must call it.  Full CPU tensors under the original names (tied parameters
+        under every alias); fp32 master values under mixed precision (reference: pyrannc/__init__.py:401-436)."""
+        if not self.ready:
+            return self.model.state_dict(*args, **kwargs)
+        keep = comm.get_rank() == 0 or not rank0_only
+        out = OrderedDict()
+        by_id = {}
+        for n, p in self.model.named_parameters(remove_duplicate=False):
+            canon = by_id.setdefault(id(p), n)
+            if canon == n:
+                v = self.get_param(n, amp_master_params and self.use_amp_master_params)
+                if keep:
+                    out[n] = v
+            elif keep:
+                out[n] = out[canon]
+        sd_keys = self.model.state_dict().keys()
+        for n, b in self.model.named_buffers(remove_duplicate=False):
+            if n not in sd_keys:
+                continue
+            v = b.detach().to(comm.device()).clone()
+            if comm.get_world_size() > 1:
+                comm.bcast(v, 0)
+            if keep:
+                out[n] = v.cpu()
+        return out if keep else None
+
+    def load_state_dict(self, state_dict, strict: bool = True):
+        if self.ready:
+            raise RuntimeError("load_state_dict must be called before the first forward")
+        return self.model.load_state_dict(state_dict, strict)
+
+    def save_deployment(self, path: str) -> None:
+        if comm.get_rank() == 0:
+            with open(path, "wb") as f:
+                f.write(_core.save_deployment(self._dep, comm.get_world_size(), self._dev_mem))
+
+    def undeploy(self) -> None:
+        if self._runtime is not None:
+            self._runtime.clear()
+        self._runtime = None
+        self._stages = {}
+        self.ready = False
+
+    def enable_dropout(self, enable: bool) -> None:
+        self._dropout = bool(enable)
+        for st in getattr(self, "_stages", {}).values():
+            set_dropout(st.gm, enable)
+
+    def is_checkpointing_enabled(self) -> bool:
+        return bool(self._dep.checkpointing) if self.ready else False
+
+    def __getattr__(self, name):
+        model = self.__dict__.get("model")
+        if model is not None and hasattr(model, name):
+            return getattr(model, name)
+        raise AttributeError(name)
+
+    def __del__(self):
+        try:
+            self.undeploy()
+        except Exception:  # noqa: BLE001
+            pass

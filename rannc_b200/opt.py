@@ -1,0 +1,341 @@
+"""Optimizer patching and optimizer checkpoints.
+
+Same contract as the reference's ``pyrannc/opt.py``:
+
+* ``patch_optimizer`` rewrites ``param_groups`` so the optimizer only sees the
+  parameters placed on this rank (under mixed precision: their fp32 master
+  copies; under ZeRO: the local fp32 segments, empty segments dropped --
+  pyrannc/opt.py:205-246), and patches ``step``, ``zero_grad``, ``state_dict``
+  and ``load_state_dict``;
+* ``optimizer.state_dict(from_global=True)`` gathers the state of every
+  parameter to rank 0 in the format
+  ``{'state': {global_param_order: {...}}, 'param_groups': <original groups>}``
+  (pyrannc/opt.py:98-157) and ``load_state_dict(sd, from_global=True)``
+  re-shards it (pyrannc/opt.py:186-202,276-289).
+
+What differs: for Adam / AdamW / SGD the patched ``step`` runs ONE fused kernel
+per (flat buffer, param group) over the flat master / gradient / moment buffers
+-- un-scaling, clipping, overflow skip, update and the 16-bit write-back in one
+pass -- instead of stepping per parameter (``ops/kernels.py: adam_flat``).  Any
+other optimizer class still works through its own ``step`` on the master views.
+"""
+from __future__ import annotations
+
+import copy
+import types
+from typing import Dict, List, Optional
+
+import torch
+
+from .parallel import comm
+from .utils.config import conf
+from .utils.log import get_logger
+
+logger = get_logger("Optimizer")
+
+
+def _fusable(opt) -> Optional[str]:
+    if not bool(conf("fused_kernels")):
+        return None
+    if type(opt) in (torch.optim.Adam, torch.optim.AdamW):
+        for g in opt.param_groups:
+            if g.get("amsgrad") or g.get("maximize") or g.get("capturable"):
+                return None
+        return "adam"
+    if type(opt) is torch.optim.SGD:
+        for g in opt.param_groups:
+            if g.get("maximize"):
+                return None
+        return "sgd"
+    return None
+
+
+class _FlatState:
+    """Moment buffers of one flat group, indexed like its master buffer (the shard under ZeRO)."""
+
+    def __init__(self, n: int, device, kind: str):
+        self.m = torch.zeros(n, dtype=torch.float32, device=device)
+        self.v = torch.zeros(n, dtype=torch.float32, device=device) if kind == "adam" else None
+        self.step = 0
+
+
+def patch_optimizer(module, optimizer):
+    """``module`` is the RaNNCModule that owns the ParamStorage."""
+    storage = module._storage
+    amp = storage.amp
+    optimizer._rannc_orig_param_groups = [
+        {k: (list(v) if k == "params" else v) for k, v in g.items()} for g in optimizer.param_groups]
+    orig_params_flat = [p for g in optimizer._rannc_orig_param_groups for p in g["params"]]
+    optimizer._rannc_orig_ids = [id(p) for p in orig_params_flat]
+
+    # model parameter -> the tensor the optimizer updates on this rank
+    local_of: Dict[int, Optional[torch.nn.Parameter]] = {}
+    for g in storage.groups:
+        for i, p in enumerate(g.params):
+            if amp and g.master_params and g.master_params[i] is not None:
+                local_of[id(p)] = g.master_params[i]
+            elif amp and g.flat_master is not None:
+                local_of[id(p)] = None  # empty segment on this rank
+            else:
+                local_of[id(p)] = p
+    local_to_global: Dict[int, int] = {}
+    new_groups = []
+    for gi, g in enumerate(optimizer.param_groups):
+        kept = []
+        for p in g["params"]:
+            lp = local_of.get(id(p), None)
+            if lp is None:
+                continue
+            kept.append(lp)
+            local_to_global[id(lp)] = module._global_param_order[id(p)]
+        g["params"] = kept
+        new_groups.append(g)
+    optimizer.state.clear()
+    optimizer._rannc_local_to_global = local_to_global
+    optimizer._rannc_kind = _fusable(optimizer)
+    optimizer._rannc_flat_state = {}
+    optimizer._rannc_module = module
+
+    orig_step = optimizer.step
+    orig_state_dict = optimizer.state_dict
+    orig_load_state_dict = optimizer.load_state_dict
+
+    def _flat_ranges():
+        """(flat group, optimizer group index, a, b) with [a, b) in flat coordinates, clipped to the shard."""
+        out = []
+        for g in storage.groups:
+            spans: Dict[int, List[int]] = {}
+            for i, og in enumerate(g.opt_group):
+                if og < 0 or not g.params[i].requires_grad:
+                    continue
+                lo, hi = g.param_range(i)
+                s = spans.setdefault(og, [lo, hi])
+                s[0], s[1] = min(s[0], lo), max(s[1], hi)
+            for og, (lo, hi) in sorted(spans.items()):
+                a, b = max(lo, g.shard[0]), min(hi, g.shard[1])
+                if b > a:
+                    out.append((g, og, a, b))
+        return out
+
+    def _publish_state(g, fs):
+        """Per-parameter views of the flat moments in ``optimizer.state`` (torch's own layout)."""
+        lo = g.shard[0]
+        for i, p in enumerate(g.params):
+            target = g.master_params[i] if (g.flat_master is not None and g.master_params) else p
+            if target is None or g.opt_group[i] < 0:
+                continue
+            a, b = g.local_range(i)
+            if b <= a:
+                continue
+            st = optimizer.state[target]
+            st["step"] = torch.tensor(float(fs.step))
+            if optimizer._rannc_kind == "adam":
+                st["exp_avg"] = fs.m[a - lo:b - lo].view(target.shape)
+                st["exp_avg_sq"] = fs.v[a - lo:b - lo].view(target.shape)
+            else:
+                st["momentum_buffer"] = fs.m[a - lo:b - lo].view(target.shape)
+
+    def fused_step(ctrl=None):
+        from .ops import kernels as K
+
+        kind = optimizer._rannc_kind
+        for g in storage.groups:
+            fs = optimizer._rannc_flat_state.get(id(g))
+            if fs is None:
+                n = g.shard[1] - g.shard[0]
+                fs = optimizer._rannc_flat_state[id(g)] = _FlatState(n, g.device, kind)
+            fs.step += 1
+        for g, og, a, b in _flat_ranges():
+            fs = optimizer._rannc_flat_state[id(g)]
+            hp = optimizer.param_groups[og]
+            lo = g.shard[0]
+            is_amp = g.flat_master is not None
+            master = g.flat_master[a - lo:b - lo] if is_amp else g.flat_param[a:b]
+            model16 = g.flat_param[a:b] if is_amp else None
+            grad = g.flat_grad[a:b]
+            if kind == "adam":
+                b1, b2 = hp["betas"]
+                K.adam_flat(master, grad, fs.m[a - lo:b - lo], fs.v[a - lo:b - lo], model16, float(hp["lr"]), b1,
+                            b2, float(hp["eps"]), float(hp["weight_decay"]), fs.step,
+                            type(optimizer) is torch.optim.AdamW, ctrl)
+            else:
+                K.sgd_flat(master, grad, fs.m[a - lo:b - lo], model16, float(hp["lr"]), float(hp["momentum"]),
+                           float(hp.get("dampening", 0.0)), float(hp["weight_decay"]), bool(hp.get("nesterov")),
+                           fs.step == 1, ctrl)
+        for g in storage.groups:
+            fs = optimizer._rannc_flat_state.get(id(g))
+            if fs is not None:
+                _publish_state(g, fs)
+
+    def step(self, closure=None):
+        mod = optimizer._rannc_module
+        ctrl = mod._amp_prepare_step() if mod is not None else None
+        if ctrl is False:
+            return None  # overflow: skipped, scale already lowered
+        use_fused = optimizer._rannc_kind is not None and all(
+            g.flat_grad.is_cuda and g.flat_grad.dtype == torch.float32 for g in storage.groups)
+        if use_fused:
+            fused_step(ctrl if isinstance(ctrl, torch.Tensor) else None)
+            loss = None
+        else:
+            if isinstance(ctrl, torch.Tensor):
+                mul = float(ctrl[0].item())
+                if mul != 1.0:
+                    for g in storage.groups:
+                        g.flat_grad.mul_(mul)
+            loss = orig_step(closure) if closure is not None else orig_step()
+            if amp:
+                for g in storage.groups:
+                    if g.flat_master is not None:
+                        lo, hi = g.shard
+                        g.flat_param[lo:hi].copy_(g.flat_master)
+        if storage.zero:
+            storage.allgather_params_zero()
+        return loss
+
+    def zero_grad(self, set_to_none: bool = False):
+        storage.zero_grad()
+
+    def state_dict(self, from_global: bool = False, **kwargs):
+        if not from_global:
+            return orig_state_dict()
+        return gather_optimizer_state_dict(optimizer, **kwargs)
+
+    def load_state_dict(self, state_dict, from_global: bool = False, **kwargs):
+        if not from_global:
+            return orig_load_state_dict(state_dict)
+        return load_global_optimizer_state(optimizer, state_dict)
+
+    optimizer.step = types.MethodType(step, optimizer)
+    optimizer.zero_grad = types.MethodType(zero_grad, optimizer)
+    optimizer.state_dict = types.MethodType(state_dict, optimizer)
+    optimizer.load_state_dict = types.MethodType(load_state_dict, optimizer)
+    return optimizer
+
+
+def gather_optimizer_state_dict(optimizer, root: int = 0, to_cpu: bool = True) -> Optional[dict]:
+    """Collective over the world.  Returns the global state dict on ``root``, None elsewhere."""
+    mod = optimizer._rannc_module
+    storage = mod._storage
+    me = comm.get_rank()
+    state = {}
+    for name, order in sorted(mod._param_order_by_name.items(), key=lambda kv: kv[1]):
+        ranks = storage.param_ranks.get(name)
+        if ranks is None:
+            continue
+        owner = ranks[0]
+        # item names and non-tensor items from the lowest owner rank
+        items = None
+        tensors = {}
+        if name in storage.by_name:
+            g, i = storage.by_name[name]
+            target = g.master_params[i] if (g.flat_master is not None and g.master_params) else g.params[i]
+            st = optimizer.state.get(target, {}) if target is not None else {}
+            if me == owner:
+                items = {k: (("tensor", None) if (torch.is_tensor(v) and v.dim() > 0) else ("value", _plain(v)))
+                         for k, v in st.items()}
+        items = comm.bcast_obj(items, owner)
+        if not items:
+            continue
+        entry = {}
+        p_shape, _ = mod._param_meta[name]
+        for k, (kind, val) in items.items():
+            if kind == "value":
+                entry[k] = val
+                continue
+            # tensor item: assemble from the owner set (shards under ZeRO), then hand to root
+            full = _gather_state_tensor(storage, optimizer, name, k, p_shape)
+            if me == root:
+                entry[k] = full.cpu() if to_cpu else full
+        if me == root:
+            state[order] = entry
+    if me != root:
+        return None
+    groups = []
+    idx = 0
+    for g in optimizer._rannc_orig_param_groups:
+        ng = {k: v for k, v in g.items() if k != "params"}
+        ng["params"] = list(range(idx, idx + len(g["params"])))
+        idx += len(g["params"])
+        groups.append(ng)
+    return {"state": state, "param_groups": groups}
+
+
+def _plain(v):
+    if torch.is_tensor(v):
+        return v.item()
+    return v
+
+
+def _gather_state_tensor(storage, optimizer, name: str, key: str, shape) -> torch.Tensor:
+    """Collective over the world: full fp32 tensor of optimizer-state item ``key`` of parameter ``name``."""
+    ranks = storage.param_ranks[name]
+    numel = 1
+    for d in shape:
+        numel *= d
+    dev = comm.device()
+    full = torch.zeros(numel, dtype=torch.float32, device=dev)
+    if name in storage.by_name:
+        g, i = storage.by_name[name]
+        target = g.master_params[i] if (g.flat_master is not None and g.master_params) else g.params[i]
+        if target is not None and target in optimizer.state and key in optimizer.state[target]:
+            a, b = g.local_range(i)
+            lo, _ = g.param_range(i)
+            if storage.zero or comm.get_rank() == ranks[0]:
+                full[a - lo:b - lo] = optimizer.state[target][key].reshape(-1).to(dev, torch.float32)
+    if comm.get_world_size() > 1:
+        comm.allreduce(full, "sum")
+        if not storage.zero:
+            pass  # only the lowest owner contributed
+    return full.view(shape)
+
+
+def load_global_optimizer_state(optimizer, sd: dict) -> None:
+    """Takes a dict made by ``state_dict(from_global=True)`` (present on every rank) and keeps the
+    slices this rank owns."""
+    mod = optimizer._rannc_module
+    storage = mod._storage
+    for hp_new, hp in zip(sd["param_groups"], optimizer.param_groups):
+        for k, v in hp_new.items():
+            if k != "params":
+                hp[k] = v
+    order_to_name = {o: n for n, o in mod._param_order_by_name.items()}
+    steps = {}
+    for order, entry in sd["state"].items():
+        name = order_to_name.get(int(order))
+        if name is None or name not in storage.by_name:
+            continue
+        g, i = storage.by_name[name]
+        target = g.master_params[i] if (g.flat_master is not None and g.master_params) else g.params[i]
+        if target is None:
+            continue
+        a, b = g.local_range(i)
+        lo, _ = g.param_range(i)
+        st = optimizer.state[target]
+        for k, v in entry.items():
+            if torch.is_tensor(v) and v.dim() > 0:
+                piece = v.reshape(-1)[a - lo:b - lo].to(target.device, torch.float32).view(target.shape)
+                st[k] = piece.clone()
+            else:
+                st[k] = torch.tensor(float(v)) if k == "step" else v
+                if k == "step":
+                    steps[id(g)] = int(float(v))
+    # the fused step keeps flat moments: refill them from the per-parameter entries
+    if optimizer._rannc_kind is not None:
+        for g in storage.groups:
+            n = g.shard[1] - g.shard[0]
+            fs = _FlatState(n, g.device, optimizer._rannc_kind)
+            fs.step = steps.get(id(g), 0)
+            lo = g.shard[0]
+            for i, p in enumerate(g.params):
+                target = g.master_params[i] if (g.flat_master is not None and g.master_params) else p
+                if target is None or target not in optimizer.state:
+                    continue
+                a, b = g.local_range(i)
+                st = optimizer.state[target]
+                if optimizer._rannc_kind == "adam" and "exp_avg" in st:
+                    fs.m[a - lo:b - lo] = st["exp_avg"].reshape(-1)
+                    fs.v[a - lo:b - lo] = st["exp_avg_sq"].reshape(-1)
+                elif "momentum_buffer" in st and st["momentum_buffer"] is not None:
+                    fs.m[a - lo:b - lo] = st["momentum_buffer"].reshape(-1)
+            optimizer._rannc_flat_state[id(g)] = fs

@@ -1,0 +1,291 @@
+"""Process bootstrap and host-issued communication.
+
+One process per GPU, started by ``torchrun`` (or anything that sets RANK /
+WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT).  ``torch.distributed``
+takes the place of the reference's MPI + hand-rolled NCCL wrapper:
+
+* control plane (ids, deployment, pickled objects): object collectives over the
+  default group (reference: src/comm/ObjectComm.cpp, MPI + msgpack);
+* one communicator per distinct rank set, created in a deterministic order --
+  smaller sets first (reference: src/comm/NCCLWrapper.cpp:90-131,
+  src/comp/ParamStorage.cpp:336-345);
+* ``redist``: contiguous-row all-to-all-v between two rank sets with grouped
+  send/recv (reference: NCCLWrapper.cpp:445-564), used by pipeline routes;
+* all-reduce / broadcast / all-gather / reduce-scatter for the baseline gradient
+  path, checkpoint gathering and ``tensor_coll``.
+
+A world of one process needs no process group at all; every call degenerates to
+a local operation.  Without CUDA the backend is gloo (CPU rank harness).
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _core
+from ..utils.config import conf
+from ..utils.log import get_logger
+
+logger = get_logger("Comm")
+
+
+class CommError(RuntimeError):
+    """A collective failed or a peer disappeared (reference: CommErrorException)."""
+
+
+class _State:
+    def __init__(self):
+        self.initialized = False
+        self.rank = 0
+        self.world = 1
+        self.local_rank = 0
+        self.device = torch.device("cpu")
+        self.backend = None
+        self.groups: Dict[Tuple[int, ...], object] = {}
+        self.owns_pg = False
+        self.cpu_group = None
+
+
+_S = _State()
+
+
+def start(device: Optional[torch.device] = None) -> None:
+    """Counterpart of RaNNCProcess::start (src/bind/RaNNCProcess.cpp:20-104)."""
+    if _S.initialized:
+        return
+    _S.rank = int(os.environ.get("RANK", "0"))
+    _S.world = int(os.environ.get("WORLD_SIZE", "1"))
+    _S.local_rank = int(os.environ.get("LOCAL_RANK", str(_S.rank)))
+    use_cuda = torch.cuda.is_available() and os.environ.get("RANNC_FORCE_CPU", "0") != "1"
+    if device is not None:
+        _S.device = device
+    elif use_cuda:
+        _S.device = torch.device("cuda", _S.local_rank % torch.cuda.device_count())
+        torch.cuda.set_device(_S.device)
+    else:
+        _S.device = torch.device("cpu")
+    if _S.world > 1:
+        if not dist.is_initialized():
+            backend = "nccl" if _S.device.type == "cuda" else "gloo"
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29500")
+            timeout = datetime.timedelta(seconds=float(conf("comm_timeout_s")))
+            kwargs = {}
+            if backend == "nccl":
+                kwargs["device_id"] = _S.device
+            dist.init_process_group(backend, rank=_S.rank, world_size=_S.world, timeout=timeout, **kwargs)
+            _S.owns_pg = True
+        _S.backend = dist.get_backend()
+    _core.set_log_rank(_S.rank)
+    _S.initialized = True
+    logger.debug("rank %d of %d on %s", _S.rank, _S.world, str(_S.device))
+
+
+def clear() -> None:
+    """Destroys communicators (reference: RaNNCProcess::clear)."""
+    _S.groups.clear()
+    if _S.owns_pg and dist.is_initialized():
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+    _S.owns_pg = False
+    _S.initialized = False
+    _S.cpu_group = None
+
+
+def get_rank() -> int:
+    start()
+    return _S.rank
+
+
+def get_world_size() -> int:
+    start()
+    return _S.world
+
+
+def get_local_rank() -> int:
+    start()
+    return _S.local_rank
+
+
+def device() -> torch.device:
+    start()
+    return _S.device
+
+
+def is_cuda() -> bool:
+    return device().type == "cuda"
+
+
+def barrier() -> None:
+    if get_world_size() > 1:
+        if is_cuda():
+            dist.barrier(device_ids=[_S.device.index])
+        else:
+            dist.barrier()
+
+
+# ---------------------------------------------------------------- groups
+def _key(ranks: Sequence[int]) -> Tuple[int, ...]:
+    return tuple(sorted(set(int(r) for r in ranks)))
+
+
+def create_groups(rank_sets: Sequence[Sequence[int]]) -> None:
+    """Collective over the world: creates a communicator for every rank set not seen before,
+    smaller sets first, ties broken by the ranks themselves."""
+    start()
+    if _S.world == 1:
+        return
+    keys = sorted({_key(r) for r in rank_sets}, key=lambda k: (len(k), k))
+    for k in keys:
+        if k in _S.groups or len(k) == 0:
+            continue
+        if len(k) == _S.world:
+            _S.groups[k] = dist.group.WORLD
+        else:
+            _S.groups[k] = dist.new_group(list(k))
+
+
+def group(ranks: Optional[Sequence[int]] = None):
+    start()
+    if _S.world == 1:
+        return None
+    if ranks is None:
+        return dist.group.WORLD
+    k = _key(ranks)
+    if len(k) == _S.world:
+        return dist.group.WORLD
+    if k not in _S.groups:
+        raise CommError(f"no communicator for ranks {k}; create_groups() must run on every rank first")
+    return _S.groups[k]
+
+
+def recreate_all_communicators() -> None:
+    """Abort + re-create every communicator in creation order (reference: NCCLWrapper.cpp:667-703)."""
+    if _S.world == 1:
+        return
+    keys = list(_S.groups.keys())
+    for k in keys:
+        g = _S.groups[k]
+        if g is not dist.group.WORLD:
+            try:
+                dist.destroy_process_group(g)
+            except Exception:  # noqa: BLE001
+                pass
+    _S.groups.clear()
+    create_groups(keys)
+
+
+# ---------------------------------------------------------------- objects
+def bcast_obj(obj, root: int = 0, ranks: Optional[Sequence[int]] = None):
+    if get_world_size() == 1:
+        return obj
+    box = [obj if get_rank() == root else None]
+    dist.broadcast_object_list(box, src=root, group=group(ranks), device=_S.device if is_cuda() else None)
+    return box[0]
+
+
+def allgather_obj(obj, ranks: Optional[Sequence[int]] = None) -> list:
+    if get_world_size() == 1:
+        return [obj]
+    g = group(ranks)
+    n = dist.get_world_size(g)
+    out = [None] * n
+    dist.all_gather_object(out, obj, group=g)
+    return out
+
+
+def bcast_bytes(data: bytes, root: int = 0) -> bytes:
+    return bcast_obj(data, root)
+
+
+# ---------------------------------------------------------------- tensors
+def allreduce(t: torch.Tensor, op: str = "sum", ranks: Optional[Sequence[int]] = None, async_op: bool = False):
+    if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
+        return None
+    rop = {"sum": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op]
+    return dist.all_reduce(t, op=rop, group=group(ranks), async_op=async_op)
+
+
+def bcast(t: torch.Tensor, root: int, ranks: Optional[Sequence[int]] = None) -> None:
+    if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
+        return
+    dist.broadcast(t, src=root, group=group(ranks))
+
+
+def allgather_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Sequence[int]] = None) -> None:
+    if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
+        out.view(-1)[: inp.numel()].copy_(inp.view(-1))
+        return
+    dist.all_gather_into_tensor(out, inp, group=group(ranks))
+
+
+def reduce_scatter_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Sequence[int]] = None) -> None:
+    if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
+        out.copy_(inp.view(-1)[: out.numel()].view_as(out))
+        return
+    dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=group(ranks))
+
+
+class PendingOps:
+    """Handles of posted sends; buffers stay referenced until ``wait``."""
+
+    def __init__(self):
+        self.reqs = []
+        self.keep = []
+
+    def wait(self):
+        for r in self.reqs:
+            r.wait()
+        self.reqs.clear()
+        self.keep.clear()
+
+
+def redist(src_rows: Optional[torch.Tensor], args, recv_rows: int, like: Optional[torch.Tensor],
+           row_shape: Sequence[int], dtype: torch.dtype, pending: Optional[PendingOps] = None) -> Optional[torch.Tensor]:
+    """Contiguous-row all-to-all-v.  ``args`` is a ``_core.RedistArgs`` for this rank: row counts and
+    displacements per global rank.  Returns the received tensor ([recv_rows, *row_shape]) or None when
+    this rank receives nothing.  Booleans travel as bytes (the reference widens them to int32)."""
+    me = get_rank()
+    out = None
+    if recv_rows > 0:
+        out = torch.empty((recv_rows, *row_shape), dtype=dtype, device=device())
+    ops, is_send = [], []
+    wire = lambda t: t.view(torch.uint8) if t.dtype == torch.bool else t  # noqa: E731
+    world = get_world_size()
+    # lower ranks first on both sides keeps the pairing order identical everywhere
+    for r in range(world):
+        sc = args.sendcounts[r]
+        if sc > 0 and src_rows is not None:
+            piece = src_rows[args.sdispls[r]: args.sdispls[r] + sc]
+            if r == me:
+                out[args.rdispls[r]: args.rdispls[r] + sc].copy_(piece)
+            else:
+                piece = piece.contiguous()
+                ops.append(dist.P2POp(dist.isend, wire(piece), r))
+                is_send.append(True)
+                if pending is not None:
+                    pending.keep.append(piece)
+        rc = args.recvcounts[r]
+        if rc > 0 and r != me:
+            ops.append(dist.P2POp(dist.irecv, wire(out[args.rdispls[r]: args.rdispls[r] + rc]), r))
+            is_send.append(False)
+    if ops:
+        reqs = dist.batch_isend_irecv(ops)
+        if pending is not None and len(reqs) == len(ops):
+            # one request per operation (gloo): receives are needed now, sends may finish later
+            for q, s in zip(reqs, is_send):
+                if s:
+                    pending.reqs.append(q)
+                else:
+                    q.wait()
+        else:
+            # one coalesced request (NCCL): waiting only orders the current stream after it
+            for q in reqs:
+                q.wait()
+    return out

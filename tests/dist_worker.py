@@ -1,0 +1,117 @@
+"""One rank of a CPU (gloo) multi-process test.  Launched by tests/test_dist_cpu.py.
+
+Oracle: the same model trained in the same process with plain eager PyTorch on the
+FULL global batch (every rank can compute it, inputs come from a shared seed)."""
+import copy
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+os.environ.setdefault("RANNC_FORCE_CPU", "1")
+
+import torch  # noqa: E402
+import torch.nn as nn  # noqa: E402
+
+import rannc_b200 as pyrannc  # noqa: E402
+from tests import zoo  # noqa: E402
+
+
+def main():
+    import faulthandler
+    if os.environ.get("RANNC_TEST_DUMP"):
+        faulthandler.dump_traceback_later(int(os.environ["RANNC_TEST_DUMP"]), exit=True)
+    case = json.loads(sys.argv[1])
+    torch.manual_seed(case.get("seed", 0))
+    rank, world = pyrannc.get_rank(), pyrannc.get_world_size()
+    model = zoo.build(case["model"])
+    ref = copy.deepcopy(model)
+    lr = 0.05
+    mk = (lambda ps: torch.optim.SGD(ps, lr=lr, momentum=0.9)) if case.get("opt", "sgd") == "sgd" else \
+        (lambda ps: torch.optim.Adam(ps, lr=0.01))
+    opt, ropt = mk(model.parameters()), mk(ref.parameters())
+    wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=case.get("amp", False),
+                                  enable_zero=case.get("zero", False), check_unused_values=False)
+    B = case.get("batch", 8)
+    lb = B // world
+    g = torch.Generator().manual_seed(123)
+    accum = case.get("accum", 1)
+    tol = case.get("tol", 1e-4)
+    ok = True
+    msgs = []
+    for it in range(case.get("iters", 3)):
+        pyrannc.delay_grad_allreduce(accum > 1)
+        for a in range(accum):
+            inputs = zoo.inputs(case["model"], B, g)
+            local = tuple(t[rank * lb:(rank + 1) * lb] for t in inputs)
+            out = wrapped(*local)
+            rout = ref(*inputs)
+            if out.dim() == 0:
+                if abs(float(out) - float(rout)) > tol * max(1.0, abs(float(rout))):
+                    ok = False
+                    msgs.append(f"it {it}: loss {float(out)} vs {float(rout)}")
+                out.backward()
+                (rout / 1.0).backward()
+            else:
+                if not torch.allclose(out, rout[rank * lb:(rank + 1) * lb], rtol=tol, atol=tol):
+                    ok = False
+                    msgs.append(f"it {it}: output mismatch {(out - rout[rank * lb:(rank + 1) * lb]).abs().max()}")
+                go = torch.randn(rout.shape, generator=g)
+                out.backward(go[rank * lb:(rank + 1) * lb])
+                # DDP semantics: gradients are averaged over the ranks
+                rout.backward(go / world)
+        if accum > 1:
+            wrapped.allreduce_grads_zero() if case.get("zero") else wrapped.allreduce_grads()
+            for p in ref.parameters():
+                if p.grad is not None:
+                    p.grad /= 1.0
+        for n, p in ref.named_parameters():
+            if p.grad is None:
+                continue
+            gr = wrapped.get_param_grad(n)
+            scale = 1.0 / accum if False else 1.0
+            if not torch.allclose(gr.float(), p.grad.float() * scale, rtol=tol * 10, atol=tol * 10):
+                ok = False
+                msgs.append(f"it {it}: grad {n} differs by {(gr.float() - p.grad.float()).abs().max().item()}")
+        opt.step()
+        ropt.step()
+        opt.zero_grad()
+        ropt.zero_grad()
+        for n, p in ref.named_parameters():
+            v = wrapped.get_param(n)
+            if not torch.allclose(v.float(), p.detach().float(), rtol=tol * 10, atol=tol * 10):
+                ok = False
+                msgs.append(f"it {it}: param {n} differs by {(v.float() - p.detach().float()).abs().max().item()}")
+    # checkpoint round trip
+    sd = wrapped.state_dict()
+    osd = opt.state_dict(from_global=True)
+    if rank == 0:
+        for n, p in ref.named_parameters():
+            if not torch.allclose(sd[n].float(), p.detach().float(), rtol=tol * 10, atol=tol * 10):
+                ok = False
+                msgs.append(f"state_dict {n} differs")
+        rsd = ropt.state_dict()
+        for k, st in rsd["state"].items():
+            for item, v in st.items():
+                if torch.is_tensor(v) and v.dim() > 0:
+                    if k not in osd["state"] or item not in osd["state"][k]:
+                        ok = False
+                        msgs.append(f"optimizer state {k}/{item} missing")
+                    elif not torch.allclose(osd["state"][k][item].float(), v.float(), rtol=tol * 10, atol=tol * 10):
+                        ok = False
+                        msgs.append(f"optimizer state {k}/{item} differs")
+    osd = pyrannc.comm_utils.bcast_obj(osd, 0)
+    opt.load_state_dict(osd, from_global=True)
+    stages = len(wrapped._dep.fwd_graph_order)
+    res = {"ok": ok, "msgs": msgs[:8], "stages": stages, "pipeline": wrapped._dep.pipeline_num,
+           "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}}
+    all_res = pyrannc._comm.allgather_obj(res)
+    if rank == 0:
+        print("RESULT " + json.dumps({"ok": all(r["ok"] for r in all_res), "ranks": all_res}))
+    pyrannc.barrier()
+    pyrannc.clear()
+    sys.exit(0 if all(r["ok"] for r in all_res) else 1)
+
+
+if __name__ == "__main__":
+    main()

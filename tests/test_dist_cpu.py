@@ -1,0 +1,83 @@
+"""Full trace -> partition -> deploy -> train path on CPU ranks (gloo), checked against eager PyTorch on the
+global batch: losses / outputs, gradients, parameters after the step, and the checkpoint round trip."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def run_case(world, case, env_extra=None, timeout=240):
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ)
+        env.update({"RANK": str(r), "WORLD_SIZE": str(world), "LOCAL_RANK": str(r), "MASTER_ADDR": "127.0.0.1",
+                    "MASTER_PORT": str(port), "RANNC_FORCE_CPU": "1", "OMP_NUM_THREADS": "1",
+                    "RANNC_LOG_LEVEL": "warning"})
+        env.update(env_extra or {})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "dist_worker.py"),
+                                       json.dumps(case)], env=env, cwd=ROOT, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append(o)
+    res = None
+    for line in outs[0].splitlines():
+        if line.startswith("RESULT "):
+            res = json.loads(line[7:])
+    assert res is not None, "no result from rank 0:\n" + "\n----\n".join(o[-3000:] for o in outs)
+    assert res["ok"], json.dumps(res, indent=1)[:4000]
+    return res
+
+
+@pytest.mark.parametrize("model", ["basic", "forkjoin", "shared_input", "loss", "emb", "tied", "layernorm"])
+def test_dp2(model):
+    run_case(2, {"model": model, "batch": 8})
+
+
+@pytest.mark.parametrize("model", ["deep", "loss", "forkjoin", "shared_input", "tied"])
+def test_pp2(model):
+    res = run_case(2, {"model": model, "batch": 8}, {"RANNC_PARTITION_NUM": "2"})
+    assert res["ranks"][0]["stages"] == 2
+
+
+def test_pp2_dp2_pipeline2():
+    res = run_case(4, {"model": "deep", "batch": 16}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2"})
+    assert res["ranks"][0]["stages"] == 2 and res["ranks"][0]["pipeline"] == 2
+
+
+def test_pp_checkpointing():
+    run_case(2, {"model": "loss", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2",
+                                                "RANNC_CHECKPOINTING": "true"})
+
+
+def test_grad_accumulation():
+    run_case(2, {"model": "loss", "batch": 8, "accum": 2})
+
+
+def test_adam_dp2():
+    run_case(2, {"model": "layernorm", "batch": 8, "opt": "adam"})
+
+
+def test_uneven_stage_replicas():
+    # 3 ranks cannot be split evenly: stage counts / replica counts come from the search
+    run_case(3, {"model": "deep", "batch": 12}, {"RANNC_LIMIT_DEV_NUM_POT": "false"})

@@ -1,0 +1,133 @@
+"""Small models that each exercise one graph shape the partitioner must cope with: conv + fc, fork/join,
+shared (fan-out) activations, tied weights, scalar-loss output, integer inputs, mixed LayerNorm, BatchNorm
+buffers.  Same coverage as the reference's test zoo (test/models.py), written independently."""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class Basic(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.c1 = nn.Conv2d(1, 4, 3, padding=1)
+        self.c2 = nn.Conv2d(4, 8, 3, padding=1)
+        self.f1 = nn.Linear(8 * 4 * 4, 32)
+        self.f2 = nn.Linear(32, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.c1(x)), 2)
+        x = F.max_pool2d(F.relu(self.c2(x)), 2)
+        return self.f2(F.relu(self.f1(x.flatten(1))))
+
+
+class ForkJoin(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = nn.Linear(16, 16)
+        self.b1 = nn.Linear(16, 16)
+        self.b2 = nn.Linear(16, 16)
+        self.c = nn.Linear(16, 8)
+
+    def forward(self, x):
+        h = torch.relu(self.a(x))
+        return self.c(torch.relu(self.b1(h)) + torch.tanh(self.b2(h)))
+
+
+class SharedInput(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(16, 16)
+        self.l2 = nn.Linear(16, 16)
+        self.l3 = nn.Linear(16, 16)
+
+    def forward(self, x):
+        h = self.l1(x)
+        return self.l3(torch.relu(self.l2(h)) + h) + x
+
+
+class SharedParam(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(16, 16)
+        self.mid = nn.Linear(16, 16)
+
+    def forward(self, x):
+        return self.l1(torch.relu(self.mid(torch.relu(self.l1(x)))))
+
+
+class LossOut(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(16, 32)
+        self.l2 = nn.Linear(32, 32)
+        self.l3 = nn.Linear(32, 5)
+
+    def forward(self, x, y):
+        h = torch.relu(self.l2(torch.relu(self.l1(x))))
+        return F.cross_entropy(self.l3(h), y)
+
+
+class Emb(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.emb = nn.Embedding(50, 16)
+        self.l1 = nn.Linear(16, 16)
+        self.l2 = nn.Linear(16, 50)
+
+    def forward(self, ids):
+        return self.l2(torch.relu(self.l1(self.emb(ids)))).mean(1)
+
+
+class TiedEmb(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.emb = nn.Embedding(50, 16)
+        self.l1 = nn.Linear(16, 16)
+        self.ln = nn.LayerNorm(16)
+
+    def forward(self, ids, y):
+        h = self.ln(torch.relu(self.l1(self.emb(ids))))
+        logits = F.linear(h, self.emb.weight)
+        return F.cross_entropy(logits.reshape(-1, 50), y.reshape(-1))
+
+
+class LayerNormNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(16, 32)
+        self.ln = nn.LayerNorm(32)
+        self.l2 = nn.Linear(32, 16)
+
+    def forward(self, x):
+        return self.l2(self.ln(F.gelu(self.l1(x))))
+
+
+class Deep(nn.Module):
+    def __init__(self, n=8):
+        super().__init__()
+        self.layers = nn.ModuleList([nn.Linear(16, 16) for _ in range(n)])
+
+    def forward(self, x):
+        for l in self.layers:
+            x = torch.tanh(l(x))
+        return x
+
+
+_MODELS = {"basic": Basic, "forkjoin": ForkJoin, "shared_input": SharedInput, "shared_param": SharedParam,
+           "loss": LossOut, "emb": Emb, "tied": TiedEmb, "layernorm": LayerNormNet, "deep": Deep}
+
+
+def build(name):
+    return _MODELS[name]()
+
+
+def inputs(name, B, g):
+    if name == "basic":
+        return (torch.randn(B, 1, 16, 16, generator=g),)
+    if name == "loss":
+        return torch.randn(B, 16, generator=g), torch.randint(0, 5, (B,), generator=g)
+    if name == "emb":
+        return (torch.randint(0, 50, (B, 6), generator=g),)
+    if name == "tied":
+        return torch.randint(0, 50, (B, 6), generator=g), torch.randint(0, 50, (B, 6), generator=g)
+    return (torch.randn(B, 16, generator=g),)
