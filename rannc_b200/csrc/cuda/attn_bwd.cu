@@ -15,42 +15,25 @@
 // Takes the place of the autograd graph the reference runs for the traced
 // attention chain (src/torch/TorchDriver.cpp:642-847).
 #include "attn.h"
+#include "attn_common.cuh"
 #include "tc_common.cuh"
 
 namespace rb {
 
 constexpr int BQ = 128, BKEYS = 128, BD = 64;
-constexpr int TILE = 128 * 64 * 2;     // 16 KiB
+constexpr int TILE = 128 * 64 * 2;       // 16 KiB
 constexpr int SQ_BYTES = 128 * 128 * 2;  // 32 KiB
-constexpr int BWD_THREADS = 160;
+constexpr int BWD_MATH = 256;
+constexpr int BWD_THREADS = BWD_MATH + 32;
 constexpr int BWD_TMEM_COLS = 512;
 constexpr int C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
-constexpr int BWD_SMEM = 2 * TILE /*K,V*/ + 4 * TILE /*Q,dO x2*/ + 2 * SQ_BYTES /*Pt,dSt*/ +
-                         4 * 128 * 4 /*lse,delta x2*/ + 1024 + 256;
+// K, V + (Q, dO) x 2 stages + Pt, dSt + per-step (lse, delta, row hash) x 2 + barriers
+constexpr int BWD_SMEM = 2 * TILE + 4 * TILE + 2 * SQ_BYTES + 6 * 128 * 4 + 128;
 
-__device__ __forceinline__ void tma_load_4d_b(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
-                                              int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        :
-        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
-          "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-        : "memory");
-}
-__device__ __forceinline__ uint32_t mix32b(uint64_t seed, uint64_t idx) {
-    uint64_t z = idx * 0x9E3779B97F4A7C15ull + seed;
-    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-    return static_cast<uint32_t>(z ^ (z >> 31));
-}
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
                  "f"(d)
                  : "memory");
-}
-__device__ __forceinline__ void bar_sync_math() {
-    asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
 struct AttnBwdParams {
@@ -65,7 +48,7 @@ struct AttnBwdParams {
     long long dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
     uint32_t thr16;
     float inv_keep;
-    uint64_t seed;
+    uint32_t seed;
     int* err;
 };
 
@@ -74,18 +57,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const AttnBwdParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~static_cast<uintptr_t>(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = smem + TILE;
-    uint8_t* sQ = smem + 2 * TILE;    // [2]
-    uint8_t* sdO = smem + 4 * TILE;   // [2]
+    uint8_t* sQ = smem + 2 * TILE;   // [2]
+    uint8_t* sdO = smem + 4 * TILE;  // [2]
     uint8_t* sPt = smem + 6 * TILE;
     uint8_t* sdSt = sPt + SQ_BYTES;
-    float* s_lse = reinterpret_cast<float*>(sdSt + SQ_BYTES);  // [2][128]
-    float* s_delta = s_lse + 256;                              // [2][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 256);
+    float* s_lse = reinterpret_cast<float*>(sdSt + SQ_BYTES);       // [2][128]
+    float* s_delta = s_lse + 256;                                   // [2][128]
+    uint32_t* s_rhash = reinterpret_cast<uint32_t*>(s_delta + 256);  // [2][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_rhash + 256);
     uint64_t* kv_full = bars;
     uint64_t* qd_full = bars + 1;  // [2]
     uint64_t* s_full = bars + 3;
@@ -104,13 +86,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         mbar_init(&qd_full[0], 1);
         mbar_init(&qd_full[1], 1);
         mbar_init(s_full, 1);
-        mbar_init(s_free, 128);
-        mbar_init(pds_ready, 128);
+        mbar_init(s_free, BWD_MATH);
+        mbar_init(pds_ready, BWD_MATH);
         mbar_init(mma_done, 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 4) {
+    if (warp == 8) {
         tmem_alloc(tmem_slot, BWD_TMEM_COLS);
         tmem_relinquish();
     }
@@ -120,16 +102,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const uint32_t tmem = *tmem_slot;
     constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
             const uint32_t id_s = make_idesc_f16(fmt, 0, 0, 128, 128);
-            const uint32_t id_kn = make_idesc_f16(fmt, 0, 1, 128, 64);   // A K-major, B MN-major
-            const uint32_t id_nn = make_idesc_f16(fmt, 1, 1, 128, 64);   // A MN-major, B MN-major
+            const uint32_t id_kn = make_idesc_f16(fmt, 0, 1, 128, 64);  // A K-major, B MN-major
+            const uint32_t id_nn = make_idesc_f16(fmt, 1, 1, 128, 64);  // A MN-major, B MN-major
             auto load_qd = [&](int i) {
                 const int st = i & 1;
                 mbar_arrive_expect_tx(&qd_full[st], 2 * TILE);
-                tma_load_4d_b(sQ + st * TILE, &tmQ, &qd_full[st], 0, i * BQ, h, b);
-                tma_load_4d_b(sdO + st * TILE, &tmdO, &qd_full[st], 0, i * BQ, h, b);
+                tma_load_4d(sQ + st * TILE, &tmQ, &qd_full[st], 0, i * BQ, h, b);
+                tma_load_4d(sdO + st * TILE, &tmdO, &qd_full[st], 0, i * BQ, h, b);
             };
             auto issue_s = [&](int i) {
                 const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
@@ -145,8 +127,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 umma_commit(s_full);
             };
             mbar_arrive_expect_tx(kv_full, 2 * TILE);
-            tma_load_4d_b(sK, &tmK, kv_full, 0, key0, h, b);
-            tma_load_4d_b(sV, &tmV, kv_full, 0, key0, h, b);
+            tma_load_4d(sK, &tmK, kv_full, 0, key0, h, b);
+            tma_load_4d(sV, &tmV, kv_full, 0, key0, h, b);
             load_qd(0);
             if (nq > 1) load_qd(1);
             bool ok = mbar_wait(kv_full, 0, abort_flag) && mbar_wait(&qd_full[0], 0, abort_flag);
@@ -190,8 +172,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             }
         }
     } else {
-        const int r = threadIdx.x;  // TMEM lane: key row for St/dPt/dV/dK, query row for dQ
-        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+        // thread pair (r, r + 128): TMEM lane r = key row for St/dPt/dV/dK and query row for dQ;
+        // `half` selects 64 of the 128 query columns of St/dPt and 32 of the 64 columns of dQ/dK/dV
+        const int r = threadIdx.x & 127;
+        const int half = threadIdx.x >> 7;
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int key = key0 + r;
         const bool key_ok = key < p.S;
         const float kbias = (p.key_bias && key_ok)
@@ -199,45 +184,85 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                                 : 0.f;
         const long long bh = static_cast<long long>(b) * p.H + h;
         const uint32_t sw = r & 7;
-        uint8_t* prow = sPt + (r >> 3) * 1024 + sw * 128;
-        uint8_t* drow = sdSt + (r >> 3) * 1024 + sw * 128;
-        const uint64_t half_s = static_cast<uint64_t>((p.S + 1) / 2);
+        const uint32_t row_off = half * (SQ_BYTES / 2) + (r >> 3) * 1024 + sw * 128;
+        uint8_t* prow = sPt + row_off;
+        uint8_t* drow = sdSt + row_off;
+        const uint32_t key_mix = static_cast<uint32_t>(key >> 1) * 0x9E3779B1u;
+        const bool key_odd = key & 1;
         bool ok = true;
 
         auto drain_dq = [&](int i) {
-            // dQ block i: lane r = query row q0 + r
+            // dQ block i: lane r = query row i*128 + r; this thread adds 32 of its 64 columns
             const int q = i * BQ + r;
-            float* dst = p.dq_accum + ((static_cast<long long>(b) * p.S + q) * p.H + h) * BD;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_addr + C_DQ + c * 32, v);
-                tmem_ld_wait();
-                if (q < p.S) {
+            float* dst = p.dq_accum + ((static_cast<long long>(b) * p.S + q) * p.H + h) * BD + half * 32;
+            uint32_t v[32];
+            tmem_ld32(tmem + lane_addr + C_DQ + half * 32, v);
+            tmem_ld_wait();
+            if (q < p.S) {
 #pragma unroll
-                    for (int g = 0; g < 8; ++g)
-                        red_add_v4(dst + c * 32 + g * 4, __uint_as_float(v[g * 4]) * p.scale,
-                                   __uint_as_float(v[g * 4 + 1]) * p.scale,
-                                   __uint_as_float(v[g * 4 + 2]) * p.scale,
-                                   __uint_as_float(v[g * 4 + 3]) * p.scale);
-                }
+                for (int g = 0; g < 8; ++g)
+                    red_add_v4(dst + g * 4, __uint_as_float(v[g * 4]) * p.scale,
+                               __uint_as_float(v[g * 4 + 1]) * p.scale, __uint_as_float(v[g * 4 + 2]) * p.scale,
+                               __uint_as_float(v[g * 4 + 3]) * p.scale);
             }
         };
 
         for (int i = 0; i < nq; ++i) {
             const int st = i & 1;
             const int q0 = i * BQ;
-            {
+            if (half == 0) {
                 const int q = q0 + r;
                 s_lse[st * 128 + r] = q < p.S ? p.lse[bh * p.S + q] * 1.4426950408889634f : 0.f;
                 s_delta[st * 128 + r] = q < p.S ? p.delta[bh * p.S + q] : 0.f;
+                s_rhash[st * 128 + r] = drop_row_hash(p.seed, b, h, q, p.H, p.S);
             }
-            bar_sync_math();
+            bar_sync_named(1, BWD_MATH);
             if (!mbar_wait(s_full, i & 1, abort_flag)) {
                 ok = false;
                 break;
             }
+            tc_fence_after();
+            // Pt / dSt of this thread's 64 columns, packed to 16 bits, held in registers: the whole
+            // computation overlaps the tensor-core work of the previous step, whose operands still
+            // occupy the shared-memory tiles
+            uint4 pk[2][4], dk4[2][4];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tmem + lane_addr + C_ST + half * 64 + c * 32, sv);
+                tmem_ld32(tmem + lane_addr + C_DPT + half * 64 + c * 32, dv);
+                tmem_ld_wait();
+                if (c == 1) {
+                    // both TMEM tiles are in registers: the next step's MMAs may overwrite them
+                    tc_fence_before();
+                    mbar_arrive(s_free);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    T* ea = reinterpret_cast<T*>(&pk[c][g]);
+                    T* ed = reinterpret_cast<T*>(&dk4[c][g]);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                        const int ql = half * 64 + c * 32 + g * 8 + x;
+                        float pr = 0.f;
+                        if (key_ok && q0 + ql < p.S)
+                            pr = exp2f(__uint_as_float(sv[g * 8 + x]) * p.scale_log2 + kbias - s_lse[st * 128 + ql]);
+                        float dp = __uint_as_float(dv[g * 8 + x]);
+                        float pd = pr;
+                        if (p.thr16) {
+                            const uint32_t bits = hash32(s_rhash[st * 128 + ql] + key_mix);
+                            const uint32_t hb = key_odd ? (bits >> 16) : (bits & 0xffffu);
+                            const float keep = hb >= p.thr16 ? p.inv_keep : 0.f;
+                            pd = pr * keep;
+                            dp *= keep;
+                        }
+                        ea[x] = from_f32<T>(pd);
+                        ed[x] = from_f32<T>(pr * (dp - s_delta[st * 128 + ql]));
+                    }
+                }
+            }
             if (i > 0) {
+                // the previous step's dV / dK / dQ products read Pt / dSt: wait, collect dQ, then overwrite
                 if (!mbar_wait(mma_done, (i - 1) & 1, abort_flag)) {
                     ok = false;
                     break;
@@ -245,80 +270,42 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_fence_after();
                 drain_dq(i - 1);
             }
-            tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tmem + lane_addr + C_ST + c * 32, sv);
-                tmem_ld32(tmem + lane_addr + C_DPT + c * 32, dv);
-                tmem_ld_wait();
-                float pt[32], ds[32];
 #pragma unroll
-                for (int x = 0; x < 32; ++x) {
-                    const int ql = c * 32 + x;
-                    const int q = q0 + ql;
-                    float pr = 0.f;
-                    if (key_ok && q < p.S)
-                        pr = exp2f(__uint_as_float(sv[x]) * p.scale_log2 + kbias - s_lse[st * 128 + ql]);
-                    float dp = __uint_as_float(dv[x]);
-                    float pd = pr;
-                    if (p.thr16) {
-                        const uint64_t row = (static_cast<uint64_t>(bh) * p.S + q) * half_s;
-                        const uint32_t bits = mix32b(p.seed, row + (key >> 1));
-                        const uint32_t hbits = (key & 1) ? (bits >> 16) : (bits & 0xffffu);
-                        const float keep = hbits >= p.thr16 ? p.inv_keep : 0.f;
-                        pd = pr * keep;
-                        dp *= keep;
-                    }
-                    pt[x] = pd;
-                    ds[x] = pr * (dp - s_delta[st * 128 + ql]);
-                }
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    uint4 a, d;
-                    T* ea = reinterpret_cast<T*>(&a);
-                    T* ed = reinterpret_cast<T*>(&d);
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) {
-                        ea[x] = from_f32<T>(pt[g * 8 + x]);
-                        ed[x] = from_f32<T>(ds[g * 8 + x]);
-                    }
-                    const int kk = c * 32 + g * 8;
-                    const uint32_t off = (kk >> 6) * (SQ_BYTES / 2) + ((((kk & 63) >> 3) ^ sw) << 4);
-                    *reinterpret_cast<uint4*>(prow + off) = a;
-                    *reinterpret_cast<uint4*>(drow + off) = d;
+                    const uint32_t off = (static_cast<uint32_t>(c * 4 + g) ^ sw) << 4;
+                    *reinterpret_cast<uint4*>(prow + off) = pk[c][g];
+                    *reinterpret_cast<uint4*>(drow + off) = dk4[c][g];
                 }
-            }
             tc_fence_before();
-            mbar_arrive(s_free);
             fence_proxy_async();
             mbar_arrive(pds_ready);
         }
         if (ok && mbar_wait(mma_done, (nq - 1) & 1, abort_flag)) {
             tc_fence_after();
             drain_dq(nq - 1);
-            T* dk = reinterpret_cast<T*>(p.dK) + b * p.dk_sb + static_cast<long long>(key) * p.dk_ss + h * p.dk_sh;
-            T* dvp = reinterpret_cast<T*>(p.dV) + b * p.dv_sb + static_cast<long long>(key) * p.dv_ss + h * p.dv_sh;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t a[32], d[32];
-                tmem_ld32(tmem + lane_addr + C_DV + c * 32, a);
-                tmem_ld32(tmem + lane_addr + C_DK + c * 32, d);
-                tmem_ld_wait();
-                if (key_ok) {
+            T* dk = reinterpret_cast<T*>(p.dK) + b * p.dk_sb + static_cast<long long>(key) * p.dk_ss + h * p.dk_sh +
+                    half * 32;
+            T* dvp = reinterpret_cast<T*>(p.dV) + b * p.dv_sb + static_cast<long long>(key) * p.dv_ss + h * p.dv_sh +
+                     half * 32;
+            uint32_t a[32], d[32];
+            tmem_ld32(tmem + lane_addr + C_DV + half * 32, a);
+            tmem_ld32(tmem + lane_addr + C_DK + half * 32, d);
+            tmem_ld_wait();
+            if (key_ok) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 qa, qd;
-                        T* ea = reinterpret_cast<T*>(&qa);
-                        T* ed = reinterpret_cast<T*>(&qd);
+                for (int g = 0; g < 4; ++g) {
+                    uint4 qa, qd;
+                    T* ea = reinterpret_cast<T*>(&qa);
+                    T* ed = reinterpret_cast<T*>(&qd);
 #pragma unroll
-                        for (int x = 0; x < 8; ++x) {
-                            ea[x] = from_f32<T>(__uint_as_float(a[g * 8 + x]));
-                            ed[x] = from_f32<T>(__uint_as_float(d[g * 8 + x]) * p.scale);
-                        }
-                        *reinterpret_cast<uint4*>(dvp + c * 32 + g * 8) = qa;
-                        *reinterpret_cast<uint4*>(dk + c * 32 + g * 8) = qd;
+                    for (int x = 0; x < 8; ++x) {
+                        ea[x] = from_f32<T>(__uint_as_float(a[g * 8 + x]));
+                        ed[x] = from_f32<T>(__uint_as_float(d[g * 8 + x]) * p.scale);
                     }
+                    *reinterpret_cast<uint4*>(dvp + g * 8) = qa;
+                    *reinterpret_cast<uint4*>(dk + g * 8) = qd;
                 }
             }
         }
@@ -335,7 +322,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         __syncthreads();
     }
-    if (warp == 4) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem, BWD_TMEM_COLS);
     }
@@ -409,7 +396,7 @@ static int launch_bwd(const RbAttnArgs& a, cudaStream_t st) {
     p.dv_sb = a.dv_sb; p.dv_ss = a.dv_ss; p.dv_sh = a.dv_sh;
     p.thr16 = a.p_drop > 0.f ? static_cast<uint32_t>(a.p_drop * 65536.f + 0.5f) : 0u;
     p.inv_keep = a.p_drop > 0.f ? 1.f / (1.f - a.p_drop) : 1.f;
-    p.seed = a.seed * 0x2545F4914F6CDD1Dull + a.offset;
+    p.seed = drop_seed(a.seed, a.offset);
     p.err = error_word_ptr();
     if (!p.err) return -3;
     auto kern = attn_bwd_kernel<T>;

@@ -2,52 +2,41 @@
 //
 //   O = dropout(softmax(Q K^T * scale + key_bias)) V        head dim D = 64
 //
-// One CTA handles 128 query rows of one (batch, head).  Keys/values stream
-// through a 2-stage TMA ring in chunks of 128.  S = Q K^T is accumulated in
-// TMEM (128 lanes x 128 columns); each of the 128 softmax threads owns one
-// query row (= one TMEM lane), so row max / sum need no shuffles.  P is written
-// as bf16 into shared memory in the 128-byte-swizzled K-major layout and fed
-// back to the tensor core as the A operand of O += P V, with V consumed as an
-// MN-major B operand straight from its [key, d] layout.  The S^2 score matrix
-// never reaches HBM.  Warps 0..3 = softmax, warp 4 = TMA + MMA issue.
+// One CTA per SM (a CTA that holds tensor memory does not share its SM), so the
+// CTA keeps the tensor core busy by itself: it owns TWO 128-row query tiles of
+// one (batch, head) and interleaves their dependency chains -- while one tile's
+// softmax runs, the other tile's Q K^T or P V is on the tensor core.  Keys and
+// values stream through a 2-stage TMA ring in chunks of 128 and are shared by
+// both tiles.  Per tile: S = Q K^T accumulates in TMEM (128 lanes x 128
+// columns); 256 softmax threads, the pair (t, t + 128) owns query row t
+// (= TMEM lane t) and splits the chunk's columns in halves, so row max / sum
+// need one shared-memory exchange and no shuffles; P goes to shared memory as
+// 16-bit in the 128-byte-swizzled K-major layout and returns to the tensor
+// core as the A operand of O += P V, with V read as an MN-major B operand
+// straight from its [key, d] layout.  The S^2 score matrix never reaches HBM.
+// Warps 0..7 = tile 0, warps 8..15 = tile 1, warp 16 = TMA + MMA issue.
 //
 // Takes the place of the matmul -> div -> add(mask) -> softmax -> dropout ->
 // matmul chain of the traced BERT attention, which the reference runs as
 // separate cuBLAS / ATen kernels (src/torch/TorchDriver.cpp:566).
 #include "attn.h"
-
+#include "attn_common.cuh"
 #include "tc_common.cuh"
 
 namespace rb {
 
-constexpr int AQ = 128;   // query rows per CTA
+constexpr int AQ = 128;   // query rows per tile
 constexpr int AK = 128;   // keys per chunk
 constexpr int AD = 64;    // head dim
-constexpr int TILE_B = AQ * AD * 2;  // 16 KiB: one [128 x 64] 16-bit tile
-constexpr int P_BYTES = AQ * AK * 2; // 32 KiB
-constexpr int ATT_THREADS = 160;
-constexpr int ATT_TMEM_COLS = 256;
-constexpr int COL_S = 0, COL_O = 128;
-constexpr int ATT_SMEM = TILE_B /*Q*/ + 4 * TILE_B /*K,V x2*/ + P_BYTES + 1024 + 256;
-
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
-                                            int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        :
-        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
-          "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-        : "memory");
-}
-
-// 32-bit mix of (seed, offset, index); two 16-bit dropout decisions per call
-__device__ __forceinline__ uint32_t mix32(uint64_t seed, uint64_t idx) {
-    uint64_t z = idx * 0x9E3779B97F4A7C15ull + seed;
-    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-    return static_cast<uint32_t>(z ^ (z >> 31));
-}
+constexpr int TILE_B = AQ * AD * 2;   // 16 KiB: one [128 x 64] 16-bit tile
+constexpr int P_BYTES = AQ * AK * 2;  // 32 KiB
+constexpr int GROUP = 256;            // softmax threads per query tile
+constexpr int ATT_THREADS = 2 * GROUP + 32;
+constexpr int ATT_TMEM_COLS = 512;
+constexpr int TILE_COLS = 192;        // S (128) + O (64) per tile
+constexpr int KB_MAX = 1024;          // key-bias entries staged in shared memory
+// Q (2 tiles) + K, V (2 stages each) + P (2 tiles) + row-stat exchange [tile][parity][half][128] + barriers
+constexpr int ATT_SMEM = 2 * TILE_B + 4 * TILE_B + 2 * P_BYTES + 2 * 2 * 2 * 128 * 4 + 256;
 
 struct AttnFwdParams {
     int B, H, S;
@@ -58,7 +47,7 @@ struct AttnFwdParams {
     float* lse;  // [B, H, S]
     uint32_t thr16;
     float inv_keep;
-    uint64_t seed;
+    uint32_t seed;
     int* err;
 };
 
@@ -66,39 +55,48 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~static_cast<uintptr_t>(1023));
-    uint8_t* sQ = smem;
-    uint8_t* sK = smem + TILE_B;               // [2][TILE_B]
-    uint8_t* sV = smem + 3 * TILE_B;           // [2][TILE_B]
-    uint8_t* sP = smem + 5 * TILE_B;           // [2 col blocks][128 rows x 128 B]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 5 * TILE_B + P_BYTES);
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ float s_kb[KB_MAX];
+    uint8_t* sQ = smem;               // [2 tiles][TILE_B]
+    uint8_t* sK = smem + 2 * TILE_B;  // [2 stages][TILE_B]
+    uint8_t* sV = smem + 4 * TILE_B;  // [2 stages][TILE_B]
+    uint8_t* sP = smem + 6 * TILE_B;  // [2 tiles][2 column blocks][128 rows x 128 B]
+    float* s_xch = reinterpret_cast<float*>(smem + 6 * TILE_B + 2 * P_BYTES);  // [2][2][2][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_xch + 1024);
     uint64_t* q_full = bars;
-    uint64_t* kv_full = bars + 1;  // [2]
-    uint64_t* s_full = bars + 3;
-    uint64_t* s_free = bars + 4;
-    uint64_t* p_ready = bars + 5;
-    uint64_t* o_done = bars + 6;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    uint64_t* k_full = bars + 1;    // [2 stages]
+    uint64_t* v_full = bars + 3;    // [2 stages]
+    uint64_t* s_full = bars + 5;    // [2 tiles]
+    uint64_t* s_free = bars + 7;    // [2 tiles]
+    uint64_t* p_ready = bars + 9;   // [2 tiles]
+    uint64_t* o_done = bars + 11;   // [2 tiles]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * AQ, h = blockIdx.y, b = blockIdx.z;
+    const int q_base = blockIdx.x * 2 * AQ, h = blockIdx.y, b = blockIdx.z;
     const int nchunks = (p.S + AK - 1) / AK;
+    const int ntiles = (q_base + AQ < p.S) ? 2 : 1;
+    const bool kb_smem = p.key_bias && p.S <= KB_MAX;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        mbar_init(&kv_full[0], 1);
-        mbar_init(&kv_full[1], 1);
-        mbar_init(s_full, 1);
-        mbar_init(s_free, 128);
-        mbar_init(p_ready, 128);
-        mbar_init(o_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_free[i], GROUP);
+            mbar_init(&p_ready[i], GROUP);
+            mbar_init(&o_done[i], 1);
+        }
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 4) {
+    if (kb_smem) {
+        const float* kb = p.key_bias + static_cast<long long>(b) * p.S;
+        for (int i = threadIdx.x; i < p.S; i += ATT_THREADS) s_kb[i] = kb[i] * 1.4426950408889634f;
+    }
+    if (warp == 16) {
         tmem_alloc(tmem_slot, ATT_TMEM_COLS);
         tmem_relinquish();
     }
@@ -108,186 +106,194 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const uint32_t tmem = *tmem_slot;
     constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
-    if (warp == 4) {
+    if (warp == 16) {
         if (lane == 0) {
             const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AQ, AK);
             const uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, AQ, AD);
             auto load_kv = [&](int j) {
                 const int st = j & 1;
-                mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_B);
-                tma_load_4d(sK + st * TILE_B, &tmK, &kv_full[st], 0, j * AK, h, b);
-                tma_load_4d(sV + st * TILE_B, &tmV, &kv_full[st], 0, j * AK, h, b);
+                mbar_arrive_expect_tx(&k_full[st], TILE_B);
+                tma_load_4d(sK + st * TILE_B, &tmK, &k_full[st], 0, j * AK, h, b);
+                mbar_arrive_expect_tx(&v_full[st], TILE_B);
+                tma_load_4d(sV + st * TILE_B, &tmV, &v_full[st], 0, j * AK, h, b);
             };
-            auto issue_s = [&](int j) {
-                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + (j & 1) * TILE_B);
+            auto issue_s = [&](int t, int j) {
+                const uint32_t qa = smem_u32(sQ + t * TILE_B), ka = smem_u32(sK + (j & 1) * TILE_B);
 #pragma unroll
                 for (int k = 0; k < AD / 16; ++k)
-                    umma_f16(tmem + COL_S, make_smem_desc_sw128(qa + k * 32, 16, 1024),
+                    umma_f16(tmem + t * TILE_COLS, make_smem_desc_sw128(qa + k * 32, 16, 1024),
                              make_smem_desc_sw128(ka + k * 32, 16, 1024), idesc_s, k != 0);
-                umma_commit(s_full);
+                umma_commit(&s_full[t]);
             };
-            mbar_arrive_expect_tx(q_full, TILE_B);
-            tma_load_4d(sQ, &tmQ, q_full, 0, q0, h, b);
+            mbar_arrive_expect_tx(q_full, ntiles * TILE_B);
+            for (int t = 0; t < ntiles; ++t) tma_load_4d(sQ + t * TILE_B, &tmQ, q_full, 0, q_base + t * AQ, h, b);
             load_kv(0);
             if (nchunks > 1) load_kv(1);
-            bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
+            bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
             if (ok) {
                 tc_fence_after();
-                issue_s(0);
+                for (int t = 0; t < ntiles; ++t) issue_s(t, 0);
             }
             for (int j = 0; j < nchunks && ok; ++j) {
-                if (j + 1 < nchunks) {
-                    ok = mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag) &&
-                         mbar_wait(s_free, j & 1, abort_flag);
+                const uint32_t kv_phase = (j >> 1) & 1, nkv_phase = ((j + 1) >> 1) & 1;
+                for (int t = 0; t < ntiles && ok; ++t) {
+                    if (j + 1 < nchunks) {
+                        ok = mbar_wait(&k_full[(j + 1) & 1], nkv_phase, abort_flag) &&
+                             mbar_wait(&s_free[t], j & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_s(t, j + 1);
+                    }
+                    ok = mbar_wait(&p_ready[t], j & 1, abort_flag) && mbar_wait(&v_full[j & 1], kv_phase, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_s(j + 1);
-                }
-                if (!mbar_wait(p_ready, j & 1, abort_flag)) break;
-                tc_fence_after();
-                const uint32_t pa = smem_u32(sP), va = smem_u32(sV + (j & 1) * TILE_B);
+                    const uint32_t pa = smem_u32(sP + t * P_BYTES), va = smem_u32(sV + (j & 1) * TILE_B);
 #pragma unroll
-                for (int k = 0; k < AK / 16; ++k)
-                    umma_f16(tmem + COL_O,
-                             make_smem_desc_sw128(pa + (k >> 2) * (P_BYTES / 2) + (k & 3) * 32, 16, 1024),
-                             make_smem_desc_sw128(va + k * 2048, 8192, 1024), idesc_o,
-                             (j | k) != 0);
-                umma_commit(o_done);
-                if (j + 2 < nchunks) {
-                    if (!mbar_wait(o_done, j & 1, abort_flag)) break;
-                    load_kv(j + 2);
+                    for (int k = 0; k < AK / 16; ++k)
+                        umma_f16(tmem + t * TILE_COLS + 128,
+                                 make_smem_desc_sw128(pa + (k >> 2) * (P_BYTES / 2) + (k & 3) * 32, 16, 1024),
+                                 make_smem_desc_sw128(va + k * 2048, 8192, 1024), idesc_o, (j | k) != 0);
+                    umma_commit(&o_done[t]);
+                }
+                if (ok && j + 2 < nchunks) {
+                    // stage j & 1 is free once both tiles' products with chunk j are done
+                    for (int t = 0; t < ntiles && ok; ++t) ok = mbar_wait(&o_done[t], j & 1, abort_flag);
+                    if (ok) load_kv(j + 2);
                 }
             }
         }
-    } else {
-        // ------------- softmax threads: one query row each -------------
-        const int r = threadIdx.x;  // row in tile == TMEM lane
-        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-        const int q = q0 + r;
-        const float* kb = p.key_bias ? p.key_bias + static_cast<long long>(b) * p.S : nullptr;
-        const uint64_t drop_row =
-            ((static_cast<uint64_t>(b) * p.H + h) * p.S + static_cast<uint64_t>(q)) *
-            static_cast<uint64_t>((p.S + 1) / 2);
+    } else if ((warp >> 3) < ntiles) {
+        // ------------- softmax: in tile t the thread pair (r, r + 128) owns query row r -------------
+        const int t = warp >> 3;
+        const int idx = threadIdx.x & (GROUP - 1);
+        const int r = idx & 127;     // row in tile == TMEM lane
+        const int half = idx >> 7;   // which 64 columns of a chunk / 32 columns of O
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t col_s = tmem + t * TILE_COLS, col_o = col_s + 128;
+        const int q = q_base + t * AQ + r;
+        const float* kbg = p.key_bias ? p.key_bias + static_cast<long long>(b) * p.S : nullptr;
+        const uint32_t row_hash = drop_row_hash(p.seed, b, h, q, p.H, p.S);
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         const uint32_t sw = r & 7;
-        uint8_t* prow = sP + (r >> 3) * 1024 + sw * 128;
+        uint8_t* prow = sP + t * P_BYTES + half * (P_BYTES / 2) + (r >> 3) * 1024 + sw * 128;
+        float* xbase = s_xch + t * 512;
         for (int j = 0; j < nchunks; ++j) {
-            if (!mbar_wait(s_full, j & 1, abort_flag)) {
+            if (!mbar_wait(&s_full[t], j & 1, abort_flag)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const int key0 = j * AK;
-            // pass 1: row max of the scaled, biased scores
+            const int key0 = j * AK + half * 64;
+            // scaled, biased score of column `key` (log2 units)
+            auto score = [&](uint32_t raw, int key) -> float {
+                float s = __uint_as_float(raw) * p.scale_log2;
+                if (kb_smem) s += s_kb[min(key, p.S - 1)];
+                else if (kbg) s += kbg[min(key, p.S - 1)] * 1.4426950408889634f;
+                return key < p.S ? s : -INFINITY;
+            };
+            // pass 1: maximum over this thread's 64 columns
             float cm = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem + lane_addr + COL_S + c * 32, v);
+                tmem_ld32(col_s + lane_addr + half * 64 + c * 32, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c * 32 + i;
-                    float s = __uint_as_float(v[i]) * p.scale_log2;
-                    if (kb) s += (key < p.S ? kb[key] : 0.f) * 1.4426950408889634f;
-                    if (key >= p.S) s = -INFINITY;
-                    cm = fmaxf(cm, s);
-                }
+                for (int i = 0; i < 32; ++i) cm = fmaxf(cm, score(v[i], key0 + c * 32 + i));
             }
+            float* xch = xbase + (j & 1) * 256;
+            xch[half * 128 + r] = cm;
+            bar_sync_named(1 + t, GROUP);
+            cm = fmaxf(cm, xch[(half ^ 1) * 128 + r]);
             const float m_new = fmaxf(m, cm);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = exp2f(m - m_use);
             // the previous P V product must be complete before P is overwritten and O rescaled
             if (j > 0) {
-                if (!mbar_wait(o_done, (j - 1) & 1, abort_flag)) {
+                if (!mbar_wait(&o_done[t], (j - 1) & 1, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem + lane_addr + COL_O + c * 32, v);
-                        tmem_ld_wait();
+                    uint32_t v[32];
+                    tmem_ld32(col_o + lane_addr + half * 32, v);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(tmem + lane_addr + COL_O + c * 32, v);
-                    }
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st32(col_o + lane_addr + half * 32, v);
                     tmem_st_wait();
                 }
             }
-            // pass 2: probabilities -> shared memory (bf16, swizzled K-major)
+            // pass 2: probabilities -> shared memory (16-bit, swizzled K-major)
             float rs = 0.f;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem + lane_addr + COL_S + c * 32, v);
+                tmem_ld32(col_s + lane_addr + half * 64 + c * 32, v);
                 tmem_ld_wait();
-                float pr[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c * 32 + i;
-                    float s = __uint_as_float(v[i]) * p.scale_log2;
-                    if (kb) s += (key < p.S ? kb[key] : 0.f) * 1.4426950408889634f;
-                    const float e = key < p.S ? exp2f(s - m_use) : 0.f;
-                    rs += e;
-                    pr[i] = e;
+                if (c == 1) {
+                    // last read of S: the next Q K^T may overwrite it
+                    tc_fence_before();
+                    mbar_arrive(&s_free[t]);
                 }
-                if (p.thr16) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int key = key0 + c * 32 + i;
-                        const uint32_t bits = mix32(p.seed, drop_row + (key >> 1));
-                        pr[i] = (bits & 0xffffu) >= p.thr16 ? pr[i] * p.inv_keep : 0.f;
-                        pr[i + 1] = (bits >> 16) >= p.thr16 ? pr[i + 1] * p.inv_keep : 0.f;
+                for (int g = 0; g < 4; ++g) {
+                    float pr[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float e = exp2f(score(v[g * 8 + i], key0 + c * 32 + g * 8 + i) - m_use);
+                        rs += e;
+                        pr[i] = e;
                     }
+                    if (p.thr16) {
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2) {
+                            const uint32_t bits = drop_bits(row_hash, (key0 + c * 32 + g * 8 + i) >> 1);
+                            pr[i] = (bits & 0xffffu) >= p.thr16 ? pr[i] * p.inv_keep : 0.f;
+                            pr[i + 1] = (bits >> 16) >= p.thr16 ? pr[i + 1] * p.inv_keep : 0.f;
+                        }
+                    }
+                    uint4 qv;
+                    T* e = reinterpret_cast<T*>(&qv);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(pr[i]);
+                    *reinterpret_cast<uint4*>(prow + ((static_cast<uint32_t>(c * 4 + g) ^ sw) << 4)) = qv;
                 }
+            }
+            l = l * alpha + rs;
+            m = m_new;
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(&p_ready[t]);
+        }
+        if (ok && mbar_wait(&o_done[t], (nchunks - 1) & 1, abort_flag)) {
+            tc_fence_after();
+            // the pair's partial row sums
+            float* xch = xbase + (nchunks & 1) * 256;
+            xch[half * 128 + r] = l;
+            bar_sync_named(1 + t, GROUP);
+            l += xch[(half ^ 1) * 128 + r];
+            const float inv_l = l > 0.f ? 1.f / l : 0.f;
+            T* orow = reinterpret_cast<T*>(p.O) + b * p.o_sb + static_cast<long long>(q) * p.o_ss + h * p.o_sh +
+                      half * 32;
+            uint32_t v[32];
+            tmem_ld32(col_o + lane_addr + half * 32, v);
+            tmem_ld_wait();
+            if (q < p.S) {
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     uint4 qv;
                     T* e = reinterpret_cast<T*>(&qv);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(pr[g * 8 + i]);
-                    const int kk = c * 32 + g * 8;
-                    const uint32_t c16 = (kk & 63) >> 3;
-                    *reinterpret_cast<uint4*>(prow + (kk >> 6) * (P_BYTES / 2) + ((c16 ^ sw) << 4)) = qv;
+                    for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(v[g * 8 + i]) * inv_l);
+                    *reinterpret_cast<uint4*>(orow + g * 8) = qv;
                 }
+                if (half == 0)
+                    p.lse[(static_cast<long long>(b) * p.H + h) * p.S + q] =
+                        (m == -INFINITY ? 0.f : m) * 0.6931471805599453f + __logf(fmaxf(l, 1e-30f));
             }
-            tc_fence_before();
-            mbar_arrive(s_free);
-            l = l * alpha + rs;
-            m = m_new;
-            fence_proxy_async();
-            mbar_arrive(p_ready);
-        }
-        if (ok && mbar_wait(o_done, (nchunks - 1) & 1, abort_flag)) {
-            tc_fence_after();
-            const float inv_l = l > 0.f ? 1.f / l : 0.f;
-            T* orow = reinterpret_cast<T*>(p.O) + b * p.o_sb + static_cast<long long>(q) * p.o_ss +
-                      h * p.o_sh;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_addr + COL_O + c * 32, v);
-                tmem_ld_wait();
-                if (q < p.S) {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 qv;
-                        T* e = reinterpret_cast<T*>(&qv);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            e[i] = from_f32<T>(__uint_as_float(v[g * 8 + i]) * inv_l);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = qv;
-                    }
-                }
-            }
-            if (q < p.S)
-                p.lse[(static_cast<long long>(b) * p.H + h) * p.S + q] =
-                    (m == -INFINITY ? 0.f : m) * 0.6931471805599453f + __logf(fmaxf(l, 1e-30f));
         }
     }
 
@@ -302,7 +308,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         }
         __syncthreads();
     }
-    if (warp == 4) {
+    if (warp == 16) {
         tc_fence_after();
         tmem_dealloc(tmem, ATT_TMEM_COLS);
     }
@@ -329,7 +335,7 @@ static int launch_fwd(const RbAttnArgs& a, cudaStream_t st) {
     p.lse = a.lse;
     p.thr16 = a.p_drop > 0.f ? static_cast<uint32_t>(a.p_drop * 65536.f + 0.5f) : 0u;
     p.inv_keep = a.p_drop > 0.f ? 1.f / (1.f - a.p_drop) : 1.f;
-    p.seed = a.seed * 0x2545F4914F6CDD1Dull + a.offset;
+    p.seed = drop_seed(a.seed, a.offset);
     p.err = error_word_ptr();
     if (!p.err) return -3;
     auto kern = attn_fwd_kernel<T>;
@@ -341,7 +347,7 @@ static int launch_fwd(const RbAttnArgs& a, cudaStream_t st) {
             return -4;
         attr_set[dev & 63] = true;
     }
-    dim3 grid((a.S + AQ - 1) / AQ, a.H, a.B);
+    dim3 grid((a.S + 2 * AQ - 1) / (2 * AQ), a.H, a.B);
     kern<<<grid, ATT_THREADS, ATT_SMEM, st>>>(tq, tk, tv, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -68,19 +68,18 @@ __global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ y, size_
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         float a[8];
         ld8e(x + i * 8, a);
-        const Philox4 r0 = philox4x32_10(seed, offset, i * 2);
-        const Philox4 r1 = philox4x32_10(seed, offset, i * 2 + 1);
+        bool k[8];
+        keep8(seed, offset, i * 8, thr, k);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            a[j] = r0.v[j] >= thr ? a[j] * scale : 0.f;
-            a[4 + j] = r1.v[j] >= thr ? a[4 + j] * scale : 0.f;
-        }
+        for (int j = 0; j < 8; ++j) a[j] = k[j] ? a[j] * scale : 0.f;
         st8e(y + i * 8, a);
     }
     if (blockIdx.x == 0 && threadIdx.x < n % 8) {
         const size_t i = nv * 8 + threadIdx.x;
-        const Philox4 r = philox4x32_10(seed, offset, i >> 2);
-        y[i] = from_f32<T>(r.v[i & 3] >= thr ? to_f32<T>(x[i]) * scale : 0.f);
+        const Philox4 r = philox4x32(seed, offset, i >> 3);
+        const uint32_t w = r.v[(i & 7) >> 1];
+        const uint32_t bits = (i & 1) ? (w >> 16) : (w & 0xffffu);
+        y[i] = from_f32<T>(bits >= thr ? to_f32<T>(x[i]) * scale : 0.f);
     }
 }
 
@@ -115,6 +114,46 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
         if (col < N) atomicAdd(out + col, s0);
         if (col + 1 < N) atomicAdd(out + col + 1, s1);
     }
+}
+
+// Vector variant: a thread owns 8 adjacent columns (one 16-byte load per row), a block of (32, 8)
+// covers 256 columns; rows are strided over threadIdx.y and blockIdx.y.  Needs N % 8 == 0,
+// ld % 8 == 0 and a 16-byte aligned base.
+template <typename T>
+__global__ void colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, int M, int N,
+                                  long long ld) {
+    __shared__ float red[8][256 + 8];
+    const int col = blockIdx.x * 256 + threadIdx.x * 8;
+    float s[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] = 0.f;
+    if (col < N) {
+        const int step = gridDim.y * 8;
+        int m = blockIdx.y * 8 + threadIdx.y;
+        // two rows in flight per iteration
+        for (; m + step < M; m += 2 * step) {
+            float a[8], b[8];
+            ld8e(x + static_cast<long long>(m) * ld + col, a);
+            ld8e(x + static_cast<long long>(m + step) * ld + col, b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] += a[j] + b[j];
+        }
+        if (m < M) {
+            float a[8];
+            ld8e(x + static_cast<long long>(m) * ld + col, a);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] += a[j];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[threadIdx.y][threadIdx.x * 8 + j] = s[j];
+    __syncthreads();
+    const int t = threadIdx.y * 32 + threadIdx.x;  // 256 threads, one column each
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) acc += red[w][t];
+    const int c = blockIdx.x * 256 + t;
+    if (c < N) atomicAdd(out + c, acc);
 }
 
 // dst(fp32) += src(16-bit) * scale
@@ -224,6 +263,20 @@ extern "C" int rb_colsum(const void* x, float* out, int M, int N, long long ld, 
                          void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (M <= 0 || N <= 0) return 0;
+    if (N % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const int cols = (N + 255) / 256;
+        int split = (148 * 6 + cols - 1) / cols;  // about six blocks per SM in total
+        const int max_split = (M + 15) / 16;
+        if (split > max_split) split = max_split;
+        if (split < 1) split = 1;
+        dim3 grid(cols, split), block(32, 8);
+        if (dtype == 1)
+            colsum_vec_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, M,
+                                                                    N, ld);
+        else
+            colsum_vec_kernel<__half><<<grid, block, 0, st>>>(static_cast<const __half*>(x), out, M, N, ld);
+        return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    }
     int split = (M + 255) / 256;
     if (split > 64) split = 64;
     dim3 grid((N + 63) / 64, split), block(32, 8);

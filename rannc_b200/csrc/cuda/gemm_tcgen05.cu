@@ -42,6 +42,7 @@ struct GemmKernelParams {
     int M, N, K, batch;
     int a_major, b_major;
     int num_m_blocks, num_n_blocks, num_tiles, num_kb;
+    int base_tiles, split_k, kb_per_split;  // split-K: num_tiles = base_tiles * split_k
     void* D;
     const void* bias;
     const void* residual;
@@ -54,7 +55,11 @@ struct GemmKernelParams {
 };
 
 __device__ __forceinline__ void tile_coords(const GemmKernelParams& p, int tile, int& mb, int& nb,
-                                            int& b) {
+                                            int& b, int& kb_begin, int& kb_end) {
+    const int ks = tile / p.base_tiles;
+    tile -= ks * p.base_tiles;
+    kb_begin = ks * p.kb_per_split;
+    kb_end = min(p.num_kb, kb_begin + p.kb_per_split);
     const int per_batch = p.num_m_blocks * p.num_n_blocks;
     b = tile / per_batch;
     int t = tile - b * per_batch;
@@ -172,10 +177,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                int mb, nb, b;
-                tile_coords(p, tile, mb, nb, b);
+                int mb, nb, b, kb_begin, kb_end;
+                tile_coords(p, tile, mb, nb, b, kb_begin, kb_end);
                 const int m0 = mb * BM, n0 = nb * BN;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         ok = false;
                         break;
@@ -227,7 +232,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.num_kb; ++kb) {
+                int mb_, nb_, b_, kb_begin, kb_end;
+                tile_coords(p, tile, mb_, nb_, b_, kb_begin, kb_end);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort_flag)) {
                         ok = false;
                         break;
@@ -239,7 +246,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint64_t da = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
                         const uint64_t db = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
-                        umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_f16(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[stage]);
                     if (++stage == STAGES) {
@@ -264,8 +271,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const bool out_al = (sizeof(OutT) == 2) ? (p.ldd % 8 == 0) : (p.ldd % 4 == 0);
         int it = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-            int mb, nb, b;
-            tile_coords(p, tile, mb, nb, b);
+            int mb, nb, b, kb_begin, kb_end;
+            tile_coords(p, tile, mb, nb, b, kb_begin, kb_end);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
@@ -287,6 +294,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+                if constexpr (std::is_same<OutT, float>::value) {
+                    if (p.split_k > 1) {
+                        // partial sums of a K slice: accumulate with vector reductions
+                        float* dptr = reinterpret_cast<float*>(p.D) + row_off + col;
+                        if (full_chunk && out_al) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dptr + j),
+                                             "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
+                                             : "memory");
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < valid) atomicAdd(dptr + j, v[j]);
+                        }
+                        continue;
+                    }
+                }
                 if (has_bias) {
                     float t[32];
                     load32(reinterpret_cast<const InT*>(p.bias) + col, full_chunk, valid, t);
@@ -482,8 +507,27 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     p.b_major = a->b_major;
     p.num_m_blocks = (p.M + BM - 1) / BM;
     p.num_n_blocks = (p.N + BN - 1) / BN;
-    p.num_tiles = p.num_m_blocks * p.num_n_blocks * p.batch;
+    p.base_tiles = p.num_m_blocks * p.num_n_blocks * p.batch;
     p.num_kb = (p.K + BK - 1) / BK;
+    p.split_k = 1;
+    // Few output tiles and a long K (weight gradients): split K over CTAs and accumulate with
+    // reductions.  Only for fp32 outputs that accumulate and have no other epilogue work.
+    if (a->out_dtype == 1 && a->flags == RB_GEMM_ACCUM && p.base_tiles < num_sms() && p.num_kb >= 8) {
+        const int sms = num_sms();
+        double best = 0.0;
+        for (int s = 1; s <= 16 && s * 4 <= p.num_kb; ++s) {
+            const int work = p.base_tiles * s;
+            const int waves = (work + sms - 1) / sms;
+            const double eff = static_cast<double>(work) / (waves * sms) - 0.01 * s;
+            if (eff > best + 1e-9) {
+                best = eff;
+                p.split_k = s;
+            }
+        }
+    }
+    p.kb_per_split = (p.num_kb + p.split_k - 1) / p.split_k;
+    p.split_k = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    p.num_tiles = p.base_tiles * p.split_k;
     p.D = a->D;
     p.bias = a->bias;
     p.residual = a->residual;

@@ -44,18 +44,6 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
-// keep flags of 8 consecutive elements starting at linear index idx (idx % 8 == 0)
-__device__ __forceinline__ void keep8(uint64_t seed, uint64_t offset, uint64_t idx, uint32_t thr,
-                                      bool (&k)[8]) {
-    const Philox4 a = philox4x32_10(seed, offset, idx >> 2);
-    const Philox4 b = philox4x32_10(seed, offset, (idx >> 2) + 1);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        k[j] = a.v[j] >= thr;
-        k[4 + j] = b.v[j] >= thr;
-    }
-}
-
 // sum over the WPR warps that share a row (warps [slot*WPR, slot*WPR+WPR))
 template <int WPR>
 __device__ __forceinline__ float group_sum(float v, float* sm, int warp, int lane) {

@@ -1,0 +1,260 @@
+// Fused data-parallel gradient step over NVLink / NVSwitch peer memory:
+//
+//   reduce-scatter(fp32 grads over the owner set) * 1/world * unscale
+//     -> Adam on this rank's fp32 master shard
+//     -> all-gather of the updated 16-bit parameters
+//
+// in ONE kernel per rank.  Each rank owns the contiguous shard [lo, lo+len) of
+// the flat gradient / parameter buffers, which live in symmetric memory: every
+// rank holds the peers' base pointers.  The kernel
+//   0. tells every peer "my gradients are complete" (flag store, release.sys)
+//      and waits for the same word from every peer (acquire.sys, bounded);
+//   1. for every 16-byte group of its shard: loads the group from every peer's
+//      gradient buffer (plain peer loads, or ONE multimem.ld_reduce through the
+//      switch when a multicast mapping exists), scales, runs Adam on the local
+//      master / moments, and stores the bf16 result into every peer's parameter
+//      buffer (peer stores, or one multimem.st);
+//   2. the last CTA to finish publishes "my writes are done" and waits for the
+//      peers' words, so that on return every rank's parameters are complete.
+// No TMA and no cluster multicast is involved: remote data moves with ordinary
+// ld/st/multimem instructions issued by the SMs.
+//
+// Replaces, per owner rank set, the reference's per-parameter ncclAllReduce /
+// bucketed ncclReduceScatter + pack/unpack copies + mul_ scaling + Apex Adam +
+// per-forward ncclAllGather (src/comp/ParamStorage.cpp:347-596,
+// src/comm/NCCLWrapper.cpp:324-437, pyrannc/opt.py:205-312).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "rs_adam.h"
+#include "tc_common.cuh"
+
+namespace rb {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc) {
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_st_b128(void* mc, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc),
+                 "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                 "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
+// Waits until *flag >= expected.  Returns false when `max_polls` ran out.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t expected,
+                                          unsigned long long max_polls) {
+    for (unsigned long long i = 0; i < max_polls; ++i) {
+        const uint32_t v = ld_acquire_sys(flag);
+        if (static_cast<int32_t>(v - expected) >= 0) return true;
+        __nanosleep(100);
+    }
+    return false;
+}
+
+struct RsAdamParams {
+    const float* peer_grad[RB_MAX_PEERS];   // each rank's flat fp32 gradient buffer
+    void* peer_param[RB_MAX_PEERS];         // each rank's flat 16-bit parameter buffer
+    uint32_t* peer_flags[RB_MAX_PEERS];     // each rank's flag block: [2][RB_MAX_PEERS] words
+    const float* mc_grad;                   // multicast alias of the gradient buffers (or null)
+    void* mc_param;                         // multicast alias of the parameter buffers (or null)
+    float* master;                          // local: fp32 master shard [len]
+    float* m;
+    float* v;
+    unsigned int* done_counter;             // local scratch word, zero on entry, zero on exit
+    long long lo, len;                      // shard in flat coordinates (elements, multiples of 8)
+    int nranks, my_idx;
+    uint32_t epoch;
+    float grad_mul;                         // 1/world * 1/loss_scale
+    float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2;
+    int adamw;
+    const float* ctrl;                      // optional [mul, skip]
+    unsigned long long max_polls;
+    int* err;
+};
+
+template <typename T16>
+__global__ void __launch_bounds__(512)
+    rs_adam_ag_kernel(const RsAdamParams p) {
+    __shared__ int s_ok;
+    __shared__ int s_last;
+    // ---- phase 0: everyone's gradients are complete
+    if (blockIdx.x == 0 && threadIdx.x < p.nranks) {
+        __threadfence_system();
+        st_release_sys(p.peer_flags[threadIdx.x] + 0 * RB_MAX_PEERS + p.my_idx, p.epoch);
+    }
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < p.nranks) {
+        if (!wait_flag(p.peer_flags[p.my_idx] + 0 * RB_MAX_PEERS + threadIdx.x, p.epoch, p.max_polls)) {
+            s_ok = 0;
+            atomicExch(p.err, ERR_PEER_TIMEOUT);
+        }
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    const bool skip = p.ctrl && p.ctrl[1] != 0.f;
+    const float gmul = p.grad_mul * (p.ctrl ? p.ctrl[0] : 1.f);
+
+    // ---- phase 1: reduce -> Adam -> scatter the 16-bit result (8 elements = one 16-byte store per step)
+    if (ok && !skip) {
+        const long long nvec = p.len / 8;
+        for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+             i += static_cast<long long>(gridDim.x) * blockDim.x) {
+            const long long e = p.lo + i * 8;
+            float g[8];
+            if (p.mc_grad) {
+                const float4 a = multimem_ld_reduce_f32x4(p.mc_grad + e);
+                const float4 b = multimem_ld_reduce_f32x4(p.mc_grad + e + 4);
+                g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+                g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g[j] = 0.f;
+#pragma unroll 1
+                for (int r = 0; r < p.nranks; ++r) {
+                    // own buffer first, then the peers in a per-rank rotated order
+                    const int src = (p.my_idx + r) % p.nranks;
+                    const float4 a = *reinterpret_cast<const float4*>(p.peer_grad[src] + e);
+                    const float4 b = *reinterpret_cast<const float4*>(p.peer_grad[src] + e + 4);
+                    g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+                    g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+                }
+            }
+            float w[8], mm[8], vv[8];
+            *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i * 8);
+            *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(p.master + i * 8 + 4);
+            *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(p.m + i * 8);
+            *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(p.m + i * 8 + 4);
+            *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(p.v + i * 8);
+            *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(p.v + i * 8 + 4);
+            uint4 packed;
+            T16* o = reinterpret_cast<T16*>(&packed);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float gg = g[j] * gmul;
+                if (!p.adamw && p.weight_decay != 0.f) gg += p.weight_decay * w[j];
+                mm[j] = p.beta1 * mm[j] + (1.f - p.beta1) * gg;
+                vv[j] = p.beta2 * vv[j] + (1.f - p.beta2) * gg * gg;
+                float u = (mm[j] / p.bias_corr1) / (sqrtf(vv[j] / p.bias_corr2) + p.eps);
+                if (p.adamw && p.weight_decay != 0.f) u += p.weight_decay * w[j];
+                w[j] -= p.lr * u;
+                o[j] = from_f32<T16>(w[j]);
+            }
+            *reinterpret_cast<float4*>(p.master + i * 8) = *reinterpret_cast<float4*>(w);
+            *reinterpret_cast<float4*>(p.master + i * 8 + 4) = *reinterpret_cast<float4*>(w + 4);
+            *reinterpret_cast<float4*>(p.m + i * 8) = *reinterpret_cast<float4*>(mm);
+            *reinterpret_cast<float4*>(p.m + i * 8 + 4) = *reinterpret_cast<float4*>(mm + 4);
+            *reinterpret_cast<float4*>(p.v + i * 8) = *reinterpret_cast<float4*>(vv);
+            *reinterpret_cast<float4*>(p.v + i * 8 + 4) = *reinterpret_cast<float4*>(vv + 4);
+            if (p.mc_param) {
+                multimem_st_b128(reinterpret_cast<T16*>(p.mc_param) + e, packed);
+            } else {
+#pragma unroll 1
+                for (int r = 0; r < p.nranks; ++r) {
+                    const int dst = (p.my_idx + r) % p.nranks;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<T16*>(p.peer_param[dst]) + e) = packed;
+                }
+            }
+        }
+    }
+
+    // ---- phase 2: the last CTA publishes completion and waits for the peers
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(p.done_counter, 1u);
+        s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        if (threadIdx.x == 0) *p.done_counter = 0;  // ready for the next launch
+        __threadfence_system();
+        if (threadIdx.x < p.nranks)
+            st_release_sys(p.peer_flags[threadIdx.x] + 1 * RB_MAX_PEERS + p.my_idx, p.epoch);
+        if (threadIdx.x < p.nranks && ok) {
+            if (!wait_flag(p.peer_flags[p.my_idx] + 1 * RB_MAX_PEERS + threadIdx.x, p.epoch, p.max_polls))
+                atomicExch(p.err, ERR_PEER_TIMEOUT);
+        }
+    }
+}
+
+// Single-GPU check of the bounded wait: polls a flag nobody sets.
+__global__ void wait_flag_probe_kernel(const uint32_t* flag, uint32_t expected,
+                                       unsigned long long max_polls, int* err) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        if (!wait_flag(flag, expected, max_polls)) atomicExch(err, ERR_PEER_TIMEOUT);
+    }
+}
+
+int* error_word_ptr();
+
+}  // namespace rb
+
+extern "C" int rb_rs_adam_ag(const RbRsAdamArgs* a, void* stream) {
+    using namespace rb;
+    if (a->nranks < 1 || a->nranks > RB_MAX_PEERS) return -2;
+    if ((a->lo % 8) || (a->len % 8)) return -2;
+    if (a->len <= 0) return 0;
+    RsAdamParams p;
+    for (int r = 0; r < RB_MAX_PEERS; ++r) {
+        p.peer_grad[r] = r < a->nranks ? static_cast<const float*>(a->peer_grad[r]) : nullptr;
+        p.peer_param[r] = r < a->nranks ? a->peer_param[r] : nullptr;
+        p.peer_flags[r] = r < a->nranks ? static_cast<uint32_t*>(a->peer_flags[r]) : nullptr;
+    }
+    p.mc_grad = static_cast<const float*>(a->mc_grad);
+    p.mc_param = a->mc_param;
+    p.master = a->master;
+    p.m = a->m;
+    p.v = a->v;
+    p.done_counter = static_cast<unsigned int*>(a->done_counter);
+    p.lo = a->lo;
+    p.len = a->len;
+    p.nranks = a->nranks;
+    p.my_idx = a->my_idx;
+    p.epoch = a->epoch;
+    p.grad_mul = a->grad_mul;
+    p.lr = a->lr;
+    p.beta1 = a->beta1;
+    p.beta2 = a->beta2;
+    p.eps = a->eps;
+    p.weight_decay = a->weight_decay;
+    p.bias_corr1 = a->bias_corr1;
+    p.bias_corr2 = a->bias_corr2;
+    p.adamw = a->adamw;
+    p.ctrl = a->ctrl;
+    p.max_polls = a->max_polls ? a->max_polls : (1ull << 26);
+    p.err = error_word_ptr();
+    if (!p.err) return -3;
+    int grid = a->num_ctas > 0 ? a->num_ctas : 148;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->dtype16 == 1)
+        rs_adam_ag_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(p);
+    else
+        rs_adam_ag_kernel<__half><<<grid, 512, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+extern "C" int rb_wait_flag_probe(const void* flag, unsigned int expected, unsigned long long max_polls,
+                                  void* stream) {
+    int* err = rb::error_word_ptr();
+    if (!err) return -3;
+    rb::wait_flag_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint32_t*>(flag), expected, max_polls, err);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}

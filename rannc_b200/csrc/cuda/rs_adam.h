@@ -1,0 +1,41 @@
+// C ABI of the fused reduce-scatter + Adam + all-gather kernel (rs_adam.cu).
+#pragma once
+#include <stdint.h>
+
+#define RB_MAX_PEERS 8
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct RbRsAdamArgs {
+    const void* peer_grad[RB_MAX_PEERS];   // fp32 flat gradient buffer of every rank of the owner set
+    void* peer_param[RB_MAX_PEERS];        // 16-bit flat parameter buffer of every rank
+    void* peer_flags[RB_MAX_PEERS];        // flag block of every rank: uint32 [2][RB_MAX_PEERS], zero-initialised
+    const void* mc_grad;                   // multicast address of the gradient buffers, or null
+    void* mc_param;                        // multicast address of the parameter buffers, or null
+    float* master;                         // this rank's fp32 master shard
+    float* m;
+    float* v;
+    void* done_counter;                    // one zero-initialised uint32 in local device memory
+    int64_t lo, len;                       // shard [lo, lo + len) in elements; multiples of 8
+    int32_t nranks, my_idx;
+    uint32_t epoch;                        // strictly increasing per launch, same on every rank
+    float grad_mul;                        // 1/world * 1/loss_scale
+    float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2;
+    int32_t adamw;
+    int32_t dtype16;                       // 0 fp16, 1 bf16
+    int32_t num_ctas;                      // 0: 148
+    int32_t pad_;
+    const float* ctrl;                     // optional [gradient multiplier, skip flag]
+    uint64_t max_polls;                    // bound of every flag wait (0: 2^26 polls of >= 100 ns)
+} RbRsAdamArgs;
+
+// 0 on success.  A wait that runs out sets the device error word to 2 and the kernel returns.
+int rb_rs_adam_ag(const RbRsAdamArgs* args, void* stream);
+// polls `flag` until it reaches `expected` or `max_polls` ran out (error word 2); for tests of the bound
+int rb_wait_flag_probe(const void* flag, unsigned int expected, unsigned long long max_polls, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

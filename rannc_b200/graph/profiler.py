@@ -82,6 +82,13 @@ def analytic_profiles(gm: fx.GraphModule) -> Dict[str, "_core.NodeProfile"]:
                 for d in xs[:-1]:
                     m *= d
                 act = out_bytes + 2 * m * w1[0] * args[0].meta["val"].element_size()
+            elif name == "rannc::qkv_attention":
+                xs, ws = _shape(args[0].meta["val"]), _shape(args[1].meta["val"])
+                B, S = xs[0], xs[1]
+                H = int(args[11])
+                D = ws[0] // H
+                flops = 3 * 2.0 * B * S * ws[0] * ws[1] + 4.0 * B * H * S * S * D
+                act = 5 * B * S * ws[0] * args[0].meta["val"].element_size() + B * H * S * 4
             elif name in ("rannc::sdpa", "aten::scaled_dot_product_attention"):
                 B, H, S, D = _shape(args[0].meta["val"])
                 flops = 4.0 * B * H * S * S * D

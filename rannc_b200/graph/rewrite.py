@@ -94,6 +94,50 @@ def fuse(gm: fx.GraphModule, training: bool = True) -> dict:
     drop_asserts(gm)
     g = gm.graph
 
+    # ---- q/k/v projections of one input + attention -> one operator
+    def _proj(node):
+        """transpose(view(linear(x, w, b), [B, S, H, D]), 1, 2) -> (linear node, H) or None"""
+        if not _is(node, aten.transpose.int) or sorted(node.args[1:3]) != [1, 2] or len(_users(node)) != 1:
+            return None
+        v = node.args[0]
+        if not _is(v, aten.view.default, aten.reshape.default) or len(_users(v)) != 1 or len(v.args[1]) != 4:
+            return None
+        lin = v.args[0]
+        if not _is(lin, aten.linear.default) or len(_users(lin)) != 1:
+            return None
+        heads = v.args[1][2]
+        return (lin, v, int(heads)) if isinstance(heads, int) else None
+
+    for n in list(g.nodes):
+        if not _is(n, aten.scaled_dot_product_attention.default):
+            continue
+        pq, pk, pv = (_proj(a) for a in n.args[:3])
+        if pq is None or pk is None or pv is None:
+            continue
+        x = pq[0].args[0]
+        if pk[0].args[0] is not x or pv[0].args[0] is not x or not (pq[2] == pk[2] == pv[2]):
+            continue
+        xv = _val(x)
+        if xv is None or xv.dim() != 3:
+            continue
+        u = _single_user(n)
+        if u is None or not _is(u, aten.transpose.int) or sorted(u.args[1:3]) != [1, 2]:
+            continue
+        u2 = _single_user(u)
+        if u2 is None or not _is(u2, aten.reshape.default, aten.view.default, aten._unsafe_view.default) or \
+                len(u2.args[1]) != 3:
+            continue
+        mask = _arg(n, 3, "attn_mask")
+        pdrop = _arg(n, 4, "dropout_p", 0.0)
+        causal = _arg(n, 5, "is_causal", False)
+        scale = n.kwargs.get("scale")
+        args = (x, pq[0].args[1], _arg(pq[0], 2, "bias"), pk[0].args[1], _arg(pk[0], 2, "bias"),
+                pv[0].args[1], _arg(pv[0], 2, "bias"), mask, pdrop, causal, scale, pq[2])
+        _replace(gm, u2, RF.qkv_attention, args)
+        _erase_if_dead(gm, u, n)
+        bump("qkv_attention")
+    g.eliminate_dead_code()
+
     # ---- linear -> gelu -> linear  /  linear -> gelu
     for n in list(g.nodes):
         if not _is(n, aten.linear.default) or n not in g.nodes:

@@ -263,8 +263,11 @@ class RaNNCModule:
         self._storage = ParamStorage(self.use_amp_master_params, self.enable_zero, self.allreduce_amp_master_params)
         self._storage.sync_on_init = _sync_params_on_init
         local_params = {n: name_to_param[n] for n in self._used_param_names}
+        want_fused = (self.use_amp_master_params and self.enable_zero and dev.type == "cuda" and world > 1 and
+                      bool(conf("fused_kernels")) and bool(conf("fused_grad_allreduce")) and
+                      type(self.optimizer) in (torch.optim.Adam, torch.optim.AdamW))
         self._storage.deploy(local_params, {n: sorted(r) for n, r in owner.items()}, opt_group_of, dev,
-                             self._param_order_by_name)
+                             self._param_order_by_name, symmetric=want_fused)
         for n in self._used_buffer_names:
             b = name_to_buffer[n]
             b.data = b.data.to(dev)
@@ -299,7 +302,7 @@ class RaNNCModule:
             from .opt import patch_optimizer
 
             patch_optimizer(self, self.optimizer)
-        if self.use_amp_master_params and dev.type == "cuda" and bool(conf("fused_grad_allreduce")) and world > 1:
+        if want_fused:
             self._setup_fused_reducer()
         self.ready = True
         comm.barrier()
@@ -337,6 +340,11 @@ class RaNNCModule:
             self._fused_reducer.mark_ready()
             return
         self._storage.allreduce_grads_zero()
+
+    def _needs_grad_norm(self) -> bool:
+        scaler = _amp.get_scaler()
+        return (self.use_amp_master_params and (self.amp_dtype == torch.float16 or scaler.loss_scale() != 1.0)) or \
+            self.max_grad_norm > 0.0
 
     def _amp_prepare_step(self):
         """Called by the patched optimizer step.  Returns None (nothing to do), False (overflow: skip the step)

@@ -16,6 +16,40 @@ _HERE = Path(__file__).resolve().parent.parent
 _lock = threading.Lock()
 _lib = None
 
+# device kernels launched per C entry point (the optimizer / element-wise entries launch one)
+_KERNELS_PER_CALL = {"rb_ln_bwd": 2, "rb_xent_fwd": 2, "rb_attn_bwd": 3, "rb_read_error": 0, "rb_ln_supported": 0,
+                     "rb_ln_bwd_grid": 0}
+_launches = 0
+
+
+class _Counting:
+    """Forwards attribute access to the CDLL and counts kernel launches per call."""
+
+    def __init__(self, dll):
+        object.__setattr__(self, "_dll", dll)
+        object.__setattr__(self, "_cache", {})
+
+    def __getattr__(self, name):
+        cache = object.__getattribute__(self, "_cache")
+        fn = cache.get(name)
+        if fn is None:
+            raw = getattr(object.__getattribute__(self, "_dll"), name)
+            n = _KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*a, __raw=raw, __n=n):
+                global _launches
+                _launches += __n
+                return __raw(*a)
+
+            fn.raw = raw
+            cache[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far in this process."""
+    return _launches
+
 
 class KernelLibraryError(RuntimeError):
     pass
@@ -41,6 +75,7 @@ def lib() -> ctypes.CDLL:
         except OSError as e:
             raise KernelLibraryError(f"cannot load {path}: {e}") from e
         _lib.rb_read_error.restype = ctypes.c_int
+        _lib = _Counting(_lib)
         return _lib
 
 

@@ -1,0 +1,152 @@
+"""Micro-benchmarks of the sm_100a kernels (CUDA-event timing, L2 flushed between iterations).
+
+    python -m rannc_b200.ops.bench_kernels gemm --m 16384 --n 4096 --k 1024 [--layout nt|nn|tn] [--acc]
+    python -m rannc_b200.ops.bench_kernels attn --batch 8 --heads 16 --seq 512 [--dropout 0.1]
+    python -m rannc_b200.ops.bench_kernels ln --rows 32768 --hidden 1024
+    python -m rannc_b200.ops.bench_kernels adam --numel 100000000
+
+Each prints one JSON line with the time per call and the achieved fraction of the measured peaks
+(``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).
+``--iters`` small and ``--no-flush`` make the run suitable for a profiler capture.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def _time(fn, iters, warmup, flush):
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()  # 256 MiB > the 126 MB L2
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters * 1e-3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attn", "attn_bwd", "ln", "ln_bwd", "adam", "xent", "colsum"])
+    ap.add_argument("--m", type=int, default=16384)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--layout", default="nt", help="nt: forward, nn: dgrad, tn: wgrad")
+    ap.add_argument("--acc", action="store_true", help="fp32 output with accumulation (wgrad epilogue)")
+    ap.add_argument("--gelu", action="store_true")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=512)
+    ap.add_argument("--dropout", type=float, default=0.0)
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--hidden", type=int, default=1024)
+    ap.add_argument("--numel", type=int, default=100_000_000)
+    ap.add_argument("--vocab", type=int, default=30522)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args()
+
+    from . import _lib
+    from . import kernels as K
+    from .gemm import gemm
+
+    hbm, flops_peak, src = _peaks()
+    dt = torch.bfloat16
+    out = {"kernel": a.kernel, "peaks": src}
+    if a.kernel == "gemm":
+        M, N, Kd = a.m, a.n, a.k
+        ta, tb = {"nt": (False, True), "nn": (False, False), "tn": (True, False)}[a.layout]
+        A = torch.randn((Kd, M) if ta else (M, Kd), device="cuda", dtype=dt)
+        B = torch.randn((N, Kd) if tb else (Kd, N), device="cuda", dtype=dt)
+        D = torch.zeros(M, N, device="cuda", dtype=torch.float32 if a.acc else dt)
+        bias = torch.randn(N, device="cuda", dtype=dt) if a.gelu else None
+        fn = lambda: gemm(A, B, trans_a=ta, trans_b=tb, out=D, accumulate=a.acc, bias=bias, gelu=a.gelu)  # noqa: E731
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        fl = 2.0 * M * N * Kd
+        out.update(M=M, N=N, K=Kd, layout=a.layout, acc=a.acc, ms=t * 1e3, tflops=fl / t / 1e12,
+                   frac_of_peak=fl / t / flops_peak)
+    elif a.kernel in ("attn", "attn_bwd"):
+        B, H, S, D = a.batch, a.heads, a.seq, 64
+        qkv = torch.randn(B, S, 3, H, D, device="cuda", dtype=dt)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        if a.kernel == "attn":
+            fn = lambda: K.attn_fwd(q, k, v, p_drop=a.dropout, seed=1, offset=1)  # noqa: E731
+            fl = 4.0 * B * H * S * S * D
+        else:
+            o, lse = K.attn_fwd(q, k, v, p_drop=a.dropout, seed=1, offset=1)
+            do = torch.randn_like(o)
+            fn = lambda: K.attn_bwd(q, k, v, o, lse, do, p_drop=a.dropout, seed=1, offset=1)  # noqa: E731
+            fl = 10.0 * B * H * S * S * D
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        out.update(B=B, H=H, S=S, D=D, dropout=a.dropout, ms=t * 1e3, tflops=fl / t / 1e12,
+                   frac_of_peak=fl / t / flops_peak)
+    elif a.kernel in ("ln", "ln_bwd"):
+        R, Hd = a.rows, a.hidden
+        x = torch.randn(R, Hd, device="cuda", dtype=dt)
+        r = torch.randn(R, Hd, device="cuda", dtype=dt)
+        g = torch.ones(Hd, device="cuda", dtype=dt)
+        b = torch.zeros(Hd, device="cuda", dtype=dt)
+        if a.kernel == "ln":
+            fn = lambda: K.ln_fwd(x, r, g, b, 1e-5, a.dropout, 1, 1)  # noqa: E731
+            nbytes = 4 * R * Hd * 2
+        else:
+            y, z, mean, rstd = K.ln_fwd(x, r, g, b, 1e-5, a.dropout, 1, 1)
+            dy = torch.randn_like(x)
+            fn = lambda: K.ln_bwd(dy, z, g, mean, rstd, a.dropout, 1, 1)  # noqa: E731
+            nbytes = (3 + (1 if a.dropout > 0 else 0)) * R * Hd * 2
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        out.update(rows=R, hidden=Hd, dropout=a.dropout, ms=t * 1e3, gbs=nbytes / t / 1e9,
+                   frac_of_peak=nbytes / t / hbm)
+    elif a.kernel == "adam":
+        n = a.numel
+        p, gr, m, v = (torch.randn(n, device="cuda") for _ in range(4))
+        p16 = torch.empty(n, device="cuda", dtype=dt)
+        fn = lambda: K.adam_flat(p, gr, m, v, p16, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, False)  # noqa: E731
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        nbytes = n * (4 * 4 + 3 * 4 + 2)
+        out.update(numel=n, ms=t * 1e3, gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / hbm)
+    elif a.kernel == "xent":
+        R, V = a.rows, a.vocab
+        ld = (V + 63) // 64 * 64
+        logits = torch.randn(R, ld, device="cuda", dtype=dt)
+        labels = torch.randint(0, V, (R,), device="cuda")
+        labels[torch.rand(R, device="cuda") > 0.15] = -100
+        fn = lambda: K.xent_fwd(logits, labels, V)  # noqa: E731
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        nbytes = int(0.15 * R) * ld * 2
+        out.update(rows=R, vocab=V, ms=t * 1e3, gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / hbm)
+    elif a.kernel == "colsum":
+        x = torch.randn(a.rows, a.hidden, device="cuda", dtype=dt)
+        o = torch.zeros(a.hidden, device="cuda")
+        fn = lambda: K.colsum(x, o)  # noqa: E731
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        nbytes = a.rows * a.hidden * 2
+        out.update(rows=a.rows, hidden=a.hidden, ms=t * 1e3, gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / hbm)
+    out["device_error_word"] = _lib.read_error()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

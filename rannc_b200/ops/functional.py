@@ -361,3 +361,97 @@ def cross_entropy(logits, labels, num_classes=None, ignore_index: int = -100, we
     if not (_kernel_ok(l2) and l2.stride(1) == 1):
         return torch.nn.functional.cross_entropy(l2[:, :V].float(), labels.reshape(-1), ignore_index=ignore_index) * weight
     return _SoftmaxXent.apply(l2, labels.reshape(-1).contiguous(), V, ignore_index, float(weight))
+
+
+# ----------------------------------------------------------------------------- fused QKV projection + attention
+param_epoch = 0  # bumped whenever parameter values change in place (optimizer step, parameter sync)
+_cat_cache = {}
+
+
+def bump_param_epoch() -> None:
+    global param_epoch
+    param_epoch += 1
+
+
+def _cat_params(tensors):
+    """Concatenation of a few parameters along dim 0, cached until the parameters next change."""
+    key = tuple(id(t) for t in tensors)
+    hit = _cat_cache.get(key)
+    if hit is not None and hit[0] == param_epoch and hit[2] == tuple(t.data_ptr() for t in tensors):
+        return hit[1]
+    with torch.no_grad():
+        cat = torch.cat([t.detach() for t in tensors], 0)
+    _cat_cache[key] = (param_epoch, cat, tuple(t.data_ptr() for t in tensors))
+    return cat
+
+
+class _QkvAttention(torch.autograd.Function):
+    """softmax((x Wq^T)(x Wk^T)^T) (x Wv^T) with ONE projection GEMM over the concatenated weights; the
+    attention kernels read q / k / v as strided views of its [B, S, 3, H, D] output and write dq / dk / dv
+    into one buffer that the single dgrad GEMM consumes."""
+
+    @staticmethod
+    def forward(ctx, x, wq, bq, wk, bk, wv, bv, key_bias, p, scale, H):
+        B, S, hid = x.shape
+        x2 = x.reshape(B * S, hid)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        wcat = _cat_params((wq, wk, wv))
+        bcat = _cat_params((bq, bk, bv)) if bq is not None else None
+        Ho = wq.shape[0]
+        D = Ho // H
+        qkv = gemm(x2, wcat, bias=bcat).view(B, S, 3, H, D)
+        seed, offset = rng.next() if p > 0.0 else (0, 0)
+        o, lse = K.attn_fwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], key_bias, scale, p, seed, offset)
+        ctx.save_for_backward(x2, qkv, o, lse, key_bias)
+        ctx.ws = (wq, wk, wv)
+        ctx.bs = (bq, bk, bv)
+        ctx.mgs = tuple(_main_grad(t) if t is not None else None for t in (wq, wk, wv, bq, bk, bv))
+        ctx.p, ctx.seed, ctx.offset, ctx.scale = p, seed, offset, scale
+        ctx.dims = (B, S, hid, H, D)
+        return o.view(B, S, Ho)
+
+    @staticmethod
+    def backward(ctx, do):
+        x2, qkv, o, lse, key_bias = ctx.saved_tensors
+        B, S, hid, H, D = ctx.dims
+        Ho = H * D
+        do4 = do.reshape(B, S, H, D)
+        dqkv = torch.empty(B, S, 3, H, D, dtype=qkv.dtype, device=qkv.device)
+        K.attn_bwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], o, lse, do4, key_bias, ctx.scale, ctx.p, ctx.seed,
+                   ctx.offset, dq=dqkv[:, :, 0], dk=dqkv[:, :, 1], dv=dqkv[:, :, 2])
+        d2 = dqkv.view(B * S, 3 * Ho)
+        wcat = _cat_params(ctx.ws)
+        dx = gemm(d2, wcat, trans_b=False).view(B, S, hid) if ctx.needs_input_grad[0] else None
+        grads_w, grads_b = [], []
+        for i in range(3):
+            sl = d2[:, i * Ho:(i + 1) * Ho]
+            grads_w.append(_wgrad(sl, x2, ctx.ws[i], ctx.mgs[i]))
+            grads_b.append(_bgrad(sl, ctx.bs[i], ctx.mgs[3 + i]) if ctx.bs[i] is not None else None)
+        return (dx, grads_w[0], grads_b[0], grads_w[1], grads_b[1], grads_w[2], grads_b[2], None, None, None, None)
+
+
+def qkv_attention(x, wq, bq, wk, bk, wv, bv, attn_mask=None, dropout_p: float = 0.0, is_causal: bool = False,
+                  scale=None, num_heads: int = 1):
+    """Self-attention block input side: the three projections of ``x`` [B, S, hid] and the attention itself.
+    Returns [B, S, H * D].  Falls back to separate projections + ``sdpa`` when the fused kernels do not apply."""
+    B, S, _ = x.shape
+    Ho = wq.shape[0]
+    D = Ho // num_heads
+    same = wk.shape == wq.shape and wv.shape == wq.shape and (bq is None) == (bk is None) == (bv is None)
+    ok = (_kernel_ok(x) and same and D == 64 and not is_causal and _aligned(x) and _aligned(wq)
+          and wq.dtype == x.dtype)
+    key_bias = None
+    if ok and attn_mask is not None:
+        if attn_mask.dtype != torch.bool and tuple(attn_mask.shape) == (B, 1, 1, S):
+            key_bias = attn_mask.reshape(B, S).float().contiguous()
+        else:
+            ok = False
+    if ok:
+        sc = float(scale) if scale is not None else D ** -0.5
+        return _QkvAttention.apply(x, wq, bq, wk, bk, wv, bv, key_bias, float(dropout_p), sc, num_heads)
+    q = linear(x, wq, bq).view(B, S, num_heads, D).transpose(1, 2)
+    k = linear(x, wk, bk).view(B, S, num_heads, D).transpose(1, 2)
+    v = linear(x, wv, bv).view(B, S, num_heads, D).transpose(1, 2)
+    o = sdpa(q, k, v, attn_mask, dropout_p, is_causal, scale)
+    return o.transpose(1, 2).reshape(B, S, Ho)

@@ -33,15 +33,29 @@ def _dt(t: torch.Tensor) -> int:
     raise TypeError(f"gemm: unsupported input dtype {t.dtype}")
 
 
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """TMA wants a 16-byte aligned base and row strides that are multiples of 16 bytes.  Operands that do
+    not qualify (e.g. a [M, 2] gradient) are copied into a buffer whose rows are padded to 8 elements; the
+    logical extents stay the same, so the padding is never read as data."""
+    ok = t.data_ptr() % 16 == 0 and t.stride(-1) == 1 and t.stride(-2) % 8 == 0 and \
+        (t.dim() == 2 or t.stride(0) % 8 == 0)
+    if ok:
+        return t
+    cols = t.shape[-1]
+    pc = (cols + 7) // 8 * 8
+    buf = torch.zeros(*t.shape[:-1], pc, dtype=t.dtype, device=t.device)
+    view = buf[..., :cols]
+    view.copy_(t)
+    return view
+
+
 def _mat(t: torch.Tensor):
     """Returns (tensor, rows, cols, ld, batch, batch_stride) for a 2-D/3-D tensor whose last dim is contiguous."""
     if t.dim() == 2:
-        if t.stride(1) != 1:
-            t = t.contiguous()
+        t = _tma_ready(t)
         return t, t.shape[0], t.shape[1], t.stride(0), 1, 0
     if t.dim() == 3:
-        if t.stride(2) != 1:
-            t = t.contiguous()
+        t = _tma_ready(t)
         return t, t.shape[1], t.shape[2], t.stride(1), t.shape[0], t.stride(0)
     raise ValueError("gemm operands must be 2-D or 3-D")
 

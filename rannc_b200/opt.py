@@ -27,6 +27,7 @@ from typing import Dict, List, Optional
 
 import torch
 
+from .ops import functional as RF
 from .parallel import comm
 from .utils.config import conf
 from .utils.log import get_logger
@@ -169,9 +170,20 @@ def patch_optimizer(module, optimizer):
 
     def step(self, closure=None):
         mod = optimizer._rannc_module
+        red = getattr(mod, "_fused_reducer", None)
+        if red is not None and red.pending and mod._needs_grad_norm():
+            # clipping / fp16 overflow checks need the reduced gradients first
+            storage.allreduce_grads_zero()
+            red.pending = False
         ctrl = mod._amp_prepare_step() if mod is not None else None
         if ctrl is False:
             return None  # overflow: skipped, scale already lowered
+        if red is not None and red.pending:
+            # reduce-scatter + Adam + all-gather in one kernel per rank
+            red.step(None)
+            red.publish_state()
+            RF.bump_param_epoch()
+            return None
         use_fused = optimizer._rannc_kind is not None and all(
             g.flat_grad.is_cuda and g.flat_grad.dtype == torch.float32 for g in storage.groups)
         if use_fused:
@@ -191,6 +203,7 @@ def patch_optimizer(module, optimizer):
                         g.flat_param[lo:hi].copy_(g.flat_master)
         if storage.zero:
             storage.allgather_params_zero()
+        RF.bump_param_epoch()
         return loss
 
     def zero_grad(self, set_to_none: bool = False):

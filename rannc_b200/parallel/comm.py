@@ -48,6 +48,8 @@ class _State:
         self.groups: Dict[Tuple[int, ...], object] = {}
         self.owns_pg = False
         self.cpu_group = None
+        self.watchdog = None
+        self.failed_peer = -1
 
 
 _S = _State()
@@ -82,11 +84,47 @@ def start(device: Optional[torch.device] = None) -> None:
         _S.backend = dist.get_backend()
     _core.set_log_rank(_S.rank)
     _S.initialized = True
+    if bool(conf("run_watchdog")) and _S.world > 1:
+        start_watchdog()
     logger.debug("rank %d of %d on %s", _S.rank, _S.world, str(_S.device))
+
+
+def start_watchdog(directory: Optional[str] = None) -> None:
+    """Heartbeat files in a directory every rank can see; a missing or stale peer file marks the job as
+    failed, and the next ``check_peers()`` -- called on the host before every forward / backward, i.e.
+    before anything is launched -- raises ``CommError`` instead of entering a collective that would never
+    complete (reference: SyncWatchDog, src/cuda/CudaSync.cpp:22-112)."""
+    d = directory or os.environ.get("RANNC_WATCHDOG_LOCKFILE_DIR") or str(conf("watchdog_lockfile_dir"))
+    if not d:
+        raise RuntimeError("run_watchdog needs watchdog_lockfile_dir (or RANNC_WATCHDOG_LOCKFILE_DIR)")
+    os.makedirs(d, exist_ok=True)
+
+    def on_failure(peer: int):
+        _S.failed_peer = int(peer)
+
+    _S.watchdog = _core.Watchdog()
+    _S.watchdog.start(d, _S.rank, _S.world, float(conf("watchdog_period_s")), float(conf("watchdog_stale_s")),
+                      on_failure)
+
+
+def stop_watchdog(remove_own_file: bool = True) -> None:
+    """A rank that fails (or leaves between steps) removes its heartbeat file so the others notice."""
+    if _S.watchdog is not None:
+        _S.watchdog.stop(remove_own_file)
+        _S.watchdog = None
+
+
+def check_peers() -> None:
+    if _S.failed_peer >= 0:
+        peer = _S.failed_peer
+        stop_watchdog(True)
+        raise CommError(f"rank {peer} stopped responding (heartbeat file missing or stale)")
 
 
 def clear() -> None:
     """Destroys communicators (reference: RaNNCProcess::clear)."""
+    stop_watchdog(True)
+    _S.failed_peer = -1
     _S.groups.clear()
     if _S.owns_pg and dist.is_initialized():
         try:

@@ -71,7 +71,7 @@ class FlatGroup:
         self.params.append(p)
         self.opt_group.append(opt_group)
 
-    def finalize(self, amp: bool, zero: bool):
+    def finalize(self, amp: bool, zero: bool, symmetric: bool = False):
         # 16-byte aligned slots so every parameter view can feed TMA / vector loads
         es = torch.empty((), dtype=self.dtype).element_size()
         unit = max(1, 16 // es)
@@ -82,9 +82,17 @@ class FlatGroup:
             off += _align(p.numel(), unit)
         # whole buffer divisible into equal 16-byte aligned shards
         self.total = _align(max(off, 1), unit * self.nranks * 8)
-        self.flat_param = torch.zeros(self.total, dtype=self.dtype, device=self.device)
         gdtype = torch.float32 if amp else self.dtype
-        self.flat_grad = torch.zeros(self.total, dtype=gdtype, device=self.device)
+        self.symmetric = bool(symmetric and self.nranks > 1 and self.device.type == "cuda")
+        if self.symmetric:
+            # peers read / write these buffers directly (fused gradient path)
+            from .fused_reduce import symm_empty
+
+            self.flat_param = symm_empty(self.total, self.dtype, self.device).zero_()
+            self.flat_grad = symm_empty(self.total, gdtype, self.device).zero_()
+        else:
+            self.flat_param = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+            self.flat_grad = torch.zeros(self.total, dtype=gdtype, device=self.device)
         seg = self.total // self.nranks
         self.shard = (seg * self.my_index, seg * (self.my_index + 1)) if zero else (0, self.total)
         for p, o, n in zip(self.params, self.offsets, self.numels):
@@ -124,7 +132,8 @@ class ParamStorage:
 
     # ---------------------------------------------------------------- deploy
     def deploy(self, named_params: Dict[str, torch.nn.Parameter], owner_ranks: Dict[str, Sequence[int]],
-               opt_group_of: Dict[int, int], device: torch.device, global_order: Dict[str, int]):
+               opt_group_of: Dict[int, int], device: torch.device, global_order: Dict[str, int],
+               symmetric: bool = False):
         """``named_params``: parameters used on this rank (fqn -> Parameter, tied names deduplicated);
         ``owner_ranks``: fqn -> ranks of every stage using it (for ALL parameters of the model, so that every
         rank can create the same communicators in the same order)."""
@@ -147,7 +156,7 @@ class ParamStorage:
         # deterministic group order on every rank: smaller rank sets first
         self.groups = [keyed[k] for k in sorted(keyed, key=lambda k: (len(k[0]), k[0], str(k[1])))]
         for g in self.groups:
-            g.finalize(self.amp and g.dtype in (torch.float16, torch.bfloat16), self.zero)
+            g.finalize(self.amp and g.dtype in (torch.float16, torch.bfloat16), self.zero, symmetric)
             for i, n in enumerate(g.names):
                 self.by_name[n] = (g, i)
         if self.sync_on_init:

@@ -103,6 +103,7 @@ class PipelineRuntime:
 
     # ---------------------------------------------------------------- forward
     def forward(self, inputs: Sequence[torch.Tensor], grad_enabled: bool = True):
+        comm.check_peers()
         P = self.P
         by_name = dict(zip(self.user_inputs, inputs))
         # cumulative local row offsets of this rank's share of each micro-batch
@@ -209,6 +210,7 @@ class PipelineRuntime:
 
     # ---------------------------------------------------------------- backward
     def backward(self, out_grads: Sequence[Optional[torch.Tensor]]):
+        comm.check_peers()
         P = self.P
         offs, _ = self._fwd_state
         gmap = dict(zip(self.user_outputs, out_grads))

@@ -53,6 +53,12 @@ def set_dropout(gm: fx.GraphModule, enabled: bool) -> None:
             a = list(n.args)
             a[6] = bool(enabled)
             n.args = tuple(a)
+        elif n.target is RF.qkv_attention:
+            a = list(n.args)
+            if "orig_p" not in n.meta:
+                n.meta["orig_p"] = a[8]
+            a[8] = n.meta["orig_p"] if enabled else 0.0
+            n.args = tuple(a)
         elif n.target is RF.sdpa or n.target is aten.scaled_dot_product_attention.default:
             a = list(n.args)
             if "orig_p" not in n.meta:

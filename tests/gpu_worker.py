@@ -1,0 +1,53 @@
+"""One rank of a multi-GPU test (launched by tests/test_multi_gpu.py): tiny BERT, bf16 master-weight
+training with ZeRO; writes the final parameters of rank 0 to a file so that two runs can be compared."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+import rannc_b200 as pyrannc  # noqa: E402
+from rannc_b200.models.bert import BertConfig, BertForPreTraining, synthetic_batch  # noqa: E402
+from rannc_b200.ops import _lib  # noqa: E402
+from rannc_b200.ops import functional as RF  # noqa: E402
+
+
+def main():
+    case = json.loads(sys.argv[1])
+    rank, world = pyrannc.get_rank(), pyrannc.get_world_size()
+    torch.manual_seed(0)
+    RF.manual_seed(5)
+    cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
+                          num_hidden_layers=case.get("layers", 2))
+    model = BertForPreTraining(cfg)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=True, enable_zero=case.get("zero", True))
+    B = case.get("batch", 16)
+    lb = B // world
+    dev = pyrannc._comm.device()
+    losses = []
+    for it in range(case.get("iters", 3)):
+        full = synthetic_batch(cfg, B, 128, seed=it)
+        local = tuple(t[rank * lb:(rank + 1) * lb].to(dev) for t in full)
+        loss = wrapped(*local)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(float(loss))
+    torch.cuda.synchronize()
+    sd = wrapped.state_dict()
+    osd = opt.state_dict(from_global=True)
+    err = _lib.read_error()
+    info = {"fused": wrapped._fused_reducer is not None, "stages": len(wrapped._dep.fwd_graph_order),
+            "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}, "losses": losses, "err": err}
+    infos = pyrannc._comm.allgather_obj(info)
+    if rank == 0:
+        torch.save({"sd": sd, "opt": osd, "infos": infos}, case["out"])
+    pyrannc.barrier()
+    pyrannc.clear()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,361 @@
+"""Unit tests of the native core: msgpack codec, IR, value classification, batch arithmetic, redistribution
+plans, segment math, coarsening + stage search on synthetic profiles, deployment files, configuration, event
+trace, time counters and the watchdog.  CPU only."""
+import json
+import os
+import time
+
+import pytest
+
+from rannc_b200 import _core
+
+
+# ----------------------------------------------------------------------------- msgpack
+def test_msgpack_roundtrip_and_wire_format():
+    obj = {"a": [1, -2, 3.5, None, True, "x" * 40, b"\x00\x01"], "n": {"k": [2 ** 40, -2 ** 40, 2 ** 64 - 1]}}
+    data = _core.msgpack_pack(obj)
+    assert _core.msgpack_unpack(data) == obj
+    # fixed points of the wire format
+    assert _core.msgpack_pack(None) == b"\xc0"
+    assert _core.msgpack_pack(True) == b"\xc3"
+    assert _core.msgpack_pack(5) == b"\x05"
+    assert _core.msgpack_pack(-1) == b"\xff"
+    assert _core.msgpack_pack(300) == b"\xcd\x01\x2c"
+    assert _core.msgpack_pack("ab") == b"\xa2ab"
+    assert _core.msgpack_pack([1, 2]) == b"\x92\x01\x02"
+    assert _core.msgpack_pack({"a": 1}) == b"\x81\xa1a\x01"
+    assert _core.msgpack_pack(2 ** 64 - 1) == b"\xcf" + b"\xff" * 8  # size_t(-1): default list_size
+
+
+# ----------------------------------------------------------------------------- IR
+def _t(dims, elem=None, rg=False):
+    return _core.IRType.tensor(elem or _core.IRTensorElemType.FLOAT, dims, rg)
+
+
+def make_mlp_graph(layers=4, hidden=16, batch=8, with_loss=True):
+    g = _core.IRGraph()
+    g.name = "mlp"
+    g.batch_size = batch
+    g.add_input(_core.IRValue("x", _t([batch, hidden])))
+    if with_loss:
+        g.add_input(_core.IRValue("y", _t([batch], _core.IRTensorElemType.LONG)))
+    for i in range(layers):
+        g.add_input(_core.IRValue(f"w{i}", _t([hidden, hidden], rg=True), True))
+        g.add_input(_core.IRValue(f"b{i}", _t([hidden], rg=True), True))
+    prev = "x"
+    for i in range(layers):
+        g.add_value(_core.IRValue(f"h{i}", _t([batch, hidden])))
+        g.add_node(_core.IRNode("aten::linear", [prev, f"w{i}", f"b{i}"], [f"h{i}"], f"lin{i}"))
+        g.add_value(_core.IRValue(f"a{i}", _t([batch, hidden])))
+        g.add_node(_core.IRNode("aten::relu", [f"h{i}"], [f"a{i}"], f"relu{i}"))
+        prev = f"a{i}"
+    if with_loss:
+        g.add_value(_core.IRValue("loss", _t([])))
+        g.add_node(_core.IRNode("aten::cross_entropy_loss", [prev, "y"], ["loss"], "ce"))
+        g.add_output("loss")
+    else:
+        g.add_output(prev)
+    g.check()
+    return _core.guess_value_types(g)
+
+
+def test_ir_classification_and_serialisation():
+    g = make_mlp_graph()
+    vals = g.values
+    assert vals["x"].is_batch and not vals["x"].is_param
+    assert vals["w0"].is_param and not vals["w0"].is_batch
+    assert vals["h2"].is_batch and vals["h2"].batch_size == 8
+    assert vals["loss"].is_loss and not vals["loss"].is_batch
+    nodes = {n.id: n for n in g.nodes}
+    assert nodes["lin0"].is_batch and not nodes["lin0"].is_criterion
+    assert nodes["ce"].is_criterion
+    g2 = _core.IRGraph.loads(g.dumps())
+    assert str(g2) == str(g)
+    # positional layout: name, nodes, values, input_names, output_names, is_replicable, batch_size
+    raw = _core.msgpack_unpack(g.dumps())
+    assert raw[0] == "mlp" and raw[5] is True and raw[6] == 8
+    node0 = raw[1][0]
+    assert node0[0] == "aten::linear" and node0[1] == ["x", "w0", "b0"] and node0[3] == "lin0"
+    v = raw[2]["w0"]
+    assert v[0] == "w0" and v[2] is True  # name, type, is_param
+    assert v[1][0] == 1 and v[1][2] == [16, 16] and v[1][3] == 3 and v[1][7] == 2 ** 64 - 1  # TENSOR, dims, FLOAT
+    assert g.param_size_in_byte() == 4 * (16 * 16 + 16) * 4
+
+
+def test_scale_graph_unused_and_shared():
+    g = make_mlp_graph(batch=8)
+    s = _core.scale_graph(g, 2)
+    assert s.batch_size == 2 and s.value("h1").type.tensor_dim == [2, 16] and s.value("w1").type.tensor_dim == [16, 16]
+    g.add_input(_core.IRValue("dangling", _t([3]), True))
+    assert "dangling" in _core.find_unused_values(g)
+    r = _core.remove_unused_nodes(g)
+    assert "dangling" not in r.input_names and len(r.nodes) == len(g.nodes)
+    g3 = _core.IRGraph()
+    g3.batch_size = 4
+    g3.add_input(_core.IRValue("x", _t([4, 2])))
+    g3.add_value(_core.IRValue("a", _t([4, 2])))
+    g3.add_value(_core.IRValue("b", _t([4, 2])))
+    g3.add_node(_core.IRNode("aten::relu", ["x"], ["a"], "n0"))
+    g3.add_node(_core.IRNode("aten::add", ["x", "a"], ["b"], "n1"))
+    g3.add_output("b")
+    assert _core.shared_inputs(g3) == ["x"]
+    # inputs + outputs + input grads + 2 x shared clones
+    assert g3.comm_buf_size() == 32 + 32 + 32 + 64
+
+
+# ----------------------------------------------------------------------------- batch arithmetic
+def test_batch_size_calculator_rotation():
+    c = _core.BatchSizeCalculator(3, 10)  # micro-batches of 4, 3, 3
+    assert [c.split_size(i) for i in range(3)] == [4, 3, 3]
+    # 4 rows over 3 ranks: the extra row goes to rank 0 for split 0
+    assert [c.local_split_size(r, 3, 0) for r in range(3)] == [2, 1, 1]
+    # split 1 (3 rows, previous total 4 -> offset 1): equal
+    assert [c.local_split_size(r, 3, 1) for r in range(3)] == [1, 1, 1]
+    c2 = _core.BatchSizeCalculator(2, 10)  # 5 + 5 over 2 ranks: the extra row alternates
+    assert [c2.local_split_size(r, 2, 0) for r in range(2)] == [3, 2]
+    assert [c2.local_split_size(r, 2, 1) for r in range(2)] == [2, 3]
+    assert sum(c2.local_batch_size(r, 2) for r in range(2)) == 10
+    assert c2.local_dims(10, 2, 0) == [6, 4]  # first dim is 2 x the split size
+
+
+@pytest.mark.parametrize("src,dst,rows", [([0, 1], [2, 3], 8), ([0, 1, 2, 3], [1, 2], 12), ([0], [0, 1, 2], 7),
+                                          ([0, 1, 2], [3], 9)])
+def test_redist_args_conserve_rows(src, dst, rows):
+    world = 4
+    args = [_core.get_redist_args(r, world, rows, src, dst, 0, 1, rows) for r in range(world)]
+    for a in range(world):
+        for b in range(world):
+            assert args[a].sendcounts[b] == args[b].recvcounts[a]
+    assert sum(sum(a.sendcounts) for a in args) == rows
+    # every destination rank receives one contiguous, gap-free range
+    for r in dst:
+        got = sorted((args[r].rdispls[s], args[r].recvcounts[s]) for s in range(world) if args[r].recvcounts[s])
+        pos = 0
+        for d, c in got:
+            assert d == pos
+            pos += c
+
+
+def test_segment_math():
+    # padded to 16 B x ranks: fp16 -> 8 elements x 4 ranks
+    assert _core.aligned_numel(100, 2, 4) == 128
+    assert [_core.segment_range(100, 2, 4, i) for i in range(4)] == [(0, 32), (32, 64), (64, 96), (96, 100)]
+    # short / empty trailing segments
+    assert [_core.segment_range(10, 4, 4, i) for i in range(4)] == [(0, 4), (4, 8), (8, 10), (10, 10)]
+
+
+# ----------------------------------------------------------------------------- partitioner
+def _profiles(g, fwd=100.0, bwd=200.0, act=1 << 20):
+    return {n.id: _core.NodeProfile(fwd, bwd, act, 0, True) for n in g.nodes}
+
+
+def _conf(dev, batch, mem=0):
+    c = _core.PartitioningConf()
+    c.dev_num, c.batch_size, c.dev_mem = dev, batch, mem
+    return c
+
+
+def test_small_model_is_pure_data_parallel():
+    g = make_mlp_graph(layers=10, hidden=512, batch=128, with_loss=False)
+    np_ = _profiles(g, act=128 * 512 * 4)
+    conf = _conf(2, 128, 38 * 1024 ** 3)
+    pm = _core.ProfileModel(g, np_, conf.link)
+    ml = _core.ml_partition(pm, conf)
+    assert 1 <= len(ml.nodes) <= 32
+    sol, est, _ = _core.dp_staging(pm, ml, conf)
+    assert len(sol.graphs) == 1 and sol.dev_nums == [2] and sol.pipeline_num == 1
+
+
+def test_large_model_is_split_into_stages():
+    # 100 x Linear(5000): 2.5 G parameters, 10 GB in fp32 -> does not fit one 40 GB device with its optimizer
+    # state and gradients (10 + 10 + 20 GB), so the search needs at least two stages
+    g = make_mlp_graph(layers=100, hidden=5000, batch=512, with_loss=False)
+    np_ = _profiles(g, fwd=300, bwd=600, act=512 * 5000 * 4)
+    conf = _conf(8, 512, 38255689728)
+    pm = _core.ProfileModel(g, np_, conf.link)
+    ml = _core.ml_partition(pm, conf)
+    sol, est, _ = _core.dp_staging(pm, ml, conf)
+    assert len(sol.graphs) >= 2
+    assert sum(sol.dev_nums) == 8
+    assert all(e.total_mem < conf.dev_mem for e in est)
+    # stages cover the whole model exactly once
+    owned = [n.id for sg in sol.graphs for n in sg.nodes if n.is_batch]
+    assert sorted(owned) == sorted(n.id for n in g.nodes if n.is_batch)
+    dep = _core.create_deployment(g, sol, 8, True, "d")
+    assert _core.verify_deployment(dep) == ""
+    # ranks are used exactly once
+    used = sorted(r for v in dep.allocation.values() for r in v)
+    assert used == list(range(8))
+
+
+def test_nothing_fits_raises():
+    g = make_mlp_graph(layers=4, hidden=4096, batch=8, with_loss=False)
+    conf = _conf(1, 8, 1 << 20)
+    pm = _core.ProfileModel(g, _profiles(g), conf.link)
+    ml = _core.ml_partition(pm, conf)
+    with pytest.raises(RuntimeError):
+        _core.dp_staging(pm, ml, conf)
+
+
+def test_forced_stage_and_pipeline_counts_and_dry_run():
+    g = make_mlp_graph(layers=8, batch=16)
+    conf = _conf(4, 16)
+    conf.cfg_partition_num, conf.cfg_pipeline_num = 2, 4
+    np_ = _profiles(g)
+    pm = _core.ProfileModel(g, np_, conf.link)
+    ml = _core.ml_partition(pm, conf)
+    sol, est, node_json = _core.dp_staging(pm, ml, conf)
+    assert len(sol.graphs) == 2 and sol.pipeline_num == 4 and sum(sol.dev_nums) == 4
+    assert "nodes" in json.loads(node_json)
+    # the dumped cache replays the search without profiles from a device
+    cache = _core.dump_dp_cache(ml, g, np_, conf)
+    sol2 = _core.run_dp_dry(cache)
+    assert [sg.name for sg in sol2.graphs] == [sg.name for sg in sol.graphs] and sol2.dev_nums == sol.dev_nums
+    s3 = _core.AllocSolution.loads(sol.dumps())
+    assert s3.pipeline_num == 4 and s3.boundaries == sol.boundaries
+
+
+def test_subgraph_cut_replicates_non_batch_nodes():
+    g = _core.IRGraph()
+    g.batch_size = 4
+    g.add_input(_core.IRValue("x", _t([4, 8])))
+    g.add_input(_core.IRValue("w", _t([8, 8], rg=True), True))
+    for name, dims in [("wt", [8, 8]), ("h", [4, 8]), ("o", [4, 8])]:
+        g.add_value(_core.IRValue(name, _t(dims)))
+    g.add_node(_core.IRNode("aten::t", ["w"], ["wt"], "t"))           # parameter-only computation
+    g.add_node(_core.IRNode("aten::matmul", ["x", "wt"], ["h"], "m1"))
+    g.add_node(_core.IRNode("aten::matmul", ["h", "wt"], ["o"], "m2"))
+    g.add_output("o")
+    g = _core.guess_value_types(g)
+    assert not {n.id: n for n in g.nodes}["t"].is_batch
+    parts = _core.create_subgraphs(g, [-1, 0, 1], 2, "P_")
+    for p in parts:
+        assert "t" in [n.id for n in p.nodes] and "w" in p.input_names  # copied into both parts
+    assert parts[0].output_names == ["h"] and "h" in parts[1].input_names and parts[1].output_names == ["o"]
+    merged = _core.merge_subgraphs(g, parts, 0, 1, "M")
+    assert merged.output_names == ["o"] and [n.id for n in merged.nodes] == ["t", "m1", "m2"]
+
+
+def test_deployment_file_roundtrip_and_routes():
+    g = make_mlp_graph(layers=6, batch=8)
+    conf = _conf(2, 8)
+    conf.cfg_partition_num = 2
+    pm = _core.ProfileModel(g, _profiles(g), conf.link)
+    sol, _, _ = _core.dp_staging(pm, _core.ml_partition(pm, conf), conf)
+    dep = _core.create_deployment(g, sol, 2, True, "dep1")
+    assert _core.verify_deployment(dep) == ""
+    data = _core.save_deployment(dep, 2, 12345)
+    dep2, world, mem = _core.load_deployment(data)
+    assert (world, mem) == (2, 12345) and dep2.fwd_graph_order == dep.fwd_graph_order
+    assert dep2.allocation == dep.allocation and dep2.pipeline_num == dep.pipeline_num
+    # DeploymentState = [deployment, world_size, dev_mem]; Deployment has 17 positional fields
+    raw = _core.msgpack_unpack(data)
+    assert len(raw) == 3 and len(raw[0]) == 17 and raw[0][0] == "dep1"
+    # labels enter at the last stage from the caller, activations cross between the stages, the loss leaves
+    assert {r.value_name for r in dep.fwd_in_routes} == {"x", "y"}
+    assert len(dep.fwd_routes) == 1 and dep.fwd_routes[0].type == _core.RouteType.REDIST
+    assert dep.fwd_out_routes[0].type == _core.RouteType.WEIGHTED_REDUCE
+    assert len(dep.bwd_routes) == 1 and dep.bwd_in_routes[0].type == _core.RouteType.BROADCAST
+    # a broken deployment is reported
+    dep.fwd_routes = []
+    assert "no forward route" in _core.verify_deployment(dep)
+
+
+def test_allocation_strategies():
+    order = ["a", "b"]
+    flat = _core.search_allocation_flat(order, {"a": 2, "b": 2}, 4)
+    assert flat == {"a": [0, 2], "b": [1, 3]}  # each pipeline replica on neighbouring devices
+    simple = _core.search_allocation_simple(order, {"a": 1, "b": 3}, 4)
+    assert simple == {"b": [0, 1, 2], "a": [3]}
+    assert _core.tag_of_ranks([3, 1]) == _core.tag_of_ranks([1, 3, 3]) and _core.tag_of_ranks([0]) < 30000
+
+
+def test_cost_model():
+    link = _core.LinkModel()
+    assert _core.calc_comm_time(link, 0) == 0
+    assert abs(_core.calc_comm_time(link, 770_000_000) - (link.latency_us + 1000.0)) < 1e-6
+    # bus-bandwidth convention: 2 (n-1)/n x bytes / busbw
+    assert abs(_core.calc_allreduce_time(link, 725_000_000, 8) - (link.latency_us + 1750.0)) < 1e-6
+    assert _core.calc_allreduce_time(link, 1 << 20, 1) == 0
+    g = make_mlp_graph(layers=2, hidden=64, batch=8, with_loss=False)
+    conf = _conf(1, 8)
+    params = g.param_size_in_byte()
+    assert _core.get_opt_mem_size(g, conf, 1) == params + 2 * params  # gradient + 2 x state
+    conf.enable_zero = True
+    assert _core.get_opt_mem_size(g, conf, 4) == params + 2 * params // 4
+
+
+def test_profile_db_roundtrip():
+    db = _core.ProfileDB()
+    g = make_mlp_graph(layers=2)
+    p = _core.GraphProfile()
+    p.name, p.fwd_time, p.bwd_time, p.max_allocated_mem = "g", 11, 22, 33
+    db.add({"g": g}, 8, 1, False, {"g": p})
+    db2 = _core.ProfileDB()
+    db2.loads(db.dumps())
+    got = db2.get({"g": g}, 8, 1, False)
+    assert got["g"].fwd_time == 11 and got["g"].bwd_time == 22
+    assert db2.get({"g": g}, 4, 1, False) is None
+    # GraphProfile has 14 positional fields, working_mem / activation_size before checkpointing
+    raw = _core.msgpack_unpack(p.dumps())
+    assert len(raw) == 14 and raw[0] == "g" and raw[1] == 11 and raw[4] == 22 and raw[13] is False
+
+
+# ----------------------------------------------------------------------------- config / logging / trace
+def test_config_defaults_env_and_toml(tmp_path, monkeypatch):
+    monkeypatch.delenv("RANNC_CONF_DIR", raising=False)
+    _core.config_reload()
+    assert _core.config_get("max_pipeline") == 32 and _core.config_get("min_partition_num") == 5
+    assert _core.config_get("decomposer") == "ml_part" and abs(_core.config_get("mem_margin") - 0.1) < 1e-9
+    assert _core.config_get("deployment_file") == "/tmp/rannc_deployment.bin"
+    assert _core.config_get("save_deployment") is False
+    (tmp_path / "rannc_conf.toml").write_text('max_pipeline = 8  # comment\ndecomposer = "fair_weight"\nbogus = 1\n')
+    monkeypatch.setenv("RANNC_CONF_DIR", str(tmp_path))
+    monkeypatch.setenv("RANNC_MAX_PIPELINE", "4")  # the environment wins over the file
+    _core.config_reload()
+    assert _core.config_get("max_pipeline") == 4 and _core.config_get("decomposer") == "fair_weight"
+    assert any("bogus" in w for w in _core.config_warnings())
+    monkeypatch.delenv("RANNC_CONF_DIR")
+    monkeypatch.delenv("RANNC_MAX_PIPELINE")
+    _core.config_reload()
+    assert len(_core.config_items()) >= 62
+    with pytest.raises(RuntimeError):
+        _core.config_get("no_such_item")
+
+
+def test_event_trace_and_time_counter():
+    _core.trace_clear()
+    _core.trace_enable(True)
+    _core.trace_begin(_core.func_key("forward", "g0", 1, False))
+    _core.trace_end(_core.func_key("forward", "g0", 1, False))
+    _core.trace_enable(False)
+    _core.trace_begin("ignored")
+    assert _core.trace_size() == 2
+    doc = json.loads(_core.trace_merge([_core.trace_dump_local(0), _core.trace_dump_local(1)]))
+    ev = doc["traceEvents"]
+    assert len(ev) == 4 and {e["ph"] for e in ev} == {"B", "E"} and {e["pid"] for e in ev} == {0, 1}
+    assert "graph=g0" in ev[0]["name"] and "split=1" in ev[0]["name"]
+    _core.trace_clear()
+    tc = _core.TimeCounter(True)
+    tc.start("a")
+    time.sleep(0.01)
+    tc.stop("a")
+    assert tc.count("a") == 1 and tc.total_us("a") >= 9000 and "a:" in tc.summary()
+
+
+def test_watchdog_detects_missing_peer(tmp_path):
+    """Failure detection on the host: the peer's heartbeat file disappears; no GPU is involved."""
+    d = str(tmp_path)
+    failed = []
+    peer = _core.Watchdog()
+    peer.start(d, 1, 2, 0.05, 5.0, None)
+    wd = _core.Watchdog()
+    wd.start(d, 0, 2, 0.05, 5.0, lambda r: failed.append(r))
+    time.sleep(0.3)
+    assert wd.running() and not failed and os.path.exists(_core.Watchdog.lock_path(d, 1))
+    peer.stop(True)  # a failing rank removes its own file so that the others notice
+    deadline = time.time() + 5
+    while not failed and time.time() < deadline:
+        time.sleep(0.05)
+    assert failed == [1] and wd.failed_peer() == 1 and not wd.running()
+    wd.stop(True)

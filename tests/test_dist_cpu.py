@@ -81,3 +81,22 @@ def test_adam_dp2():
 def test_uneven_stage_replicas():
     # 3 ranks cannot be split evenly: stage counts / replica counts come from the search
     run_case(3, {"model": "deep", "batch": 12}, {"RANNC_LIMIT_DEV_NUM_POT": "false"})
+
+
+def test_peer_failure_is_detected_on_the_host(tmp_path):
+    """Failure detection without any device fault: a rank leaves between steps; the survivor's watchdog sees
+    the missing heartbeat file and the next forward raises CommError before anything is launched."""
+    port = _free_port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ)
+        env.update({"RANK": str(r), "WORLD_SIZE": "2", "LOCAL_RANK": str(r), "MASTER_ADDR": "127.0.0.1",
+                    "MASTER_PORT": str(port), "RANNC_FORCE_CPU": "1", "OMP_NUM_THREADS": "1",
+                    "RANNC_LOG_LEVEL": "warning", "RANNC_RUN_WATCHDOG": "true",
+                    "RANNC_WATCHDOG_LOCKFILE_DIR": str(tmp_path), "RANNC_WATCHDOG_PERIOD_S": "0.1",
+                    "RANNC_WATCHDOG_STALE_S": "5"})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "failure_worker.py")], env=env,
+                                      cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    assert "LEFT" in outs[1], outs[1][-2000:]
+    assert "DETECTED" in outs[0] and "NOT DETECTED" not in outs[0], outs[0][-2000:]

@@ -1,0 +1,87 @@
+"""Multi-GPU paths (need >= 2 devices): the fused reduce-scatter + Adam + all-gather kernel against the NCCL
+collectives path, and a pipeline split across GPUs against pure data parallelism."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run(world, case, extra_env=None, timeout=600):
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ)
+        env.update({"RANK": str(r), "WORLD_SIZE": str(world), "LOCAL_RANK": str(r), "MASTER_ADDR": "127.0.0.1",
+                    "MASTER_PORT": str(port), "RANNC_LOG_LEVEL": "warning"})
+        env.update(extra_env or {})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "gpu_worker.py"),
+                                       json.dumps(case)], env=env, cwd=ROOT, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append(o)
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o[-4000:]
+    return torch.load(case["out"], weights_only=False)
+
+
+def _compare(a, b, tol):
+    for k in a["sd"]:
+        x, y = a["sd"][k].float(), b["sd"][k].float()
+        assert (x - y).abs().max().item() <= tol * (y.abs().max().item() + 1e-3), k
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_reduce_matches_nccl_path(tmp_path):
+    fused = _run(2, {"out": str(tmp_path / "fused.pt")})
+    plain = _run(2, {"out": str(tmp_path / "plain.pt")}, {"RANNC_FUSED_GRAD_ALLREDUCE": "false"})
+    assert all(i["fused"] for i in fused["infos"]) and not any(i["fused"] for i in plain["infos"])
+    assert all(i["err"] == 0 for i in fused["infos"])
+    for lf, lp in zip(fused["infos"][0]["losses"], plain["infos"][0]["losses"]):
+        assert abs(lf - lp) < 2e-2 * abs(lp)
+    _compare(fused, plain, 2e-2)
+    # optimizer state gathered to the global layout in both
+    assert set(fused["opt"]["state"].keys()) == set(plain["opt"]["state"].keys())
+    k0 = sorted(fused["opt"]["state"].keys())[0]
+    assert fused["opt"]["state"][k0]["exp_avg"].shape == plain["opt"]["state"][k0]["exp_avg"].shape
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_reduce_without_multimem(tmp_path):
+    a = _run(2, {"out": str(tmp_path / "a.pt")}, {"RANNC_USE_MULTIMEM": "0"})
+    b = _run(2, {"out": str(tmp_path / "b.pt")}, {"RANNC_FUSED_GRAD_ALLREDUCE": "false"})
+    assert all(i["err"] == 0 for i in a["infos"])
+    _compare(a, b, 2e-2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pipeline_over_two_gpus_matches_data_parallel(tmp_path):
+    pp = _run(2, {"out": str(tmp_path / "pp.pt"), "zero": False}, {"RANNC_PARTITION_NUM": "2"})
+    dp = _run(2, {"out": str(tmp_path / "dp.pt"), "zero": False})
+    assert pp["infos"][0]["stages"] == 2 and dp["infos"][0]["stages"] == 1
+    _compare(pp, dp, 3e-2)
