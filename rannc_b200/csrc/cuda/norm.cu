@@ -341,3 +341,50 @@ extern "C" int rb_ln_bwd(const void* dy, const void* z, const void* gamma, const
                                                                  accumulate);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of rb_ln_bwd (declared and documented in norm_noalloc.h)
+// ---------------------------------------------------------------------------
+#include "norm_noalloc.h"
+
+// Scratch for the per-CTA partial sums of dgamma / dbeta.  In host code this name is only a
+// stand-in for the symbol: kernels must be given the address cudaGetSymbolAddress returns.
+static __device__ __align__(256) float g_ln_noalloc_scratch[RB_LN_NOALLOC_MAX_FLOATS];
+
+static float* ln_noalloc_scratch_ptr() {
+    static float* ptrs[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) {
+        float* p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_noalloc_scratch) != cudaSuccess) return nullptr;
+        ptrs[dev] = p;
+    }
+    return ptrs[dev];
+}
+
+extern "C" const char* rb_ln_bwd_noalloc_strerror(int code) {
+    switch (code) {
+        case RB_LN_NOALLOC_OK: return "ok";
+        case RB_LN_NOALLOC_LAUNCH_FAILED: return "kernel launch failed";
+        case RB_LN_NOALLOC_BAD_WIDTH: return "unsupported row width H (supported: 256, 512, 768, 1024, 1536, 2048, 3072, 4096)";
+        case RB_LN_NOALLOC_NO_SYMBOL: return "could not resolve the device address of the built-in scratch array";
+        case RB_LN_NOALLOC_TOO_LARGE: return "rows x H needs more scratch than the built-in array holds (RB_LN_NOALLOC_MAX_FLOATS)";
+        default: return "unknown error";
+    }
+}
+
+extern "C" int rb_ln_bwd_noalloc(const void* dy, const void* z, const void* gamma, const float* mean,
+                                 const float* rstd, void* dz, void* dx, float* dgamma, float* dbeta, int rows,
+                                 int H, float p, uint64_t seed, uint64_t offset, int accumulate, int dtype,
+                                 void* stream) {
+    if (rows <= 0) return RB_LN_NOALLOC_OK;
+    if (!rb_ln_supported(H)) return RB_LN_NOALLOC_BAD_WIDTH;
+    const long long need = static_cast<long long>(rb_ln_bwd_grid(rows)) * 2 * H;
+    if (need > RB_LN_NOALLOC_MAX_FLOATS) return RB_LN_NOALLOC_TOO_LARGE;
+    float* scratch = ln_noalloc_scratch_ptr();
+    if (!scratch) return RB_LN_NOALLOC_NO_SYMBOL;
+    const int rc = rb_ln_bwd(dy, z, gamma, mean, rstd, dz, dx, dgamma, dbeta, scratch, rows, H, p, seed, offset,
+                             accumulate, dtype, stream);
+    return rc == 0 ? RB_LN_NOALLOC_OK : (rc == -2 ? RB_LN_NOALLOC_BAD_WIDTH : RB_LN_NOALLOC_LAUNCH_FAILED);
+}
