@@ -43,6 +43,13 @@ struct GemmKernelParams {
     int a_major, b_major;
     int num_m_blocks, num_n_blocks, num_tiles, num_kb;
     int base_tiles, split_k, kb_per_split;  // split-K: num_tiles = base_tiles * split_k
+    int rs_nranks, rs_cols;                 // reduce-scatter epilogue: column block j -> rs_peer[j]
+    void* rs_peer[8];
+    // all-gather prologue: B is assembled in local memory from column shards held by the ranks of a group
+    int ag_nranks, ag_my_idx, ag_rows, ag_cols;  // shard r = [ag_rows, ag_cols] at ag_src[r]
+    const void* ag_src[8];
+    void* ag_dst;                                // [ag_rows, ag_nranks * ag_cols] (the B operand)
+    unsigned int* ag_flags;                      // [8] counters, zero at launch: CTAs done copying shard r
     void* D;
     const void* bias;
     const void* residual;
@@ -175,12 +182,47 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             // ---------------- TMA producer ----------------
             int stage = 0;
             uint32_t phase = 0;
+            uint32_t ag_ready = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
                 int mb, nb, b, kb_begin, kb_end;
                 tile_coords(p, tile, mb, nb, b, kb_begin, kb_end);
                 const int m0 = mb * BM, n0 = nb * BN;
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
+                    int kb = kbi;
+                    if (p.ag_nranks > 1) {
+                        // start with the k-range (or column block) this rank holds itself; wait until every
+                        // CTA has copied the shard this step reads into the local B buffer
+                        int shard;
+                        if (p.b_major == 0) {
+                            kb = kbi + p.ag_my_idx * (p.ag_cols / BK);
+                            if (kb >= p.num_kb) kb -= p.num_kb;
+                            shard = (kb * BK) / p.ag_cols;
+                        } else {
+                            shard = n0 / p.ag_cols;
+                        }
+                        if (!(ag_ready & (1u << shard))) {
+                            bool got = false;
+                            const uint64_t t0 = globaltimer_ns();
+                            for (uint32_t it = 0; it < RB_MBAR_SPIN_LIMIT && !*abort_flag; ++it) {
+                                unsigned int v;
+                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ag_flags + shard) : "memory");
+                                if (v >= gridDim.x) {
+                                    got = true;
+                                    break;
+                                }
+                                if ((it & 0xff) == 0xff && globaltimer_ns() - t0 > RB_WAIT_LIMIT_NS) break;
+                                __nanosleep(64);
+                            }
+                            if (!got) {
+                                *abort_flag = 1;
+                                ok = false;
+                                break;
+                            }
+                            asm volatile("fence.proxy.async.global;" ::: "memory");
+                            ag_ready |= 1u << shard;
+                        }
+                    }
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         ok = false;
                         break;
@@ -259,6 +301,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
+        if (p.ag_nranks > 1) {
+            // all-gather prologue: the 128 epilogue threads of every CTA copy their share of each peer's
+            // shard into the local B buffer (plain 16-byte peer loads), own shard last in the rotation so
+            // remote traffic starts first; a counter per shard tells the TMA producers when it is whole
+            const int t = threadIdx.x - 64;
+            const int vec_per_row = p.ag_cols / 8;
+            const long long total = static_cast<long long>(p.ag_rows) * vec_per_row;
+            const long long dst_ld = static_cast<long long>(p.ag_nranks) * p.ag_cols;
+            for (int rr = 1; rr <= p.ag_nranks; ++rr) {
+                const int r = (p.ag_my_idx + rr) % p.ag_nranks;
+                const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[r]);
+                InT* dst = reinterpret_cast<InT*>(p.ag_dst) + static_cast<long long>(r) * p.ag_cols;
+                for (long long i = static_cast<long long>(blockIdx.x) * 128 + t; i < total;
+                     i += static_cast<long long>(gridDim.x) * 128 * 4) {
+                    uint4 v[4];
+                    long long idx[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        idx[u] = i + static_cast<long long>(u) * gridDim.x * 128;
+                        if (idx[u] < total) v[u] = src[idx[u]];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (idx[u] < total) {
+                            const long long row = idx[u] / vec_per_row, c = idx[u] - row * vec_per_row;
+                            *reinterpret_cast<uint4*>(dst + row * dst_ld + c * 8) = v[u];
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (t == 0) atomicAdd(p.ag_flags + r, 1u);
+            }
+        }
         const int q = warp & 3;  // TMEM lane quarter this warp may access
         const int row_in_tile = q * 32 + lane;
         const bool has_bias = p.flags & RB_GEMM_BIAS;
@@ -295,9 +372,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
                 if constexpr (std::is_same<OutT, float>::value) {
-                    if (p.split_k > 1) {
-                        // partial sums of a K slice: accumulate with vector reductions
+                    if (p.split_k > 1 || p.rs_nranks > 1) {
+                        // partial sums (a K slice, and/or one replica's share of a reduce-scatter):
+                        // accumulate with vector reductions.  With rs_nranks > 1 the output columns
+                        // are split in equal blocks and block j lives in rank j's buffer, so the
+                        // reduction goes to that peer's memory over NVLink.
                         float* dptr = reinterpret_cast<float*>(p.D) + row_off + col;
+                        if (p.rs_nranks > 1) {
+                            const int owner = col / p.rs_cols;
+                            dptr = reinterpret_cast<float*>(p.rs_peer[owner]) + row_off + (col - owner * p.rs_cols);
+                        }
                         if (full_chunk && out_al) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)
@@ -509,7 +593,28 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     p.num_n_blocks = (p.N + BN - 1) / BN;
     p.base_tiles = p.num_m_blocks * p.num_n_blocks * p.batch;
     p.num_kb = (p.K + BK - 1) / BK;
+    p.ag_nranks = a->ag_nranks > 1 ? a->ag_nranks : 0;
+    p.ag_my_idx = a->ag_my_idx;
+    p.ag_rows = a->ag_rows;
+    p.ag_cols = a->ag_cols;
+    p.ag_dst = const_cast<void*>(a->B);
+    p.ag_flags = static_cast<unsigned int*>(a->ag_flags);
+    for (int r = 0; r < 8; ++r) p.ag_src[r] = a->ag_nranks > 1 ? a->ag_src[r] : nullptr;
+    if (p.ag_nranks > 1) {
+        // shards are column blocks of the stored B matrix: [rows, ag_cols] each, ag_cols a multiple of the tile
+        const long long stored_cols = a->b_major == 0 ? a->K : a->N;
+        if (a->ag_nranks > 8 || a->batch != 1 || !a->ag_flags || a->ag_cols % 256 ||
+            static_cast<long long>(a->ag_cols) * a->ag_nranks != stored_cols || a->ldb != stored_cols)
+            return -6;
+        cudaMemsetAsync(a->ag_flags, 0, 8 * sizeof(unsigned int), stream);
+    }
     p.split_k = 1;
+    p.rs_nranks = a->rs_nranks > 1 ? a->rs_nranks : 0;
+    p.rs_cols = a->rs_nranks > 1 ? static_cast<int>(a->N / a->rs_nranks) : 0;
+    for (int r = 0; r < 8; ++r) p.rs_peer[r] = a->rs_nranks > 1 ? a->rs_peer[r] : nullptr;
+    if (p.rs_nranks > 1 && (a->out_dtype != 1 || a->flags != RB_GEMM_ACCUM || a->N % a->rs_nranks || p.rs_cols % 32 ||
+                            a->rs_nranks > 8 || a->batch != 1))
+        return -5;
     // Few output tiles and a long K (weight gradients): split K over CTAs and accumulate with
     // reductions.  Only for fp32 outputs that accumulate and have no other epilogue work.
     if (a->out_dtype == 1 && a->flags == RB_GEMM_ACCUM && p.base_tiles < num_sms() && p.num_kb >= 8) {

@@ -34,7 +34,16 @@ typedef struct RbGemmArgs {
     int32_t flags;
     int32_t max_ctas;   // 0 = one per SM
     float alpha;
-    int32_t pad_;
+    int32_t rs_nranks;  // > 1: reduce-scatter epilogue (fp32 output, RB_GEMM_ACCUM only): the N columns are split
+                        // in rs_nranks equal blocks (multiples of 32); block j is ADDED into rs_peer[j], a
+                        // [M, N / rs_nranks] fp32 buffer with leading dimension ldd in rank j's memory
+    void* rs_peer[8];
+    // all-gather prologue (ag_nranks > 1): B (stored [rows, ag_nranks * ag_cols], ldb = that width) is a local
+    // buffer the kernel fills itself from the column shards ag_src[r] ([ag_rows, ag_cols] each, in rank r's
+    // memory, own shard included) while the GEMM already consumes the shards that have arrived
+    int32_t ag_nranks, ag_my_idx, ag_rows, ag_cols;
+    void* ag_flags;        // 8 x uint32 of local device memory (cleared by the call)
+    const void* ag_src[8];
 } RbGemmArgs;
 
 // returns 0 on success, <0 on a host-side error (-2: operand not 16 B aligned)

@@ -56,12 +56,18 @@ __device__ __forceinline__ void multimem_st_b128(void* mc, uint4 v) {
                  : "memory");
 }
 
-// Waits until *flag >= expected.  Returns false when `max_polls` ran out.
+// Waits until *flag >= expected.  Returns false when `max_polls` ran out or after RB_PEER_WAIT_LIMIT_NS of
+// wall-clock time (peers may reach the kernel late, so this cap is longer than the one for on-chip waits).
+#ifndef RB_PEER_WAIT_LIMIT_NS
+#define RB_PEER_WAIT_LIMIT_NS 20000000000ull
+#endif
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t expected,
                                           unsigned long long max_polls) {
+    const uint64_t t0 = globaltimer_ns();
     for (unsigned long long i = 0; i < max_polls; ++i) {
         const uint32_t v = ld_acquire_sys(flag);
         if (static_cast<int32_t>(v - expected) >= 0) return true;
+        if ((i & 0xff) == 0xff && globaltimer_ns() - t0 > RB_PEER_WAIT_LIMIT_NS) return false;
         __nanosleep(100);
     }
     return false;
@@ -256,5 +262,38 @@ extern "C" int rb_wait_flag_probe(const void* flag, unsigned int expected, unsig
     if (!err) return -3;
     rb::wait_flag_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint32_t*>(flag), expected, max_polls, err);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+namespace rb {
+// Barrier among the ranks of a group through flags in symmetric memory: every rank stores `epoch`
+// into slot [row][my_idx] of every peer's flag block and waits for all slots of its own block.
+__global__ void peer_barrier_kernel(uint32_t* const* peer_flags_dev, uint32_t* f0, uint32_t* f1, uint32_t* f2,
+                                    uint32_t* f3, uint32_t* f4, uint32_t* f5, uint32_t* f6, uint32_t* f7, int nranks,
+                                    int my_idx, int row, uint32_t epoch, unsigned long long max_polls, int* err) {
+    uint32_t* flags[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
+    const int t = threadIdx.x;
+    if (t < nranks) {
+        __threadfence_system();
+        st_release_sys(flags[t] + row * RB_MAX_PEERS + my_idx, epoch);
+        if (!wait_flag(flags[my_idx] + row * RB_MAX_PEERS + t, epoch, max_polls)) atomicExch(err, ERR_PEER_TIMEOUT);
+    }
+}
+}  // namespace rb
+
+// Stream-ordered barrier over a rank set: work enqueued before it on every rank is complete (and visible
+// system-wide) on all ranks once it returns on this rank's stream.  peer_flags[r]: rank r's flag block
+// (uint32 [2][RB_MAX_PEERS], zero-initialised, symmetric memory); `row` selects one of its two rows.
+extern "C" int rb_peer_barrier(void* const* peer_flags, int nranks, int my_idx, int row, unsigned int epoch,
+                               unsigned long long max_polls, void* stream) {
+    using namespace rb;
+    if (nranks < 1 || nranks > RB_MAX_PEERS || row < 0 || row > 1) return -2;
+    int* err = error_word_ptr();
+    if (!err) return -3;
+    uint32_t* f[8];
+    for (int r = 0; r < 8; ++r) f[r] = r < nranks ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        nullptr, f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], nranks, my_idx, row, epoch,
+        max_polls ? max_polls : (1ull << 26), err);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -77,11 +77,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #ifndef RB_MBAR_SPIN_LIMIT
 #define RB_MBAR_SPIN_LIMIT (1u << 24)
 #endif
+// Wall-clock cap on any one wait (nanoseconds of %globaltimer): how long a try_wait may suspend is up to
+// the hardware, so the iteration limit alone does not bound the time.
+#ifndef RB_WAIT_LIMIT_NS
+#define RB_WAIT_LIMIT_NS 4000000000ull
+#endif
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag) {
+    uint64_t t0 = 0;
     for (uint32_t it = 0; it < RB_MBAR_SPIN_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 0xff) == 0xff && *abort_flag) return false;
+        if ((it & 0xff) == 0xff) {
+            if (*abort_flag) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > RB_WAIT_LIMIT_NS) break;
+        }
     }
     *abort_flag = 1;
     return false;

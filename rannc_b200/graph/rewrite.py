@@ -69,6 +69,38 @@ def drop_asserts(gm: fx.GraphModule) -> int:
     return k
 
 
+def after_effects(effects, value):
+    """Identity on ``value``; ``effects`` are the results of in-place updates that must run with it."""
+    return value
+
+
+def anchor_mutations(gm: fx.GraphModule) -> int:
+    """An in-place update whose result nothing reads (``num_batches_tracked.add_(1)`` of BatchNorm) would
+    belong to no stage, because stages are cut along data dependencies.  Each such node is tied to the next
+    node that produces a used tensor from the same module call: that node's result is routed through
+    ``after_effects(update, result)``, so the update travels with its consumer's stage."""
+    pending, k = [], 0
+    for n in list(gm.graph.nodes):
+        if n.op != "call_function":
+            continue
+        tgt = n.target
+        inplace = isinstance(tgt, torch._ops.OpOverload) and tgt._schema.name.endswith("_") and tgt._schema.is_mutable
+        if inplace and not n.users:
+            pending.append(n)
+            continue
+        val = n.meta.get("val")
+        if pending and n.users and isinstance(val, torch.Tensor) and val.is_floating_point():
+            users = list(n.users)
+            with gm.graph.inserting_after(n):
+                tie = gm.graph.call_function(after_effects, (tuple(pending), n))
+            tie.meta = dict(n.meta)
+            for u in users:
+                u.replace_input_with(n, tie)
+            k += len(pending)
+            pending = []
+    return k
+
+
 def _replace(gm, old: fx.Node, fn, args, kwargs=None):
     with gm.graph.inserting_before(old):
         new = gm.graph.call_function(fn, tuple(args), kwargs or {})
@@ -92,6 +124,7 @@ def fuse(gm: fx.GraphModule, training: bool = True) -> dict:
         stats[k] = stats.get(k, 0) + 1
 
     drop_asserts(gm)
+    anchor_mutations(gm)
     g = gm.graph
 
     # ---- q/k/v projections of one input + attention -> one operator

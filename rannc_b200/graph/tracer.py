@@ -193,6 +193,7 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
         from . import rewrite
 
         rewrite.drop_asserts(gm)
+        rewrite.anchor_mutations(gm)
         gm.graph.eliminate_dead_code()
         gm.recompile()
     batch = 0

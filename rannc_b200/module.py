@@ -249,6 +249,7 @@ class RaNNCModule:
             owner[n] = {0}
         self._used_param_names = [n for n in name_to_param if rank in owner[n]]
         self._used_buffer_names = [n for n in name_to_buffer if rank in buf_owner[n] or not buf_owner[n]]
+        self._buffer_root = {n: (min(r) if r else 0) for n, r in buf_owner.items()}
 
         # parameters sharded at construction are assembled on their owners only (collective, global order)
         for n, p in name_to_param.items():
@@ -464,7 +465,8 @@ class RaNNCModule:
                 continue
             v = b.detach().to(comm.device()).clone()
             if comm.get_world_size() > 1:
-                comm.bcast(v, 0)
+                # the stage that holds a buffer updates it (BatchNorm statistics); its first rank is the source
+                comm.bcast(v, self._buffer_root.get(n, 0))
             if keep:
                 out[n] = v.cpu()
         return out if keep else None

@@ -21,7 +21,10 @@ class _Args(ctypes.Structure):
         ("a_major", ctypes.c_int32), ("b_major", ctypes.c_int32),
         ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
         ("flags", ctypes.c_int32), ("max_ctas", ctypes.c_int32),
-        ("alpha", ctypes.c_float), ("pad_", ctypes.c_int32),
+        ("alpha", ctypes.c_float), ("rs_nranks", ctypes.c_int32),
+        ("rs_peer", ctypes.c_void_p * 8),
+        ("ag_nranks", ctypes.c_int32), ("ag_my_idx", ctypes.c_int32), ("ag_rows", ctypes.c_int32),
+        ("ag_cols", ctypes.c_int32), ("ag_flags", ctypes.c_void_p), ("ag_src", ctypes.c_void_p * 8),
     ]
 
 
@@ -63,7 +66,8 @@ def _mat(t: torch.Tensor):
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
          bias=None, residual=None, aux_in=None, aux_out=None, gelu: bool = False,
          dgelu: bool = False, out: torch.Tensor | None = None, accumulate: bool = False,
-         out_dtype: torch.dtype | None = None, alpha: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+         out_dtype: torch.dtype | None = None, alpha: float = 1.0, max_ctas: int = 0,
+         rs_peers=None, rs_ld: int = 0, gather=None) -> torch.Tensor:
     """``out = epilogue(alpha * op(a) @ op(b))``.
 
     ``a`` is stored ``[M, K]`` (``trans_a=False``) or ``[K, M]`` (``trans_a=True``).
@@ -107,6 +111,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         _lib.ptr(aux_in), _lib.ptr(aux_out), M, N, K, batch, lda, ldb, ldd, sa, sb, sd,
         1 if trans_a else 0, 0 if trans_b else 1, _dt(a), 0 if odt == a.dtype else 1, flags,
         max_ctas, float(alpha), 0)
+    if rs_peers is not None and len(rs_peers) > 1:
+        # reduce-scatter epilogue: column block j of the product is added into rank j's buffer
+        args.rs_nranks = len(rs_peers)
+        for i, ptr in enumerate(rs_peers):
+            args.rs_peer[i] = int(ptr)
+        if rs_ld:
+            args.ldd = int(rs_ld)
+    if gather is not None:
+        args.ag_nranks = gather["nranks"]
+        args.ag_my_idx = gather["my_idx"]
+        args.ag_rows = gather["rows"]
+        args.ag_cols = gather["cols"]
+        args.ag_flags = gather["flags"]
+        for i, ptr in enumerate(gather["src"]):
+            args.ag_src[i] = int(ptr)
     rc = _lib.lib().rb_gemm(ctypes.byref(args), _lib.stream_ptr())
     _lib.check(rc, "rb_gemm")
     return out

@@ -90,6 +90,10 @@ def main():
             if not torch.allclose(sd[n].float(), p.detach().float(), rtol=tol * 10, atol=tol * 10):
                 ok = False
                 msgs.append(f"state_dict {n} differs")
+        for n, b in ref.named_buffers():
+            if n not in sd or not torch.allclose(sd[n].float(), b.float(), rtol=tol * 10, atol=tol * 10):
+                ok = False
+                msgs.append(f"state_dict buffer {n} differs or is missing")
         rsd = ropt.state_dict()
         for k, st in rsd["state"].items():
             for item, v in st.items():

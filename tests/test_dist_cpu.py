@@ -65,6 +65,16 @@ def test_pp2_dp2_pipeline2():
     assert res["ranks"][0]["stages"] == 2 and res["ranks"][0]["pipeline"] == 2
 
 
+def test_batchnorm_buffers_single_rank():
+    # running statistics and num_batches_tracked follow eager exactly when one replica sees the whole batch
+    run_case(1, {"model": "bn", "batch": 8})
+
+
+def test_batchnorm_buffers_two_stages():
+    res = run_case(2, {"model": "bn", "batch": 8}, {"RANNC_PARTITION_NUM": "2"})
+    assert res["ranks"][0]["stages"] == 2
+
+
 def test_pp_checkpointing():
     run_case(2, {"model": "loss", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2",
                                                 "RANNC_CHECKPOINTING": "true"})

@@ -113,7 +113,24 @@ class Deep(nn.Module):
         return x
 
 
-_MODELS = {"basic": Basic, "forkjoin": ForkJoin, "shared_input": SharedInput, "shared_param": SharedParam,
+class BNNet(nn.Module):
+    """BatchNorm buffers (running statistics) are non-gradient state that must live with their stage."""
+
+    def __init__(self):
+        super().__init__()
+        self.c1 = nn.Conv2d(1, 4, 3, padding=1)
+        self.bn1 = nn.BatchNorm2d(4)
+        self.c2 = nn.Conv2d(4, 4, 3, padding=1)
+        self.bn2 = nn.BatchNorm2d(4)
+        self.fc = nn.Linear(4, 3)
+
+    def forward(self, x):
+        x = F.relu(self.bn1(self.c1(x)))
+        x = F.relu(self.bn2(self.c2(x)))
+        return self.fc(x.mean((2, 3)))
+
+
+_MODELS = {"bn": BNNet, "basic": Basic, "forkjoin": ForkJoin, "shared_input": SharedInput, "shared_param": SharedParam,
            "loss": LossOut, "emb": Emb, "tied": TiedEmb, "layernorm": LayerNormNet, "deep": Deep}
 
 
@@ -122,6 +139,8 @@ def build(name):
 
 
 def inputs(name, B, g):
+    if name == "bn":
+        return (torch.randn(B, 1, 8, 8, generator=g),)
     if name == "basic":
         return (torch.randn(B, 1, 16, 16, generator=g),)
     if name == "loss":
