@@ -46,7 +46,7 @@ struct AttnBwdParams {
     void* dK;
     void* dV;
     long long dk_sb, dk_ss, dk_sh, dv_sb, dv_ss, dv_sh;
-    uint32_t thr16;
+    uint32_t thr32;   // keep an element when its 32-bit hash >= thr32 (0: no dropout)
     float inv_keep;
     uint32_t seed;
     int* err;
@@ -179,16 +179,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int key = key0 + r;
         const bool key_ok = key < p.S;
-        const float kbias = (p.key_bias && key_ok)
-                                ? p.key_bias[static_cast<long long>(b) * p.S + key] * 1.4426950408889634f
-                                : 0.f;
+        // -inf for keys past the end of the sequence: their probabilities come out as exp2(-inf) = 0
+        const float kbias =
+            key_ok ? (p.key_bias ? p.key_bias[static_cast<long long>(b) * p.S + key] * 1.4426950408889634f : 0.f)
+                   : -INFINITY;
+        const uint32_t key_hash = drop_key_hash(p.seed, key);
         const long long bh = static_cast<long long>(b) * p.H + h;
         const uint32_t sw = r & 7;
         const uint32_t row_off = half * (SQ_BYTES / 2) + (r >> 3) * 1024 + sw * 128;
         uint8_t* prow = sPt + row_off;
         uint8_t* drow = sdSt + row_off;
-        const uint32_t key_mix = static_cast<uint32_t>(key >> 1) * 0x9E3779B1u;
-        const bool key_odd = key & 1;
         bool ok = true;
 
         auto drain_dq = [&](int i) {
@@ -211,8 +211,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             const int st = i & 1;
             const int q0 = i * BQ;
             if (half == 0) {
+                // +inf for rows past the end of the sequence: their probabilities come out as exp2(-inf) = 0
                 const int q = q0 + r;
-                s_lse[st * 128 + r] = q < p.S ? p.lse[bh * p.S + q] * 1.4426950408889634f : 0.f;
+                s_lse[st * 128 + r] = q < p.S ? p.lse[bh * p.S + q] * 1.4426950408889634f : INFINITY;
                 s_delta[st * 128 + r] = q < p.S ? p.delta[bh * p.S + q] : 0.f;
                 s_rhash[st * 128 + r] = drop_row_hash(p.seed, b, h, q, p.H, p.S);
             }
@@ -224,7 +225,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             tc_fence_after();
             // Pt / dSt of this thread's 64 columns, packed to 16 bits, held in registers: the whole
             // computation overlaps the tensor-core work of the previous step, whose operands still
-            // occupy the shared-memory tiles
+            // occupy the shared-memory tiles.  Pt carries the dropout mask without its 1 / (1 - p)
+            // factor (dV is scaled once at the end); dSt = P (mask dP / (1 - p) - delta).
             uint4 pk[2][4], dk4[2][4];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
@@ -239,26 +241,38 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    T* ea = reinterpret_cast<T*>(&pk[c][g]);
-                    T* ed = reinterpret_cast<T*>(&dk4[c][g]);
+                    float pd[8], ds[8];
 #pragma unroll
-                    for (int x = 0; x < 8; ++x) {
-                        const int ql = half * 64 + c * 32 + g * 8 + x;
-                        float pr = 0.f;
-                        if (key_ok && q0 + ql < p.S)
-                            pr = exp2f(__uint_as_float(sv[g * 8 + x]) * p.scale_log2 + kbias - s_lse[st * 128 + ql]);
-                        float dp = __uint_as_float(dv[g * 8 + x]);
-                        float pd = pr;
-                        if (p.thr16) {
-                            const uint32_t bits = hash32(s_rhash[st * 128 + ql] + key_mix);
-                            const uint32_t hb = key_odd ? (bits >> 16) : (bits & 0xffffu);
-                            const float keep = hb >= p.thr16 ? p.inv_keep : 0.f;
-                            pd = pr * keep;
-                            dp *= keep;
+                    for (int hq = 0; hq < 2; ++hq) {
+                        const int qb = st * 128 + half * 64 + c * 32 + g * 8 + hq * 4;
+                        const float4 ls4 = *reinterpret_cast<const float4*>(s_lse + qb);
+                        const float4 dl4 = *reinterpret_cast<const float4*>(s_delta + qb);
+                        const float lsv[4] = {ls4.x, ls4.y, ls4.z, ls4.w};
+                        const float dlv[4] = {dl4.x, dl4.y, dl4.z, dl4.w};
+                        uint32_t rhv[4] = {0, 0, 0, 0};
+                        if (p.thr32) {
+                            const uint4 rh4 = *reinterpret_cast<const uint4*>(s_rhash + qb);
+                            rhv[0] = rh4.x, rhv[1] = rh4.y, rhv[2] = rh4.z, rhv[3] = rh4.w;
                         }
-                        ea[x] = from_f32<T>(pd);
-                        ed[x] = from_f32<T>(pr * (dp - s_delta[st * 128 + ql]));
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const int e = g * 8 + hq * 4 + x;
+                            const float pr = exp2f(fmaf(__uint_as_float(sv[e]), p.scale_log2, kbias) - lsv[x]);
+                            const float dp = __uint_as_float(dv[e]);
+                            if (p.thr32) {
+                                const bool keep = drop_keep(rhv[x], key_hash, p.thr32);
+                                pd[hq * 4 + x] = keep ? pr : 0.f;
+                                ds[hq * 4 + x] = pr * fmaf(keep ? dp : 0.f, p.inv_keep, -dlv[x]);
+                            } else {
+                                pd[hq * 4 + x] = pr;
+                                ds[hq * 4 + x] = pr * (dp - dlv[x]);
+                            }
+                        }
                     }
+                    pk[c][g] = make_uint4(pack2<T>(pd[0], pd[1]), pack2<T>(pd[2], pd[3]), pack2<T>(pd[4], pd[5]),
+                                          pack2<T>(pd[6], pd[7]));
+                    dk4[c][g] = make_uint4(pack2<T>(ds[0], ds[1]), pack2<T>(ds[2], ds[3]), pack2<T>(ds[4], ds[5]),
+                                           pack2<T>(ds[6], ds[7]));
                 }
             }
             if (i > 0) {
@@ -301,7 +315,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     T* ed = reinterpret_cast<T*>(&qd);
 #pragma unroll
                     for (int x = 0; x < 8; ++x) {
-                        ea[x] = from_f32<T>(__uint_as_float(a[g * 8 + x]));
+                        ea[x] = from_f32<T>(__uint_as_float(a[g * 8 + x]) * p.inv_keep);
                         ed[x] = from_f32<T>(__uint_as_float(d[g * 8 + x]) * p.scale);
                     }
                     *reinterpret_cast<uint4*>(dvp + g * 8) = qa;
@@ -394,7 +408,7 @@ static int launch_bwd(const RbAttnArgs& a, cudaStream_t st) {
     p.dK = a.dK; p.dV = a.dV;
     p.dk_sb = a.dk_sb; p.dk_ss = a.dk_ss; p.dk_sh = a.dk_sh;
     p.dv_sb = a.dv_sb; p.dv_ss = a.dv_ss; p.dv_sh = a.dv_sh;
-    p.thr16 = a.p_drop > 0.f ? static_cast<uint32_t>(a.p_drop * 65536.f + 0.5f) : 0u;
+    p.thr32 = drop_threshold(a.p_drop);
     p.inv_keep = a.p_drop > 0.f ? 1.f / (1.f - a.p_drop) : 1.f;
     p.seed = drop_seed(a.seed, a.offset);
     p.err = error_word_ptr();

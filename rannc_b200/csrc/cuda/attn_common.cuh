@@ -25,7 +25,10 @@ __device__ __forceinline__ void bar_sync_named(int id, int count) {
 // ---- attention dropout -----------------------------------------------------
 // The keep decision of element (b, h, q, key) is a pure function of the dropout
 // site's seed and the element's coordinates, so the backward regenerates it.
-// One 32-bit hash serves the key pair (2k, 2k + 1): low half = even key.
+// It is separable: a well-mixed hash per query row and one per key are computed
+// once each (per thread, or staged in shared memory), and an element costs one
+// XOR, one multiply and one compare against the 32-bit threshold p * 2^32 -- in
+// the forward kernel (thread = query row) and in the backward (thread = key) alike.
 __host__ __device__ inline uint32_t drop_seed(uint64_t seed, uint64_t offset) {
     uint64_t z = seed * 0x9E3779B97F4A7C15ull + offset * 0xBF58476D1CE4E5B9ull + 0x94D049BB133111EBull;
     z ^= z >> 31;
@@ -45,8 +48,16 @@ __device__ __forceinline__ uint32_t drop_row_hash(uint32_t seed, int b, int h, i
     const uint32_t row = (static_cast<uint32_t>(b) * H + h) * static_cast<uint32_t>(S) + q;
     return hash32(row ^ seed) + seed;
 }
-__device__ __forceinline__ uint32_t drop_bits(uint32_t row_hash, int key_pair) {
-    return hash32(row_hash + static_cast<uint32_t>(key_pair) * 0x9E3779B1u);
+__device__ __forceinline__ uint32_t drop_key_hash(uint32_t seed, int key) {
+    return hash32(static_cast<uint32_t>(key) * 0x9E3779B1u + (seed ^ 0x85EBCA6Bu));
+}
+__device__ __forceinline__ bool drop_keep(uint32_t row_hash, uint32_t key_hash, uint32_t thr32) {
+    return (row_hash ^ key_hash) * 0x9E3779B1u >= thr32;
+}
+__host__ inline uint32_t drop_threshold(float p_drop) {
+    if (!(p_drop > 0.f)) return 0u;
+    const double t = static_cast<double>(p_drop) * 4294967296.0;
+    return t >= 4294967295.0 ? 4294967295u : static_cast<uint32_t>(t);
 }
 
 }  // namespace rb

@@ -45,18 +45,20 @@ struct AttnFwdParams {
     void* O;
     long long o_sb, o_ss, o_sh;
     float* lse;  // [B, H, S]
-    uint32_t thr16;
+    uint32_t thr32;   // keep an element when its 32-bit hash >= thr32 (0: no dropout)
     float inv_keep;
     uint32_t seed;
     int* err;
 };
 
-template <typename T>
+// FAST: the sequence fits the staged per-key tables (bias and dropout hash in shared memory)
+template <typename T, bool FAST>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ float s_kb[KB_MAX];
+    __shared__ __align__(16) float s_kb[KB_MAX];
+    __shared__ __align__(16) uint32_t s_kh[KB_MAX];
     uint8_t* sQ = smem;               // [2 tiles][TILE_B]
     uint8_t* sK = smem + 2 * TILE_B;  // [2 stages][TILE_B]
     uint8_t* sV = smem + 4 * TILE_B;  // [2 stages][TILE_B]
@@ -77,7 +79,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const int q_base = blockIdx.x * 2 * AQ, h = blockIdx.y, b = blockIdx.z;
     const int nchunks = (p.S + AK - 1) / AK;
     const int ntiles = (q_base + AQ < p.S) ? 2 : 1;
-    const bool kb_smem = p.key_bias && p.S <= KB_MAX;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -92,9 +93,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (kb_smem) {
-        const float* kb = p.key_bias + static_cast<long long>(b) * p.S;
-        for (int i = threadIdx.x; i < p.S; i += ATT_THREADS) s_kb[i] = kb[i] * 1.4426950408889634f;
+    if (FAST) {
+        // per-key tables for the whole (padded) sequence: -inf bias masks the keys past its end
+        const float* kb = p.key_bias ? p.key_bias + static_cast<long long>(b) * p.S : nullptr;
+        for (int i = threadIdx.x; i < nchunks * AK; i += ATT_THREADS) {
+            s_kb[i] = i < p.S ? (kb ? kb[i] * 1.4426950408889634f : 0.f) : -INFINITY;
+            s_kh[i] = drop_key_hash(p.seed, i);
+        }
     }
     if (warp == 16) {
         tmem_alloc(tmem_slot, ATT_TMEM_COLS);
@@ -178,6 +183,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         const uint32_t sw = r & 7;
         uint8_t* prow = sP + t * P_BYTES + half * (P_BYTES / 2) + (r >> 3) * 1024 + sw * 128;
         float* xbase = s_xch + t * 512;
+        // bias (log2 units, -inf past the end of the sequence) and dropout hash of 4 consecutive keys
+        auto cols4 = [&](int key, float4& kb, uint4& kh) {
+            if (FAST) {
+                kb = *reinterpret_cast<const float4*>(s_kb + key);
+                if (p.thr32) kh = *reinterpret_cast<const uint4*>(s_kh + key);
+            } else {
+                float kbv[4];
+                uint32_t khv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int kk = key + i;
+                    kbv[i] = kk < p.S ? (kbg ? kbg[kk] * 1.4426950408889634f : 0.f) : -INFINITY;
+                    khv[i] = drop_key_hash(p.seed, kk);
+                }
+                kb = make_float4(kbv[0], kbv[1], kbv[2], kbv[3]);
+                kh = make_uint4(khv[0], khv[1], khv[2], khv[3]);
+            }
+        };
         for (int j = 0; j < nchunks; ++j) {
             if (!mbar_wait(&s_full[t], j & 1, abort_flag)) {
                 ok = false;
@@ -185,14 +208,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
             tc_fence_after();
             const int key0 = j * AK + half * 64;
-            // scaled, biased score of column `key` (log2 units)
-            auto score = [&](uint32_t raw, int key) -> float {
-                float s = __uint_as_float(raw) * p.scale_log2;
-                if (kb_smem) s += s_kb[min(key, p.S - 1)];
-                else if (kbg) s += kbg[min(key, p.S - 1)] * 1.4426950408889634f;
-                return key < p.S ? s : -INFINITY;
-            };
-            // pass 1: maximum over this thread's 64 columns
+            // pass 1: maximum over this thread's 64 columns of the scaled, biased scores (log2 units)
             float cm = -INFINITY;
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
@@ -200,7 +216,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 tmem_ld32(col_s + lane_addr + half * 64 + c * 32, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) cm = fmaxf(cm, score(v[i], key0 + c * 32 + i));
+                for (int g = 0; g < 8; ++g) {
+                    float4 kb;
+                    uint4 kh = make_uint4(0, 0, 0, 0);
+                    cols4(key0 + c * 32 + g * 4, kb, kh);
+                    const float s0 = fmaf(__uint_as_float(v[g * 4]), p.scale_log2, kb.x);
+                    const float s1 = fmaf(__uint_as_float(v[g * 4 + 1]), p.scale_log2, kb.y);
+                    const float s2 = fmaf(__uint_as_float(v[g * 4 + 2]), p.scale_log2, kb.z);
+                    const float s3 = fmaf(__uint_as_float(v[g * 4 + 3]), p.scale_log2, kb.w);
+                    cm = fmaxf(fmaxf(cm, s0), fmaxf(s1, fmaxf(s2, s3)));
+                }
             }
             float* xch = xbase + (j & 1) * 256;
             xch[half * 128 + r] = cm;
@@ -226,7 +251,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     tmem_st_wait();
                 }
             }
-            // pass 2: probabilities -> shared memory (16-bit, swizzled K-major)
+            // pass 2: probabilities -> shared memory (16-bit, swizzled K-major).  Dropped entries are
+            // zeroed here; the 1 / (1 - p) factor is applied once to the finished row.
             float rs = 0.f;
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
@@ -242,23 +268,25 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 for (int g = 0; g < 4; ++g) {
                     float pr[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float e = exp2f(score(v[g * 8 + i], key0 + c * 32 + g * 8 + i) - m_use);
-                        rs += e;
-                        pr[i] = e;
-                    }
-                    if (p.thr16) {
+                    for (int hq = 0; hq < 2; ++hq) {
+                        float4 kb;
+                        uint4 kh = make_uint4(0, 0, 0, 0);
+                        cols4(key0 + c * 32 + g * 8 + hq * 4, kb, kh);
+                        const float kbv[4] = {kb.x, kb.y, kb.z, kb.w};
+                        const uint32_t khv[4] = {kh.x, kh.y, kh.z, kh.w};
 #pragma unroll
-                        for (int i = 0; i < 8; i += 2) {
-                            const uint32_t bits = drop_bits(row_hash, (key0 + c * 32 + g * 8 + i) >> 1);
-                            pr[i] = (bits & 0xffffu) >= p.thr16 ? pr[i] * p.inv_keep : 0.f;
-                            pr[i + 1] = (bits >> 16) >= p.thr16 ? pr[i + 1] * p.inv_keep : 0.f;
+                        for (int i = 0; i < 4; ++i) {
+                            const float e =
+                                exp2f(fmaf(__uint_as_float(v[g * 8 + hq * 4 + i]), p.scale_log2, kbv[i]) - m_use);
+                            rs += e;
+                            pr[hq * 4 + i] = (!p.thr32 || drop_keep(row_hash, khv[i], p.thr32)) ? e : 0.f;
                         }
                     }
                     uint4 qv;
-                    T* e = reinterpret_cast<T*>(&qv);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(pr[i]);
+                    qv.x = pack2<T>(pr[0], pr[1]);
+                    qv.y = pack2<T>(pr[2], pr[3]);
+                    qv.z = pack2<T>(pr[4], pr[5]);
+                    qv.w = pack2<T>(pr[6], pr[7]);
                     *reinterpret_cast<uint4*>(prow + ((static_cast<uint32_t>(c * 4 + g) ^ sw) << 4)) = qv;
                 }
             }
@@ -275,7 +303,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             xch[half * 128 + r] = l;
             bar_sync_named(1 + t, GROUP);
             l += xch[(half ^ 1) * 128 + r];
-            const float inv_l = l > 0.f ? 1.f / l : 0.f;
+            const float inv_l = l > 0.f ? p.inv_keep / l : 0.f;
             T* orow = reinterpret_cast<T*>(p.O) + b * p.o_sb + static_cast<long long>(q) * p.o_ss + h * p.o_sh +
                       half * 32;
             uint32_t v[32];
@@ -285,9 +313,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     uint4 qv;
-                    T* e = reinterpret_cast<T*>(&qv);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(__uint_as_float(v[g * 8 + i]) * inv_l);
+                    qv.x = pack2<T>(__uint_as_float(v[g * 8]) * inv_l, __uint_as_float(v[g * 8 + 1]) * inv_l);
+                    qv.y = pack2<T>(__uint_as_float(v[g * 8 + 2]) * inv_l, __uint_as_float(v[g * 8 + 3]) * inv_l);
+                    qv.z = pack2<T>(__uint_as_float(v[g * 8 + 4]) * inv_l, __uint_as_float(v[g * 8 + 5]) * inv_l);
+                    qv.w = pack2<T>(__uint_as_float(v[g * 8 + 6]) * inv_l, __uint_as_float(v[g * 8 + 7]) * inv_l);
                     *reinterpret_cast<uint4*>(orow + g * 8) = qv;
                 }
                 if (half == 0)
@@ -333,19 +362,20 @@ static int launch_fwd(const RbAttnArgs& a, cudaStream_t st) {
     p.o_ss = a.o_ss;
     p.o_sh = a.o_sh;
     p.lse = a.lse;
-    p.thr16 = a.p_drop > 0.f ? static_cast<uint32_t>(a.p_drop * 65536.f + 0.5f) : 0u;
+    p.thr32 = drop_threshold(a.p_drop);
     p.inv_keep = a.p_drop > 0.f ? 1.f / (1.f - a.p_drop) : 1.f;
     p.seed = drop_seed(a.seed, a.offset);
     p.err = error_word_ptr();
     if (!p.err) return -3;
-    auto kern = attn_fwd_kernel<T>;
-    static bool attr_set[64] = {false};
+    const bool fast = (a.S + AK - 1) / AK * AK <= KB_MAX;
+    auto kern = fast ? attn_fwd_kernel<T, true> : attn_fwd_kernel<T, false>;
+    static bool attr_set[64][2] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!attr_set[dev & 63]) {
+    if (!attr_set[dev & 63][fast]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess)
             return -4;
-        attr_set[dev & 63] = true;
+        attr_set[dev & 63][fast] = true;
     }
     dim3 grid((a.S + 2 * AQ - 1) / (2 * AQ), a.H, a.B);
     kern<<<grid, ATT_THREADS, ATT_SMEM, st>>>(tq, tk, tv, p);

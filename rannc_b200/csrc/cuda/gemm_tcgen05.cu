@@ -489,10 +489,17 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int dtype_16bit_kind, uint6
     cuuint32_t estr[3] = {1, 1, 1};
     CUtensorMapDataType dt =
         dtype_16bit_kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = CUDA_SUCCESS;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE,
+               swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+        // a thread that has made no runtime call yet (an autograd worker whose first operator is ours) has
+        // no context bound for driver entry points: bind the device's primary context and try again
+        cudaFree(nullptr);
+    }
     return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
 }
 
@@ -506,9 +513,14 @@ int make_tmap_4d(CUtensorMap* out, const void* base, int fmt, uint64_t d0, uint6
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUtensorMapDataType dt =
         fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = fn(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = CUDA_SUCCESS;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        r = fn(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+        cudaFree(nullptr);
+    }
     return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
 }
 

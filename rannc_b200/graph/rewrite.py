@@ -116,8 +116,10 @@ def _erase_if_dead(gm, *nodes):
             gm.graph.erase_node(n)
 
 
-def fuse(gm: fx.GraphModule, training: bool = True) -> dict:
-    """Rewrites ``gm`` in place; returns a count of each rewrite applied."""
+def fuse(gm: fx.GraphModule, training: bool = True, keep_linear: bool = False) -> dict:
+    """Rewrites ``gm`` in place; returns a count of each rewrite applied.  With ``keep_linear`` every
+    ``linear`` stays a node of its own (no q/k/v or MLP fusion), so that it can be turned into a
+    tensor-partitioned linear once the replica sets are known."""
     stats = {}
 
     def bump(k):
@@ -142,7 +144,7 @@ def fuse(gm: fx.GraphModule, training: bool = True) -> dict:
         return (lin, v, int(heads)) if isinstance(heads, int) else None
 
     for n in list(g.nodes):
-        if not _is(n, aten.scaled_dot_product_attention.default):
+        if keep_linear or not _is(n, aten.scaled_dot_product_attention.default):
             continue
         pq, pk, pv = (_proj(a) for a in n.args[:3])
         if pq is None or pk is None or pv is None:
@@ -173,7 +175,7 @@ def fuse(gm: fx.GraphModule, training: bool = True) -> dict:
 
     # ---- linear -> gelu -> linear  /  linear -> gelu
     for n in list(g.nodes):
-        if not _is(n, aten.linear.default) or n not in g.nodes:
+        if keep_linear or not _is(n, aten.linear.default) or n not in g.nodes:
             continue
         u = _single_user(n)
         if u is not None and _is(u, aten.gelu.default) and u.kwargs.get("approximate", "none") == "none":

@@ -188,7 +188,9 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
     if use_kernels:
         from . import rewrite
 
-        stats = rewrite.fuse(gm, training=model.training)
+        from ..utils.config import conf
+
+        stats = rewrite.fuse(gm, training=model.training, keep_linear=bool(conf("force_dist_matmul")))
     else:
         from . import rewrite
 

@@ -117,6 +117,7 @@ class RaNNCModule:
                     raise RuntimeError("All inputs to RaNNCModule must be on a CUDA device")
         if not self.ready:
             self._init(args)
+        self._dist_barrier()
         outs = self._runtime.forward(args, grad_enabled=torch.is_grad_enabled())
         if torch.is_grad_enabled():
             outs = list(_DistBackward.apply(weakref.ref(self), self._anchor, *outs))
@@ -244,6 +245,25 @@ class RaNNCModule:
                     if fq in seen and seen[fq] != sname and name_to_param[fq].requires_grad and world > 1:
                         raise RuntimeError(f"parameter {fq} is shared by stages {seen[fq]} and {sname} on rank {rank}")
                     seen[fq] = sname
+        if bool(conf("verify_partitioning")) and rank == 0:
+            self._verify_partitioning(tm, dep, args, name_to_param, name_to_buffer)
+        # tensor-partitioned linear layers: which nodes, which weights, over which ranks
+        dist_kernels = dev.type == "cuda" and bool(conf("fused_kernels")) and self.use_amp_master_params
+        dist_nodes, sliced = self._select_dist_linears(tm, dep, name_to_param, owner, 256 if dist_kernels else 1) \
+            if bool(conf("force_dist_matmul")) else ({}, {})
+        for fq, ranks in sliced.items():
+            p = name_to_param[fq]
+            if _dp.dist_param_registered(id(p)):
+                raise RuntimeError(f"{fq}: a parameter cannot be both a dist_param and tensor-partitioned")
+            if _sync_params_on_init:
+                comm.create_groups([ranks])
+            if rank in ranks:
+                full = p.data.to(dev)
+                if _sync_params_on_init:
+                    comm.bcast(full, ranks[0], ranks)
+                ks = full.shape[1] // len(ranks)
+                i = ranks.index(rank)
+                p.data = full[:, i * ks:(i + 1) * ks].contiguous()
         unused_params = [n for n, r in owner.items() if not r]
         for n in unused_params:
             owner[n] = {0}
@@ -268,7 +288,8 @@ class RaNNCModule:
                       bool(conf("fused_kernels")) and bool(conf("fused_grad_allreduce")) and
                       type(self.optimizer) in (torch.optim.Adam, torch.optim.AdamW))
         self._storage.deploy(local_params, {n: sorted(r) for n, r in owner.items()}, opt_group_of, dev,
-                             self._param_order_by_name, symmetric=want_fused)
+                             self._param_order_by_name, symmetric=want_fused, sliced=sliced,
+                             symmetric_slices=dist_kernels)
         for n in self._used_buffer_names:
             b = name_to_buffer[n]
             b.data = b.data.to(dev)
@@ -291,6 +312,9 @@ class RaNNCModule:
                     tensors[pin] = name_to_buffer[tm.buffers[pin]]
                 elif pin in tm.constants:
                     tensors[pin] = tm.constants[pin].to(dev)
+            if sname in dist_nodes:
+                self._install_dist_linears(gm, sname, dist_nodes[sname], tuple(dep.allocation[sname]), name_to_param,
+                                           dist_kernels, dev)
             st = StageExec(sname, gm, sg, tensors)
             st.keep_graph = _keep_graph
             stages[sname] = st
@@ -310,6 +334,154 @@ class RaNNCModule:
         _core.trace_enable(bool(conf("trace_events")))
         logger.info("RaNNCModule is ready. (rank %d: stages %s)", rank, str(local_stage_names))
 
+    # ------------------------------------------------------------------ validation
+    def _verify_partitioning(self, tm, dep, args, name_to_param, name_to_buffer):
+        """Runs the traced graph as a whole and as the chain of its stage graphs (dropout off) on the same
+        inputs and compares every user output (reference: Validator::validate, src/comp/Validator.cpp:109-226).
+        Runs on rank 0, on whatever device the parameters are on at this point; buffers that the graphs update
+        in place (BatchNorm statistics) are copied first."""
+        import copy as _copy
+
+        from .parallel.stage import build_stage_module, set_dropout
+
+        ph = {n.name: n for n in tm.gm.graph.nodes if n.op == "placeholder"}
+        env: Dict[str, torch.Tensor] = {}
+        pdev = next((p.device for p in name_to_param.values()), torch.device("cpu"))
+        for nm, a in zip(tm.user_inputs, args):
+            env[nm] = a.to(pdev) if isinstance(a, torch.Tensor) else a
+        for nm in ph:
+            if nm in tm.params:
+                env[nm] = name_to_param[tm.params[nm]].detach()
+            elif nm in tm.buffers:
+                env[nm] = name_to_buffer[tm.buffers[nm]].detach()
+            elif nm in tm.constants:
+                env[nm] = tm.constants[nm].to(pdev)
+
+        def run(gm, names, values):
+            gm = _copy.deepcopy(gm)
+            set_dropout(gm, False)
+            gm.recompile()
+            vals = [values[n].clone() if n in tm.buffers else values[n] for n in names]
+            with torch.no_grad():
+                return gm(*vals)
+
+        whole_names = [n.name for n in tm.gm.graph.nodes if n.op == "placeholder"]
+        whole = run(tm.gm, whole_names, env)
+        whole = whole if isinstance(whole, (tuple, list)) else (whole,)
+        out_nodes = []
+        for n in tm.gm.graph.nodes:
+            if n.op == "output":
+                import torch.utils._pytree as pytree
+
+                out_nodes = [a.name for a in pytree.tree_leaves(n.args) if isinstance(a, torch.fx.Node)]
+        expected = dict(zip(out_nodes, whole))
+        chained = dict(env)
+        for sname in dep.fwd_graph_order:
+            sg = dep.subgraphs[sname]
+            outs = run(build_stage_module(tm.gm, sg), list(sg.input_names), chained)
+            outs = outs if isinstance(outs, (tuple, list)) else (outs,)
+            chained.update(zip(sg.output_names, outs))
+        bad = []
+        for o in tm.user_outputs:
+            a, b = expected[o].float(), chained[o].float()
+            tol = 1e-4 if expected[o].dtype == torch.float32 else 2e-2
+            if a.shape != b.shape or not torch.allclose(a, b, rtol=tol, atol=tol * max(1.0, float(a.abs().max()))):
+                bad.append(o)
+        if bad:
+            raise RuntimeError(f"verify_partitioning: outputs {bad} of the partitioned graphs differ from the "
+                               f"original graph")
+        logger.info("verify_partitioning: %d stage graph(s) reproduce the original graph", len(dep.fwd_graph_order))
+
+    # ------------------------------------------------------------------ tensor-partitioned linear layers
+    @staticmethod
+    def _select_dist_linears(tm, dep, name_to_param, owner, col_unit: int = 1):
+        """Every ``linear`` whose stage has more than one replica and whose weight is a plain 2-D parameter
+        used by that node alone is partitioned along its input dimension over the replicas
+        (reference: src/distop/PartitionTensor.cpp:230-298, config force_dist_matmul).  Deterministic: every
+        rank derives the same selection from the deployment."""
+        from .ops import functional as RF
+
+        by_name = {n.name: n for n in tm.gm.graph.nodes}
+        use_count: Dict[str, int] = {}
+        for n in tm.gm.graph.nodes:
+            if n.op == "placeholder":
+                use_count[n.name] = len(n.users)
+        dist_nodes: Dict[str, Dict[str, str]] = {}
+        sliced: Dict[str, tuple] = {}
+        for sname in dep.fwd_graph_order:
+            ranks = tuple(sorted(dep.allocation[sname]))
+            n = len(ranks)
+            if n < 2:
+                continue
+            for irn in dep.subgraphs[sname].nodes:
+                fxn = by_name.get(irn.id)
+                if fxn is None or fxn.op != "call_function":
+                    continue
+                if fxn.target is torch.ops.aten.linear.default:
+                    pass
+                elif fxn.target is RF.linear and (len(fxn.args) < 4 or fxn.args[3] is None):
+                    pass
+                else:
+                    continue
+                w = fxn.args[1]
+                if not isinstance(w, torch.fx.Node) or w.op != "placeholder" or w.name not in tm.params:
+                    continue
+                fq = tm.params[w.name]
+                p = name_to_param.get(fq)
+                if p is None or p.dim() != 2 or use_count.get(w.name, 0) != 1 or set(owner[fq]) != set(ranks):
+                    continue
+                if p.shape[1] % (col_unit * n):   # the kernels move slices in 256-column tiles
+                    continue
+                dist_nodes.setdefault(sname, {})[fxn.name] = fq
+                sliced[fq] = ranks
+        return dist_nodes, sliced
+
+    def _install_dist_linears(self, gm, sname, nodes, ranks, name_to_param, kernels, dev):
+        """Turns the selected ``linear`` nodes of a stage graph into ``linear_dist_op`` calls.  With the
+        kernels, peers read each other's weight slices and add into each other's gradient slices directly:
+        both live in this rank's symmetric flat buffers, whose peer addresses are resolved here."""
+        from .parallel import distop
+
+        if not hasattr(self, "_dist_groups"):
+            self._dist_groups = {}
+        sizes = [name_to_param[fq].numel() * len(ranks) for fq in nodes.values()]
+        dtype = next(iter(name_to_param[fq].dtype for fq in nodes.values()))
+        grp = distop.DistGroup(ranks, max(sizes), dtype, dev, kernels=kernels)
+        self._dist_groups[sname] = grp
+        ptrs = {}
+        if kernels:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            seen = {}
+            for fq in nodes.values():
+                g, i = self._storage.by_name[fq]
+                if id(g) not in seen:
+                    pg = comm.group(ranks)
+                    seen[id(g)] = (symm_mem.rendezvous(g.flat_param, pg), symm_mem.rendezvous(g.flat_grad, pg))
+                ph, gh = seen[id(g)]
+                off = g.offsets[i]
+                ptrs[fq] = ([int(b) + off * g.flat_param.element_size() for b in ph.buffer_ptrs],
+                            [int(b) + off * g.flat_grad.element_size() for b in gh.buffer_ptrs])
+            self._dist_keep = getattr(self, "_dist_keep", []) + list(seen.values())
+        for n in gm.graph.nodes:
+            if n.name in nodes:
+                fq = nodes[n.name]
+                sp, gp = ptrs.get(fq, ([], []))
+                key = distop.register_site(distop.LinearDistSite(grp, sp, gp))
+                bias = n.args[2] if len(n.args) > 2 else n.kwargs.get("bias")
+                n.target = distop.linear_dist_op
+                n.args = (n.args[0], n.args[1], bias, key)
+                n.kwargs = {}
+        gm.graph.lint()
+        gm.recompile()
+
+    def _dist_barrier(self):
+        """Peers read this rank's weight slices and write into its gradient slices from their own streams:
+        a stream-ordered barrier over each replica set separates those accesses from this rank's optimizer
+        step and zero_grad (before the first forward of a step and after the last backward)."""
+        for grp in getattr(self, "_dist_groups", {}).values():
+            grp.barrier()
+
     def _setup_fused_reducer(self):
         try:
             from .parallel.fused_reduce import FusedGradReducer
@@ -322,6 +494,7 @@ class RaNNCModule:
     # ------------------------------------------------------------------ backward
     def _run_backward(self, grads):
         self._runtime.backward(grads)
+        self._dist_barrier()
         if not _delay_grad_allreduce:
             if self.enable_zero:
                 self.allreduce_grads_zero()

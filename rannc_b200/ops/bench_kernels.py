@@ -4,6 +4,14 @@
     python -m rannc_b200.ops.bench_kernels attn --batch 8 --heads 16 --seq 512 [--dropout 0.1]
     python -m rannc_b200.ops.bench_kernels ln --rows 32768 --hidden 1024
     python -m rannc_b200.ops.bench_kernels adam --numel 100000000
+    python -m rannc_b200.ops.bench_kernels ag_gemm --m 8192 --n 4096 --k 4096 --ranks 4
+    python -m rannc_b200.ops.bench_kernels gemm_rs --m 8192 --n 4096 --k 4096 --ranks 4
+    python -m rannc_b200.ops.bench_kernels rs_adam --numel 100000000
+
+``ag_gemm`` / ``gemm_rs`` run the all-gather -> GEMM and GEMM -> reduce-scatter kernels with the group's
+``--ranks`` shards all placed on this GPU (the peers' buffers are local allocations), ``rs_adam`` runs the
+reduce-scatter + Adam + all-gather kernel for a rank set of one: the same kernels as over NVLink, without
+the link.
 
 Each prints one JSON line with the time per call and the achieved fraction of the measured peaks
 (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).
@@ -48,7 +56,9 @@ def _time(fn, iters, warmup, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn", "attn_bwd", "ln", "ln_bwd", "adam", "xent", "colsum"])
+    ap.add_argument("kernel", choices=["gemm", "attn", "attn_bwd", "ln", "ln_bwd", "adam", "xent", "colsum",
+                                      "ag_gemm", "gemm_rs", "rs_adam"])
+    ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -144,6 +154,57 @@ def main():
         t = _time(fn, a.iters, a.warmup, not a.no_flush)
         nbytes = a.rows * a.hidden * 2
         out.update(rows=a.rows, hidden=a.hidden, ms=t * 1e3, gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / hbm)
+    elif a.kernel in ("ag_gemm", "gemm_rs"):
+        from ..parallel.distop import DistGroup, _gather_spec, _gemm_rs
+
+        M, N, Kd, n = a.m, a.n, a.k, a.ranks
+        ks = Kd // n
+        grp = DistGroup(list(range(n)), N * Kd, dt, torch.device("cuda"), local=True)
+        x = torch.randn(M, Kd, device="cuda", dtype=dt)
+        if a.kernel == "ag_gemm":
+            shards = [torch.randn(N, ks, device="cuda", dtype=dt) for _ in range(n)]
+            wfull = grp.staging[: N * Kd].view(N, Kd)
+            spec = _gather_spec(grp, [t.data_ptr() for t in shards], N, ks)
+            fn = lambda: gemm(x, wfull, gather=spec)  # noqa: E731
+        else:
+            dy = torch.randn(M, N, device="cuda", dtype=dt)
+            grads = [torch.zeros(N, ks, device="cuda") for _ in range(n)]
+            ptrs = [t.data_ptr() for t in grads]
+            fn = lambda: _gemm_rs(dy, x, N, Kd, ptrs, ks, 1.0)  # noqa: E731
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        fl = 2.0 * M * N * Kd
+        # bytes that would cross NVLink with real peers: the other ranks' slices (in), or the other ranks'
+        # gradient blocks (out, fp32)
+        link = (n - 1) / n * N * Kd * (2 if a.kernel == "ag_gemm" else 4)
+        t_roof = max(fl / flops_peak, link / 770e9)
+        out.update(M=M, N=N, K=Kd, ranks=n, ms=t * 1e3, tflops=fl / t / 1e12, frac_of_peak=fl / t / flops_peak,
+                   link_bytes=link, roofline_ms=t_roof * 1e3, frac_of_roofline=t_roof / t)
+    elif a.kernel == "rs_adam":
+        import ctypes
+
+        from ..parallel.fused_reduce import MAX_PEERS, _Args
+
+        n = a.numel // 64 * 64
+        grad = torch.randn(n, device="cuda")
+        p16 = torch.zeros(n, device="cuda", dtype=dt)
+        master, m, v = (torch.randn(n, device="cuda") for _ in range(3))
+        flags = torch.zeros(2 * MAX_PEERS, dtype=torch.int32, device="cuda")
+        done = torch.zeros(1, dtype=torch.int32, device="cuda")
+        state = {"epoch": 0}
+
+        def fn():
+            state["epoch"] += 1
+            g = _Args()
+            g.peer_grad[0], g.peer_param[0], g.peer_flags[0] = grad.data_ptr(), p16.data_ptr(), flags.data_ptr()
+            g.master, g.m, g.v, g.done_counter = master.data_ptr(), m.data_ptr(), v.data_ptr(), done.data_ptr()
+            g.lo, g.len, g.nranks, g.my_idx, g.epoch = 0, n, 1, 0, state["epoch"]
+            g.grad_mul, g.lr, g.beta1, g.beta2, g.eps = 1.0, 1e-3, 0.9, 0.999, 1e-8
+            g.weight_decay, g.bias_corr1, g.bias_corr2, g.adamw, g.dtype16 = 0.0, 0.1, 0.001, 0, 1
+            _lib.check(_lib.lib().rb_rs_adam_ag(ctypes.byref(g), _lib.stream_ptr()), "rb_rs_adam_ag")
+
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        nbytes = n * (4 + 3 * 4 + 3 * 4 + 2)   # grad in; master, m, v in and out; 16-bit parameter out
+        out.update(numel=n, ms=t * 1e3, gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / hbm)
     out["device_error_word"] = _lib.read_error()
     print(json.dumps(out))
 

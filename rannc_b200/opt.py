@@ -288,13 +288,20 @@ def _gather_state_tensor(storage, optimizer, name: str, key: str, shape) -> torc
         numel *= d
     dev = comm.device()
     full = torch.zeros(numel, dtype=torch.float32, device=dev)
+    sl = storage.sliced.get(name)
     if name in storage.by_name:
         g, i = storage.by_name[name]
         target = g.master_params[i] if (g.flat_master is not None and g.master_params) else g.params[i]
         if target is not None and target in optimizer.state and key in optimizer.state[target]:
             a, b = g.local_range(i)
             lo, _ = g.param_range(i)
-            if storage.zero or comm.get_rank() == ranks[0]:
+            if sl:
+                # a tensor-partitioned weight: every holder contributes its column block
+                ks = shape[1] // len(sl)
+                idx = sl.index(comm.get_rank())
+                full.view(shape)[:, idx * ks:(idx + 1) * ks] = \
+                    optimizer.state[target][key].reshape(shape[0], ks).to(dev, torch.float32)
+            elif storage.zero or comm.get_rank() == ranks[0]:
                 full[a - lo:b - lo] = optimizer.state[target][key].reshape(-1).to(dev, torch.float32)
     if comm.get_world_size() > 1:
         comm.allreduce(full, "sum")
@@ -325,8 +332,13 @@ def load_global_optimizer_state(optimizer, sd: dict) -> None:
         a, b = g.local_range(i)
         lo, _ = g.param_range(i)
         st = optimizer.state[target]
+        sl = storage.sliced.get(name)
         for k, v in entry.items():
             if torch.is_tensor(v) and v.dim() > 0:
+                if sl:
+                    ks = v.shape[1] // len(sl)
+                    idx = sl.index(comm.get_rank())
+                    v = v[:, idx * ks:(idx + 1) * ks].contiguous()
                 piece = v.reshape(-1)[a - lo:b - lo].to(target.device, torch.float32).view(target.shape)
                 st[k] = piece.clone()
             else:

@@ -37,21 +37,26 @@ class DistGroup:
     how the kernels are tested on a single device."""
 
     def __init__(self, ranks: Sequence[int], max_weight_numel: int, dtype=torch.bfloat16, device=None,
-                 local: bool = False):
+                 local: bool = False, kernels: Optional[bool] = None):
         self.ranks = tuple(sorted(ranks))
         self.n = len(self.ranks)
         self.local = local
         self.device = device or comm.device()
         self.dtype = dtype
         self.my_idx = 0 if local else self.ranks.index(comm.get_rank())
-        self.staging = torch.empty(max_weight_numel, dtype=dtype, device=self.device)
-        self.ag_flags = torch.zeros(8, dtype=torch.int32, device=self.device)
+        # without the kernels (CPU ranks, or fused_kernels=false) the same operator runs on collectives
+        self.kernels = self.device.type == "cuda" if kernels is None else bool(kernels)
         self.epoch = 0
         self._flag_ptrs = None
+        if not self.kernels:
+            return
+        self.staging = torch.empty(max_weight_numel, dtype=dtype, device=self.device)
+        self.ag_flags = torch.zeros(8, dtype=torch.int32, device=self.device)
         if not local and self.n > 1:
             import torch.distributed._symmetric_memory as symm_mem
 
             self.flags = symm_mem.empty(2 * MAX_PEERS, dtype=torch.int32, device=self.device).zero_()
+            torch.cuda.synchronize(self.device)   # zeroed before any peer can learn the address
             hdl = symm_mem.rendezvous(self.flags, comm.group(self.ranks))
             self._flag_ptrs = [int(p) for p in hdl.buffer_ptrs]
             self._keep = [hdl]
@@ -61,7 +66,7 @@ class DistGroup:
 
     def barrier(self):
         """Stream-ordered barrier over the group (flag handshake kernel; bounded waits)."""
-        if self.local or self.n == 1:
+        if self.local or self.n == 1 or not self.kernels:
             return
         self.epoch += 1
         arr = (ctypes.c_void_p * 8)(*([ctypes.c_void_p(p) for p in self._flag_ptrs] + [None] * (8 - self.n)))
@@ -83,6 +88,7 @@ class SharedTensor:
             import torch.distributed._symmetric_memory as symm_mem
 
             self.t = symm_mem.empty(numel, dtype=dtype, device=grp.device).zero_()
+            torch.cuda.synchronize(grp.device)
             self.hdl = symm_mem.rendezvous(self.t, comm.group(grp.ranks))
             self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
 
@@ -94,7 +100,7 @@ def _gather_spec(grp: DistGroup, shard_ptrs: List[int], rows: int, cols: int):
 
 class _LinearDist(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w_shard, bias, grp, shard_ptrs, grad_ptrs, w_main_grad):
+    def forward(ctx, x, w_shard, bias, grp, shard_ptrs, grad_ptrs, w_main_grad, grad_scale):
         # w_shard: [N, K / n]; shard_ptrs[r]: rank r's shard; grad_ptrs[r]: rank r's fp32 [N, K / n] gradient
         N, Ks = w_shard.shape
         Kfull = Ks * grp.n
@@ -104,13 +110,13 @@ class _LinearDist(torch.autograd.Function):
         wfull = grp.staging[: N * Kfull].view(N, Kfull)
         y = gemm(x2, wfull, bias=bias, gather=_gather_spec(grp, shard_ptrs, N, Ks))
         ctx.save_for_backward(x2)
-        ctx.meta = (grp, shard_ptrs, grad_ptrs, N, Ks, bias, w_main_grad, x.shape)
+        ctx.meta = (grp, shard_ptrs, grad_ptrs, N, Ks, bias, w_main_grad, x.shape, grad_scale)
         return y.view(*x.shape[:-1], N)
 
     @staticmethod
     def backward(ctx, dy):
         (x2,) = ctx.saved_tensors
-        grp, shard_ptrs, grad_ptrs, N, Ks, bias, w_mg, x_shape = ctx.meta
+        grp, shard_ptrs, grad_ptrs, N, Ks, bias, w_mg, x_shape, grad_scale = ctx.meta
         Kfull = Ks * grp.n
         dy2 = dy.reshape(-1, N)
         if not dy2.is_contiguous():
@@ -120,11 +126,8 @@ class _LinearDist(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             # the weight is gathered again (it is not kept between forward and backward)
             dx = gemm(dy2, wfull, trans_b=False, gather=_gather_spec(grp, shard_ptrs, N, Ks)).view(x_shape)
-        world = comm.get_world_size() if not grp.local else 1
-        # dW = dy^T x for this rank's batch slice; column block j is added into rank j's gradient buffer.
-        # The world-size average of data-parallel gradients is folded in here, as those parameters take no
-        # part in the gradient all-reduce (reference: ParamStorage.cpp:377-379).
-        _gemm_rs(dy2, x2, N, Kfull, grad_ptrs, Ks, 1.0 / world)
+        # dW = dy^T x for this rank's batch slice; column block j is added into rank j's gradient buffer
+        _gemm_rs(dy2, x2, N, Kfull, grad_ptrs, Ks, grad_scale)
         db = None
         if bias is not None and ctx.needs_input_grad[2]:
             mg = getattr(bias, "main_grad", None)
@@ -132,7 +135,45 @@ class _LinearDist(torch.autograd.Function):
                 K.colsum(dy2, out=mg)
             else:
                 db = K.colsum(dy2).to(bias.dtype)
-        return dx, None, db, None, None, None, None
+        return dx, None, db, None, None, None, None, None
+
+
+class _LinearDistCollective(torch.autograd.Function):
+    """The same operator on library collectives (gloo on CPU ranks, NCCL when the kernels are switched off):
+    all-gather of the slices, a plain matmul, and an all-reduce of the full weight gradient of which each
+    rank keeps its block -- the way the reference runs it (src/distop/DistMatmul.cpp:97-214)."""
+
+    @staticmethod
+    def _gather(w, grp):
+        import torch.distributed as dist
+
+        if grp.n == 1:
+            return w.detach()
+        parts = [torch.empty_like(w) for _ in range(grp.n)]
+        dist.all_gather(parts, w.detach().contiguous(), group=comm.group(grp.ranks))
+        return torch.cat(parts, dim=1)
+
+    @staticmethod
+    def forward(ctx, x, w_shard, bias, grp, grad_scale):
+        wfull = _LinearDistCollective._gather(w_shard, grp)
+        ctx.save_for_backward(x, w_shard)
+        ctx.meta = (grp, bias is not None, grad_scale)
+        return torch.nn.functional.linear(x, wfull, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_shard = ctx.saved_tensors
+        grp, has_bias, grad_scale = ctx.meta
+        wfull = _LinearDistCollective._gather(w_shard, grp)
+        dx = dy @ wfull if ctx.needs_input_grad[0] else None
+        dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
+        dw = (dy2.t() @ x2) * grad_scale
+        if grp.n > 1:
+            comm.allreduce(dw, "sum", grp.ranks)
+        ks = w_shard.shape[1]
+        gw = dw[:, grp.my_idx * ks:(grp.my_idx + 1) * ks].contiguous()
+        db = dy2.sum(0) if has_bias and ctx.needs_input_grad[2] else None
+        return dx, gw, db, None, None
 
 
 def _gemm_rs(dy2, x2, N, Kfull, grad_ptrs, Ks, alpha):
@@ -151,9 +192,45 @@ def _gemm_rs(dy2, x2, N, Kfull, grad_ptrs, Ks, alpha):
     _lib.check(_lib.lib().rb_gemm(ctypes.byref(args), _lib.stream_ptr()), "rb_gemm (reduce-scatter)")
 
 
-def linear_dist(x, w_shard, bias, grp: DistGroup, shard_ptrs: List[int], grad_ptrs: List[int]):
-    """``x @ gather(w_shards).T + bias`` for a weight sliced along its input dimension over ``grp``."""
-    return _LinearDist.apply(x, w_shard, bias, grp, shard_ptrs, grad_ptrs, getattr(w_shard, "main_grad", None))
+def linear_dist(x, w_shard, bias, grp: DistGroup, shard_ptrs: List[int], grad_ptrs: List[int],
+                grad_scale: Optional[float] = None):
+    """``x @ gather(w_shards).T + bias`` for a weight sliced along its input dimension over ``grp``.
+
+    The weight gradient is the SUM over the group's batch slices times ``grad_scale``; by default that is
+    1 / world size, the data-parallel average (reference: ParamStorage.cpp:377-379).  Inside RaNNCModule
+    the storage applies that average to every gradient buffer itself, so it passes 1."""
+    if grad_scale is None:
+        grad_scale = 1.0 / (comm.get_world_size() if not grp.local else 1)
+    if not grp.kernels:
+        return _LinearDistCollective.apply(x, w_shard, bias, grp, grad_scale)
+    return _LinearDist.apply(x, w_shard, bias, grp, shard_ptrs, grad_ptrs, getattr(w_shard, "main_grad", None),
+                             grad_scale)
+
+
+class LinearDistSite:
+    """What one rewritten ``linear`` node of a stage graph needs at run time."""
+
+    def __init__(self, grp: DistGroup, shard_ptrs: List[int], grad_ptrs: List[int]):
+        self.grp, self.shard_ptrs, self.grad_ptrs = grp, shard_ptrs, grad_ptrs
+
+
+_SITES: dict = {}
+
+
+def register_site(site: LinearDistSite) -> int:
+    key = len(_SITES) + 1
+    _SITES[key] = site
+    return key
+
+
+def clear_sites() -> None:
+    _SITES.clear()
+
+
+def linear_dist_op(x, w_shard, bias, key: int):
+    """Graph-level form of ``linear_dist``: ``key`` names a registered site (graphs hold plain values only)."""
+    st = _SITES[key]
+    return linear_dist(x, w_shard, bias, st.grp, st.shard_ptrs, st.grad_ptrs, 1.0)
 
 
 class DistLinear(torch.nn.Module):

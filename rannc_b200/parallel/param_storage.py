@@ -57,6 +57,7 @@ class FlatGroup:
         self.master_params: List[Optional[torch.nn.Parameter]] = []
         self.shard: Tuple[int, int] = (0, 0)     # [lo, hi) of the flat buffer this rank updates
         self.symm = None                         # symmetric-memory handles of the fused gradient path
+        self.slice_ranks: Optional[Tuple[int, ...]] = None  # tensor-partitioned weights: ranks holding the slices
 
     @property
     def nranks(self) -> int:
@@ -83,7 +84,7 @@ class FlatGroup:
         # whole buffer divisible into equal 16-byte aligned shards
         self.total = _align(max(off, 1), unit * self.nranks * 8)
         gdtype = torch.float32 if amp else self.dtype
-        self.symmetric = bool(symmetric and self.nranks > 1 and self.device.type == "cuda")
+        self.symmetric = bool(symmetric and (self.nranks > 1 or self.slice_ranks) and self.device.type == "cuda")
         if self.symmetric:
             # peers read / write these buffers directly (fused gradient path)
             from .fused_reduce import symm_empty
@@ -124,6 +125,7 @@ class ParamStorage:
         self.by_name: Dict[str, Tuple[FlatGroup, int]] = {}
         self.buffers: Dict[str, torch.Tensor] = {}
         self.param_ranks: Dict[str, Tuple[int, ...]] = {}
+        self.sliced: Dict[str, Tuple[int, ...]] = {}   # weight sliced along dim 1 over these ranks
         self.global_order: Dict[str, int] = {}
         self.sync_on_init = True
         self._sumsq = None
@@ -133,15 +135,19 @@ class ParamStorage:
     # ---------------------------------------------------------------- deploy
     def deploy(self, named_params: Dict[str, torch.nn.Parameter], owner_ranks: Dict[str, Sequence[int]],
                opt_group_of: Dict[int, int], device: torch.device, global_order: Dict[str, int],
-               symmetric: bool = False):
-        """``named_params``: parameters used on this rank (fqn -> Parameter, tied names deduplicated);
+               symmetric: bool = False, sliced: Optional[Dict[str, Sequence[int]]] = None,
+               symmetric_slices: bool = False):
+        """``sliced``: fqn -> ranks for weights stored as column slices (tensor-partitioned linear layers);
+        such a parameter's local slice belongs to a flat buffer only this rank reduces and updates.
+        ``named_params``: parameters used on this rank (fqn -> Parameter, tied names deduplicated);
         ``owner_ranks``: fqn -> ranks of every stage using it (for ALL parameters of the model, so that every
         rank can create the same communicators in the same order)."""
         me = comm.get_rank()
         self.global_order = dict(global_order)
         self.param_ranks = {k: tuple(sorted(set(v))) for k, v in owner_ranks.items()}
-        comm.create_groups(list(self.param_ranks.values()))
-        keyed: Dict[Tuple[Tuple[int, ...], torch.dtype], FlatGroup] = {}
+        self.sliced = {k: tuple(sorted(set(v))) for k, v in (sliced or {}).items()}
+        comm.create_groups(list(self.param_ranks.values()) + list(self.sliced.values()))
+        keyed: Dict[tuple, FlatGroup] = {}
         order = sorted(named_params.items(),
                        key=lambda kv: (opt_group_of.get(id(kv[1]), 1 << 30), global_order.get(kv[0], 0)))
         for name, p in order:
@@ -149,14 +155,17 @@ class ParamStorage:
             if me not in ranks:
                 continue
             dtype = p.dtype
-            key = (ranks, dtype)
+            sl = self.sliced.get(name)
+            key = ((me,), dtype, sl) if sl else (ranks, dtype, ())
             if key not in keyed:
-                keyed[key] = FlatGroup(ranks, dtype, device)
+                keyed[key] = FlatGroup(key[0], dtype, device)
+                keyed[key].slice_ranks = sl
             keyed[key].add(name, p, opt_group_of.get(id(p), -1))
         # deterministic group order on every rank: smaller rank sets first
-        self.groups = [keyed[k] for k in sorted(keyed, key=lambda k: (len(k[0]), k[0], str(k[1])))]
+        self.groups = [keyed[k] for k in sorted(keyed, key=lambda k: (len(k[0]), k[0], str(k[1]), k[2]))]
         for g in self.groups:
-            g.finalize(self.amp and g.dtype in (torch.float16, torch.bfloat16), self.zero, symmetric)
+            g.finalize(self.amp and g.dtype in (torch.float16, torch.bfloat16), self.zero,
+                       symmetric_slices if g.slice_ranks else symmetric)
             for i, n in enumerate(g.names):
                 self.by_name[n] = (g, i)
         if self.sync_on_init:
@@ -313,6 +322,7 @@ class ParamStorage:
         numel = 1
         for d in shape:
             numel *= d
+        sl = self.sliced.get(name)
         if name in self.by_name:
             g, i = self.by_name[name]
             lo, hi = g.param_range(i)
@@ -328,9 +338,23 @@ class ParamStorage:
                     full = g.flat_master[lo - g.shard[0]:hi - g.shard[0]]
             else:
                 full = g.flat_param[lo:hi]
-            val = full.to(out_dtype).reshape(shape).clone()
+            if sl:
+                # this rank's column block of the full weight; the blocks are summed below
+                ks = shape[1] // len(sl)
+                idx = sl.index(me)
+                val = torch.zeros(shape, dtype=out_dtype, device=full.device)
+                val[:, idx * ks:(idx + 1) * ks] = full.to(out_dtype).reshape(shape[0], ks)
+            else:
+                val = full.to(out_dtype).reshape(shape).clone()
+        elif sl:
+            val = torch.zeros(shape, dtype=out_dtype, device=dev)
         else:
             val = torch.empty(shape, dtype=out_dtype, device=dev)
+        if sl:
+            if comm.get_world_size() > 1:
+                val = val.to(dev)
+                comm.allreduce(val, "sum")
+            return val.cpu()
         if comm.get_world_size() > 1:
             if val.device != dev:
                 val = val.to(dev)

@@ -107,7 +107,7 @@ def main():
     osd = pyrannc.comm_utils.bcast_obj(osd, 0)
     opt.load_state_dict(osd, from_global=True)
     stages = len(wrapped._dep.fwd_graph_order)
-    res = {"ok": ok, "msgs": msgs[:8], "stages": stages, "pipeline": wrapped._dep.pipeline_num,
+    res = {"ok": ok, "msgs": msgs[:8], "stages": stages, "pipeline": wrapped._dep.pipeline_num, "sliced": len(wrapped._storage.sliced),
            "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}}
     all_res = pyrannc._comm.allgather_obj(res)
     if rank == 0:

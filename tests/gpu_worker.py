@@ -41,7 +41,8 @@ def main():
     osd = opt.state_dict(from_global=True)
     err = _lib.read_error()
     info = {"fused": wrapped._fused_reducer is not None, "stages": len(wrapped._dep.fwd_graph_order),
-            "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}, "losses": losses, "err": err}
+            "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}, "losses": losses, "err": err,
+            "sliced": len(wrapped._storage.sliced)}
     infos = pyrannc._comm.allgather_obj(info)
     if rank == 0:
         torch.save({"sd": sd, "opt": osd, "infos": infos}, case["out"])

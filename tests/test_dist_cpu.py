@@ -75,6 +75,26 @@ def test_batchnorm_buffers_two_stages():
     assert res["ranks"][0]["stages"] == 2
 
 
+@pytest.mark.parametrize("opt", ["sgd", "adam"])
+def test_force_dist_matmul_dp2(opt):
+    # every linear weight is stored as column slices over the two replicas; forward, gradients, updates,
+    # state_dict and the gathered optimizer state must still match eager on the full batch
+    res = run_case(2, {"model": "deep", "batch": 8, "opt": opt}, {"RANNC_FORCE_DIST_MATMUL": "true"})
+    assert res["ranks"][0]["sliced"] > 0
+
+
+def test_force_dist_matmul_with_pipeline():
+    res = run_case(4, {"model": "deep", "batch": 16}, {"RANNC_FORCE_DIST_MATMUL": "true",
+                                                       "RANNC_PARTITION_NUM": "2"})
+    assert res["ranks"][0]["stages"] == 2 and res["ranks"][0]["sliced"] > 0
+
+
+def test_verify_partitioning_runs_with_two_stages():
+    # the in-product self check: whole graph vs chained stage graphs on rank 0
+    run_case(2, {"model": "bn", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_VERIFY_PARTITIONING": "true"})
+    run_case(2, {"model": "forkjoin", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_VERIFY_PARTITIONING": "true"})
+
+
 def test_pp_checkpointing():
     run_case(2, {"model": "loss", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2",
                                                 "RANNC_CHECKPOINTING": "true"})

@@ -188,6 +188,44 @@ def test_attention_fwd_bwd(B, S, H, use_bias):
     _close(dq, qr.grad, 3e-2)
 
 
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_attention_dropout_forward_backward_consistency(use_bias):
+    """The backward regenerates the forward's dropout mask.  The mask depends on (seed, b, h, q, key) only,
+    so it can be read out with uniform attention over one-hot values, and then used in an fp32 reference."""
+    from rannc_b200.ops import _lib
+    from rannc_b200.ops import kernels as K
+
+    torch.manual_seed(1)
+    B, S, H, D, pd = 2, 64, 3, 64, 0.25
+    z = torch.zeros(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+    eye = torch.eye(S, device="cuda", dtype=torch.bfloat16)[None, :, None, :].expand(B, S, H, D).contiguous()
+    o, _ = K.attn_fwd(z, z, eye, p_drop=pd, seed=21, offset=2)
+    mask = (o.float() > 0).permute(0, 2, 1, 3).float()          # [B, H, q, key]
+    assert abs(mask.mean().item() - (1 - pd)) < 0.03
+    qkv = torch.randn(B, S, 3, H, D, device="cuda", dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    bias = None
+    if use_bias:
+        bias = torch.zeros(B, S, device="cuda", dtype=torch.float32)
+        bias[:, S - 9:] = -10000.0
+    o, lse = K.attn_fwd(q, k, v, key_bias=bias, p_drop=pd, seed=21, offset=2)
+    qr, kr, vr = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    sc = torch.einsum("bqhd,bkhd->bhqk", qr, kr) * D ** -0.5
+    if bias is not None:
+        sc = sc + bias[:, None, None, :]
+    a = sc.softmax(-1) * mask / (1 - pd)
+    ref = torch.einsum("bhqk,bkhd->bqhd", a, vr)
+    _close(o, ref, 2e-2)
+    do = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+    dq, dk, dv = K.attn_bwd(q, k, v, o, lse, do, key_bias=bias, p_drop=pd, seed=21, offset=2)
+    torch.cuda.synchronize()
+    assert _lib.read_error() == 0
+    ref.backward(do.float())
+    _close(dv, vr.grad, 3e-2)
+    _close(dk, kr.grad, 3e-2)
+    _close(dq, qr.grad, 3e-2)
+
+
 def test_attention_dropout_statistics():
     from rannc_b200.ops import kernels as K
 
@@ -203,3 +241,11 @@ def test_attention_dropout_statistics():
     assert o.float().std().item() > 0.01
     o2, _ = K.attn_fwd(q, k, v, p_drop=0.5, seed=11, offset=1)
     assert torch.equal(o, o2)
+    # keep decisions of neighbouring rows / keys are uncorrelated, and another offset gives another mask
+    vv = torch.eye(64, device="cuda", dtype=torch.bfloat16)[None, :, None, :].expand(1, 64, 2, 64).contiguous()
+    zz = torch.zeros(1, 64, 2, 64, device="cuda", dtype=torch.bfloat16)
+    m1 = (K.attn_fwd(zz, zz, vv, p_drop=0.5, seed=11, offset=1)[0].float() > 0).float()   # [1, q, h, key]
+    m2 = (K.attn_fwd(zz, zz, vv, p_drop=0.5, seed=11, offset=2)[0].float() > 0).float()
+    c = lambda a, b: ((a - a.mean()) * (b - b.mean())).mean().item() / 0.25  # noqa: E731
+    assert abs(c(m1[:, :-1], m1[:, 1:])) < 0.06 and abs(c(m1[..., :-1], m1[..., 1:])) < 0.06
+    assert abs(c(m1[:, :, 0], m1[:, :, 1])) < 0.06 and abs(c(m1, m2)) < 0.06

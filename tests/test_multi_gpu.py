@@ -25,7 +25,7 @@ def _free_port():
     return p
 
 
-def _run(world, case, extra_env=None, timeout=600):
+def _run(world, case, extra_env=None, timeout=600, worker="gpu_worker.py"):
     port = _free_port()
     procs = []
     for r in range(world):
@@ -33,7 +33,7 @@ def _run(world, case, extra_env=None, timeout=600):
         env.update({"RANK": str(r), "WORLD_SIZE": str(world), "LOCAL_RANK": str(r), "MASTER_ADDR": "127.0.0.1",
                     "MASTER_PORT": str(port), "RANNC_LOG_LEVEL": "warning"})
         env.update(extra_env or {})
-        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "gpu_worker.py"),
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", worker),
                                        json.dumps(case)], env=env, cwd=ROOT, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
     outs = []
@@ -47,6 +47,9 @@ def _run(world, case, extra_env=None, timeout=600):
         outs.append(o)
     for p, o in zip(procs, outs):
         assert p.returncode == 0, o[-4000:]
+    if worker != "gpu_worker.py":
+        with open(case["out"]) as f:
+            return json.load(f)
     return torch.load(case["out"], weights_only=False)
 
 
@@ -92,3 +95,23 @@ def test_pipeline_over_two_gpus_matches_data_parallel(tmp_path):
     dp = _run(2, {"out": str(tmp_path / "dp.pt"), "zero": False})
     assert pp["infos"][0]["stages"] == 2 and dp["infos"][0]["stages"] == 1
     _compare(pp, dp, 3e-2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tensor_partitioned_linear_over_peers(tmp_path):
+    n = 4 if _ngpu() >= 4 else 2
+    infos = _run(n, {"out": str(tmp_path / "distop.json")}, {"NCCL_NVLS_ENABLE": "0"}, worker="distop_worker.py")
+    for i in infos:
+        assert i["err_word"] == 0
+        for k, v in i["errs"].items():
+            assert v < 2e-2, (k, v)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_force_dist_matmul_over_two_gpus(tmp_path):
+    env = {"NCCL_NVLS_ENABLE": "0", "RANNC_USE_MULTIMEM": "0"}
+    a = _run(2, {"out": str(tmp_path / "a.pt")}, dict(env, RANNC_FORCE_DIST_MATMUL="true"))
+    b = _run(2, {"out": str(tmp_path / "b.pt")}, env)
+    assert a["infos"][0]["sliced"] > 0 and b["infos"][0]["sliced"] == 0
+    assert all(i["err"] == 0 for i in a["infos"])
+    _compare(a, b, 3e-2)
