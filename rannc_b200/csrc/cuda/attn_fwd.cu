@@ -14,7 +14,8 @@
 // 16-bit in the 128-byte-swizzled K-major layout and returns to the tensor
 // core as the A operand of O += P V, with V read as an MN-major B operand
 // straight from its [key, d] layout.  The S^2 score matrix never reaches HBM.
-// Warps 0..7 = tile 0, warps 8..15 = tile 1, warp 16 = TMA + MMA issue.
+// Warps 0..7 = tile 0, warps 8..15 = tile 1, warps 16 / 17 = MMA issue for tile 0 / 1 (one warp each, so
+// neither tile's chain waits on the other's barriers), warp 18 = TMA loads.
 //
 // Takes the place of the matmul -> div -> add(mask) -> softmax -> dropout ->
 // matmul chain of the traced BERT attention, which the reference runs as
@@ -31,7 +32,7 @@ constexpr int AD = 64;    // head dim
 constexpr int TILE_B = AQ * AD * 2;   // 16 KiB: one [128 x 64] 16-bit tile
 constexpr int P_BYTES = AQ * AK * 2;  // 32 KiB
 constexpr int GROUP = 256;            // softmax threads per query tile
-constexpr int ATT_THREADS = 2 * GROUP + 32;
+constexpr int ATT_THREADS = 2 * GROUP + 96;   // + one MMA-issue warp per tile + the K / V loader
 constexpr int ATT_TMEM_COLS = 512;
 constexpr int TILE_COLS = 192;        // S (128) + O (64) per tile
 constexpr int KB_MAX = 1024;          // key-bias entries staged in shared memory
@@ -72,7 +73,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     uint64_t* s_free = bars + 7;    // [2 tiles]
     uint64_t* p_ready = bars + 9;   // [2 tiles]
     uint64_t* o_done = bars + 11;   // [2 tiles]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* kv_free = bars + 13;  // [2 stages]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,6 +91,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             mbar_init(&s_free[i], GROUP);
             mbar_init(&p_ready[i], GROUP);
             mbar_init(&o_done[i], 1);
+            mbar_init(&kv_free[i], ntiles);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -111,10 +114,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const uint32_t tmem = *tmem_slot;
     constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
 
-    if (warp == 16) {
+    if (warp == 18) {
+        // ------------- K / V loader: stage (j & 1) is refilled once every tile's P V of chunk j is done -------------
         if (lane == 0) {
-            const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AQ, AK);
-            const uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, AQ, AD);
             auto load_kv = [&](int j) {
                 const int st = j & 1;
                 mbar_arrive_expect_tx(&k_full[st], TILE_B);
@@ -122,7 +124,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 mbar_arrive_expect_tx(&v_full[st], TILE_B);
                 tma_load_4d(sV + st * TILE_B, &tmV, &v_full[st], 0, j * AK, h, b);
             };
-            auto issue_s = [&](int t, int j) {
+            mbar_arrive_expect_tx(q_full, ntiles * TILE_B);
+            for (int t = 0; t < ntiles; ++t) tma_load_4d(sQ + t * TILE_B, &tmQ, q_full, 0, q_base + t * AQ, h, b);
+            load_kv(0);
+            if (nchunks > 1) load_kv(1);
+            for (int j = 0; j + 2 < nchunks; ++j) {
+                if (!mbar_wait(&kv_free[j & 1], (j >> 1) & 1, abort_flag)) break;
+                load_kv(j + 2);
+            }
+        }
+    } else if (warp >= 16) {
+        // ------------- MMA issue, one warp per query tile: the two tiles' chains advance independently -------------
+        const int t = warp - 16;
+        if (lane == 0 && t < ntiles) {
+            const uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, AQ, AK);
+            const uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, AQ, AD);
+            auto issue_s = [&](int j) {
                 const uint32_t qa = smem_u32(sQ + t * TILE_B), ka = smem_u32(sK + (j & 1) * TILE_B);
 #pragma unroll
                 for (int k = 0; k < AD / 16; ++k)
@@ -130,41 +147,31 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                              make_smem_desc_sw128(ka + k * 32, 16, 1024), idesc_s, k != 0);
                 umma_commit(&s_full[t]);
             };
-            mbar_arrive_expect_tx(q_full, ntiles * TILE_B);
-            for (int t = 0; t < ntiles; ++t) tma_load_4d(sQ + t * TILE_B, &tmQ, q_full, 0, q_base + t * AQ, h, b);
-            load_kv(0);
-            if (nchunks > 1) load_kv(1);
             bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
             if (ok) {
                 tc_fence_after();
-                for (int t = 0; t < ntiles; ++t) issue_s(t, 0);
+                issue_s(0);
             }
             for (int j = 0; j < nchunks && ok; ++j) {
                 const uint32_t kv_phase = (j >> 1) & 1, nkv_phase = ((j + 1) >> 1) & 1;
-                for (int t = 0; t < ntiles && ok; ++t) {
-                    if (j + 1 < nchunks) {
-                        ok = mbar_wait(&k_full[(j + 1) & 1], nkv_phase, abort_flag) &&
-                             mbar_wait(&s_free[t], j & 1, abort_flag);
-                        if (!ok) break;
-                        tc_fence_after();
-                        issue_s(t, j + 1);
-                    }
-                    ok = mbar_wait(&p_ready[t], j & 1, abort_flag) && mbar_wait(&v_full[j & 1], kv_phase, abort_flag);
+                if (j + 1 < nchunks) {
+                    ok = mbar_wait(&k_full[(j + 1) & 1], nkv_phase, abort_flag) &&
+                         mbar_wait(&s_free[t], j & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t pa = smem_u32(sP + t * P_BYTES), va = smem_u32(sV + (j & 1) * TILE_B);
+                    issue_s(j + 1);
+                }
+                ok = mbar_wait(&p_ready[t], j & 1, abort_flag) && mbar_wait(&v_full[j & 1], kv_phase, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t pa = smem_u32(sP + t * P_BYTES), va = smem_u32(sV + (j & 1) * TILE_B);
 #pragma unroll
-                    for (int k = 0; k < AK / 16; ++k)
-                        umma_f16(tmem + t * TILE_COLS + 128,
-                                 make_smem_desc_sw128(pa + (k >> 2) * (P_BYTES / 2) + (k & 3) * 32, 16, 1024),
-                                 make_smem_desc_sw128(va + k * 2048, 8192, 1024), idesc_o, (j | k) != 0);
-                    umma_commit(&o_done[t]);
-                }
-                if (ok && j + 2 < nchunks) {
-                    // stage j & 1 is free once both tiles' products with chunk j are done
-                    for (int t = 0; t < ntiles && ok; ++t) ok = mbar_wait(&o_done[t], j & 1, abort_flag);
-                    if (ok) load_kv(j + 2);
-                }
+                for (int k = 0; k < AK / 16; ++k)
+                    umma_f16(tmem + t * TILE_COLS + 128,
+                             make_smem_desc_sw128(pa + (k >> 2) * (P_BYTES / 2) + (k & 3) * 32, 16, 1024),
+                             make_smem_desc_sw128(va + k * 2048, 8192, 1024), idesc_o, (j | k) != 0);
+                umma_commit(&o_done[t]);
+                umma_commit(&kv_free[j & 1]);
             }
         }
     } else if ((warp >> 3) < ntiles) {
@@ -231,8 +238,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             xch[half * 128 + r] = cm;
             bar_sync_named(1 + t, GROUP);
             cm = fmaxf(cm, xch[(half ^ 1) * 128 + r]);
+            // Lazy rescaling: the running reference m only moves when the row maximum grew by more than
+            // 2^8 since it was set; until then probabilities are taken relative to the old reference
+            // (at most 256, exact in the final normalisation), and the accumulator round trip through
+            // tensor memory is skipped for the whole warp.
             const float m_new = fmaxf(m, cm);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            float m_use;
+            if (m_new - m <= 8.f)
+                m_use = m;
+            else
+                m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = exp2f(m - m_use);
             // the previous P V product must be complete before P is overwritten and O rescaled
             if (j > 0) {
@@ -291,7 +306,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 }
             }
             l = l * alpha + rs;
-            m = m_new;
+            m = m_new == -INFINITY ? -INFINITY : m_use;
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(&p_ready[t]);

@@ -13,13 +13,22 @@
 // Structure: persistent CTAs (one per SM), 128 x 256 output tile, K step 64,
 // 4-stage TMA->smem ring, fp32 accumulators double-buffered in TMEM (2 x 256
 // columns) so the epilogue of tile i overlaps the main loop of tile i+1.
-// Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue.
+// Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = epilogue (with K = 1024 a tile's main loop is
+// only 16 k steps, and four warps could not drain a 128 x 256 accumulator in that time).
+//
+// PAIR variant (cta_group::2): two CTAs of a cluster -- the two SMs of a TPC -- share a 256 x 256 tile.
+// Each CTA loads its own 128 rows of A and HALF of the B tile (so a k step moves 32 KiB per SM instead
+// of 48 KiB: the single-CTA tile is limited by the L2 -> shared-memory path, not by the tensor core),
+// one thread of the first CTA issues the MMAs for both, and each CTA keeps and drains the accumulator of
+// its own 128 rows.  Completion of both CTAs' loads is counted on the first CTA's barrier; stage-free
+// and accumulator-full signals go to both CTAs with one multicast commit.  No load is multicast.
 //
 // This kernel takes the place of the cuBLAS calls the reference reaches through
 // aten::linear / aten::matmul in its TorchScript interpreter
 // (src/torch/TorchDriver.cpp:566) and in src/distop/DistMatmul.cpp:97-214.
 #include "gemm_tcgen05.h"
 
+#include <cstdlib>
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -29,14 +38,22 @@ namespace rb {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;                         // two per TMEM lane quarter: each drains 128 of the 256 columns
+constexpr int EPI_THREADS = 32 * EPI_WARPS;
+constexpr int GEMM_THREADS = 64 + EPI_THREADS;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int GROUP_M = 8;
+
+template <bool PAIR>
+struct Cfg {
+    static constexpr int STAGES = PAIR ? 6 : 4;
+    static constexpr int B_ROWS = PAIR ? BN / 2 : BN;       // extent of the B tile one CTA loads
+    static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;   // 16 / 32 KiB
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int TILE_M = PAIR ? 2 * BM : BM;       // rows of the output tile of a CTA (pair)
+};
 
 struct GemmKernelParams {
     int M, N, K, batch;
@@ -134,10 +151,14 @@ __device__ __forceinline__ void store32(T* ptr, bool vec_ok, int valid, const fl
     }
 }
 
-template <typename InT, typename OutT>
+template <typename InT, typename OutT, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                         const __grid_constant__ CUtensorMap tmB, const GemmKernelParams p) {
+    constexpr int STAGES = Cfg<PAIR>::STAGES;
+    constexpr int B_STAGE_BYTES = Cfg<PAIR>::B_STAGE_BYTES;
+    constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
+    constexpr int TILE_M = Cfg<PAIR>::TILE_M;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -153,6 +174,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // PAIR: rank of this CTA in its pair; the first CTA issues the MMAs and owns the `full` / `tempty` counts
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+    const int tile0 = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -161,7 +186,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tfull[a], 1);
-            mbar_init(&tempty[a], 128);
+            mbar_init(&tempty[a], PAIR ? 2 * EPI_WARPS : EPI_THREADS);   // PAIR: one arrival per epilogue warp of both CTAs
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -169,11 +194,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         tma_prefetch_desc(&tmB);
     }
     if (warp == 2) {
-        tmem_alloc(tmem_slot, TMEM_COLS);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, TMEM_COLS);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, TMEM_COLS);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -184,10 +215,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t phase = 0;
             uint32_t ag_ready = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            for (int tile = tile0; tile < p.num_tiles && ok; tile += tile_step) {
                 int mb, nb, b, kb_begin, kb_end;
                 tile_coords(p, tile, mb, nb, b, kb_begin, kb_end);
-                const int m0 = mb * BM, n0 = nb * BN;
+                const int m0 = mb * TILE_M + static_cast<int>(crank) * BM;
+                const int n0 = nb * BN + (PAIR ? static_cast<int>(crank) * (BN / 2) : 0);
                 for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
                     int kb = kbi;
                     if (p.ag_nranks > 1) {
@@ -227,25 +259,45 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
                     uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
                     uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
                     const int k0 = kb * BK;
-                    if (p.a_major == 0) {
-                        tma_load_3d(a_dst, &tmA, &full[stage], k0, m0, b);
-                    } else {
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the first CTA's barrier
+                        if (crank == 0) mbar_arrive_expect_tx(&full[stage], 2 * STAGE_BYTES);
+                        const uint32_t fb = mapa_shared(smem_u32(&full[stage]), 0);
+                        if (p.a_major == 0) {
+                            tma_load_3d_pair(a_dst, &tmA, fb, k0, m0, b);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BM / 64; ++c)
-                            tma_load_3d(a_dst + c * (BK * 128), &tmA, &full[stage], m0 + c * 64,
-                                        k0, b);
-                    }
-                    if (p.b_major == 0) {
-                        tma_load_3d(b_dst, &tmB, &full[stage], k0, n0, b);
-                    } else {
+                            for (int c = 0; c < BM / 64; ++c)
+                                tma_load_3d_pair(a_dst + c * (BK * 128), &tmA, fb, m0 + c * 64, k0, b);
+                        }
+                        if (p.b_major == 0) {
+                            tma_load_3d_pair(b_dst, &tmB, fb, k0, n0, b);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BN / 64; ++c)
-                            tma_load_3d(b_dst + c * (BK * 128), &tmB, &full[stage], n0 + c * 64,
-                                        k0, b);
+                            for (int c = 0; c < Cfg<PAIR>::B_ROWS / 64; ++c)
+                                tma_load_3d_pair(b_dst + c * (BK * 128), &tmB, fb, n0 + c * 64, k0, b);
+                        }
+                    } else {
+                        mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+                        if (p.a_major == 0) {
+                            tma_load_3d(a_dst, &tmA, &full[stage], k0, m0, b);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BM / 64; ++c)
+                                tma_load_3d(a_dst + c * (BK * 128), &tmA, &full[stage], m0 + c * 64,
+                                            k0, b);
+                        }
+                        if (p.b_major == 0) {
+                            tma_load_3d(b_dst, &tmB, &full[stage], k0, n0, b);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BN / 64; ++c)
+                                tma_load_3d(b_dst + c * (BK * 128), &tmB, &full[stage], n0 + c * 64,
+                                            k0, b);
+                        }
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -255,10 +307,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---------------- MMA issuer ----------------
+        if (lane == 0 && crank == 0) {
+            // ---------------- MMA issuer (PAIR: the first CTA issues for both) ----------------
             constexpr int fmt = (sizeof(InT) == 2 && std::is_same<InT, __nv_bfloat16>::value) ? 1 : 0;
-            const uint32_t idesc = make_idesc_f16(fmt, p.a_major, p.b_major, BM, BN);
+            const uint32_t idesc = make_idesc_f16(fmt, p.a_major, p.b_major, TILE_M, BN);
             // per-UMMA_K (16 elements) advance of the smem start address
             const uint32_t a_kstep = (p.a_major == 0) ? 32u : 2048u;
             const uint32_t b_kstep = (p.b_major == 0) ? 32u : 2048u;
@@ -268,16 +320,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t phase = 0;
             bool ok = true;
             int it = 0;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            for (int tile = tile0; tile < p.num_tiles && ok; tile += tile_step, ++it) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
-                if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) break;
+                if (!(PAIR ? mbar_wait_cluster(&tempty[acc], acc_phase ^ 1, abort_flag)
+                           : mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)))
+                    break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 int mb_, nb_, b_, kb_begin, kb_end;
                 tile_coords(p, tile, mb_, nb_, b_, kb_begin, kb_end);
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    if (!mbar_wait(&full[stage], phase, abort_flag)) {
+                    if (!(PAIR ? mbar_wait_cluster(&full[stage], phase, abort_flag)
+                               : mbar_wait(&full[stage], phase, abort_flag))) {
                         ok = false;
                         break;
                     }
@@ -288,38 +343,49 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint64_t da = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
                         const uint64_t db = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
-                        umma_f16(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+                        if constexpr (PAIR)
+                            umma_f16_pair(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+                        else
+                            umma_f16(d_tmem, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
                     }
-                    umma_commit(&empty[stage]);
+                    if constexpr (PAIR)
+                        umma_commit_pair(&empty[stage], 3);   // frees the stage in both CTAs
+                    else
+                        umma_commit(&empty[stage]);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
-                if (ok) umma_commit(&tfull[acc]);
+                if (ok) {
+                    if constexpr (PAIR)
+                        umma_commit_pair(&tfull[acc], 3);
+                    else
+                        umma_commit(&tfull[acc]);
+                }
             }
         }
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
         if (p.ag_nranks > 1) {
-            // all-gather prologue: the 128 epilogue threads of every CTA copy their share of each peer's
-            // shard into the local B buffer (plain 16-byte peer loads), own shard last in the rotation so
-            // remote traffic starts first; a counter per shard tells the TMA producers when it is whole
+            // all-gather prologue: the epilogue threads of every CTA copy their share of each peer's
+            // shard into the local B buffer (plain 16-byte peer loads), in the order the k loop consumes
+            // them (own shard first); a counter per shard tells the TMA producers when it is whole
             const int t = threadIdx.x - 64;
             const int vec_per_row = p.ag_cols / 8;
             const long long total = static_cast<long long>(p.ag_rows) * vec_per_row;
             const long long dst_ld = static_cast<long long>(p.ag_nranks) * p.ag_cols;
-            for (int rr = 1; rr <= p.ag_nranks; ++rr) {
-                const int r = (p.ag_my_idx + rr) % p.ag_nranks;
+            for (int rr = 0; rr < p.ag_nranks; ++rr) {
+                const int r = (p.ag_my_idx + rr) % p.ag_nranks;   // the order in which the k loop needs them
                 const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[r]);
                 InT* dst = reinterpret_cast<InT*>(p.ag_dst) + static_cast<long long>(r) * p.ag_cols;
-                for (long long i = static_cast<long long>(blockIdx.x) * 128 + t; i < total;
-                     i += static_cast<long long>(gridDim.x) * 128 * 4) {
+                for (long long i = static_cast<long long>(blockIdx.x) * EPI_THREADS + t; i < total;
+                     i += static_cast<long long>(gridDim.x) * EPI_THREADS * 4) {
                     uint4 v[4];
                     long long idx[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
-                        idx[u] = i + static_cast<long long>(u) * gridDim.x * 128;
+                        idx[u] = i + static_cast<long long>(u) * gridDim.x * EPI_THREADS;
                         if (idx[u] < total) v[u] = src[idx[u]];
                     }
 #pragma unroll
@@ -332,11 +398,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 }
                 asm volatile("fence.proxy.async.global;" ::: "memory");
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (t == 0) atomicAdd(p.ag_flags + r, 1u);
             }
         }
         const int q = warp & 3;  // TMEM lane quarter this warp may access
+        const int chalf = (warp - 2) >> 2;   // which 128 of the tile's 256 columns this warp drains
         const int row_in_tile = q * 32 + lane;
         const bool has_bias = p.flags & RB_GEMM_BIAS;
         const bool has_res = p.flags & RB_GEMM_RESIDUAL;
@@ -347,19 +414,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const bool in_al = (p.ldd % 8 == 0);
         const bool out_al = (sizeof(OutT) == 2) ? (p.ldd % 8 == 0) : (p.ldd % 4 == 0);
         int it = 0;
-        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+        for (int tile = tile0; tile < p.num_tiles; tile += tile_step, ++it) {
             int mb, nb, b, kb_begin, kb_end;
             tile_coords(p, tile, mb, nb, b, kb_begin, kb_end);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
             tc_fence_after();
-            const int row = mb * BM + row_in_tile;
+            const int row = mb * TILE_M + static_cast<int>(crank) * BM + row_in_tile;
             const bool row_ok = row < p.M;
             const long long row_off = static_cast<long long>(b) * p.strideD +
                                       static_cast<long long>(row) * p.ldd;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
                 const int col = nb * BN + c * 32;
                 if (col >= p.N) break;
                 uint32_t r[32];
@@ -433,7 +500,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 store32(dptr, full_chunk && out_al, valid, v);
             }
             tc_fence_before();
-            mbar_arrive(&tempty[acc]);
+            if constexpr (PAIR) {
+                // the accumulator may be overwritten once the epilogue warps of BOTH CTAs have drained it
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+            } else {
+                mbar_arrive(&tempty[acc]);
+            }
         }
     }
 
@@ -450,9 +523,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         __syncthreads();
     }
+    // PAIR: neither CTA leaves (or frees tensor memory) while the other may still signal its barriers or
+    // its MMAs may still write this CTA's accumulators
+    if (PAIR) cluster_sync_all();
     if (warp == 2) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if (PAIR)
+            tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else
+            tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -549,24 +628,60 @@ int num_sms() {
     return n[dev];
 }
 
-template <typename InT, typename OutT>
+template <typename InT, typename OutT, bool PAIR>
 static int launch(const RbGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB,
                   const GemmKernelParams& p, cudaStream_t stream) {
-    auto kern = gemm_tcgen05_kernel<InT, OutT>;
+    auto kern = gemm_tcgen05_kernel<InT, OutT, PAIR>;
+    constexpr int smem = Cfg<PAIR>::SMEM_BYTES;
     static bool attr_set[64] = {false};
+    static int max_clusters[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63]) {
-        cudaError_t e =
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return -static_cast<int>(e);
         attr_set[dev & 63] = true;
     }
-    int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
-    if (a.max_ctas > 0 && grid > a.max_ctas) grid = a.max_ctas;
-    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
-    cudaError_t e = cudaGetLastError();
+    if (!PAIR) {
+        int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
+        if (a.max_ctas > 0 && grid > a.max_ctas) grid = a.max_ctas;
+        kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, p);
+        cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? 0 : -static_cast<int>(e);
+    }
+    // one cluster of two CTAs per TPC; persistent over the pair tiles
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (!max_clusters[dev & 63]) {
+        cfg.gridDim = dim3(num_sms(), 1, 1);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = num_sms() / 2;
+        max_clusters[dev & 63] = n;
+    }
+    int clusters = p.num_tiles < max_clusters[dev & 63] ? p.num_tiles : max_clusters[dev & 63];
+    if (a.max_ctas > 1 && clusters > a.max_ctas / 2) clusters = a.max_ctas / 2;
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+// RB_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel
+static bool pair_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RB_GEMM_PAIR");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
 }
 
 }  // namespace rb
@@ -579,21 +694,6 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) ||
         (a->lda % 8) || (a->ldb % 8) || (a->batch > 1 && ((a->strideA % 8) || (a->strideB % 8))))
         return -2;
-    CUtensorMap tmA, tmB;
-    int rc;
-    const uint64_t sA = a->batch > 1 ? a->strideA * 2 : (a->a_major == 0 ? a->M : a->K) * a->lda * 2;
-    const uint64_t sB = a->batch > 1 ? a->strideB * 2 : (a->b_major == 0 ? a->N : a->K) * a->ldb * 2;
-    if (a->a_major == 0)
-        rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->K, a->M, a->batch, a->lda * 2, sA, BK, BM, 1);
-    else
-        rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->M, a->K, a->batch, a->lda * 2, sA, 64, BK, 1);
-    if (rc) return rc;
-    if (a->b_major == 0)
-        rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->K, a->N, a->batch, a->ldb * 2, sB, BK, BN, 1);
-    else
-        rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->N, a->K, a->batch, a->ldb * 2, sB, 64, BK, 1);
-    if (rc) return rc;
-
     GemmKernelParams p;
     p.M = static_cast<int>(a->M);
     p.N = static_cast<int>(a->N);
@@ -601,7 +701,17 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     p.batch = static_cast<int>(a->batch);
     p.a_major = a->a_major;
     p.b_major = a->b_major;
-    p.num_m_blocks = (p.M + BM - 1) / BM;
+    // The pair kernel (256 x 256 tile over two SMs) serves every GEMM with enough work to fill the GPU:
+    // enough tiles, or few tiles and a long K that is split (weight gradients).  Gather / scatter
+    // variants and small problems stay on the single-CTA kernel.
+    const bool accum32 = a->out_dtype == 1 && a->flags == RB_GEMM_ACCUM;
+    bool pair = pair_enabled() && a->ag_nranks <= 1 && a->rs_nranks <= 1;
+    if (pair) {
+        const long long pt = ((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + BN - 1) / BN) * a->batch;
+        const long long kbs = (a->K + BK - 1) / BK;
+        if (pt < num_sms() / 2 && !(accum32 && a->M > BM && pt * (kbs / 4) >= num_sms() / 2)) pair = false;
+    }
+    p.num_m_blocks = pair ? (p.M + 2 * BM - 1) / (2 * BM) : (p.M + BM - 1) / BM;
     p.num_n_blocks = (p.N + BN - 1) / BN;
     p.base_tiles = p.num_m_blocks * p.num_n_blocks * p.batch;
     p.num_kb = (p.K + BK - 1) / BK;
@@ -629,13 +739,13 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
         return -5;
     // Few output tiles and a long K (weight gradients): split K over CTAs and accumulate with
     // reductions.  Only for fp32 outputs that accumulate and have no other epilogue work.
-    if (a->out_dtype == 1 && a->flags == RB_GEMM_ACCUM && p.base_tiles < num_sms() && p.num_kb >= 8) {
-        const int sms = num_sms();
+    const int units = pair ? num_sms() / 2 : num_sms();   // CTAs (or CTA pairs) that run at once
+    if (accum32 && p.base_tiles < units && p.num_kb >= 8) {
         double best = 0.0;
-        for (int s = 1; s <= 16 && s * 4 <= p.num_kb; ++s) {
+        for (int s = 1; s <= 32 && s * 4 <= p.num_kb; ++s) {
             const int work = p.base_tiles * s;
-            const int waves = (work + sms - 1) / sms;
-            const double eff = static_cast<double>(work) / (waves * sms) - 0.01 * s;
+            const int waves = (work + units - 1) / units;
+            const double eff = static_cast<double>(work) / (waves * units) - 0.005 * s;
             if (eff > best + 1e-9) {
                 best = eff;
                 p.split_k = s;
@@ -657,12 +767,33 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     p.err = error_word_ptr();
     if (!p.err) return -3;
 
+    CUtensorMap tmA, tmB;
+    int rc;
+    const uint64_t sA = a->batch > 1 ? a->strideA * 2 : (a->a_major == 0 ? a->M : a->K) * a->lda * 2;
+    const uint64_t sB = a->batch > 1 ? a->strideB * 2 : (a->b_major == 0 ? a->N : a->K) * a->ldb * 2;
+    if (a->a_major == 0)
+        rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->K, a->M, a->batch, a->lda * 2, sA, BK, BM, 1);
+    else
+        rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->M, a->K, a->batch, a->lda * 2, sA, 64, BK, 1);
+    if (rc) return rc;
+    if (a->b_major == 0)
+        rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->K, a->N, a->batch, a->ldb * 2, sB, BK, pair ? BN / 2 : BN, 1);
+    else
+        rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->N, a->K, a->batch, a->ldb * 2, sB, 64, BK, 1);
+    if (rc) return rc;
+
     if (a->in_dtype == 1) {
-        if (a->out_dtype == 0) return launch<__nv_bfloat16, __nv_bfloat16>(*a, tmA, tmB, p, stream);
-        return launch<__nv_bfloat16, float>(*a, tmA, tmB, p, stream);
+        if (a->out_dtype == 0)
+            return pair ? launch<__nv_bfloat16, __nv_bfloat16, true>(*a, tmA, tmB, p, stream)
+                        : launch<__nv_bfloat16, __nv_bfloat16, false>(*a, tmA, tmB, p, stream);
+        return pair ? launch<__nv_bfloat16, float, true>(*a, tmA, tmB, p, stream)
+                    : launch<__nv_bfloat16, float, false>(*a, tmA, tmB, p, stream);
     } else {
-        if (a->out_dtype == 0) return launch<__half, __half>(*a, tmA, tmB, p, stream);
-        return launch<__half, float>(*a, tmA, tmB, p, stream);
+        if (a->out_dtype == 0)
+            return pair ? launch<__half, __half, true>(*a, tmA, tmB, p, stream)
+                        : launch<__half, __half, false>(*a, tmA, tmB, p, stream);
+        return pair ? launch<__half, float, true>(*a, tmA, tmB, p, stream)
+                    : launch<__half, float, false>(*a, tmA, tmB, p, stream);
     }
 }
 

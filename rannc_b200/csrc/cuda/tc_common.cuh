@@ -369,13 +369,30 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int fmt, int a_major, int 
 // ---------------------------------------------------------------------------
 // numeric helpers
 // ---------------------------------------------------------------------------
+// GELU with the exact (erf) form.  Phi(x) = 0.5 (1 + erf(x / sqrt 2)) comes from the rational-exponential
+// approximation erf(z) = 1 - (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z), z >= 0 (absolute error
+// below 2e-7, far under 16-bit output precision): one reciprocal, one exponential and seven FMAs instead
+// of the library erff's branches.  The lower tail is formed without cancellation (Phi(x) = q for x < 0),
+// and exp(-z^2) = exp(-x^2 / 2) is shared with the density in the gradient.
+__device__ __forceinline__ float gelu_phi(float x, float& exp_half_x2) {
+    const float az = fabsf(x) * 0.70710678118654752f;
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, az, 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    exp_half_x2 = __expf(-az * az);
+    const float q = 0.5f * poly * t * exp_half_x2;
+    return x >= 0.f ? 1.0f - q : q;
+}
 __device__ __forceinline__ float gelu_erf(float x) {
-    return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    float e;
+    return x * gelu_phi(x, e);
 }
 __device__ __forceinline__ float gelu_erf_grad(float x) {
-    const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
-    const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-    return cdf + x * pdf;
+    float e;
+    const float cdf = gelu_phi(x, e);
+    return fmaf(x * 0.3989422804014327f, e, cdf);
 }
 
 template <typename T>
