@@ -127,10 +127,14 @@ int64_t getOptMemSize(const IRGraph& g, const PartitioningConf& conf, int zero_r
         const bool half = v.type.tensor_elem_type == IRTensorElemType::HALF ||
                           v.type.tensor_elem_type == IRTensorElemType::BFLOAT16;
         if (conf.use_amp_master_params && half) {
-            // fp32 gradient buffer (whole), fp32 master copy and optimizer state (sharded under ZeRO)
+            // fp32 gradient buffer (whole), fp32 master copy and optimizer state (sharded under ZeRO);
+            // with offload_params the master copy and the optimizer state live in pinned host memory and
+            // only a fixed staging window is on the device
             total += 2 * sz;
-            total += (2 * sz) / z;
-            total += (static_cast<int64_t>(conf.opt_param_factor) * 2 * sz) / z;
+            if (!conf.offload_params) {
+                total += (2 * sz) / z;
+                total += (static_cast<int64_t>(conf.opt_param_factor) * 2 * sz) / z;
+            }
         } else {
             total += sz;  // gradient
             total += (static_cast<int64_t>(conf.opt_param_factor) * sz) / z;

@@ -48,6 +48,8 @@ int rb_attn_bwd(const RbAttnArgs* args, void* stream);
 namespace rb {
 int make_tmap_4d(CUtensorMap* out, const void* base, int fmt, uint64_t d0, uint64_t d1, uint64_t d2,
                  uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1);
+int make_tmap_4d_f32(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
+                     uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1);
 int* error_word_ptr();
 }
 #endif

@@ -8,9 +8,12 @@
 // key row) and feeds them back to the tensor core:
 //     dV_j += Pt  dO_i        dK_j += dSt Q_i                  (TMEM accumulators)
 //     dQ_i  = dSt^T K_j  -- the same dSt tile read as an MN-major A operand --
-// dQ_i is drained from TMEM with vector red.global.add into an fp32 scratch
-// buffer that a last kernel converts to the 16-bit dQ.  Q_i / dO_i stream
-// through a 2-stage TMA ring.  Warps 0..3 = math, warp 4 = TMA + MMA issue.
+// dQ_i is drained from TMEM into a swizzled fp32 staging tile and added to an
+// fp32 scratch buffer by ONE bulk tensor reduction per half tile (the copy
+// engine does the read-modify-write; the math threads do not wait for it); a
+// last kernel converts the scratch to the 16-bit dQ.  Q_i / dO_i stream
+// through a 2-stage TMA ring; lse / delta of the next query block are fetched
+// while the current one is processed.  Warps 0..7 = math, warp 8 = TMA + MMA issue.
 //
 // Takes the place of the autograd graph the reference runs for the traced
 // attention chain (src/torch/TorchDriver.cpp:642-847).
@@ -20,21 +23,16 @@
 
 namespace rb {
 
-constexpr int BQ = 128, BKEYS = 128, BD = 64;
+constexpr int BQ = 128, BKEYS = 128;
 constexpr int TILE = 128 * 64 * 2;       // 16 KiB
 constexpr int SQ_BYTES = 128 * 128 * 2;  // 32 KiB
 constexpr int BWD_MATH = 256;
 constexpr int BWD_THREADS = BWD_MATH + 32;
 constexpr int BWD_TMEM_COLS = 512;
 constexpr int C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
-// K, V + (Q, dO) x 2 stages + Pt, dSt + per-step (lse, delta, row hash) x 2 + barriers
-constexpr int BWD_SMEM = 2 * TILE + 4 * TILE + 2 * SQ_BYTES + 6 * 128 * 4 + 128;
-
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
-                 "f"(d)
-                 : "memory");
-}
+constexpr int DQ_STAGE = 128 * 64 * 4;   // 32 KiB: [2 column halves][128 rows x 128 B]
+// K, V + (Q, dO) x 2 stages + Pt, dSt + dQ staging + per-step (lse, delta, row hash) x 2 + barriers
+constexpr int BWD_SMEM = 2 * TILE + 4 * TILE + 2 * SQ_BYTES + DQ_STAGE + 6 * 128 * 4 + 128;
 
 struct AttnBwdParams {
     int B, H, S;
@@ -56,7 +54,7 @@ template <typename T>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
     attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const AttnBwdParams p) {
+                    const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = smem + TILE;
@@ -64,7 +62,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     uint8_t* sdO = smem + 4 * TILE;  // [2]
     uint8_t* sPt = smem + 6 * TILE;
     uint8_t* sdSt = sPt + SQ_BYTES;
-    float* s_lse = reinterpret_cast<float*>(sdSt + SQ_BYTES);       // [2][128]
+    uint8_t* sDQ = sdSt + SQ_BYTES;
+    float* s_lse = reinterpret_cast<float*>(sDQ + DQ_STAGE);        // [2][128]
     float* s_delta = s_lse + 256;                                   // [2][128]
     uint32_t* s_rhash = reinterpret_cast<uint32_t*>(s_delta + 256);  // [2][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_rhash + 256);
@@ -74,7 +73,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     uint64_t* s_free = bars + 4;
     uint64_t* pds_ready = bars + 5;
     uint64_t* mma_done = bars + 6;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    uint64_t* dq_free = bars + 7;    // the previous bulk reduction has read the staging tile
+    uint64_t* dq_ready = bars + 8;   // every math thread has written its part of the staging tile
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,6 +90,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         mbar_init(s_free, BWD_MATH);
         mbar_init(pds_ready, BWD_MATH);
         mbar_init(mma_done, 1);
+        mbar_init(dq_free, 1);
+        mbar_init(dq_ready, BWD_MATH);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -191,31 +194,59 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         uint8_t* drow = sdSt + row_off;
         bool ok = true;
 
-        auto drain_dq = [&](int i) {
-            // dQ block i: lane r = query row i*128 + r; this thread adds 32 of its 64 columns
-            const int q = i * BQ + r;
-            float* dst = p.dq_accum + ((static_cast<long long>(b) * p.S + q) * p.H + h) * BD + half * 32;
+        auto drain_dq = [&](int i) -> bool {
+            // dQ block i: lane r = query row i*128 + r; this thread stages 32 of its 64 columns
             uint32_t v[32];
             tmem_ld32(tmem + lane_addr + C_DQ + half * 32, v);
             tmem_ld_wait();
-            if (q < p.S) {
-#pragma unroll
-                for (int g = 0; g < 8; ++g)
-                    red_add_v4(dst + g * 4, __uint_as_float(v[g * 4]) * p.scale,
-                               __uint_as_float(v[g * 4 + 1]) * p.scale, __uint_as_float(v[g * 4 + 2]) * p.scale,
-                               __uint_as_float(v[g * 4 + 3]) * p.scale);
+            if (threadIdx.x == 0) {
+                tma_store_wait_read<0>();   // the previous reduction no longer reads the staging tile
+                mbar_arrive(dq_free);
             }
+            if (!mbar_wait(dq_free, i & 1, abort_flag)) return false;
+            uint8_t* row = sDQ + half * (DQ_STAGE / 2) + (r >> 3) * 1024 + sw * 128;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+                *reinterpret_cast<float4*>(row + ((static_cast<uint32_t>(g) ^ sw) << 4)) =
+                    make_float4(__uint_as_float(v[g * 4]) * p.scale, __uint_as_float(v[g * 4 + 1]) * p.scale,
+                                __uint_as_float(v[g * 4 + 2]) * p.scale, __uint_as_float(v[g * 4 + 3]) * p.scale);
+            fence_proxy_async();
+            mbar_arrive(dq_ready);
+            if (threadIdx.x == 0) {
+                if (!mbar_wait(dq_ready, i & 1, abort_flag)) return false;
+                tma_reduce_add_4d(&tmDQ, sDQ, 0, i * BQ, h, b);
+                tma_reduce_add_4d(&tmDQ, sDQ + DQ_STAGE / 2, 32, i * BQ, h, b);
+                tma_store_commit();
+            }
+            return true;
         };
 
+        // lse / delta of the first query block; later blocks are fetched one step ahead
+        float n_lse = 0.f, n_delta = 0.f;
+        bool n_lse_raw = false;   // n_lse still in natural-log units (as loaded)
+        if (half == 0) {
+            n_lse = r < p.S ? p.lse[bh * p.S + r] * 1.4426950408889634f : INFINITY;
+            n_delta = r < p.S ? p.delta[bh * p.S + r] : 0.f;
+        }
         for (int i = 0; i < nq; ++i) {
             const int st = i & 1;
             const int q0 = i * BQ;
             if (half == 0) {
                 // +inf for rows past the end of the sequence: their probabilities come out as exp2(-inf) = 0
-                const int q = q0 + r;
-                s_lse[st * 128 + r] = q < p.S ? p.lse[bh * p.S + q] * 1.4426950408889634f : INFINITY;
-                s_delta[st * 128 + r] = q < p.S ? p.delta[bh * p.S + q] : 0.f;
-                s_rhash[st * 128 + r] = drop_row_hash(p.seed, b, h, q, p.H, p.S);
+                s_lse[st * 128 + r] = n_lse_raw ? n_lse * 1.4426950408889634f : n_lse;
+                s_delta[st * 128 + r] = n_delta;
+                s_rhash[st * 128 + r] = drop_row_hash(p.seed, b, h, q0 + r, p.H, p.S);
+                // issued here (volatile: not sunk to the use), consumed at the top of the next step
+                const int qn = q0 + BQ + r;
+                if (i + 1 < nq && qn < p.S) {
+                    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(n_lse) : "l"(p.lse + bh * p.S + qn));
+                    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(n_delta) : "l"(p.delta + bh * p.S + qn));
+                    n_lse_raw = true;
+                } else {
+                    n_lse = INFINITY;
+                    n_delta = 0.f;
+                    n_lse_raw = false;
+                }
             }
             bar_sync_named(1, BWD_MATH);
             if (!mbar_wait(s_full, i & 1, abort_flag)) {
@@ -228,17 +259,23 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             // occupy the shared-memory tiles.  Pt carries the dropout mask without its 1 / (1 - p)
             // factor (dV is scaled once at the end); dSt = P (mask dP / (1 - p) - delta).
             uint4 pk[2][4], dk4[2][4];
+            // the second half of the columns is fetched from tensor memory while the first is processed
+            uint32_t svb[2][32], dvb[2][32];
+            tmem_ld32(tmem + lane_addr + C_ST + half * 64, svb[0]);
+            tmem_ld32(tmem + lane_addr + C_DPT + half * 64, dvb[0]);
+            tmem_ld_wait();
+            tmem_ld32(tmem + lane_addr + C_ST + half * 64 + 32, svb[1]);
+            tmem_ld32(tmem + lane_addr + C_DPT + half * 64 + 32, dvb[1]);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tmem + lane_addr + C_ST + half * 64 + c * 32, sv);
-                tmem_ld32(tmem + lane_addr + C_DPT + half * 64 + c * 32, dv);
-                tmem_ld_wait();
                 if (c == 1) {
                     // both TMEM tiles are in registers: the next step's MMAs may overwrite them
+                    tmem_ld_wait();
                     tc_fence_before();
                     mbar_arrive(s_free);
                 }
+                const uint32_t(&sv)[32] = svb[c];
+                const uint32_t(&dv)[32] = dvb[c];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     float pd[8], ds[8];
@@ -282,7 +319,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     break;
                 }
                 tc_fence_after();
-                drain_dq(i - 1);
+                if (!drain_dq(i - 1)) {
+                    ok = false;
+                    break;
+                }
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -299,6 +339,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         if (ok && mbar_wait(mma_done, (nq - 1) & 1, abort_flag)) {
             tc_fence_after();
             drain_dq(nq - 1);
+            if (threadIdx.x == 0) tma_store_wait<0>();   // the last reduction has landed
             T* dk = reinterpret_cast<T*>(p.dK) + b * p.dk_sb + static_cast<long long>(key) * p.dk_ss + h * p.dk_sh +
                     half * 32;
             T* dvp = reinterpret_cast<T*>(p.dV) + b * p.dv_sb + static_cast<long long>(key) * p.dv_ss + h * p.dv_sh +
@@ -423,7 +464,9 @@ static int launch_bwd(const RbAttnArgs& a, cudaStream_t st) {
         attr_set[dev & 63] = true;
     }
     dim3 grid((a.S + BKEYS - 1) / BKEYS, a.H, a.B);
-    kern<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, p);
+    CUtensorMap tdq;
+    if ((rc = make_tmap_4d_f32(&tdq, a.dq_accum, 64, S, H, B, H * 64 * 4, 64 * 4, S * H * 64 * 4, 32, 128))) return rc;
+    kern<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, tdq, p);
     const long long groups = rows * 8;
     attn_dq_convert_kernel<T><<<static_cast<unsigned>((groups + 255) / 256), 256, 0, st>>>(
         a.dq_accum, static_cast<T*>(a.dQ), a.B, a.H, a.S, a.dq_sb, a.dq_ss, a.dq_sh);

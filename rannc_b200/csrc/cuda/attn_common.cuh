@@ -17,6 +17,18 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Adds a [32 x 128] fp32 tile of this CTA's shared memory (128-byte swizzled rows) into global memory
+// through the tensor map: one bulk reduction instead of per-thread atomics; rows past the tensor's
+// extent are dropped by the copy engine.  Completion is tracked by the bulk async-group.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* smem_src, int c0, int c1,
+                                                  int c2, int c3) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        :
+        : "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
 // barrier among `count` threads of the CTA (count % 32 == 0); id 0 is __syncthreads
 __device__ __forceinline__ void bar_sync_named(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");

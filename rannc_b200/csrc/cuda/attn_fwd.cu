@@ -215,24 +215,38 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
             tc_fence_after();
             const int key0 = j * AK + half * 64;
-            // pass 1: maximum over this thread's 64 columns of the scaled, biased scores (log2 units)
+            // pass 1: maximum over this thread's 64 columns of the scaled, biased scores (log2 units).
+            // Tensor-memory reads are pipelined in 16-column pieces: the next piece is in flight while
+            // the current one is processed.
             float cm = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tmem_ld32(col_s + lane_addr + half * 64 + c * 32, v);
-                tmem_ld_wait();
+            const uint32_t s_addr = col_s + lane_addr + half * 64;
+            {
+                uint32_t va[16], vb[16];
+                auto max16 = [&](const uint32_t(&v)[16], int colbase) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    float4 kb;
-                    uint4 kh = make_uint4(0, 0, 0, 0);
-                    cols4(key0 + c * 32 + g * 4, kb, kh);
-                    const float s0 = fmaf(__uint_as_float(v[g * 4]), p.scale_log2, kb.x);
-                    const float s1 = fmaf(__uint_as_float(v[g * 4 + 1]), p.scale_log2, kb.y);
-                    const float s2 = fmaf(__uint_as_float(v[g * 4 + 2]), p.scale_log2, kb.z);
-                    const float s3 = fmaf(__uint_as_float(v[g * 4 + 3]), p.scale_log2, kb.w);
-                    cm = fmaxf(fmaxf(cm, s0), fmaxf(s1, fmaxf(s2, s3)));
-                }
+                    for (int g = 0; g < 4; ++g) {
+                        float4 kb;
+                        uint4 kh = make_uint4(0, 0, 0, 0);
+                        cols4(key0 + colbase + g * 4, kb, kh);
+                        const float s0 = fmaf(__uint_as_float(v[g * 4]), p.scale_log2, kb.x);
+                        const float s1 = fmaf(__uint_as_float(v[g * 4 + 1]), p.scale_log2, kb.y);
+                        const float s2 = fmaf(__uint_as_float(v[g * 4 + 2]), p.scale_log2, kb.z);
+                        const float s3 = fmaf(__uint_as_float(v[g * 4 + 3]), p.scale_log2, kb.w);
+                        cm = fmaxf(fmaxf(cm, s0), fmaxf(s1, fmaxf(s2, s3)));
+                    }
+                };
+                tmem_ld16(s_addr, va);
+                tmem_ld_wait();
+                tmem_ld16(s_addr + 16, vb);
+                max16(va, 0);
+                tmem_ld_wait();
+                tmem_ld16(s_addr + 32, va);
+                max16(vb, 16);
+                tmem_ld_wait();
+                tmem_ld16(s_addr + 48, vb);
+                max16(va, 32);
+                tmem_ld_wait();
+                max16(vb, 48);
             }
             float* xch = xbase + (j & 1) * 256;
             xch[half * 128 + r] = cm;
@@ -269,41 +283,50 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             // pass 2: probabilities -> shared memory (16-bit, swizzled K-major).  Dropped entries are
             // zeroed here; the 1 / (1 - p) factor is applied once to the finished row.
             float rs = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tmem_ld32(col_s + lane_addr + half * 64 + c * 32, v);
-                tmem_ld_wait();
-                if (c == 1) {
-                    // last read of S: the next Q K^T may overwrite it
-                    tc_fence_before();
-                    mbar_arrive(&s_free[t]);
-                }
+            {
+                uint32_t va[16], vb[16];
+                auto prob16 = [&](const uint32_t(&v)[16], int colbase) {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float pr[8];
+                    for (int g = 0; g < 2; ++g) {
+                        float pr[8];
 #pragma unroll
-                    for (int hq = 0; hq < 2; ++hq) {
-                        float4 kb;
-                        uint4 kh = make_uint4(0, 0, 0, 0);
-                        cols4(key0 + c * 32 + g * 8 + hq * 4, kb, kh);
-                        const float kbv[4] = {kb.x, kb.y, kb.z, kb.w};
-                        const uint32_t khv[4] = {kh.x, kh.y, kh.z, kh.w};
+                        for (int hq = 0; hq < 2; ++hq) {
+                            float4 kb;
+                            uint4 kh = make_uint4(0, 0, 0, 0);
+                            cols4(key0 + colbase + g * 8 + hq * 4, kb, kh);
+                            const float kbv[4] = {kb.x, kb.y, kb.z, kb.w};
+                            const uint32_t khv[4] = {kh.x, kh.y, kh.z, kh.w};
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float e =
-                                exp2f(fmaf(__uint_as_float(v[g * 8 + hq * 4 + i]), p.scale_log2, kbv[i]) - m_use);
-                            rs += e;
-                            pr[hq * 4 + i] = (!p.thr32 || drop_keep(row_hash, khv[i], p.thr32)) ? e : 0.f;
+                            for (int i = 0; i < 4; ++i) {
+                                const float e =
+                                    exp2f(fmaf(__uint_as_float(v[g * 8 + hq * 4 + i]), p.scale_log2, kbv[i]) - m_use);
+                                rs += e;
+                                pr[hq * 4 + i] = (!p.thr32 || drop_keep(row_hash, khv[i], p.thr32)) ? e : 0.f;
+                            }
                         }
+                        uint4 qv;
+                        qv.x = pack2<T>(pr[0], pr[1]);
+                        qv.y = pack2<T>(pr[2], pr[3]);
+                        qv.z = pack2<T>(pr[4], pr[5]);
+                        qv.w = pack2<T>(pr[6], pr[7]);
+                        *reinterpret_cast<uint4*>(prow + ((static_cast<uint32_t>(colbase / 8 + g) ^ sw) << 4)) = qv;
                     }
-                    uint4 qv;
-                    qv.x = pack2<T>(pr[0], pr[1]);
-                    qv.y = pack2<T>(pr[2], pr[3]);
-                    qv.z = pack2<T>(pr[4], pr[5]);
-                    qv.w = pack2<T>(pr[6], pr[7]);
-                    *reinterpret_cast<uint4*>(prow + ((static_cast<uint32_t>(c * 4 + g) ^ sw) << 4)) = qv;
-                }
+                };
+                tmem_ld16(s_addr, va);
+                tmem_ld_wait();
+                tmem_ld16(s_addr + 16, vb);
+                prob16(va, 0);
+                tmem_ld_wait();
+                tmem_ld16(s_addr + 32, va);
+                prob16(vb, 16);
+                tmem_ld_wait();
+                tmem_ld16(s_addr + 48, vb);
+                prob16(va, 32);
+                tmem_ld_wait();
+                // last read of S: the next Q K^T may overwrite it
+                tc_fence_before();
+                mbar_arrive(&s_free[t]);
+                prob16(vb, 48);
             }
             l = l * alpha + rs;
             m = m_new == -INFINITY ? -INFINITY : m_use;

@@ -603,6 +603,26 @@ int make_tmap_4d(CUtensorMap* out, const void* base, int fmt, uint64_t d0, uint6
     return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
 }
 
+// fp32 tensor, 4-D, 128-byte swizzle: box [b0 <= 32 elements, b1 rows, 1, 1]
+int make_tmap_4d_f32(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
+                     uint64_t s1, uint64_t s2, uint64_t s3, uint32_t b0, uint32_t b1) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -100;
+    cuuint64_t dims[4] = {d0, d1, d2, d3};
+    cuuint64_t strides[3] = {s1, s2, s3};
+    cuuint32_t box[4] = {b0, b1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = CUDA_SUCCESS;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+        cudaFree(nullptr);
+    }
+    return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+}
+
 static __device__ int g_error_word = 0;
 
 int* error_word_ptr() {

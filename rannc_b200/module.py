@@ -283,8 +283,12 @@ class RaNNCModule:
                     opt_group_of[id(p)] = gi
         self._storage = ParamStorage(self.use_amp_master_params, self.enable_zero, self.allreduce_amp_master_params)
         self._storage.sync_on_init = _sync_params_on_init
+        self._storage.offload = bool(self.offload_params) and dev.type == "cuda" and self.use_amp_master_params
+        if self.offload_params and not self._storage.offload:
+            logger.warning("offload_params needs a CUDA device and mixed precision (fp32 master weights); ignored")
         local_params = {n: name_to_param[n] for n in self._used_param_names}
         want_fused = (self.use_amp_master_params and self.enable_zero and dev.type == "cuda" and world > 1 and
+                      not self.offload_params and
                       bool(conf("fused_kernels")) and bool(conf("fused_grad_allreduce")) and
                       type(self.optimizer) in (torch.optim.Adam, torch.optim.AdamW))
         self._storage.deploy(local_params, {n: sorted(r) for n, r in owner.items()}, opt_group_of, dev,

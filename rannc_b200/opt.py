@@ -54,10 +54,61 @@ def _fusable(opt) -> Optional[str]:
 class _FlatState:
     """Moment buffers of one flat group, indexed like its master buffer (the shard under ZeRO)."""
 
-    def __init__(self, n: int, device, kind: str):
-        self.m = torch.zeros(n, dtype=torch.float32, device=device)
-        self.v = torch.zeros(n, dtype=torch.float32, device=device) if kind == "adam" else None
+    def __init__(self, n: int, device, kind: str, host: bool = False):
+        if host:
+            # offload_params: the moments stay in pinned host memory and stream through the device
+            self.m = torch.zeros(n, dtype=torch.float32).pin_memory()
+            self.v = torch.zeros(n, dtype=torch.float32).pin_memory() if kind == "adam" else None
+        else:
+            self.m = torch.zeros(n, dtype=torch.float32, device=device)
+            self.v = torch.zeros(n, dtype=torch.float32, device=device) if kind == "adam" else None
         self.step = 0
+
+
+class _OffloadWindow:
+    """Two sets of device staging buffers and a copy stream: while the update kernel works on one chunk of
+    (master, m, v), the next chunk is on its way in and the previous one on its way out
+    (reference: offload_params moves parameters per operator with H2D / D2H hooks, TorchDriver.cpp:318-374;
+    here the 16-bit parameters stay resident and the 12 bytes / parameter of fp32 state are what leaves
+    the device)."""
+
+    def __init__(self, device, chunk: int, n_state: int):
+        self.chunk = chunk
+        self.stream = torch.cuda.Stream(device)
+        self.bufs = [[torch.empty(chunk, dtype=torch.float32, device=device) for _ in range(n_state)]
+                     for _ in range(2)]
+        self.free = [None, None]
+
+    def run(self, host_tensors, n: int, kernel):
+        """``kernel(off, cnt, dev_tensors)`` updates ``cnt`` elements at offset ``off`` in place on the device."""
+        cur = torch.cuda.current_stream()
+        k = 0
+        for off in range(0, n, self.chunk):
+            cnt = min(self.chunk, n - off)
+            set_ = self.bufs[k & 1]
+            with torch.cuda.stream(self.stream):
+                if self.free[k & 1] is not None:
+                    self.stream.wait_event(self.free[k & 1])
+                for h, d in zip(host_tensors, set_):
+                    d[:cnt].copy_(h[off:off + cnt], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(self.stream)
+            cur.wait_event(ready)
+            kernel(off, cnt, [d[:cnt] for d in set_])
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(self.stream):
+                self.stream.wait_event(done)
+                for h, d in zip(host_tensors, set_):
+                    h[off:off + cnt].copy_(d[:cnt], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+                self.free[k & 1] = ev
+            k += 1
+        # later work on this stream (and the host, at the next synchronisation) sees the written-back state
+        for ev in self.free:
+            if ev is not None:
+                cur.wait_event(ev)
 
 
 def patch_optimizer(module, optimizer):
@@ -94,6 +145,8 @@ def patch_optimizer(module, optimizer):
     optimizer.state.clear()
     optimizer._rannc_local_to_global = local_to_global
     optimizer._rannc_kind = _fusable(optimizer)
+    if getattr(storage, "offload", False) and optimizer._rannc_kind is None:
+        raise RuntimeError("offload_params supports Adam, AdamW and SGD (the streamed update kernels)")
     optimizer._rannc_flat_state = {}
     optimizer._rannc_module = module
 
@@ -136,6 +189,33 @@ def patch_optimizer(module, optimizer):
             else:
                 st["momentum_buffer"] = fs.m[a - lo:b - lo].view(target.shape)
 
+    def _offloaded_update(g, fs, hp, og, a, b, kind, ctrl):
+        """Streams [a, b) of the host-resident fp32 state through the device in chunks."""
+        from .ops import kernels as K
+
+        win = getattr(storage, "_offload_window", None)
+        if win is None:
+            chunk = max(1 << 20, int(conf("offload_chunk_numel")))
+            win = storage._offload_window = _OffloadWindow(g.device, chunk, 3)
+        lo = g.shard[0]
+        hosts = [g.flat_master[a - lo:b - lo], fs.m[a - lo:b - lo]]
+        if kind == "adam":
+            hosts.append(fs.v[a - lo:b - lo])
+
+        def kernel(off, cnt, dev):
+            grad = g.flat_grad[a + off:a + off + cnt]
+            model16 = g.flat_param[a + off:a + off + cnt]
+            if kind == "adam":
+                b1, b2 = hp["betas"]
+                K.adam_flat(dev[0], grad, dev[1], dev[2], model16, float(hp["lr"]), b1, b2, float(hp["eps"]),
+                            float(hp["weight_decay"]), fs.step, type(optimizer) is torch.optim.AdamW, ctrl)
+            else:
+                K.sgd_flat(dev[0], grad, dev[1], model16, float(hp["lr"]), float(hp["momentum"]),
+                           float(hp.get("dampening", 0.0)), float(hp["weight_decay"]), bool(hp.get("nesterov")),
+                           fs.step == 1, ctrl)
+
+        win.run(hosts, b - a, kernel)
+
     def fused_step(ctrl=None):
         from .ops import kernels as K
 
@@ -144,13 +224,18 @@ def patch_optimizer(module, optimizer):
             fs = optimizer._rannc_flat_state.get(id(g))
             if fs is None:
                 n = g.shard[1] - g.shard[0]
-                fs = optimizer._rannc_flat_state[id(g)] = _FlatState(n, g.device, kind)
+                fs = optimizer._rannc_flat_state[id(g)] = _FlatState(
+                    n, g.device, kind, host=g.flat_master is not None and not g.flat_master.is_cuda and
+                    g.flat_grad.is_cuda)
             fs.step += 1
         for g, og, a, b in _flat_ranges():
             fs = optimizer._rannc_flat_state[id(g)]
             hp = optimizer.param_groups[og]
             lo = g.shard[0]
             is_amp = g.flat_master is not None
+            if is_amp and not g.flat_master.is_cuda and g.flat_grad.is_cuda:
+                _offloaded_update(g, fs, hp, og, a, b, kind, ctrl)
+                continue
             master = g.flat_master[a - lo:b - lo] if is_amp else g.flat_param[a:b]
             model16 = g.flat_param[a:b] if is_amp else None
             grad = g.flat_grad[a:b]
@@ -349,7 +434,8 @@ def load_global_optimizer_state(optimizer, sd: dict) -> None:
     if optimizer._rannc_kind is not None:
         for g in storage.groups:
             n = g.shard[1] - g.shard[0]
-            fs = _FlatState(n, g.device, optimizer._rannc_kind)
+            fs = _FlatState(n, g.device, optimizer._rannc_kind,
+                            host=g.flat_master is not None and not g.flat_master.is_cuda and g.flat_grad.is_cuda)
             fs.step = steps.get(id(g), 0)
             lo = g.shard[0]
             for i, p in enumerate(g.params):

@@ -128,6 +128,7 @@ class ParamStorage:
         self.sliced: Dict[str, Tuple[int, ...]] = {}   # weight sliced along dim 1 over these ranks
         self.global_order: Dict[str, int] = {}
         self.sync_on_init = True
+        self.offload = False     # fp32 master copies and optimizer state in pinned host memory
         self._sumsq = None
         self._ctrl = None
         self._norm = None
@@ -185,6 +186,9 @@ class ParamStorage:
                 continue
             lo, hi = g.shard
             g.flat_master = g.flat_param[lo:hi].float()
+            host = self.offload and g.flat_master.is_cuda
+            if host:
+                g.flat_master = g.flat_master.cpu().pin_memory()
             g.master_params = []
             for i, p in enumerate(g.params):
                 a, b = g.local_range(i)
@@ -194,7 +198,8 @@ class ParamStorage:
                 full = (a, b) == g.param_range(i)
                 mview = g.flat_master[a - lo:b - lo]
                 mp = torch.nn.Parameter(mview.view(p.shape) if full else mview, requires_grad=p.requires_grad)
-                mp.grad = g.flat_grad[a:b].view(mp.shape)
+                if not host:
+                    mp.grad = g.flat_grad[a:b].view(mp.shape)
                 g.master_params.append(mp)
 
     # ---------------------------------------------------------------- gradients

@@ -23,7 +23,8 @@ def main():
                           num_hidden_layers=case.get("layers", 2))
     model = BertForPreTraining(cfg)
     opt = torch.optim.Adam(model.parameters(), lr=1e-3)
-    wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=True, enable_zero=case.get("zero", True))
+    wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=True, enable_zero=case.get("zero", True),
+                                  offload_params=case.get("offload", False))
     B = case.get("batch", 16)
     lb = B // world
     dev = pyrannc._comm.device()

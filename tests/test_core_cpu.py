@@ -359,3 +359,15 @@ def test_watchdog_detects_missing_peer(tmp_path):
         time.sleep(0.05)
     assert failed == [1] and wd.failed_peer() == 1 and not wd.running()
     wd.stop(True)
+
+
+def test_reference_package_name_is_an_alias():
+    import pyrannc
+    import pyrannc.amp  # noqa: F401
+    from pyrannc.opt import patch_optimizer  # noqa: F401
+
+    import rannc_b200
+
+    assert pyrannc.RaNNCModule is rannc_b200.RaNNCModule
+    assert pyrannc.dist_param is rannc_b200.dist_param
+    assert pyrannc.get_world_size() >= 1

@@ -115,3 +115,18 @@ def test_force_dist_matmul_over_two_gpus(tmp_path):
     assert a["infos"][0]["sliced"] > 0 and b["infos"][0]["sliced"] == 0
     assert all(i["err"] == 0 for i in a["infos"])
     _compare(a, b, 3e-2)
+
+
+@pytest.mark.skipif(_ngpu() < 1, reason="needs a GPU")
+def test_offloaded_optimizer_state_matches_resident(tmp_path):
+    # fp32 master weights and Adam moments in pinned host memory, streamed through the device in chunks
+    env = {"RANNC_OFFLOAD_CHUNK_NUMEL": "1048576"}
+    a = _run(1, {"out": str(tmp_path / "a.pt"), "zero": False, "offload": True}, env)
+    b = _run(1, {"out": str(tmp_path / "b.pt"), "zero": False})
+    assert all(i["err"] == 0 for i in a["infos"])
+    for la, lb in zip(a["infos"][0]["losses"], b["infos"][0]["losses"]):
+        assert abs(la - lb) < 1e-2 * abs(lb)
+    _compare(a, b, 1e-2)
+    k0 = sorted(a["opt"]["state"].keys())[0]
+    assert torch.allclose(a["opt"]["state"][k0]["exp_avg"].float(), b["opt"]["state"][k0]["exp_avg"].float(),
+                          rtol=1e-2, atol=1e-5)
