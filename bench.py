@@ -105,6 +105,10 @@ def main():
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--zero", type=int, default=-1, help="-1: on when more than one GPU")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--model", default="bert", choices=["bert", "wide_resnet"],
+                    help="bert: the headline benchmark; wide_resnet: ResNet-152 with every width x --width")
+    ap.add_argument("--width", type=float, default=8.0)
+    ap.add_argument("--image", type=int, default=224)
     args = ap.parse_args()
     if args.impl == "reference":
         reference_unavailable()
@@ -128,21 +132,37 @@ def main():
         print("bench.py needs a CUDA device", file=sys.stderr)
         return 2
     torch.manual_seed(1234)
-    cfg = BertConfig(hidden_size=args.hidden, num_hidden_layers=args.layers, num_attention_heads=args.heads,
-                     intermediate_size=4 * args.hidden, max_position_embeddings=max(512, args.seq))
-    model = BertForPreTraining(cfg)
-    nparams = sum(p.numel() for p in model.parameters())
-    optimizer = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0)
-    use_zero = (world > 1) if args.zero < 0 else bool(args.zero)
-    wrapped = pyrannc.RaNNCModule(model, optimizer, enable_apex_amp=True, enable_zero=use_zero)
-
     lb = args.global_batch // world
-    # a few distinct synthetic batches in pinned host memory
     n_sets = 4
     host = []
-    for s in range(n_sets):
-        full = synthetic_batch(cfg, args.global_batch, args.seq, seed=100 + s)
-        host.append(tuple(t[rank * lb:(rank + 1) * lb].contiguous().pin_memory() for t in full))
+    if args.model == "bert":
+        cfg = BertConfig(hidden_size=args.hidden, num_hidden_layers=args.layers, num_attention_heads=args.heads,
+                         intermediate_size=4 * args.hidden, max_position_embeddings=max(512, args.seq))
+        model = BertForPreTraining(cfg)
+        optimizer = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0)
+        use_zero = (world > 1) if args.zero < 0 else bool(args.zero)
+        # a few distinct synthetic batches in pinned host memory
+        for s in range(n_sets):
+            full = synthetic_batch(cfg, args.global_batch, args.seq, seed=100 + s)
+            host.append(tuple(t[rank * lb:(rank + 1) * lb].contiguous().pin_memory() for t in full))
+    else:
+        # wide ResNet-152: bottleneck blocks 3/8/36/3, every convolution x --width, BatchNorm, fp16 mixed
+        # precision with dynamic loss scaling, SGD momentum 0.9, images N(0, 1), labels uniform over 1000 classes
+        from rannc_b200.models.resnet import ResNetWithLoss, wide_resnet152
+
+        pyrannc.amp.set_dtype(torch.float16)
+        model = ResNetWithLoss(wide_resnet152(width_mult=args.width))
+        optimizer = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+        use_zero = False if args.zero < 0 else bool(args.zero)
+        n_sets = 2
+        for s in range(n_sets):
+            g = torch.Generator().manual_seed(100 + s)
+            x = torch.randn(lb, 3, args.image, args.image, generator=g).half().pin_memory()
+            y = torch.randint(0, 1000, (lb,), generator=g).pin_memory()
+            host.append((x, y))
+    nparams = sum(p.numel() for p in model.parameters())
+    wrapped = pyrannc.RaNNCModule(model, optimizer, enable_apex_amp=True, enable_zero=use_zero)
+
     h2d_bytes = sum(t.numel() * t.element_size() for t in host[0])
     dev_sets = [tuple(t.to(dev) for t in hs) for hs in host]
 
@@ -212,21 +232,30 @@ def main():
         repl = [len(dep.allocation[s]) for s in dep.fwd_graph_order]
         par = (f"pp{stages}" if stages > 1 else "") + f"dp{repl[0]}" + (f"_mb{dep.pipeline_num}" if dep.pipeline_num > 1 else "") \
             + ("_zero" if use_zero else "")
+        if args.model == "bert":
+            mname = (f"BERT-Large {args.layers}L/{args.hidden}H/{args.heads}heads MLM+NSP" if
+                     (args.layers, args.hidden) == (24, 1024) else
+                     f"BERT {args.layers}L/{args.hidden}H/{args.heads}heads MLM+NSP")
+            data = "synthetic (uniform token ids, 15% MLM labels, Bernoulli NSP), random-init weights"
+            optname, dtype = "Adam (fused, fp32 master)", "bf16"
+        else:
+            mname = f"Wide ResNet-152 (widths x{args.width:g}), {args.image}x{args.image} images"
+            data = "synthetic (N(0,1) images, uniform labels over 1000 classes), random-init weights"
+            optname, dtype = "SGD momentum 0.9 (fused, fp32 master, dynamic loss scale)", "fp16"
         out = {
-            "metric": "BERT samples/s (max over ranks)",
+            "metric": ("BERT" if args.model == "bert" else "ResNet") + " samples/s (max over ranks)",
             "value": args.global_batch * args.steps / (ms / 1e3),
             "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (uniform token ids, 15% MLM labels, Bernoulli NSP), random-init weights",
+            "dtype": dtype, "data": data,
             "impl": "ours",
-            "config": {"model": f"BERT-Large {args.layers}L/{args.hidden}H/{args.heads}heads MLM+NSP" if
-                       (args.layers, args.hidden) == (24, 1024) else
-                       f"BERT {args.layers}L/{args.hidden}H/{args.heads}heads MLM+NSP",
-                       "params": nparams, "global_batch": args.global_batch, "seq_len": args.seq,
+            "config": {"model": mname,
+                       "params": nparams, "global_batch": args.global_batch,
+                       "seq_len": args.seq if args.model == "bert" else None,
                        "parallelism": par, "stages": stages, "replicas": repl, "micro_batches": dep.pipeline_num,
-                       "checkpointing": bool(dep.checkpointing), "optimizer": "Adam (fused, fp32 master)",
+                       "checkpointing": bool(dep.checkpointing), "optimizer": optname,
                        "l2": "per-step working set (weights 0.67 GB + activations, tens of GB) far exceeds the "
                              "126 MB L2; no flush needed"},
             "clocks": clocks,

@@ -102,7 +102,7 @@ def analytic_profiles(gm: fx.GraphModule) -> Dict[str, "_core.NodeProfile"]:
                 for d in sa[:-1]:
                     m *= d
                 flops = 2.0 * m * sa[-1] * sb[-1]
-            elif name in ("aten::conv2d", "aten::convolution", "aten::_convolution"):
+            elif name in ("aten::conv2d", "aten::convolution", "aten::_convolution", "rannc::conv2d"):
                 w = _shape(args[1].meta["val"])
                 o = _shape(val)
                 flops = 2.0 * o[0] * o[1] * o[2] * o[3] * w[1] * w[2] * w[3]

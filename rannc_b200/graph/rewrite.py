@@ -126,7 +126,6 @@ def fuse(gm: fx.GraphModule, training: bool = True, keep_linear: bool = False) -
         stats[k] = stats.get(k, 0) + 1
 
     drop_asserts(gm)
-    anchor_mutations(gm)
     g = gm.graph
 
     # ---- q/k/v projections of one input + attention -> one operator
@@ -278,6 +277,52 @@ def fuse(gm: fx.GraphModule, training: bool = True, keep_linear: bool = False) -
             _erase_if_dead(gm, c)
         bump("cross_entropy")
 
+    # ---- convolution, batch norm (+ residual add) (+ relu)
+    for n in list(g.nodes):
+        if _is(n, aten.conv2d.default):
+            a = list(n.args) + [None] * (7 - len(n.args))
+            x, w, b = a[0], a[1], a[2] if a[2] is not None else n.kwargs.get("bias")
+            stride = a[3] if a[3] is not None else n.kwargs.get("stride", 1)
+            padding = a[4] if a[4] is not None else n.kwargs.get("padding", 0)
+            dilation = a[5] if a[5] is not None else n.kwargs.get("dilation", 1)
+            groups = a[6] if a[6] is not None else n.kwargs.get("groups", 1)
+            if isinstance(padding, str):
+                continue
+            _replace(gm, n, RF.conv2d, (x, w, b, stride, padding, dilation, groups))
+            bump("conv2d")
+    for n in list(g.nodes):
+        if not _is(n, aten.batch_norm.default) or n not in g.nodes:
+            continue
+        x, w, b, rm, rv, train, momentum, eps = n.args[:8]
+        xv = _val(x)
+        if xv is None or xv.dim() != 4 or w is None or b is None or not train:
+            continue
+        relu, residual, chain = False, None, []
+        u = _single_user(n)
+        if u is not None and _is(u, aten.add.Tensor) and len(u.args) == 2 and not u.kwargs and \
+                all(isinstance(t, fx.Node) for t in u.args):
+            other = u.args[1] if u.args[0] is n else u.args[0]
+            ov = _val(other)
+            u2 = _single_user(u)
+            if ov is not None and ov.shape == xv.shape and u2 is not None and _is(u2, aten.relu.default, aten.relu_.default):
+                relu, residual, chain = True, other, [u, u2]
+        elif u is not None and _is(u, aten.relu.default, aten.relu_.default):
+            relu, chain = True, [u]
+        args = (x, w, b, rm, rv, bool(train), float(momentum), float(eps), relu, residual)
+        if not chain:
+            _replace(gm, n, RF.batch_norm_act, args)
+        else:
+            # the fused node takes the place of the last node of the chain (every operand is defined by then)
+            last = chain[-1]
+            with g.inserting_before(last):
+                new = g.call_function(RF.batch_norm_act, args)
+            new.meta = dict(last.meta)
+            last.replace_all_uses_with(new)
+            for m in reversed(chain):
+                g.erase_node(m)
+            g.erase_node(n)
+        bump("batch_norm_act")
+
     # ---- stand-alone element-wise ops
     for n in list(g.nodes):
         if _is(n, aten.dropout.default):
@@ -291,6 +336,8 @@ def fuse(gm: fx.GraphModule, training: bool = True, keep_linear: bool = False) -
             _replace(gm, n, RF.embedding, (n.args[0], n.args[1], pad))
             bump("embedding")
 
+    # after the fusions, so that a batch norm and the activation behind it are still adjacent above
+    anchor_mutations(gm)
     g.eliminate_dead_code()
     g.lint()
     gm.recompile()

@@ -94,6 +94,24 @@ class TracedModel:
     trace_batch: int = 0
 
 
+def _flatten_args_keep_none(args) -> list:
+    """Leaves of an output structure in order; constants appear as None."""
+    out = []
+
+    def rec(a):
+        if isinstance(a, (list, tuple)):
+            for x in a:
+                rec(x)
+        elif isinstance(a, dict):
+            for x in a.values():
+                rec(x)
+        else:
+            out.append(a if isinstance(a, fx.Node) else None)
+
+    rec(args)
+    return out
+
+
 def _flatten_args(args) -> List[fx.Node]:
     out = []
 
@@ -198,6 +216,18 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
         rewrite.anchor_mutations(gm)
         gm.graph.eliminate_dead_code()
         gm.recompile()
+    # the rewrites may have replaced the nodes that produce the outputs: take the names from the graph
+    out_node = next(n for n in gm.graph.nodes if n.op == "output")
+    flat_out = _flatten_args_keep_none(out_node.args)
+    if len(flat_out) == len(sig.output_specs):
+        user_outputs, buffer_mutations = [], {}
+        for spec, node in zip(sig.output_specs, flat_out):
+            if node is None:
+                continue
+            if spec.kind == OutputKind.USER_OUTPUT:
+                user_outputs.append(node.name)
+            elif spec.kind == OutputKind.BUFFER_MUTATION:
+                buffer_mutations[node.name] = spec.target
     batch = 0
     for a in args:
         if isinstance(a, torch.Tensor) and a.dim() > 0:

@@ -115,6 +115,10 @@ class RaNNCModule:
             for a in args:
                 if isinstance(a, torch.Tensor) and not a.is_cuda:
                     raise RuntimeError("All inputs to RaNNCModule must be on a CUDA device")
+        if self.use_amp_master_params:
+            # floating-point inputs follow the 16-bit compute type (Apex O2 casts them in the patched forward)
+            args = tuple(a.to(self.amp_dtype) if isinstance(a, torch.Tensor) and a.is_floating_point() and
+                         a.dtype != self.amp_dtype else a for a in args)
         if not self.ready:
             self._init(args)
         self._dist_barrier()
@@ -143,8 +147,14 @@ class RaNNCModule:
         from . import dist_param as _dp
 
         if self.use_amp_master_params:
+            # batch-norm scale / shift and running statistics stay in fp32 (as Apex O2 keeps them, which is
+            # what the reference trains with); everything else goes to the 16-bit compute type
+            keep32 = set()
+            for mod in model.modules():
+                if isinstance(mod, torch.nn.modules.batchnorm._BatchNorm):
+                    keep32.update(id(t) for t in list(mod.parameters(recurse=False)) + list(mod.buffers(recurse=False)))
             for p in model.parameters():
-                if not p.is_floating_point():
+                if not p.is_floating_point() or id(p) in keep32:
                     continue
                 if _dp.dist_param_registered(id(p)):
                     _dp.set_dist_param_dtype(id(p), self.amp_dtype)
@@ -152,7 +162,7 @@ class RaNNCModule:
                 else:
                     p.data = p.data.to(self.amp_dtype)
             for b in model.buffers():
-                if b.is_floating_point():
+                if b.is_floating_point() and id(b) not in keep32:
                     b.data = b.data.to(self.amp_dtype)
 
         # global batch = sum of the local batches (reference: RaNNCModule.cpp:173-177)

@@ -455,3 +455,160 @@ def qkv_attention(x, wq, bq, wk, bk, wv, bv, attn_mask=None, dropout_p: float = 
     v = linear(x, wv, bv).view(B, S, num_heads, D).transpose(1, 2)
     o = sdpa(q, k, v, attn_mask, dropout_p, is_causal, scale)
     return o.transpose(1, 2).reshape(B, S, Ho)
+
+
+# ----------------------------------------------------------------------------- convolution / batch norm
+def _nhwc(x):
+    """[N, H, W, C] contiguous view of a logically NCHW tensor (a copy only if it is not channels-last yet)."""
+    return x.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1)
+
+
+def _conv_weight(w):
+    """[Co, kh * kw * Ci] with the taps outermost (the order ``im2col`` produces), cached until the
+    parameters next change.  A 1x1 kernel is a free view."""
+    Co, Ci, kh, kw = w.shape
+    if kh == 1 and kw == 1:
+        return w.detach().reshape(Co, Ci)
+    key = ("conv", id(w))
+    hit = _cat_cache.get(key)
+    if hit is not None and hit[0] == param_epoch and hit[2] == w.data_ptr():
+        return hit[1]
+    with torch.no_grad():
+        w2 = w.detach().permute(0, 2, 3, 1).reshape(Co, kh * kw * Ci).contiguous()
+    _cat_cache[key] = (param_epoch, w2, w.data_ptr())
+    return w2
+
+
+class _Conv2d(torch.autograd.Function):
+    """Convolution as a tcgen05 GEMM over channels-last activations: the [N*H*W, C] view itself for 1x1
+    kernels, the ``im2col`` matrix otherwise; input gradient through the adjoint gather, weight gradient as
+    one GEMM accumulated into the fp32 gradient buffer."""
+
+    @staticmethod
+    def _operand(x4, k, s, pad):
+        N, H, W, C = x4.shape
+        if k == 1 and pad == 0:
+            if s == 1:
+                return x4.reshape(N * H * W, C)
+            return x4[:, ::s, ::s, :].contiguous().reshape(-1, C)
+        return K.im2col(x4, k, s, pad)
+
+    @staticmethod
+    def forward(ctx, x, w, bias, stride, padding):
+        N, C, H, W = x.shape
+        Co, _, k, _ = w.shape
+        x4 = _nhwc(x)
+        a = _Conv2d._operand(x4, k, stride, padding)
+        y2 = gemm(a, _conv_weight(w), bias=bias)
+        Ho, Wo = K.conv_out_size(H, k, stride, padding), K.conv_out_size(W, k, stride, padding)
+        ctx.save_for_backward(x4, w)
+        ctx.meta = (stride, padding, bias, _main_grad(w), _main_grad(bias) if bias is not None else None)
+        return y2.view(N, Ho, Wo, Co).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x4, w = ctx.saved_tensors
+        stride, padding, bias, w_mg, b_mg = ctx.meta
+        N, H, W, C = x4.shape
+        Co, Ci, k, _ = w.shape
+        dy2 = _nhwc(dy).reshape(-1, Co)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            da = gemm(dy2, _conv_weight(w), trans_b=False)
+            if k == 1 and padding == 0:
+                if stride == 1:
+                    dx4 = da.view(N, H, W, C)
+                else:
+                    dx4 = torch.zeros(N, H, W, C, dtype=da.dtype, device=da.device)
+                    dx4[:, ::stride, ::stride, :] = da.view(N, -1, dx4[:, ::stride, ::stride, :].shape[2], C)
+            else:
+                dx4 = K.col2im(da, N, H, W, C, k, stride, padding)
+            dx = dx4.permute(0, 3, 1, 2)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            a = _Conv2d._operand(x4, k, stride, padding)
+            if k == 1 and w_mg is not None:
+                gemm(dy2, a, trans_a=True, trans_b=False, out=w_mg.view(Co, Ci), accumulate=True)
+            else:
+                dw2 = gemm(dy2, a, trans_a=True, trans_b=False, out_dtype=torch.float32)
+                dwt = dw2.view(Co, k, k, Ci).permute(0, 3, 1, 2)
+                if w_mg is not None:
+                    w_mg.add_(dwt)
+                else:
+                    dw = dwt.to(w.dtype)
+        db = _bgrad(dy2, bias, b_mg) if (bias is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None, None
+
+
+def _pair(v):
+    if isinstance(v, (list, tuple)):
+        return int(v[0]), int(v[1])
+    return int(v), int(v)
+
+
+def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """``torch.nn.functional.conv2d`` for square kernels, groups = 1, dilation = 1 and channel counts that are
+    multiples of 8 on the kernels; anything else goes to ATen."""
+    s, p, d = _pair(stride), _pair(padding), _pair(dilation)
+    Co, Ci, kh, kw = weight.shape
+    ok = (_kernel_ok(x) and weight.dtype == x.dtype and groups == 1 and d == (1, 1) and kh == kw and s[0] == s[1] and
+          p[0] == p[1] and Ci % 8 == 0 and Co % 8 == 0 and x.dim() == 4 and isinstance(p[0], int))
+    if not ok:
+        return torch.nn.functional.conv2d(x, weight, bias, stride, padding, dilation, groups)
+    return _Conv2d.apply(x, weight, bias, s[0], p[0])
+
+
+class _BatchNormAct(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, gamma, beta, run_mean, run_var, momentum, eps, relu):
+        N, C, H, W = x.shape
+        x2 = _nhwc(x).reshape(-1, C)
+        r2 = _nhwc(residual).reshape(-1, C) if residual is not None else None
+        g32, b32 = gamma.detach().float(), beta.detach().float()
+        rm = run_mean if (run_mean is not None and run_mean.dtype == torch.float32) else None
+        rv = run_var if rm is not None else None
+        y2, mean, rstd = K.bn_fwd(x2, r2, g32, b32, rm, rv, eps, momentum, relu)
+        if run_mean is not None and rm is None:
+            # statistics kept in a 16-bit buffer: update them with a few tiny element-wise operations
+            with torch.no_grad():
+                R = x2.shape[0]
+                var = (1.0 / (rstd * rstd) - eps) * (R / max(R - 1, 1))
+                run_mean.mul_(1 - momentum).add_((momentum * mean).to(run_mean.dtype))
+                run_var.mul_(1 - momentum).add_((momentum * var).to(run_var.dtype))
+        ctx.save_for_backward(x2, y2, mean, rstd, g32)
+        ctx.meta = (relu, residual is not None, (N, C, H, W), gamma, beta, _main_grad(gamma), _main_grad(beta))
+        return y2.view(N, H, W, C).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, y2, mean, rstd, g32 = ctx.saved_tensors
+        relu, has_res, (N, C, H, W), gamma, beta, g_mg, b_mg = ctx.meta
+        dy2 = _nhwc(dy).reshape(-1, C)
+        dx2, dres2, dgamma, dbeta = K.bn_bwd(x2, dy2, y2, mean, rstd, g32, relu, has_res)
+        dx = dx2.view(N, H, W, C).permute(0, 3, 1, 2)
+        dres = dres2.view(N, H, W, C).permute(0, 3, 1, 2) if has_res else None
+        dg = db = None
+        if g_mg is not None:
+            g_mg.add_(dgamma)
+        else:
+            dg = dgamma.to(gamma.dtype)
+        if b_mg is not None:
+            b_mg.add_(dbeta)
+        else:
+            db = dbeta.to(beta.dtype)
+        return dx, dres, dg, db, None, None, None, None, None
+
+
+def batch_norm_act(x, gamma, beta, running_mean, running_var, training: bool = True, momentum: float = 0.1,
+                   eps: float = 1e-5, relu: bool = False, residual=None):
+    """``relu(batch_norm(x) + residual)`` with ``relu`` and ``residual`` optional.  Training mode with affine
+    parameters on the kernels; evaluation mode (running statistics) and other cases on ATen."""
+    ok = (_kernel_ok(x) and training and x.dim() == 4 and x.shape[1] % 8 == 0 and gamma is not None and
+          beta is not None and (residual is None or residual.shape == x.shape))
+    if not ok:
+        y = torch.nn.functional.batch_norm(x, running_mean, running_var, gamma, beta, training, momentum, eps)
+        if residual is not None:
+            y = y + residual
+        return torch.relu(y) if relu else y
+    return _BatchNormAct.apply(x, residual, gamma, beta, running_mean, running_var, float(momentum), float(eps),
+                               bool(relu))

@@ -255,3 +255,54 @@ def attn_bwd(q, k, v, o, lse, do, key_bias=None, scale=None, p_drop=0.0, seed=0,
     a.scale, a.p_drop, a.seed, a.offset = scale, float(p_drop), int(seed), int(offset)
     _lib.check(_lib.lib().rb_attn_bwd(ctypes.byref(a), _lib.stream_ptr()), "rb_attn_bwd")
     return dq, dk, dv
+
+
+# ------------------------------------------------------------------ convolution support, batch norm (NHWC)
+def conv_out_size(H: int, k: int, s: int, pad: int) -> int:
+    return (H + 2 * pad - k) // s + 1
+
+
+def im2col(x_nhwc, k: int, s: int, pad: int):
+    """[N, H, W, C] (contiguous) -> [N * Ho * Wo, k * k * C], taps outermost within a row."""
+    N, H, W, C = x_nhwc.shape
+    Ho, Wo = conv_out_size(H, k, s, pad), conv_out_size(W, k, s, pad)
+    cols = torch.empty(N * Ho * Wo, k * k * C, dtype=x_nhwc.dtype, device=x_nhwc.device)
+    _lib.check(_lib.lib().rb_im2col(_lib.vp(x_nhwc), _lib.vp(cols), c_int(N), c_int(H), c_int(W), c_int(C), c_int(k),
+                                    c_int(s), c_int(pad), c_int(dt_code(x_nhwc)), _lib.stream_ptr()), "rb_im2col")
+    return cols
+
+
+def col2im(dcols, N: int, H: int, W: int, C: int, k: int, s: int, pad: int):
+    """Adjoint of ``im2col``: [N * Ho * Wo, k * k * C] -> [N, H, W, C]."""
+    dx = torch.empty(N, H, W, C, dtype=dcols.dtype, device=dcols.device)
+    _lib.check(_lib.lib().rb_col2im(_lib.vp(dcols), _lib.vp(dx), c_int(N), c_int(H), c_int(W), c_int(C), c_int(k),
+                                    c_int(s), c_int(pad), c_int(dt_code(dcols)), _lib.stream_ptr()), "rb_col2im")
+    return dx
+
+
+def bn_fwd(x2d, residual2d, gamma32, beta32, run_mean32, run_var32, eps: float, momentum: float, relu: bool):
+    """Training-mode batch norm over the rows of [R, C] (+ residual, + ReLU).  Returns (y, mean, rstd);
+    the running statistics (fp32, may be None) are updated in place."""
+    R, C = x2d.shape
+    y = torch.empty_like(x2d)
+    part = torch.empty(2, C, dtype=torch.float32, device=x2d.device)
+    mean = torch.empty(C, dtype=torch.float32, device=x2d.device)
+    rstd = torch.empty(C, dtype=torch.float32, device=x2d.device)
+    _lib.check(_lib.lib().rb_bn_fwd(_lib.vp(x2d), _lib.vp(residual2d), _lib.vp(gamma32), _lib.vp(beta32), _lib.vp(y),
+                                    _lib.vp(part), _lib.vp(mean), _lib.vp(rstd), _lib.vp(run_mean32),
+                                    _lib.vp(run_var32), c_longlong(R), c_int(C), c_float(eps), c_float(momentum),
+                                    c_int(1 if relu else 0), c_int(dt_code(x2d)), _lib.stream_ptr()), "rb_bn_fwd")
+    return y, mean, rstd
+
+
+def bn_bwd(x2d, dy2d, y2d, mean, rstd, gamma32, relu: bool, want_dres: bool):
+    """Returns (dx, dres or None, dgamma fp32, dbeta fp32)."""
+    R, C = x2d.shape
+    dx = torch.empty_like(x2d)
+    dres = torch.empty_like(x2d) if want_dres else None
+    part = torch.empty(2, C, dtype=torch.float32, device=x2d.device)
+    _lib.check(_lib.lib().rb_bn_bwd(_lib.vp(x2d), _lib.vp(dy2d), _lib.vp(y2d), _lib.vp(mean), _lib.vp(rstd),
+                                    _lib.vp(gamma32), _lib.vp(part), _lib.vp(dx), _lib.vp(dres), c_longlong(R),
+                                    c_int(C), c_int(1 if relu else 0), c_int(dt_code(x2d)), _lib.stream_ptr()),
+               "rb_bn_bwd")
+    return dx, dres, part[1], part[0]
