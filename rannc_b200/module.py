@@ -172,9 +172,12 @@ class RaNNCModule:
                 local_bs = int(a.shape[0])
                 break
         sizes = comm.allgather_obj(local_bs)
-        if len(set(sizes)) != 1:
-            raise RuntimeError(f"every rank must pass the same local batch size, got {sizes}")
-        global_bs = sum(sizes)
+        if not self.gather_inputs:
+            global_bs = sizes[0]     # rank 0 hands in the whole batch
+        else:
+            if len(set(sizes)) != 1:
+                raise RuntimeError(f"every rank must pass the same local batch size, got {sizes}")
+            global_bs = sum(sizes)
 
         logger.info("Tracing model ...")
         pdev = next((p.device for p in model.parameters()), torch.device("cpu"))

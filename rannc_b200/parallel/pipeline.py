@@ -64,6 +64,10 @@ class PipelineRuntime:
         self.checkpointing = bool(dep.checkpointing)
         self.pending = comm.PendingOps()
         self.gather_inputs = gather_inputs
+        # the ranks that hand inputs in and take outputs back: every rank with its slice of the batch, or
+        # (gather_inputs=False) rank 0 with the whole batch, the outputs then being broadcast
+        # (reference: GraphLauncher.cpp:41-57,110-118,412-413)
+        self.master = self.all_ranks if gather_inputs else [0]
         self._fwd_state = None
         self._in_grads: Dict = {}
         sets = [self.all_ranks] + list(self.alloc.values())
@@ -107,7 +111,8 @@ class PipelineRuntime:
         P = self.P
         by_name = dict(zip(self.user_inputs, inputs))
         # cumulative local row offsets of this rank's share of each micro-batch
-        local_rows = [self.calc.local_split_size(self.rank, self.world, i) for i in range(P)]
+        local_rows = [self.calc.local_split_size(self.master.index(self.rank), len(self.master), i)
+                      if self.rank in self.master else 0 for i in range(P)]
         offs = [0]
         for r in local_rows:
             offs.append(offs[-1] + r)
@@ -131,7 +136,7 @@ class PipelineRuntime:
                         continue
                     mult = self._mult(v, 0)
                     piece = x[offs[i] * mult: offs[i + 1] * mult]
-                    got = self._move(v, piece, self.all_ranks, ranks, i)
+                    got = self._move(v, piece, self.master, ranks, i)
                     if mine:
                         ins[r.value_name] = got
                 # stage -> stage
@@ -177,9 +182,16 @@ class PipelineRuntime:
                 pieces = []
                 for i in range(P):
                     held = stage_vals.get((i, producer), {}).get(oname)
-                    got = self._move(v, held, pr, self.all_ranks, i)
+                    got = self._move(v, held, pr, self.master, i)
                     pieces.append(got)
-                results.append(torch.cat(pieces, 0) if len(pieces) > 1 else pieces[0])
+                pieces = [p for p in pieces if p is not None]
+                full = (torch.cat(pieces, 0) if len(pieces) > 1 else pieces[0]) if pieces else None
+                if not self.gather_inputs and self.world > 1:
+                    if full is None:
+                        full = torch.empty(list(v.type.tensor_dim), dtype=_TORCH_DTYPE[v.type.tensor_elem_type],
+                                           device=dev)
+                    comm.bcast(full, self.master[0])
+                results.append(full)
         self.pending.wait()
         self._fwd_state = (offs, local_rows)
         return results
@@ -237,7 +249,7 @@ class PipelineRuntime:
                     else:
                         mult = self._mult(v, 0)
                         piece = g[offs[i] * mult: offs[i + 1] * mult]
-                        got = self._move(v, piece, self.all_ranks, ranks, i)
+                        got = self._move(v, piece, self.master, ranks, i)
                         if mine and got is not None:
                             og[r.value_name] = got if r.value_name not in og else og[r.value_name] + got
                 # later stages -> this stage: gradients of values this stage sent

@@ -31,7 +31,9 @@ def main():
         (lambda ps: torch.optim.Adam(ps, lr=0.01))
     opt, ropt = mk(model.parameters()), mk(ref.parameters())
     wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=case.get("amp", False),
-                                  enable_zero=case.get("zero", False), check_unused_values=False)
+                                  enable_zero=case.get("zero", False), check_unused_values=False,
+                                  gather_inputs=case.get("gather_inputs", True))
+    whole = not case.get("gather_inputs", True)    # every rank passes (rank 0's copy of) the whole batch
     B = case.get("batch", 8)
     lb = B // world
     g = torch.Generator().manual_seed(123)
@@ -43,7 +45,7 @@ def main():
         pyrannc.delay_grad_allreduce(accum > 1)
         for a in range(accum):
             inputs = zoo.inputs(case["model"], B, g)
-            local = tuple(t[rank * lb:(rank + 1) * lb] for t in inputs)
+            local = inputs if whole else tuple(t[rank * lb:(rank + 1) * lb] for t in inputs)
             out = wrapped(*local)
             rout = ref(*inputs)
             if out.dim() == 0:
@@ -53,11 +55,12 @@ def main():
                 out.backward()
                 (rout / 1.0).backward()
             else:
-                if not torch.allclose(out, rout[rank * lb:(rank + 1) * lb], rtol=tol, atol=tol):
+                expect = rout if whole else rout[rank * lb:(rank + 1) * lb]
+                if out.shape != expect.shape or not torch.allclose(out, expect, rtol=tol, atol=tol):
                     ok = False
-                    msgs.append(f"it {it}: output mismatch {(out - rout[rank * lb:(rank + 1) * lb]).abs().max()}")
+                    msgs.append(f"it {it}: output mismatch {tuple(out.shape)} vs {tuple(expect.shape)}")
                 go = torch.randn(rout.shape, generator=g)
-                out.backward(go[rank * lb:(rank + 1) * lb])
+                out.backward(go if whole else go[rank * lb:(rank + 1) * lb])
                 # DDP semantics: gradients are averaged over the ranks
                 rout.backward(go / world)
         if accum > 1:

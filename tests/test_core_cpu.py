@@ -371,3 +371,27 @@ def test_reference_package_name_is_an_alias():
     assert pyrannc.RaNNCModule is rannc_b200.RaNNCModule
     assert pyrannc.dist_param is rannc_b200.dist_param
     assert pyrannc.get_world_size() >= 1
+
+
+def test_tutorial_script_runs_on_cpu(tmp_path):
+    """BASELINE config 1: the tutorial MLP through trace, profile, plan and a few training steps, world size 1."""
+    import os
+    import subprocess
+    import sys
+
+    import torch
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "ckpt.pt"
+    env = dict(os.environ, RANNC_FORCE_CPU="1", RANK="0", WORLD_SIZE="1", RANNC_LOG_LEVEL="warning")
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "tutorial.py"), "--steps", "4", "--save",
+                        str(out)], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("step ")]
+    assert len(lines) == 4
+    first, last = float(lines[0].split()[-1]), float(lines[-1].split()[-1])
+    assert last < first
+    ck = torch.load(out, weights_only=False)
+    assert set(ck["model"].keys()) == {"net.fc1.weight", "net.fc1.bias", "net.fc2.weight", "net.fc2.bias",
+                                       "net.fc3.weight", "net.fc3.bias"}
+    assert len(ck["optimizer"]["state"]) == 6

@@ -95,6 +95,11 @@ def test_verify_partitioning_runs_with_two_stages():
     run_case(2, {"model": "forkjoin", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_VERIFY_PARTITIONING": "true"})
 
 
+def test_gather_inputs_false_rank0_feeds_the_whole_batch():
+    run_case(2, {"model": "basic", "batch": 8, "gather_inputs": False})
+    run_case(2, {"model": "deep", "batch": 8, "gather_inputs": False}, {"RANNC_PARTITION_NUM": "2"})
+
+
 def test_pp_checkpointing():
     run_case(2, {"model": "loss", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2",
                                                 "RANNC_CHECKPOINTING": "true"})
