@@ -13,7 +13,9 @@
 // engine does the read-modify-write; the math threads do not wait for it); a
 // last kernel converts the scratch to the 16-bit dQ.  Q_i / dO_i stream
 // through a 2-stage TMA ring; lse / delta of the next query block are fetched
-// while the current one is processed.  Warps 0..7 = math, warp 8 = TMA + MMA issue.
+// while the current one is processed.  Warps 0..7 = element math, warp 8 = TMA + MMA issue, warps
+// 9..12 = dQ drain: the math warps' chain per query block is then only "S / dP -> P / dS", and the
+// drain of block i runs beside the math of block i + 1.
 //
 // Takes the place of the autograd graph the reference runs for the traced
 // attention chain (src/torch/TorchDriver.cpp:642-847).
@@ -27,7 +29,8 @@ constexpr int BQ = 128, BKEYS = 128;
 constexpr int TILE = 128 * 64 * 2;       // 16 KiB
 constexpr int SQ_BYTES = 128 * 128 * 2;  // 32 KiB
 constexpr int BWD_MATH = 256;
-constexpr int BWD_THREADS = BWD_MATH + 32;
+constexpr int BWD_DRAIN = 128;                 // warps 9..12: move dQ out of tensor memory
+constexpr int BWD_THREADS = BWD_MATH + 32 + BWD_DRAIN;
 constexpr int BWD_TMEM_COLS = 512;
 constexpr int C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
 constexpr int DQ_STAGE = 128 * 64 * 4;   // 32 KiB: [2 column halves][128 rows x 128 B]
@@ -74,8 +77,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     uint64_t* pds_ready = bars + 5;
     uint64_t* mma_done = bars + 6;
     uint64_t* dq_free = bars + 7;    // the previous bulk reduction has read the staging tile
-    uint64_t* dq_ready = bars + 8;   // every math thread has written its part of the staging tile
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t* dq_ready = bars + 8;   // every drain thread has written its part of the staging tile
+    uint64_t* dq_taken = bars + 9;   // dQ of the last step is out of tensor memory: the next may overwrite it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,7 +95,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         mbar_init(pds_ready, BWD_MATH);
         mbar_init(mma_done, 1);
         mbar_init(dq_free, 1);
-        mbar_init(dq_ready, BWD_MATH);
+        mbar_init(dq_ready, BWD_DRAIN);
+        mbar_init(dq_taken, BWD_DRAIN);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -163,6 +168,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     umma_f16(tmem + C_DK, make_smem_desc_sw128(sa + koff, 16, 1024),
                              make_smem_desc_sw128(qa + k * 2048, 8192, 1024), id_kn, (i | k) != 0);
                 }
+                // dQ of the previous step must have left tensor memory before this step's product replaces it
+                if (i > 0) {
+                    if (!mbar_wait(dq_taken, (i - 1) & 1, abort_flag)) break;
+                    tc_fence_after();
+                }
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     umma_f16(tmem + C_DQ, make_smem_desc_sw128(sa + k * 2048, SQ_BYTES / 2, 1024),
@@ -174,8 +184,49 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 }
             }
         }
+    } else if (warp > 8) {
+        // ------------- dQ drain: thread r owns query row r of the block (TMEM lane r), all 64 columns -------------
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t sw = r & 7;
+        const bool issuer = threadIdx.x == BWD_MATH + 32;
+        for (int i = 0; i < nq; ++i) {
+            if (!mbar_wait(mma_done, i & 1, abort_flag)) break;
+            tc_fence_after();
+            uint32_t v0[32], v1[32];
+            tmem_ld32(tmem + lane_addr + C_DQ, v0);
+            tmem_ld32(tmem + lane_addr + C_DQ + 32, v1);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(dq_taken);
+            if (issuer) {
+                tma_store_wait_read<0>();   // the previous reduction no longer reads the staging tile
+                mbar_arrive(dq_free);
+            }
+            if (!mbar_wait(dq_free, i & 1, abort_flag)) break;
+            uint8_t* row = sDQ + (r >> 3) * 1024 + sw * 128;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const uint32_t off = (static_cast<uint32_t>(g) ^ sw) << 4;
+                *reinterpret_cast<float4*>(row + off) =
+                    make_float4(__uint_as_float(v0[g * 4]) * p.scale, __uint_as_float(v0[g * 4 + 1]) * p.scale,
+                                __uint_as_float(v0[g * 4 + 2]) * p.scale, __uint_as_float(v0[g * 4 + 3]) * p.scale);
+                *reinterpret_cast<float4*>(row + DQ_STAGE / 2 + off) =
+                    make_float4(__uint_as_float(v1[g * 4]) * p.scale, __uint_as_float(v1[g * 4 + 1]) * p.scale,
+                                __uint_as_float(v1[g * 4 + 2]) * p.scale, __uint_as_float(v1[g * 4 + 3]) * p.scale);
+            }
+            fence_proxy_async();
+            mbar_arrive(dq_ready);
+            if (issuer) {
+                if (!mbar_wait(dq_ready, i & 1, abort_flag)) break;
+                tma_reduce_add_4d(&tmDQ, sDQ, 0, i * BQ, h, b);
+                tma_reduce_add_4d(&tmDQ, sDQ + DQ_STAGE / 2, 32, i * BQ, h, b);
+                tma_store_commit();
+            }
+        }
+        if (issuer) tma_store_wait<0>();   // the last reduction has landed
     } else {
-        // thread pair (r, r + 128): TMEM lane r = key row for St/dPt/dV/dK and query row for dQ;
+        // thread pair (r, r + 128): TMEM lane r = key row for St/dPt/dV/dK;
         // `half` selects 64 of the 128 query columns of St/dPt and 32 of the 64 columns of dQ/dK/dV
         const int r = threadIdx.x & 127;
         const int half = threadIdx.x >> 7;
@@ -193,33 +244,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         uint8_t* prow = sPt + row_off;
         uint8_t* drow = sdSt + row_off;
         bool ok = true;
-
-        auto drain_dq = [&](int i) -> bool {
-            // dQ block i: lane r = query row i*128 + r; this thread stages 32 of its 64 columns
-            uint32_t v[32];
-            tmem_ld32(tmem + lane_addr + C_DQ + half * 32, v);
-            tmem_ld_wait();
-            if (threadIdx.x == 0) {
-                tma_store_wait_read<0>();   // the previous reduction no longer reads the staging tile
-                mbar_arrive(dq_free);
-            }
-            if (!mbar_wait(dq_free, i & 1, abort_flag)) return false;
-            uint8_t* row = sDQ + half * (DQ_STAGE / 2) + (r >> 3) * 1024 + sw * 128;
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-                *reinterpret_cast<float4*>(row + ((static_cast<uint32_t>(g) ^ sw) << 4)) =
-                    make_float4(__uint_as_float(v[g * 4]) * p.scale, __uint_as_float(v[g * 4 + 1]) * p.scale,
-                                __uint_as_float(v[g * 4 + 2]) * p.scale, __uint_as_float(v[g * 4 + 3]) * p.scale);
-            fence_proxy_async();
-            mbar_arrive(dq_ready);
-            if (threadIdx.x == 0) {
-                if (!mbar_wait(dq_ready, i & 1, abort_flag)) return false;
-                tma_reduce_add_4d(&tmDQ, sDQ, 0, i * BQ, h, b);
-                tma_reduce_add_4d(&tmDQ, sDQ + DQ_STAGE / 2, 32, i * BQ, h, b);
-                tma_store_commit();
-            }
-            return true;
-        };
 
         // lse / delta of the first query block; later blocks are fetched one step ahead
         float n_lse = 0.f, n_delta = 0.f;
@@ -259,23 +283,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             // occupy the shared-memory tiles.  Pt carries the dropout mask without its 1 / (1 - p)
             // factor (dV is scaled once at the end); dSt = P (mask dP / (1 - p) - delta).
             uint4 pk[2][4], dk4[2][4];
-            // the second half of the columns is fetched from tensor memory while the first is processed
-            uint32_t svb[2][32], dvb[2][32];
-            tmem_ld32(tmem + lane_addr + C_ST + half * 64, svb[0]);
-            tmem_ld32(tmem + lane_addr + C_DPT + half * 64, dvb[0]);
-            tmem_ld_wait();
-            tmem_ld32(tmem + lane_addr + C_ST + half * 64 + 32, svb[1]);
-            tmem_ld32(tmem + lane_addr + C_DPT + half * 64 + 32, dvb[1]);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tmem + lane_addr + C_ST + half * 64 + c * 32, sv);
+                tmem_ld32(tmem + lane_addr + C_DPT + half * 64 + c * 32, dv);
+                tmem_ld_wait();
                 if (c == 1) {
                     // both TMEM tiles are in registers: the next step's MMAs may overwrite them
-                    tmem_ld_wait();
                     tc_fence_before();
                     mbar_arrive(s_free);
                 }
-                const uint32_t(&sv)[32] = svb[c];
-                const uint32_t(&dv)[32] = dvb[c];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     float pd[8], ds[8];
@@ -313,16 +331,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 }
             }
             if (i > 0) {
-                // the previous step's dV / dK / dQ products read Pt / dSt: wait, collect dQ, then overwrite
+                // the previous step's dV / dK / dQ products read Pt / dSt: wait, then overwrite
                 if (!mbar_wait(mma_done, (i - 1) & 1, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                if (!drain_dq(i - 1)) {
-                    ok = false;
-                    break;
-                }
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -338,8 +352,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         if (ok && mbar_wait(mma_done, (nq - 1) & 1, abort_flag)) {
             tc_fence_after();
-            drain_dq(nq - 1);
-            if (threadIdx.x == 0) tma_store_wait<0>();   // the last reduction has landed
             T* dk = reinterpret_cast<T*>(p.dK) + b * p.dk_sb + static_cast<long long>(key) * p.dk_ss + h * p.dk_sh +
                     half * 32;
             T* dvp = reinterpret_cast<T*>(p.dV) + b * p.dv_sb + static_cast<long long>(key) * p.dv_ss + h * p.dv_sh +
@@ -383,24 +395,39 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     }
 }
 
-// delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d]; one warp per (b,h,q), D = 64
+// delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d], D = 64.  Rows are taken in memory order ((b, q, h): h is
+// the fastest index of a [B, S, H, D] tensor), 8 lanes x 16 bytes per row, so a warp reads 512 contiguous
+// bytes of each tensor per step.
 template <typename T>
 __global__ void attn_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO,
                                   float* __restrict__ delta, int B, int H, int S, long long o_sb,
                                   long long o_ss, long long o_sh, long long d_sb, long long d_ss,
                                   long long d_sh) {
-    const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (w >= static_cast<long long>(B) * H * S) return;
-    const int q = w % S;
-    const int h = (w / S) % H;
-    const int b = w / (static_cast<long long>(S) * H);
-    const T* o = O + b * o_sb + q * o_ss + h * o_sh + lane * 2;
-    const T* d = dO + b * d_sb + q * d_ss + h * d_sh + lane * 2;
-    float s = to_f32<T>(o[0]) * to_f32<T>(d[0]) + to_f32<T>(o[1]) * to_f32<T>(d[1]);
+    const long long rows = static_cast<long long>(B) * S * H;
+    const int sub = threadIdx.x & 7;
+    const long long step = (static_cast<long long>(gridDim.x) * blockDim.x) >> 3;
+    // warp-uniform trip count: every lane takes part in the shuffles
+    long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 3;
+    const long long first = (blockIdx.x * static_cast<long long>(blockDim.x) + (threadIdx.x & ~31)) >> 3;
+    for (long long base = first; base < rows; base += step, row += step) {
+        float s = 0.f;
+        int h = 0, q = 0, b = 0;
+        if (row < rows) {
+            h = static_cast<int>(row % H);
+            q = static_cast<int>((row / H) % S);
+            b = static_cast<int>(row / (static_cast<long long>(H) * S));
+            const uint4 ov = *reinterpret_cast<const uint4*>(O + b * o_sb + q * o_ss + h * o_sh + sub * 8);
+            const uint4 dv = *reinterpret_cast<const uint4*>(dO + b * d_sb + q * d_ss + h * d_sh + sub * 8);
+            const T* oe = reinterpret_cast<const T*>(&ov);
+            const T* de = reinterpret_cast<const T*>(&dv);
 #pragma unroll
-    for (int x = 16; x > 0; x >>= 1) s += __shfl_xor_sync(0xffffffffu, s, x);
-    if (lane == 0) delta[w] = s;
+            for (int j = 0; j < 8; ++j) s = fmaf(to_f32<T>(oe[j]), to_f32<T>(de[j]), s);
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if (sub == 0 && row < rows) delta[(static_cast<long long>(b) * H + h) * S + q] = s;
+    }
 }
 
 // dQ[b,q,h,:] = (T) acc[b,q,h,:]
@@ -434,7 +461,16 @@ static int launch_bwd(const RbAttnArgs& a, cudaStream_t st) {
     if ((rc = make_tmap_4d(&tv, a.V, a.dtype, D, S, H, B, a.v_ss * 2, a.v_sh * 2, a.v_sb * 2, 64, 128))) return rc;
     if ((rc = make_tmap_4d(&tdo, a.dO, a.dtype, D, S, H, B, a.do_ss * 2, a.do_sh * 2, a.do_sb * 2, 64, 128))) return rc;
     const long long rows = static_cast<long long>(a.B) * a.H * a.S;
-    attn_delta_kernel<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(
+    unsigned rb_delta_grid = 1;
+    {
+        // 8 lanes per row; the grid is sized so that every thread handles a few rows
+        long long blocks = (rows * 8 + 255) / 256;
+        const long long cap = 148LL * 32;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        rb_delta_grid = static_cast<unsigned>(blocks);
+    }
+    attn_delta_kernel<T><<<rb_delta_grid, 256, 0, st>>>(
         static_cast<const T*>(a.O), static_cast<const T*>(a.dO), a.delta, a.B, a.H, a.S, a.o_sb,
         a.o_ss, a.o_sh, a.do_sb, a.do_ss, a.do_sh);
     cudaMemsetAsync(a.dq_accum, 0, static_cast<size_t>(rows) * 64 * sizeof(float), st);

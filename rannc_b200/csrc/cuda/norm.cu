@@ -65,7 +65,7 @@ __device__ __forceinline__ float group_sum(float v, float* sm, int warp, int lan
 
 // A row of H = 256 * NCHUNK * WPR elements is shared by WPR warps.
 template <typename T, int NCHUNK, int WPR>
-__global__ void __launch_bounds__(LN_THREADS)
+__global__ void __launch_bounds__(LN_THREADS, 3)
     ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual,
                   const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
                   T* __restrict__ z_out, float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -75,12 +75,9 @@ __global__ void __launch_bounds__(LN_THREADS)
     __shared__ float sm[LN_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slot = warp / WPR, part = warp % WPR;
-    float g[NCHUNK][8], b[NCHUNK][8];
-#pragma unroll
-    for (int c = 0; c < NCHUNK; ++c) {
-        ld8(gamma + ((part * NCHUNK + c) * 32 + lane) * 8, g[c]);
-        ld8(beta + ((part * NCHUNK + c) * 32 + lane) * 8, b[c]);
-    }
+    // gamma / beta are re-read per row (they stay in L1): keeping them in registers costs 16 * NCHUNK
+    // registers and with them a third of the warps that could be in flight, which is what bounds a kernel
+    // whose rows are one dependent load -> reduce -> store chain each
     for (int r0 = blockIdx.x * RPB; r0 < rows; r0 += gridDim.x * RPB) {
         const int row = r0 + slot;
         const bool live = row < rows;
@@ -129,9 +126,11 @@ __global__ void __launch_bounds__(LN_THREADS)
         }
 #pragma unroll
         for (int c = 0; c < NCHUNK; ++c) {
-            float o[8];
+            float o[8], g[8], b[8];
+            ld8(gamma + ((part * NCHUNK + c) * 32 + lane) * 8, g);
+            ld8(beta + ((part * NCHUNK + c) * 32 + lane) * 8, b);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = (v[c][j] - mean) * rstd * g[c][j] + b[c][j];
+            for (int j = 0; j < 8; ++j) o[j] = (v[c][j] - mean) * rstd * g[j] + b[j];
             st8(y + base + ((part * NCHUNK + c) * 32 + lane) * 8, o);
         }
     }
@@ -249,7 +248,7 @@ static int launch_fwd(const void* x, const void* res, const void* g, const void*
     const float scale = p > 0.f ? 1.f / (1.f - p) : 1.f;
     constexpr int RPB = LN_WARPS / WPR;
     int grid = (rows + RPB - 1) / RPB;
-    const int cap = 148 * 8;
+    const int cap = 148 * 12;
     if (grid > cap) grid = cap;
     ln_fwd_kernel<T, NCHUNK, WPR><<<grid, LN_THREADS, 0, st>>>(
         static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(g),
@@ -286,6 +285,21 @@ static int launch_bwd(const void* dy, const void* z, const void* g, const float*
         default: return -2;                             \
     }
 
+// The forward kernel prefers fewer elements per thread (more warps per row): fewer registers, more CTAs
+// per SM, more loads in flight (measured at H = 1024: 0.69 of the copy bandwidth against 0.63).
+#define RB_LN_DISPATCH_FWD(T, FN, ...)                  \
+    switch (H / 256) {                                  \
+        case 1: return rb::FN<T, 1, 1>(__VA_ARGS__);    \
+        case 2: return rb::FN<T, 2, 1>(__VA_ARGS__);    \
+        case 3: return rb::FN<T, 3, 1>(__VA_ARGS__);    \
+        case 4: return rb::FN<T, 2, 2>(__VA_ARGS__);    \
+        case 6: return rb::FN<T, 3, 2>(__VA_ARGS__);    \
+        case 8: return rb::FN<T, 2, 4>(__VA_ARGS__);    \
+        case 12: return rb::FN<T, 3, 4>(__VA_ARGS__);   \
+        case 16: return rb::FN<T, 4, 4>(__VA_ARGS__);   \
+        default: return -2;                             \
+    }
+
 // 1 when H is a width the register-resident kernels cover
 extern "C" int rb_ln_supported(int H) {
     if (H % 256) return 0;
@@ -308,16 +322,11 @@ extern "C" int rb_ln_fwd(const void* x, const void* residual, const void* gamma,
                          float p, uint64_t seed, uint64_t offset, int dtype, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows <= 0) return 0;
-    static const int alt = [] { const char* e = getenv("RB_LN_ALT"); return e ? atoi(e) : 0; }();
-    if (alt && H == 1024 && dtype == 1) {
-        if (alt == 2) return rb::launch_fwd<__nv_bfloat16, 2, 2>(x, residual, gamma, beta, y, z, mean, rstd, rows, eps, p, seed, offset, st);
-        if (alt == 4) return rb::launch_fwd<__nv_bfloat16, 1, 4>(x, residual, gamma, beta, y, z, mean, rstd, rows, eps, p, seed, offset, st);
-    }
     if (dtype == 1) {
-        RB_LN_DISPATCH(__nv_bfloat16, launch_fwd, x, residual, gamma, beta, y, z, mean, rstd, rows,
+        RB_LN_DISPATCH_FWD(__nv_bfloat16, launch_fwd, x, residual, gamma, beta, y, z, mean, rstd, rows,
                        eps, p, seed, offset, st)
     } else {
-        RB_LN_DISPATCH(__half, launch_fwd, x, residual, gamma, beta, y, z, mean, rstd, rows, eps, p,
+        RB_LN_DISPATCH_FWD(__half, launch_fwd, x, residual, gamma, beta, y, z, mean, rstd, rows, eps, p,
                        seed, offset, st)
     }
 }

@@ -88,6 +88,9 @@ def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: in
          dev_total_mem: int, use_amp: bool, enable_zero: bool, offload_params: bool, dep_id: str,
          load_deployment: Optional[str] = None) -> Plan:
     """``ir_graph`` must already be scaled to the global batch size."""
+    if dev_total_mem == 0 and int(conf("partitioning_dry_run_np")) > 0 and int(conf("mem_limit_gb")) <= 0:
+        # a dry run on a machine without the target device plans for a B200's 180 GB unless told otherwise
+        dev_total_mem = 180 * 10 ** 9
     dev_mem = device_memory_budget(dev_total_mem)
     pconf = make_partitioning_conf(world_size, global_batch, dev_mem, use_amp, enable_zero, offload_params)
 

@@ -185,7 +185,7 @@ class PipelineRuntime:
                     got = self._move(v, held, pr, self.master, i)
                     pieces.append(got)
                 pieces = [p for p in pieces if p is not None]
-                full = (torch.cat(pieces, 0) if len(pieces) > 1 else pieces[0]) if pieces else None
+                full = _cat_rows(pieces) if pieces else None
                 if not self.gather_inputs and self.world > 1:
                     if full is None:
                         full = torch.empty(list(v.type.tensor_dim), dtype=_TORCH_DTYPE[v.type.tensor_elem_type],
@@ -303,6 +303,28 @@ class PipelineRuntime:
     def clear(self):
         for st in self.stages.values():
             st.clear()
+
+
+def _cat_rows(pieces: List[torch.Tensor]) -> torch.Tensor:
+    """Micro-batch outputs back into one batch: row blocks copied into one preallocated tensor by the
+    row-copy kernel (16-byte vectors) on the device, ``torch.cat`` elsewhere
+    (reference: TorchUtil.cpp:976-1006, cat of the per-split outputs)."""
+    if len(pieces) == 1:
+        return pieces[0]
+    p0 = pieces[0]
+    row_bytes = p0[0].numel() * p0.element_size() if p0.dim() > 0 and p0.shape[0] > 0 else 0
+    if not (p0.is_cuda and row_bytes > 0 and row_bytes % 16 == 0 and all(p.is_contiguous() for p in pieces)):
+        return torch.cat(pieces, 0)
+    from ..ops import kernels as K
+
+    rows = sum(p.shape[0] for p in pieces)
+    out = torch.empty((rows,) + tuple(p0.shape[1:]), dtype=p0.dtype, device=p0.device)
+    off = 0
+    for p in pieces:
+        if p.shape[0]:
+            K.rowcopy(p, out[off:], p.shape[0], row_bytes, row_bytes, row_bytes)
+        off += p.shape[0]
+    return out
 
 
 _TORCH_DTYPE = {

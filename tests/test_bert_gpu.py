@@ -74,3 +74,31 @@ def test_bert_dropout_trains_and_checkpoint_recompute_matches():
     # same dropout masks with and without recomputation
     assert abs(grads[0][0] - grads[1][0]) < 1e-3
     assert torch.allclose(grads[0][1], grads[1][1], rtol=1e-2, atol=1e-4)
+
+
+def test_micro_batched_tensor_output_is_reassembled():
+    """Two micro-batches on one GPU: the per-micro-batch output rows are copied back into one batch tensor
+    (row-copy kernel) in the caller's order."""
+    import rannc_b200 as pyrannc
+    from rannc_b200.models.mlp import TutorialMLP
+    from rannc_b200.utils.config import set_conf
+
+    torch.manual_seed(0)
+    set_conf("pipeline_num", 2)
+    try:
+        net = TutorialMLP(d_in=256, hidden=512, classes=64)
+        ref = TutorialMLP(d_in=256, hidden=512, classes=64)
+        ref.load_state_dict(net.state_dict())
+        ref = ref.cuda()
+        model = pyrannc.RaNNCModule(net, torch.optim.SGD(net.parameters(), lr=0.1), enable_apex_amp=True)
+        x = torch.randn(48, 256, device="cuda")
+        out = model(x)
+        assert model._dep.pipeline_num == 2
+        want = ref(x)
+        assert out.shape == want.shape
+        err = (out.float() - want).abs().max().item() / want.abs().max().item()
+        assert err < 3e-2, err
+        out.float().sum().backward()
+    finally:
+        set_conf("pipeline_num", 0)
+        pyrannc.clear()

@@ -395,3 +395,36 @@ def test_tutorial_script_runs_on_cpu(tmp_path):
     assert set(ck["model"].keys()) == {"net.fc1.weight", "net.fc1.bias", "net.fc2.weight", "net.fc2.bias",
                                        "net.fc3.weight", "net.fc3.bias"}
     assert len(ck["optimizer"]["state"]) == 6
+
+
+def test_dry_run_plans_a_large_model_from_meta_tensors():
+    """partitioning_dry_run_np: plan for 8 devices of 180 GB in one CPU process; the model exists only as
+    meta tensors, so nothing of its size is allocated (reference: RaNNCModule.cpp:416-421, run_dp_dry)."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r'''
+import os, sys
+sys.path.insert(0, os.getcwd())
+import torch
+import rannc_b200 as pyrannc
+from rannc_b200.models.bert import BertConfig, BertForPreTraining, synthetic_batch
+cfg = BertConfig(hidden_size=2048, num_hidden_layers=24, num_attention_heads=32, intermediate_size=8192)
+with torch.device("meta"):
+    model = BertForPreTraining(cfg)
+opt = torch.optim.Adam(model.parameters(), lr=1e-4)
+m = pyrannc.RaNNCModule(model, opt, enable_apex_amp=True, enable_zero=True, check_unused_values=False)
+batch = tuple(t.to("meta") for t in synthetic_batch(cfg, 256, 512, seed=0))
+try:
+    m(*batch)
+except SystemExit:
+    print("PLANNED")
+'''
+    env = dict(os.environ, RANNC_FORCE_CPU="1", RANK="0", WORLD_SIZE="1", RANNC_LOG_LEVEL="info",
+               RANNC_PARTITIONING_DRY_RUN_NP="8")
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=900)
+    out = r.stdout + r.stderr
+    assert "PLANNED" in out, out[-3000:]
+    assert "Assigned subgraph" in out and "repl=" in out
