@@ -34,8 +34,9 @@ constexpr int BWD_THREADS = BWD_MATH + 32 + BWD_DRAIN;
 constexpr int BWD_TMEM_COLS = 512;
 constexpr int C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
 constexpr int DQ_STAGE = 128 * 64 * 4;   // 32 KiB: [2 column halves][128 rows x 128 B]
-// K, V + (Q, dO) x 2 stages + Pt, dSt + dQ staging + per-step (lse, delta, row hash) x 2 + barriers
-constexpr int BWD_SMEM = 2 * TILE + 4 * TILE + 2 * SQ_BYTES + DQ_STAGE + 6 * 128 * 4 + 128;
+constexpr int QD_STAGES = 3;             // Q / dO ring: block i + 2 is loaded while blocks i and i + 1 are in use
+// K, V + (Q, dO) x 3 stages + Pt, dSt + dQ staging + per-step (lse, delta, row hash) + barriers
+constexpr int BWD_SMEM = 2 * TILE + 2 * QD_STAGES * TILE + 2 * SQ_BYTES + DQ_STAGE + 3 * 128 * 4 + 128;
 
 struct AttnBwdParams {
     int B, H, S;
@@ -61,25 +62,25 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = smem + TILE;
-    uint8_t* sQ = smem + 2 * TILE;   // [2]
-    uint8_t* sdO = smem + 4 * TILE;  // [2]
-    uint8_t* sPt = smem + 6 * TILE;
+    uint8_t* sQ = smem + 2 * TILE;                     // [QD_STAGES]
+    uint8_t* sdO = smem + (2 + QD_STAGES) * TILE;      // [QD_STAGES]
+    uint8_t* sPt = smem + (2 + 2 * QD_STAGES) * TILE;
     uint8_t* sdSt = sPt + SQ_BYTES;
     uint8_t* sDQ = sdSt + SQ_BYTES;
-    float* s_lse = reinterpret_cast<float*>(sDQ + DQ_STAGE);        // [2][128]
-    float* s_delta = s_lse + 256;                                   // [2][128]
-    uint32_t* s_rhash = reinterpret_cast<uint32_t*>(s_delta + 256);  // [2][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_rhash + 256);
+    float* s_lse = reinterpret_cast<float*>(sDQ + DQ_STAGE);        // [128], rewritten every step
+    float* s_delta = s_lse + 128;                                   // [128]
+    uint32_t* s_rhash = reinterpret_cast<uint32_t*>(s_delta + 128);  // [128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_rhash + 128);
     uint64_t* kv_full = bars;
-    uint64_t* qd_full = bars + 1;  // [2]
-    uint64_t* s_full = bars + 3;
-    uint64_t* s_free = bars + 4;
-    uint64_t* pds_ready = bars + 5;
-    uint64_t* mma_done = bars + 6;
-    uint64_t* dq_free = bars + 7;    // the previous bulk reduction has read the staging tile
-    uint64_t* dq_ready = bars + 8;   // every drain thread has written its part of the staging tile
-    uint64_t* dq_taken = bars + 9;   // dQ of the last step is out of tensor memory: the next may overwrite it
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* qd_full = bars + 1;  // [QD_STAGES]
+    uint64_t* s_full = bars + 4;
+    uint64_t* s_free = bars + 5;
+    uint64_t* pds_ready = bars + 6;
+    uint64_t* mma_done = bars + 7;
+    uint64_t* dq_free = bars + 8;    // the previous bulk reduction has read the staging tile
+    uint64_t* dq_ready = bars + 9;   // every drain thread has written its part of the staging tile
+    uint64_t* dq_taken = bars + 10;  // dQ of the last step is out of tensor memory: the next may overwrite it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,8 +89,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
-        mbar_init(&qd_full[0], 1);
-        mbar_init(&qd_full[1], 1);
+        for (int st = 0; st < QD_STAGES; ++st) mbar_init(&qd_full[st], 1);
         mbar_init(s_full, 1);
         mbar_init(s_free, BWD_MATH);
         mbar_init(pds_ready, BWD_MATH);
@@ -116,14 +116,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             const uint32_t id_kn = make_idesc_f16(fmt, 0, 1, 128, 64);  // A K-major, B MN-major
             const uint32_t id_nn = make_idesc_f16(fmt, 1, 1, 128, 64);  // A MN-major, B MN-major
             auto load_qd = [&](int i) {
-                const int st = i & 1;
+                const int st = i % QD_STAGES;
                 mbar_arrive_expect_tx(&qd_full[st], 2 * TILE);
                 tma_load_4d(sQ + st * TILE, &tmQ, &qd_full[st], 0, i * BQ, h, b);
                 tma_load_4d(sdO + st * TILE, &tmdO, &qd_full[st], 0, i * BQ, h, b);
             };
             auto issue_s = [&](int i) {
                 const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-                const uint32_t qa = smem_u32(sQ + (i & 1) * TILE), da = smem_u32(sdO + (i & 1) * TILE);
+                const uint32_t qa = smem_u32(sQ + (i % QD_STAGES) * TILE), da = smem_u32(sdO + (i % QD_STAGES) * TILE);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     umma_f16(tmem + C_ST, make_smem_desc_sw128(ka + k * 32, 16, 1024),
@@ -137,25 +137,32 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             mbar_arrive_expect_tx(kv_full, 2 * TILE);
             tma_load_4d(sK, &tmK, kv_full, 0, key0, h, b);
             tma_load_4d(sV, &tmV, kv_full, 0, key0, h, b);
-            load_qd(0);
-            if (nq > 1) load_qd(1);
+            for (int i = 0; i < QD_STAGES && i < nq; ++i) load_qd(i);
             bool ok = mbar_wait(kv_full, 0, abort_flag) && mbar_wait(&qd_full[0], 0, abort_flag);
             if (ok) {
                 tc_fence_after();
                 issue_s(0);
             }
             for (int i = 0; i < nq && ok; ++i) {
+                // S / dP of the next block go to the tensor core as soon as the math warps have read this
+                // block's: they run behind the previous block's products, while this block's math is busy
                 if (i + 1 < nq) {
-                    ok = mbar_wait(&qd_full[(i + 1) & 1], ((i + 1) >> 1) & 1, abort_flag) &&
+                    ok = mbar_wait(&qd_full[(i + 1) % QD_STAGES], ((i + 1) / QD_STAGES) & 1, abort_flag) &&
                          mbar_wait(s_free, i & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
                     issue_s(i + 1);
                 }
+                // the stage block i - 1 used is free once its products are done: fetch block i + 2 into it,
+                // a whole step before its S / dP products are issued
+                if (i >= 1 && i + 2 < nq) {
+                    if (!mbar_wait(mma_done, (i - 1) & 1, abort_flag)) break;
+                    load_qd(i + 2);
+                }
                 if (!mbar_wait(pds_ready, i & 1, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t pa = smem_u32(sPt), sa = smem_u32(sdSt), ka = smem_u32(sK);
-                const uint32_t qa = smem_u32(sQ + (i & 1) * TILE), da = smem_u32(sdO + (i & 1) * TILE);
+                const uint32_t qa = smem_u32(sQ + (i % QD_STAGES) * TILE), da = smem_u32(sdO + (i % QD_STAGES) * TILE);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const uint32_t koff = (k >> 2) * (SQ_BYTES / 2) + (k & 3) * 32;
@@ -178,10 +185,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     umma_f16(tmem + C_DQ, make_smem_desc_sw128(sa + k * 2048, SQ_BYTES / 2, 1024),
                              make_smem_desc_sw128(ka + k * 2048, 8192, 1024), id_nn, k != 0);
                 umma_commit(mma_done);
-                if (i + 2 < nq) {
-                    if (!mbar_wait(mma_done, i & 1, abort_flag)) break;
-                    load_qd(i + 2);
-                }
             }
         }
     } else if (warp > 8) {
@@ -253,13 +256,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             n_delta = r < p.S ? p.delta[bh * p.S + r] : 0.f;
         }
         for (int i = 0; i < nq; ++i) {
-            const int st = i & 1;
             const int q0 = i * BQ;
+            // every thread is done reading the previous step's row statistics before they are replaced
+            bar_sync_named(1, BWD_MATH);
             if (half == 0) {
                 // +inf for rows past the end of the sequence: their probabilities come out as exp2(-inf) = 0
-                s_lse[st * 128 + r] = n_lse_raw ? n_lse * 1.4426950408889634f : n_lse;
-                s_delta[st * 128 + r] = n_delta;
-                s_rhash[st * 128 + r] = drop_row_hash(p.seed, b, h, q0 + r, p.H, p.S);
+                s_lse[r] = n_lse_raw ? n_lse * 1.4426950408889634f : n_lse;
+                s_delta[r] = n_delta;
+                s_rhash[r] = drop_row_hash(p.seed, b, h, q0 + r, p.H, p.S);
                 // issued here (volatile: not sunk to the use), consumed at the top of the next step
                 const int qn = q0 + BQ + r;
                 if (i + 1 < nq && qn < p.S) {
@@ -273,9 +277,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 }
             }
             bar_sync_named(1, BWD_MATH);
+            // after a failed wait the loop keeps running (every later wait fails at once) so that all threads
+            // still meet at the named barriers
             if (!mbar_wait(s_full, i & 1, abort_flag)) {
                 ok = false;
-                break;
+                continue;
             }
             tc_fence_after();
             // Pt / dSt of this thread's 64 columns, packed to 16 bits, held in registers: the whole
@@ -299,7 +305,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     float pd[8], ds[8];
 #pragma unroll
                     for (int hq = 0; hq < 2; ++hq) {
-                        const int qb = st * 128 + half * 64 + c * 32 + g * 8 + hq * 4;
+                        const int qb = half * 64 + c * 32 + g * 8 + hq * 4;
                         const float4 ls4 = *reinterpret_cast<const float4*>(s_lse + qb);
                         const float4 dl4 = *reinterpret_cast<const float4*>(s_delta + qb);
                         const float lsv[4] = {ls4.x, ls4.y, ls4.z, ls4.w};
@@ -334,7 +340,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 // the previous step's dV / dK / dQ products read Pt / dSt: wait, then overwrite
                 if (!mbar_wait(mma_done, (i - 1) & 1, abort_flag)) {
                     ok = false;
-                    break;
+                    continue;
                 }
                 tc_fence_after();
             }

@@ -209,9 +209,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
         };
         for (int j = 0; j < nchunks; ++j) {
+            // after a failed wait the loop keeps running (every later wait fails at once) so that the pair of
+            // threads sharing a row still meets at the named barrier below
             if (!mbar_wait(&s_full[t], j & 1, abort_flag)) {
                 ok = false;
-                break;
             }
             tc_fence_after();
             const int key0 = j * AK + half * 64;
