@@ -109,6 +109,8 @@ def main():
                     help="bert: the headline benchmark; wide_resnet: ResNet-152 with every width x --width")
     ap.add_argument("--width", type=float, default=8.0)
     ap.add_argument("--image", type=int, default=224)
+    ap.add_argument("--amp-dtype", default="", choices=["", "fp16", "bf16"],
+                    help="16-bit compute type (default: bf16 for bert, fp16 for wide_resnet)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_unavailable()
@@ -150,14 +152,16 @@ def main():
         # precision with dynamic loss scaling, SGD momentum 0.9, images N(0, 1), labels uniform over 1000 classes
         from rannc_b200.models.resnet import ResNetWithLoss, wide_resnet152
 
-        pyrannc.amp.set_dtype(torch.float16)
+        half = (args.amp_dtype or "fp16") == "fp16"
+        pyrannc.amp.set_dtype(torch.float16 if half else torch.bfloat16)
         model = ResNetWithLoss(wide_resnet152(width_mult=args.width))
         optimizer = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
         use_zero = False if args.zero < 0 else bool(args.zero)
         n_sets = 2
         for s in range(n_sets):
             g = torch.Generator().manual_seed(100 + s)
-            x = torch.randn(lb, 3, args.image, args.image, generator=g).half().pin_memory()
+            x = torch.randn(lb, 3, args.image, args.image, generator=g).to(
+                torch.float16 if half else torch.bfloat16).pin_memory()
             y = torch.randint(0, 1000, (lb,), generator=g).pin_memory()
             host.append((x, y))
     nparams = sum(p.numel() for p in model.parameters())
@@ -241,7 +245,8 @@ def main():
         else:
             mname = f"Wide ResNet-152 (widths x{args.width:g}), {args.image}x{args.image} images"
             data = "synthetic (N(0,1) images, uniform labels over 1000 classes), random-init weights"
-            optname, dtype = "SGD momentum 0.9 (fused, fp32 master, dynamic loss scale)", "fp16"
+            optname = "SGD momentum 0.9 (fused, fp32 master" + (", dynamic loss scale)" if half else ")")
+            dtype = "fp16" if half else "bf16"
         out = {
             "metric": ("BERT" if args.model == "bert" else "ResNet") + " samples/s (max over ranks)",
             "value": args.global_batch * args.steps / (ms / 1e3),

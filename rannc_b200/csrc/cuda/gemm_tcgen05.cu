@@ -694,6 +694,17 @@ static int launch(const RbGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
+// RB_GEMM_PAIR_COLLECTIVE=1 also puts the gather / scatter variants on the pair kernel (same prologue and
+// epilogue code; off by default until it has been timed over real peers)
+static bool pair_collective_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RB_GEMM_PAIR_COLLECTIVE");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 // RB_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel
 static bool pair_enabled() {
     static int v = -1;
@@ -722,10 +733,10 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     p.a_major = a->a_major;
     p.b_major = a->b_major;
     // The pair kernel (256 x 256 tile over two SMs) serves every GEMM with enough work to fill the GPU:
-    // enough tiles, or few tiles and a long K that is split (weight gradients).  Gather / scatter
-    // variants and small problems stay on the single-CTA kernel.
+    // enough tiles, or few tiles and a long K that is split (weight gradients); the gather prologue and the
+    // scatter epilogue are the same code in both variants.  Small problems stay on the single-CTA kernel.
     const bool accum32 = a->out_dtype == 1 && a->flags == RB_GEMM_ACCUM;
-    bool pair = pair_enabled() && a->ag_nranks <= 1 && a->rs_nranks <= 1;
+    bool pair = pair_enabled() && ((a->ag_nranks <= 1 && a->rs_nranks <= 1) || pair_collective_enabled());
     if (pair) {
         const long long pt = ((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + BN - 1) / BN) * a->batch;
         const long long kbs = (a->K + BK - 1) / BK;

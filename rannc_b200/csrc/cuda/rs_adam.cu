@@ -143,31 +143,51 @@ __global__ void __launch_bounds__(512)
                 }
             }
             float w[8], mm[8], vv[8];
+            const bool sgd = p.adamw == 2;
             *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i * 8);
             *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(p.master + i * 8 + 4);
             *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(p.m + i * 8);
             *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(p.m + i * 8 + 4);
-            *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(p.v + i * 8);
-            *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(p.v + i * 8 + 4);
+            if (!sgd) {
+                *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(p.v + i * 8);
+                *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(p.v + i * 8 + 4);
+            }
             uint4 packed;
             T16* o = reinterpret_cast<T16*>(&packed);
+            if (sgd) {
+                // SGD with momentum (torch.optim.SGD): beta1 = momentum, beta2 = dampening, eps > 0.5 = Nesterov,
+                // bias_corr1 == 0 marks the first step (the buffer starts as the gradient)
+                const bool first = p.bias_corr1 == 0.f, nesterov = p.eps > 0.5f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float gg = g[j] * gmul;
-                if (!p.adamw && p.weight_decay != 0.f) gg += p.weight_decay * w[j];
-                mm[j] = p.beta1 * mm[j] + (1.f - p.beta1) * gg;
-                vv[j] = p.beta2 * vv[j] + (1.f - p.beta2) * gg * gg;
-                float u = (mm[j] / p.bias_corr1) / (sqrtf(vv[j] / p.bias_corr2) + p.eps);
-                if (p.adamw && p.weight_decay != 0.f) u += p.weight_decay * w[j];
-                w[j] -= p.lr * u;
-                o[j] = from_f32<T16>(w[j]);
+                for (int j = 0; j < 8; ++j) {
+                    float gg = g[j] * gmul;
+                    if (p.weight_decay != 0.f) gg += p.weight_decay * w[j];
+                    mm[j] = first ? gg : p.beta1 * mm[j] + (1.f - p.beta2) * gg;
+                    const float u = nesterov ? gg + p.beta1 * mm[j] : mm[j];
+                    w[j] -= p.lr * u;
+                    o[j] = from_f32<T16>(w[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float gg = g[j] * gmul;
+                    if (!p.adamw && p.weight_decay != 0.f) gg += p.weight_decay * w[j];
+                    mm[j] = p.beta1 * mm[j] + (1.f - p.beta1) * gg;
+                    vv[j] = p.beta2 * vv[j] + (1.f - p.beta2) * gg * gg;
+                    float u = (mm[j] / p.bias_corr1) / (sqrtf(vv[j] / p.bias_corr2) + p.eps);
+                    if (p.adamw && p.weight_decay != 0.f) u += p.weight_decay * w[j];
+                    w[j] -= p.lr * u;
+                    o[j] = from_f32<T16>(w[j]);
+                }
             }
             *reinterpret_cast<float4*>(p.master + i * 8) = *reinterpret_cast<float4*>(w);
             *reinterpret_cast<float4*>(p.master + i * 8 + 4) = *reinterpret_cast<float4*>(w + 4);
             *reinterpret_cast<float4*>(p.m + i * 8) = *reinterpret_cast<float4*>(mm);
             *reinterpret_cast<float4*>(p.m + i * 8 + 4) = *reinterpret_cast<float4*>(mm + 4);
-            *reinterpret_cast<float4*>(p.v + i * 8) = *reinterpret_cast<float4*>(vv);
-            *reinterpret_cast<float4*>(p.v + i * 8 + 4) = *reinterpret_cast<float4*>(vv + 4);
+            if (!sgd) {
+                *reinterpret_cast<float4*>(p.v + i * 8) = *reinterpret_cast<float4*>(vv);
+                *reinterpret_cast<float4*>(p.v + i * 8 + 4) = *reinterpret_cast<float4*>(vv + 4);
+            }
             if (p.mc_param) {
                 multimem_st_b128(reinterpret_cast<T16*>(p.mc_param) + e, packed);
             } else {

@@ -23,7 +23,8 @@ typedef struct RbRsAdamArgs {
     uint32_t epoch;                        // strictly increasing per launch, same on every rank
     float grad_mul;                        // 1/world * 1/loss_scale
     float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2;
-    int32_t adamw;
+    int32_t adamw;                         // 0 Adam, 1 AdamW, 2 SGD (beta1 = momentum, beta2 = dampening,
+                                           // eps > 0.5 = Nesterov, bias_corr1 == 0 = first step; v unused)
     int32_t dtype16;                       // 0 fp16, 1 bf16
     int32_t num_ctas;                      // 0: 148
     int32_t pad_;

@@ -303,7 +303,7 @@ class RaNNCModule:
         want_fused = (self.use_amp_master_params and self.enable_zero and dev.type == "cuda" and world > 1 and
                       not self.offload_params and
                       bool(conf("fused_kernels")) and bool(conf("fused_grad_allreduce")) and
-                      type(self.optimizer) in (torch.optim.Adam, torch.optim.AdamW))
+                      type(self.optimizer) in (torch.optim.Adam, torch.optim.AdamW, torch.optim.SGD))
         self._storage.deploy(local_params, {n: sorted(r) for n, r in owner.items()}, opt_group_of, dev,
                              self._param_order_by_name, symmetric=want_fused, sliced=sliced,
                              symmetric_slices=dist_kernels)

@@ -183,11 +183,13 @@ def patch_optimizer(module, optimizer):
                 continue
             st = optimizer.state[target]
             st["step"] = torch.tensor(float(fs.step))
+            # a parameter cut by the shard boundary keeps its state as a flat piece
+            shp = target.shape if (b - a) == target.numel() else (b - a,)
             if optimizer._rannc_kind == "adam":
-                st["exp_avg"] = fs.m[a - lo:b - lo].view(target.shape)
-                st["exp_avg_sq"] = fs.v[a - lo:b - lo].view(target.shape)
+                st["exp_avg"] = fs.m[a - lo:b - lo].view(shp)
+                st["exp_avg_sq"] = fs.v[a - lo:b - lo].view(shp)
             else:
-                st["momentum_buffer"] = fs.m[a - lo:b - lo].view(target.shape)
+                st["momentum_buffer"] = fs.m[a - lo:b - lo].view(shp)
 
     def _offloaded_update(g, fs, hp, og, a, b, kind, ctrl):
         """Streams [a, b) of the host-resident fp32 state through the device in chunks."""
@@ -216,11 +218,13 @@ def patch_optimizer(module, optimizer):
 
         win.run(hosts, b - a, kernel)
 
-    def fused_step(ctrl=None):
+    def fused_step(ctrl=None, only=None):
         from .ops import kernels as K
 
         kind = optimizer._rannc_kind
         for g in storage.groups:
+            if only is not None and g not in only:
+                continue
             fs = optimizer._rannc_flat_state.get(id(g))
             if fs is None:
                 n = g.shard[1] - g.shard[0]
@@ -229,6 +233,8 @@ def patch_optimizer(module, optimizer):
                     g.flat_grad.is_cuda)
             fs.step += 1
         for g, og, a, b in _flat_ranges():
+            if only is not None and g not in only:
+                continue
             fs = optimizer._rannc_flat_state[id(g)]
             hp = optimizer.param_groups[og]
             lo = g.shard[0]
@@ -249,6 +255,8 @@ def patch_optimizer(module, optimizer):
                            float(hp.get("dampening", 0.0)), float(hp["weight_decay"]), bool(hp.get("nesterov")),
                            fs.step == 1, ctrl)
         for g in storage.groups:
+            if only is not None and g not in only:
+                continue
             fs = optimizer._rannc_flat_state.get(id(g))
             if fs is not None:
                 _publish_state(g, fs)
@@ -257,16 +265,23 @@ def patch_optimizer(module, optimizer):
         mod = optimizer._rannc_module
         red = getattr(mod, "_fused_reducer", None)
         if red is not None and red.pending and mod._needs_grad_norm():
-            # clipping / fp16 overflow checks need the reduced gradients first
-            storage.allreduce_grads_zero()
+            # clipping / fp16 overflow checks need the reduced gradients first (the full-precision groups were
+            # reduced when backward finished)
+            storage.allreduce_grads_zero(only=[g for g in storage.groups if g not in red.plain_groups])
             red.pending = False
         ctrl = mod._amp_prepare_step() if mod is not None else None
         if ctrl is False:
             return None  # overflow: skipped, scale already lowered
         if red is not None and red.pending:
             # reduce-scatter + Adam + all-gather in one kernel per rank
+            plain = list(red.plain_groups)
             red.step(None)
             red.publish_state()
+            if plain:
+                # full-precision groups: gradients were reduced by the collective path, update them here
+                fused_step(None, only=plain)
+                if storage.zero:
+                    storage.allgather_params_zero(only=plain)
             RF.bump_param_epoch()
             return None
         use_fused = optimizer._rannc_kind is not None and all(
@@ -424,7 +439,9 @@ def load_global_optimizer_state(optimizer, sd: dict) -> None:
                     ks = v.shape[1] // len(sl)
                     idx = sl.index(comm.get_rank())
                     v = v[:, idx * ks:(idx + 1) * ks].contiguous()
-                piece = v.reshape(-1)[a - lo:b - lo].to(target.device, torch.float32).view(target.shape)
+                piece = v.reshape(-1)[a - lo:b - lo].to(target.device, torch.float32)
+                if piece.numel() == target.numel():
+                    piece = piece.view(target.shape)
                 st[k] = piece.clone()
             else:
                 st[k] = torch.tensor(float(v)) if k == "step" else v

@@ -75,12 +75,13 @@ class FusedGradReducer:
         self.states: Dict[int, _GroupState] = {}
         self.handles_reduce = True
         self.pending = False
+        self.plain_groups = []
         self.use_multimem = bool(int(__import__("os").environ.get("RANNC_USE_MULTIMEM", "1")))
 
     @staticmethod
     def eligible(storage, optimizer) -> Optional[str]:
-        if optimizer is None or type(optimizer) not in (torch.optim.Adam, torch.optim.AdamW):
-            return "the optimizer is not Adam / AdamW"
+        if optimizer is None or type(optimizer) not in (torch.optim.Adam, torch.optim.AdamW, torch.optim.SGD):
+            return "the optimizer is not Adam / AdamW / SGD"
         for g in optimizer.param_groups:
             if g.get("amsgrad") or g.get("maximize"):
                 return "amsgrad / maximize are not supported"
@@ -88,12 +89,13 @@ class FusedGradReducer:
             return "needs mixed precision with enable_zero (sharded fp32 master)"
         for g in storage.groups:
             if g.flat_master is None:
-                return "a parameter group has no fp32 master copy"
+                continue   # a full-precision group (batch-norm state): reduced and updated on the library path
             if g.nranks > MAX_PEERS:
                 return f"more than {MAX_PEERS} ranks in an owner set"
             if len({og for og in g.opt_group if og >= 0}) > 1:
                 hp = [optimizer.param_groups[og] for og in sorted({og for og in g.opt_group if og >= 0})]
-                keys = ("lr", "betas", "eps", "weight_decay")
+                keys = ("lr", "betas", "eps", "weight_decay") if "betas" in hp[0] else \
+                    ("lr", "momentum", "dampening", "nesterov", "weight_decay")
                 if any(tuple(h[k] for k in keys) != tuple(hp[0][k] for k in keys) for h in hp):
                     return "param groups with different hyper-parameters share a flat buffer"
         return None
@@ -106,7 +108,10 @@ class FusedGradReducer:
         import torch.distributed._symmetric_memory as symm_mem
 
         self = cls(storage, optimizer)
+        self.plain_groups = [g for g in storage.groups if g.flat_master is None]
         for g in storage.groups:
+            if g.flat_master is None:
+                continue
             st = _GroupState()
             if g.nranks > 1:
                 if not getattr(g, "symmetric", False):
@@ -127,6 +132,9 @@ class FusedGradReducer:
         """Called at the end of backward: the local gradients are final; the reduction itself happens
         inside the optimizer step's kernel."""
         self.pending = True
+        if self.plain_groups:
+            # groups without a 16-bit / fp32-master pair take the collective path right away
+            self.storage.allreduce_grads_zero(only=self.plain_groups)
 
     def _moments(self, g):
         """The flat Adam moments are shared with the non-fused optimizer step (``opt._FlatState``)."""
@@ -134,13 +142,16 @@ class FusedGradReducer:
 
         fs = self.optimizer._rannc_flat_state.get(id(g))
         if fs is None:
-            fs = self.optimizer._rannc_flat_state[id(g)] = _FlatState(g.shard[1] - g.shard[0], g.device, "adam")
+            kind = "sgd" if type(self.optimizer) is torch.optim.SGD else "adam"
+            fs = self.optimizer._rannc_flat_state[id(g)] = _FlatState(g.shard[1] - g.shard[0], g.device, kind)
         return fs
 
     def step(self, ctrl: Optional[torch.Tensor] = None):
         world = comm.get_world_size()
         lib = _lib.lib()
         for g in self.storage.groups:
+            if g.flat_master is None:
+                continue
             st = self.states[id(g)]
             fs = self._moments(g)
             fs.step += 1
@@ -149,7 +160,8 @@ class FusedGradReducer:
             if not ogs:
                 continue
             hp = self.optimizer.param_groups[ogs[0]]
-            b1, b2 = hp["betas"]
+            sgd = type(self.optimizer) is torch.optim.SGD
+            b1, b2 = (float(hp["momentum"]), float(hp.get("dampening", 0.0))) if sgd else hp["betas"]
             a = _Args()
             if g.nranks > 1:
                 for r in range(g.nranks):
@@ -166,16 +178,23 @@ class FusedGradReducer:
                 if st.flags is None:
                     st.flags = torch.zeros(2 * MAX_PEERS, dtype=torch.int32, device=g.device)
                 a.peer_flags[0] = st.flags.data_ptr()
-            a.master, a.m, a.v = g.flat_master.data_ptr(), fs.m.data_ptr(), fs.v.data_ptr()
+            a.master, a.m = g.flat_master.data_ptr(), fs.m.data_ptr()
+            a.v = fs.v.data_ptr() if fs.v is not None else fs.m.data_ptr()
             a.done_counter = st.done.data_ptr()
             a.lo, a.len = g.shard[0], g.shard[1] - g.shard[0]
             a.nranks, a.my_idx = g.nranks, g.my_index
             a.epoch = st.epoch
             a.grad_mul = 1.0 / world
-            a.lr, a.beta1, a.beta2, a.eps = float(hp["lr"]), float(b1), float(b2), float(hp["eps"])
             a.weight_decay = float(hp["weight_decay"])
-            a.bias_corr1, a.bias_corr2 = 1.0 - b1 ** fs.step, 1.0 - b2 ** fs.step
-            a.adamw = 1 if type(self.optimizer) is torch.optim.AdamW else 0
+            if sgd:
+                a.lr, a.beta1, a.beta2 = float(hp["lr"]), float(b1), float(b2)
+                a.eps = 1.0 if hp.get("nesterov") else 0.0
+                a.bias_corr1, a.bias_corr2 = (0.0 if fs.step == 1 else 1.0), 1.0
+                a.adamw = 2
+            else:
+                a.lr, a.beta1, a.beta2, a.eps = float(hp["lr"]), float(b1), float(b2), float(hp["eps"])
+                a.bias_corr1, a.bias_corr2 = 1.0 - b1 ** fs.step, 1.0 - b2 ** fs.step
+                a.adamw = 1 if type(self.optimizer) is torch.optim.AdamW else 0
             a.dtype16 = 1 if g.dtype == torch.bfloat16 else 0
             a.num_ctas = int(conf("fused_reduce_ctas")) if _has_conf("fused_reduce_ctas") else 0
             a.ctrl = None if ctrl is None else ctrl.data_ptr()
@@ -186,6 +205,8 @@ class FusedGradReducer:
     def publish_state(self):
         """Per-parameter views of the flat moments in ``optimizer.state`` (torch's layout)."""
         for g in self.storage.groups:
+            if g.flat_master is None:
+                continue
             fs = self._moments(g)
             lo = g.shard[0]
             for i, mp in enumerate(g.master_params):
@@ -193,6 +214,9 @@ class FusedGradReducer:
                     continue
                 a, b = g.local_range(i)
                 s = self.optimizer.state[mp]
+                if fs.v is None:
+                    s["momentum_buffer"] = fs.m[a - lo:b - lo].view(mp.shape)
+                    continue
                 s["step"] = torch.tensor(float(fs.step))
                 s["exp_avg"] = fs.m[a - lo:b - lo].view(mp.shape)
                 s["exp_avg_sq"] = fs.v[a - lo:b - lo].view(mp.shape)

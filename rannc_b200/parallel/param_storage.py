@@ -239,12 +239,14 @@ class ParamStorage:
             if g.nranks > 1:
                 comm.allreduce(g.flat_grad, "sum", g.ranks)
 
-    def allreduce_grads_zero(self):
+    def allreduce_grads_zero(self, only=None):
         """ZeRO baseline: reduce-scatter so each rank holds the reduced gradient of its shard
-        (reference: bucketed ncclReduceScatter, ParamStorage.cpp:396-520)."""
+        (reference: bucketed ncclReduceScatter, ParamStorage.cpp:396-520).  ``only``: a subset of the groups."""
         world = comm.get_world_size()
         self.fold_model_grads()
         for g in self.groups:
+            if only is not None and g not in only:
+                continue
             if world > 1:
                 g.flat_grad.mul_(1.0 / world)
             if g.nranks > 1:
@@ -253,9 +255,11 @@ class ParamStorage:
                 comm.reduce_scatter_into(out, g.flat_grad, g.ranks)
                 g.flat_grad[lo:hi].copy_(out)
 
-    def allgather_params_zero(self):
+    def allgather_params_zero(self, only=None):
         """Refreshes the full 16-bit parameters from the updated shards (reference: ParamStorage.cpp:559-596)."""
         for g in self.groups:
+            if only is not None and g not in only:
+                continue
             if g.nranks > 1 and self.zero:
                 lo, hi = g.shard
                 comm.allgather_into(g.flat_param, g.flat_param[lo:hi].clone(), g.ranks)

@@ -19,10 +19,20 @@ def main():
     rank, world = pyrannc.get_rank(), pyrannc.get_world_size()
     torch.manual_seed(0)
     RF.manual_seed(5)
-    cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
-                          num_hidden_layers=case.get("layers", 2))
-    model = BertForPreTraining(cfg)
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    resnet = case.get("model", "bert") == "resnet"
+    if resnet:
+        from rannc_b200.models.resnet import ResNetWithLoss, tiny_resnet
+
+        cfg = None
+        model = ResNetWithLoss(tiny_resnet())
+    else:
+        cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
+                              num_hidden_layers=case.get("layers", 2))
+        model = BertForPreTraining(cfg)
+    if case.get("opt", "adam") == "sgd":
+        opt = torch.optim.SGD(model.parameters(), lr=0.02, momentum=0.9, weight_decay=1e-4)
+    else:
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3)
     wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=True, enable_zero=case.get("zero", True),
                                   offload_params=case.get("offload", False))
     B = case.get("batch", 16)
@@ -30,7 +40,11 @@ def main():
     dev = pyrannc._comm.device()
     losses = []
     for it in range(case.get("iters", 3)):
-        full = synthetic_batch(cfg, B, 128, seed=it)
+        if resnet:
+            g = torch.Generator().manual_seed(it)
+            full = (torch.randn(B, 3, 64, 64, generator=g), torch.randint(0, 10, (B,), generator=g))
+        else:
+            full = synthetic_batch(cfg, B, 128, seed=it)
         local = tuple(t[rank * lb:(rank + 1) * lb].to(dev) for t in full)
         loss = wrapped(*local)
         loss.backward()

@@ -130,3 +130,20 @@ def test_offloaded_optimizer_state_matches_resident(tmp_path):
     k0 = sorted(a["opt"]["state"].keys())[0]
     assert torch.allclose(a["opt"]["state"][k0]["exp_avg"].float(), b["opt"]["state"][k0]["exp_avg"].float(),
                           rtol=1e-2, atol=1e-5)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("model", ["bert", "resnet"])
+def test_fused_reduce_sgd_momentum(tmp_path, model):
+    """The fused reduce-scatter + update + all-gather kernel in its SGD-momentum mode; with the ResNet the
+    fp32 batch-norm parameters form a group of their own that takes the collective path beside it."""
+    case = {"opt": "sgd", "model": model, "iters": 4}
+    a = _run(2, dict(case, out=str(tmp_path / "a.pt")))
+    b = _run(2, dict(case, out=str(tmp_path / "b.pt")), {"RANNC_FUSED_GRAD_ALLREDUCE": "false"})
+    assert all(i["fused"] for i in a["infos"]) and not any(i["fused"] for i in b["infos"])
+    assert all(i["err"] == 0 for i in a["infos"])
+    for la, lb in zip(a["infos"][0]["losses"], b["infos"][0]["losses"]):
+        assert abs(la - lb) < 3e-2 * abs(lb)
+    for k in a["sd"]:
+        x, y = a["sd"][k].float(), b["sd"][k].float()
+        assert (x - y).abs().max().item() <= 2e-2 * (y.abs().max().item() + 1e-3) + 2e-3, k
