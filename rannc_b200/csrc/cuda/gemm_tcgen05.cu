@@ -694,12 +694,14 @@ static int launch(const RbGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap
     return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
 
-// RB_GEMM_PAIR_COLLECTIVE=1 also puts the gather / scatter variants on the pair kernel (same prologue and
-// epilogue code; off by default until it has been timed over real peers)
-static bool pair_collective_enabled() {
+// RB_GEMM_PAIR_GATHER=1 also puts the gather -> GEMM variant on the pair kernel (same prologue code).  Measured
+// with four local slices it is no faster there (0.230 ms against 0.223 ms for M 8192, N = K = 4096: the
+// prologue copy, not the main loop, is what the variant adds), so it stays on the single-CTA kernel; the
+// scatter epilogue does gain from the pair kernel (0.224 ms against 0.248 ms) and uses it.
+static bool pair_gather_enabled() {
     static int v = -1;
     if (v < 0) {
-        const char* e = getenv("RB_GEMM_PAIR_COLLECTIVE");
+        const char* e = getenv("RB_GEMM_PAIR_GATHER");
         v = (e && e[0] == '1') ? 1 : 0;
     }
     return v == 1;
@@ -736,7 +738,7 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     // enough tiles, or few tiles and a long K that is split (weight gradients); the gather prologue and the
     // scatter epilogue are the same code in both variants.  Small problems stay on the single-CTA kernel.
     const bool accum32 = a->out_dtype == 1 && a->flags == RB_GEMM_ACCUM;
-    bool pair = pair_enabled() && ((a->ag_nranks <= 1 && a->rs_nranks <= 1) || pair_collective_enabled());
+    bool pair = pair_enabled() && (a->ag_nranks <= 1 || pair_gather_enabled());
     if (pair) {
         const long long pt = ((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + BN - 1) / BN) * a->batch;
         const long long kbs = (a->K + BK - 1) / BK;

@@ -121,11 +121,34 @@ class RaNNCModule:
                          a.dtype != self.amp_dtype else a for a in args)
         if not self.ready:
             self._init(args)
+        # A batch smaller than the one the deployment was made for (the last batch of an epoch) is padded by
+        # repeating rows, and the outputs are trimmed back (reference: GraphLauncher.cpp:377-404,
+        # TorchUtil.cpp:785-811).  Each rank pads its own share, so no collective is needed.
+        local_bs, want = self._batch_rows(args), self._local_batch
+        trim = 0
+        if 0 < local_bs < want:
+            idx = torch.arange(want, device=next(a.device for a in args if isinstance(a, torch.Tensor))) % local_bs
+            args = tuple(a.index_select(0, idx) if isinstance(a, torch.Tensor) and a.dim() > 0 and
+                         a.shape[0] == local_bs else a for a in args)
+            trim = local_bs
+        elif local_bs > want:
+            raise RuntimeError(f"this rank's batch ({local_bs}) is larger than the one the model was deployed "
+                               f"with ({want})")
         self._dist_barrier()
         outs = self._runtime.forward(args, grad_enabled=torch.is_grad_enabled())
         if torch.is_grad_enabled():
             outs = list(_DistBackward.apply(weakref.ref(self), self._anchor, *outs))
+        if trim:
+            outs = [o[: trim * (o.shape[0] // want)] if isinstance(o, torch.Tensor) and o.dim() > 0 and
+                    o.shape[0] % want == 0 else o for o in outs]
         return self._pack_outputs(outs)
+
+    @staticmethod
+    def _batch_rows(args) -> int:
+        for a in args:
+            if isinstance(a, torch.Tensor) and a.dim() > 0:
+                return int(a.shape[0])
+        return 0
 
     def _pack_outputs(self, outs):
         spec = self._traced.out_spec
@@ -171,6 +194,7 @@ class RaNNCModule:
             if isinstance(a, torch.Tensor) and a.dim() > 0:
                 local_bs = int(a.shape[0])
                 break
+        self._local_batch = local_bs
         sizes = comm.allgather_obj(local_bs)
         if not self.gather_inputs:
             global_bs = sizes[0]     # rank 0 hands in the whole batch

@@ -428,3 +428,55 @@ except SystemExit:
     out = r.stdout + r.stderr
     assert "PLANNED" in out, out[-3000:]
     assert "Assigned subgraph" in out and "repl=" in out
+
+
+def test_conv_bn_rewrite_keeps_the_function_on_cpu():
+    """The convolution / batch-norm fusion pass (with the batch-norm counters anchored after it) leaves the
+    traced ResNet numerically identical; on the CPU the fused operators fall back to ATen."""
+    import torch
+
+    from rannc_b200.graph import rewrite, tracer
+    from rannc_b200.models.resnet import tiny_resnet
+
+    torch.manual_seed(0)
+    m = tiny_resnet().train()
+    ref = tiny_resnet().train()
+    ref.load_state_dict(m.state_dict())
+    x = torch.randn(4, 3, 64, 64)
+    ep, _ = tracer.export_model(m, (x,))
+    gm = ep.graph_module
+    stats = rewrite.fuse(gm, training=True)
+    assert stats["conv2d"] == 17 and stats["batch_norm_act"] == 17
+    targets = [getattr(n.target, "__name__", str(n.target)) for n in gm.graph.nodes if n.op == "call_function"]
+    assert not any("relu" in t for t in targets)          # every ReLU went into a fused batch norm
+    assert targets.count("after_effects") == 17           # one anchored counter update per batch norm
+    state = dict(m.named_parameters())
+    state.update(dict(m.named_buffers()))
+    vals = [state[s.target].detach().clone() if s.kind.name in ("PARAMETER", "BUFFER") else x
+            for s in ep.graph_signature.input_specs]
+    out = gm(*vals)
+    out = out[0] if isinstance(out, (tuple, list)) else out
+    assert torch.allclose(out, ref(x), atol=1e-5)
+
+
+def test_smaller_last_batch_is_padded_and_trimmed():
+    import torch
+
+    import rannc_b200 as pyrannc
+    from rannc_b200.models.mlp import TutorialMLP
+
+    torch.manual_seed(0)
+    net = TutorialMLP(d_in=32, hidden=64, classes=8)
+    ref = TutorialMLP(d_in=32, hidden=64, classes=8)
+    ref.load_state_dict(net.state_dict())
+    model = pyrannc.RaNNCModule(net, torch.optim.SGD(net.parameters(), lr=0.1))
+    x = torch.randn(8, 32)
+    assert torch.allclose(model(x), ref(x), atol=1e-5)
+    out = model(x[:5])                       # the last, smaller batch of an epoch
+    assert out.shape == (5, 8)
+    assert torch.allclose(out, ref(x[:5]), atol=1e-5)
+    out.sum().backward()
+    import pytest
+    with pytest.raises(RuntimeError):
+        model(torch.randn(9, 32))
+    pyrannc.clear()
