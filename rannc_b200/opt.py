@@ -336,18 +336,17 @@ def gather_optimizer_state_dict(optimizer, root: int = 0, to_cpu: bool = True) -
         ranks = storage.param_ranks.get(name)
         if ranks is None:
             continue
-        owner = ranks[0]
-        # item names and non-tensor items from the lowest owner rank
+        # item names and non-tensor items from the first rank that holds state for this parameter (under ZeRO
+        # the lowest owner may hold none of it: the parameter can lie wholly in another rank's shard)
         items = None
-        tensors = {}
         if name in storage.by_name:
             g, i = storage.by_name[name]
             target = g.master_params[i] if (g.flat_master is not None and g.master_params) else g.params[i]
             st = optimizer.state.get(target, {}) if target is not None else {}
-            if me == owner:
+            if st:
                 items = {k: (("tensor", None) if (torch.is_tensor(v) and v.dim() > 0) else ("value", _plain(v)))
                          for k, v in st.items()}
-        items = comm.bcast_obj(items, owner)
+        items = next((x for x in comm.allgather_obj(items) if x), None)
         if not items:
             continue
         entry = {}

@@ -267,7 +267,16 @@ def reduce_scatter_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Se
     if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
         out.copy_(inp.view(-1)[: out.numel()].view_as(out))
         return
-    dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=group(ranks))
+    g = group(ranks)
+    if _S.backend == "gloo":
+        # gloo has no reduce-scatter: all-reduce a copy and keep this rank's piece (CPU rank harness only)
+        full = inp.clone()
+        dist.all_reduce(full, op=dist.ReduceOp.SUM, group=g)
+        n = out.numel()
+        i = dist.get_rank(g)
+        out.copy_(full.view(-1)[i * n:(i + 1) * n].view_as(out))
+        return
+    dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=g)
 
 
 class PendingOps:

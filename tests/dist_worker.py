@@ -24,8 +24,15 @@ def main():
     case = json.loads(sys.argv[1])
     torch.manual_seed(case.get("seed", 0))
     rank, world = pyrannc.get_rank(), pyrannc.get_world_size()
-    model = zoo.build(case["model"])
-    ref = copy.deepcopy(model)
+    if case.get("dist_param"):
+        # every rank declares the model but keeps 1/world of each parameter until deployment
+        with pyrannc.DistributeModelParams():
+            model = zoo.build(case["model"])
+        torch.manual_seed(case.get("seed", 0))
+        ref = zoo.build(case["model"])
+    else:
+        model = zoo.build(case["model"])
+        ref = copy.deepcopy(model)
     lr = 0.05
     mk = (lambda ps: torch.optim.SGD(ps, lr=lr, momentum=0.9)) if case.get("opt", "sgd") == "sgd" else \
         (lambda ps: torch.optim.Adam(ps, lr=0.01))
@@ -56,11 +63,11 @@ def main():
                 (rout / 1.0).backward()
             else:
                 expect = rout if whole else rout[rank * lb:(rank + 1) * lb]
-                if out.shape != expect.shape or not torch.allclose(out, expect, rtol=tol, atol=tol):
+                if out.shape != expect.shape or not torch.allclose(out.float(), expect.float(), rtol=tol, atol=tol):
                     ok = False
                     msgs.append(f"it {it}: output mismatch {tuple(out.shape)} vs {tuple(expect.shape)}")
                 go = torch.randn(rout.shape, generator=g)
-                out.backward(go if whole else go[rank * lb:(rank + 1) * lb])
+                out.backward((go if whole else go[rank * lb:(rank + 1) * lb]).to(out.dtype))
                 # DDP semantics: gradients are averaged over the ranks
                 rout.backward(go / world)
         if accum > 1:

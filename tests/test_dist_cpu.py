@@ -100,6 +100,21 @@ def test_gather_inputs_false_rank0_feeds_the_whole_batch():
     run_case(2, {"model": "deep", "batch": 8, "gather_inputs": False}, {"RANNC_PARTITION_NUM": "2"})
 
 
+def test_mixed_precision_master_weights_dp2():
+    # bf16 compute with fp32 master weights and gradients on CPU ranks; compared loosely with fp32 eager
+    run_case(2, {"model": "layernorm", "batch": 8, "amp": True, "opt": "adam", "tol": 1e-1})
+
+
+def test_mixed_precision_with_zero_sharding_dp2():
+    run_case(2, {"model": "layernorm", "batch": 8, "amp": True, "zero": True, "opt": "adam", "tol": 1e-1})
+    run_case(2, {"model": "deep", "batch": 8, "amp": True, "zero": True, "accum": 2, "tol": 1e-1})
+
+
+@pytest.mark.parametrize("env", [{}, {"RANNC_PARTITION_NUM": "2"}])
+def test_dist_param_model_declared_in_shards(env):
+    run_case(2, {"model": "deep", "batch": 8, "dist_param": True}, env)
+
+
 def test_pp_checkpointing():
     run_case(2, {"model": "loss", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2",
                                                 "RANNC_CHECKPOINTING": "true"})
