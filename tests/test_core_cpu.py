@@ -480,3 +480,47 @@ def test_smaller_last_batch_is_padded_and_trimmed():
     with pytest.raises(RuntimeError):
         model(torch.randn(9, 32))
     pyrannc.clear()
+
+
+def test_checkpoint_reload_into_a_fresh_module():
+    """state_dict() and the global optimizer state go into a newly wrapped copy of the model, which then
+    continues exactly like the original (reference: test/common.py:254-310)."""
+    import copy
+
+    import torch
+
+    import rannc_b200 as pyrannc
+    from rannc_b200.models.mlp import TutorialMLPWithLoss
+
+    torch.manual_seed(0)
+    x, y = torch.randn(16, 512), torch.randint(0, 10, (16,))
+
+    def train(model, opt, steps):
+        out = []
+        for _ in range(steps):
+            loss = model(x, y)
+            loss.backward()
+            opt.step()
+            opt.zero_grad()
+            out.append(float(loss))
+        return out
+
+    net = TutorialMLPWithLoss()
+    fresh = copy.deepcopy(net)
+    opt = torch.optim.Adam(net.parameters(), lr=1e-2)
+    m1 = pyrannc.RaNNCModule(net, opt)
+    train(m1, opt, 3)
+    sd, osd = m1.state_dict(), opt.state_dict(from_global=True)
+    after = train(m1, opt, 2)
+
+    opt2 = torch.optim.Adam(fresh.parameters(), lr=1e-2)
+    m2 = pyrannc.RaNNCModule(fresh, opt2)
+    m2.load_state_dict(sd)                       # before the first call
+    loss = m2(x, y)                              # deploys
+    opt2.load_state_dict(osd, from_global=True)
+    loss.backward()
+    opt2.step()
+    opt2.zero_grad()
+    assert abs(float(loss) - after[0]) < 1e-5
+    assert abs(float(m2(x, y)) - after[1]) < 1e-4
+    pyrannc.clear()
