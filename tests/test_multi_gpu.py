@@ -142,8 +142,13 @@ def test_fused_reduce_sgd_momentum(tmp_path, model):
     b = _run(2, dict(case, out=str(tmp_path / "b.pt")), {"RANNC_FUSED_GRAD_ALLREDUCE": "false"})
     assert all(i["fused"] for i in a["infos"]) and not any(i["fused"] for i in b["infos"])
     assert all(i["err"] == 0 for i in a["infos"])
+    # the two paths sum the gradients in a different order; batch norm amplifies that rounding noise a little
+    # with every step, so the ResNet gets a wider band
+    ltol, ptol = (3e-2, 2e-2) if model == "bert" else (1e-1, 8e-2)
+    la0, lb0 = a["infos"][0]["losses"][0], b["infos"][0]["losses"][0]
+    assert abs(la0 - lb0) < 1e-3 * abs(lb0)            # same forward before any update
     for la, lb in zip(a["infos"][0]["losses"], b["infos"][0]["losses"]):
-        assert abs(la - lb) < 3e-2 * abs(lb)
+        assert abs(la - lb) < ltol * abs(lb)
     for k in a["sd"]:
         x, y = a["sd"][k].float(), b["sd"][k].float()
-        assert (x - y).abs().max().item() <= 2e-2 * (y.abs().max().item() + 1e-3) + 2e-3, k
+        assert (x - y).abs().max().item() <= ptol * (y.abs().max().item() + 1e-3) + 2e-3, k
