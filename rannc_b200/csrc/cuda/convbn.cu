@@ -47,25 +47,31 @@ __device__ __forceinline__ void st8(T* p, const float (&v)[8]) {
 template <typename T>
 __global__ void im2col_kernel(const T* __restrict__ x, T* __restrict__ cols, int N, int H, int W, int C, int Ho,
                               int Wo, int k, int s, int pad) {
+    // one thread per (output pixel, 8 channels): the pixel coordinates are decoded once, the taps are a loop
     const int cv = C / 8;
-    const long long total = static_cast<long long>(N) * Ho * Wo * k * k * cv;
+    const long long total = static_cast<long long>(N) * Ho * Wo * cv;
+    const long long row_len = static_cast<long long>(k) * k * C;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int c8 = static_cast<int>(i % cv);
-        long long r = i / cv;
-        const int kx = static_cast<int>(r % k);
-        r /= k;
-        const int ky = static_cast<int>(r % k);
-        r /= k;
-        const int wo = static_cast<int>(r % Wo);
-        r /= Wo;
-        const int ho = static_cast<int>(r % Ho);
-        const int n = static_cast<int>(r / Ho);
-        const int h = ho * s - pad + ky, w = wo * s - pad + kx;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (h >= 0 && h < H && w >= 0 && w < W)
-            v = *reinterpret_cast<const uint4*>(x + ((static_cast<long long>(n) * H + h) * W + w) * C + c8 * 8);
-        *reinterpret_cast<uint4*>(cols + i * 8) = v;
+        const long long pix = i / cv;
+        const int wo = static_cast<int>(pix % Wo);
+        const int ho = static_cast<int>((pix / Wo) % Ho);
+        const int n = static_cast<int>(pix / (static_cast<long long>(Wo) * Ho));
+        const T* xin = x + static_cast<long long>(n) * H * W * C + c8 * 8;
+        T* out = cols + pix * row_len + c8 * 8;
+        for (int ky = 0; ky < k; ++ky) {
+            const int h = ho * s - pad + ky;
+            const bool hin = h >= 0 && h < H;
+#pragma unroll 3
+            for (int kx = 0; kx < k; ++kx) {
+                const int w = wo * s - pad + kx;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (hin && w >= 0 && w < W)
+                    v = *reinterpret_cast<const uint4*>(xin + (static_cast<long long>(h) * W + w) * C);
+                *reinterpret_cast<uint4*>(out + static_cast<long long>(ky * k + kx) * C) = v;
+            }
+        }
     }
 }
 
@@ -167,8 +173,10 @@ __global__ void bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ 
     }
 }
 
-// mean / rstd from the sums, running statistics (momentum, unbiased variance), and zeroing of the partials
+// mean / rstd from the sums, running statistics (momentum, unbiased variance); the per-channel scale and shift
+// of the element-wise pass replace the sums in `part`: y = x * part[0][c] + part[1][c]
 __global__ void bn_finalize_kernel(float* __restrict__ part, float* __restrict__ mean, float* __restrict__ rstd,
+                                   const float* __restrict__ gamma, const float* __restrict__ beta,
                                    float* __restrict__ run_mean, float* __restrict__ run_var, long long R, int C,
                                    float eps, float momentum) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -176,8 +184,12 @@ __global__ void bn_finalize_kernel(float* __restrict__ part, float* __restrict__
     const float inv = 1.f / static_cast<float>(R);
     const float m = part[c] * inv;
     const float var = fmaxf(part[C + c] * inv - m * m, 0.f);
+    const float rs = rsqrtf(var + eps);
     mean[c] = m;
-    rstd[c] = rsqrtf(var + eps);
+    rstd[c] = rs;
+    const float sc = rs * gamma[c];
+    part[c] = sc;
+    part[C + c] = beta[c] - m * sc;
     if (run_mean) {
         const float unbiased = R > 1 ? var * static_cast<float>(R) / static_cast<float>(R - 1) : var;
         run_mean[c] = (1.f - momentum) * run_mean[c] + momentum * m;
@@ -185,23 +197,42 @@ __global__ void bn_finalize_kernel(float* __restrict__ part, float* __restrict__
     }
 }
 
-// y = act((x - mean) * rstd * gamma + beta (+ residual))
+// backward coefficients: dx = A g + B x + Cc with A = gamma rstd, B = -gamma rstd^2 sum(g xhat) / R,
+// Cc = -A sum(g) / R - B mean; written behind the two sums: part[2..4][C]
+__global__ void bn_bwd_coef_kernel(float* __restrict__ part, const float* __restrict__ mean,
+                                   const float* __restrict__ rstd, const float* __restrict__ gamma, long long R,
+                                   int C) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float inv = 1.f / static_cast<float>(R);
+    const float A = gamma[c] * rstd[c];
+    const float B = -A * rstd[c] * part[C + c] * inv;
+    part[2 * C + c] = A;
+    part[3 * C + c] = B;
+    part[4 * C + c] = -A * part[c] * inv - B * mean[c];
+}
+
+__device__ __forceinline__ void ldf8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+
+// y = act(x * scale + shift (+ residual)); scale / shift per channel, 8 channels = two 16-byte loads each
 template <typename T>
-__global__ void bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ res, const float* __restrict__ mean,
-                                const float* __restrict__ rstd, const float* __restrict__ gamma,
-                                const float* __restrict__ beta, T* __restrict__ y, long long R, int C, int relu) {
+__global__ void bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ res, const float* __restrict__ scale,
+                                const float* __restrict__ shift, T* __restrict__ y, long long R, int C, int relu) {
     const int cv = C / 8;
     const long long total = R * cv;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int c = static_cast<int>(i % cv) * 8;
-        float v[8], o[8];
+        float v[8], o[8], sc[8], sh[8];
         ld8(x + i * 8, v);
+        ldf8(scale + c, sc);
+        ldf8(shift + c, sh);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float sc = rstd[c + j] * gamma[c + j];
-            o[j] = fmaf(v[j] - mean[c + j], sc, beta[c + j]);
-        }
+        for (int j = 0; j < 8; ++j) o[j] = fmaf(v[j], sc[j], sh[j]);
         if (res) {
             float rr[8];
             ld8(res + i * 8, rr);
@@ -216,19 +247,17 @@ __global__ void bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ r
     }
 }
 
-// dx = gamma * rstd * (g - sum_g / R - xhat * sum_gx / R), g = dy masked by relu; dres = g (optional)
+// dx = A g + B x + Cc, g = dy masked by relu; dres = g (optional).  coef = [A, B, Cc][C]
 template <typename T>
 __global__ void bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ y,
-                                    const float* __restrict__ mean, const float* __restrict__ rstd,
-                                    const float* __restrict__ gamma, const float* __restrict__ part,
-                                    T* __restrict__ dx, T* __restrict__ dres, long long R, int C, int relu) {
+                                    const float* __restrict__ coef, T* __restrict__ dx, T* __restrict__ dres,
+                                    long long R, int C, int relu) {
     const int cv = C / 8;
     const long long total = R * cv;
-    const float inv = 1.f / static_cast<float>(R);
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int c = static_cast<int>(i % cv) * 8;
-        float v[8], g[8], o[8];
+        float v[8], g[8], o[8], A[8], B[8], Cc[8];
         ld8(x + i * 8, v);
         ld8(dy + i * 8, g);
         if (relu) {
@@ -237,11 +266,11 @@ __global__ void bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict
 #pragma unroll
             for (int j = 0; j < 8; ++j) g[j] = yy[j] > 0.f ? g[j] : 0.f;
         }
+        ldf8(coef + c, A);
+        ldf8(coef + C + c, B);
+        ldf8(coef + 2 * C + c, Cc);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float xh = (v[j] - mean[c + j]) * rstd[c + j];
-            o[j] = gamma[c + j] * rstd[c + j] * (g[j] - part[c + j] * inv - xh * part[C + c + j] * inv);
-        }
+        for (int j = 0; j < 8; ++j) o[j] = fmaf(A[j], g[j], fmaf(B[j], v[j], Cc[j]));
         st8(dx + i * 8, o);
         if (dres) st8(dres + i * 8, g);
     }
@@ -311,20 +340,21 @@ extern "C" int rb_bn_fwd(const void* x, const void* res, const float* gamma, con
     else
         bn_reduce_kernel<__half, 0><<<grid, block, 0, st>>>(static_cast<const __half*>(x), nullptr, nullptr, nullptr,
                                                            nullptr, part, R, C, 0);
-    bn_finalize_kernel<<<(C + 255) / 256, 256, 0, st>>>(part, mean, rstd, run_mean, run_var, R, C, eps, momentum);
+    bn_finalize_kernel<<<(C + 255) / 256, 256, 0, st>>>(part, mean, rstd, gamma, beta, run_mean, run_var, R, C, eps,
+                                                        momentum);
     const long long total = R * (C / 8);
     if (dtype == 1)
         bn_apply_kernel<__nv_bfloat16><<<ew_grid(total), 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res), mean, rstd, gamma, beta,
+            static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res), part, part + C,
             static_cast<__nv_bfloat16*>(y), R, C, relu);
     else
         bn_apply_kernel<__half><<<ew_grid(total), 256, 0, st>>>(static_cast<const __half*>(x),
-                                                               static_cast<const __half*>(res), mean, rstd, gamma, beta,
+                                                               static_cast<const __half*>(res), part, part + C,
                                                                static_cast<__half*>(y), R, C, relu);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-// Backward.  part: fp32 [2, C] scratch; on return part[0] = d beta, part[1] = d gamma.
+// Backward.  part: fp32 [5, C] scratch; on return part[0] = d beta, part[1] = d gamma (part[2..4]: coefficients).
 extern "C" int rb_bn_bwd(const void* x, const void* dy, const void* y, const float* mean, const float* rstd,
                          const float* gamma, float* part, void* dx, void* dres, long long R, int C, int relu, int dtype,
                          void* stream) {
@@ -343,17 +373,19 @@ extern "C" int rb_bn_bwd(const void* x, const void* dy, const void* y, const flo
         bn_reduce_kernel<__nv_bfloat16, 1><<<grid, block, 0, st>>>(
             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
             static_cast<const __nv_bfloat16*>(y), mean, rstd, part, R, C, relu);
+        bn_bwd_coef_kernel<<<(C + 255) / 256, 256, 0, st>>>(part, mean, rstd, gamma, R, C);
         bn_bwd_apply_kernel<__nv_bfloat16><<<ew_grid(total), 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
-            static_cast<const __nv_bfloat16*>(y), mean, rstd, gamma, part, static_cast<__nv_bfloat16*>(dx),
+            static_cast<const __nv_bfloat16*>(y), part + 2 * C, static_cast<__nv_bfloat16*>(dx),
             static_cast<__nv_bfloat16*>(dres), R, C, relu);
     } else {
         bn_reduce_kernel<__half, 1><<<grid, block, 0, st>>>(static_cast<const __half*>(x),
                                                            static_cast<const __half*>(dy),
                                                            static_cast<const __half*>(y), mean, rstd, part, R, C, relu);
+        bn_bwd_coef_kernel<<<(C + 255) / 256, 256, 0, st>>>(part, mean, rstd, gamma, R, C);
         bn_bwd_apply_kernel<__half><<<ew_grid(total), 256, 0, st>>>(
-            static_cast<const __half*>(x), static_cast<const __half*>(dy), static_cast<const __half*>(y), mean, rstd,
-            gamma, part, static_cast<__half*>(dx), static_cast<__half*>(dres), R, C, relu);
+            static_cast<const __half*>(x), static_cast<const __half*>(dy), static_cast<const __half*>(y),
+            part + 2 * C, static_cast<__half*>(dx), static_cast<__half*>(dres), R, C, relu);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

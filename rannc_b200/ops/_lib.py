@@ -17,7 +17,7 @@ _lock = threading.Lock()
 _lib = None
 
 # device kernels launched per C entry point (the optimizer / element-wise entries launch one)
-_KERNELS_PER_CALL = {"rb_bn_fwd": 3, "rb_bn_bwd": 2, "rb_ln_bwd": 2, "rb_xent_fwd": 2, "rb_attn_bwd": 3, "rb_read_error": 0, "rb_ln_supported": 0,
+_KERNELS_PER_CALL = {"rb_bn_fwd": 3, "rb_bn_bwd": 3, "rb_ln_bwd": 2, "rb_xent_fwd": 2, "rb_attn_bwd": 3, "rb_read_error": 0, "rb_ln_supported": 0,
                      "rb_ln_bwd_grid": 0}
 _launches = 0
 

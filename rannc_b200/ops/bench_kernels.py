@@ -7,6 +7,7 @@
     python -m rannc_b200.ops.bench_kernels ag_gemm --m 8192 --n 4096 --k 4096 --ranks 4
     python -m rannc_b200.ops.bench_kernels gemm_rs --m 8192 --n 4096 --k 4096 --ranks 4
     python -m rannc_b200.ops.bench_kernels rs_adam --numel 100000000
+    python -m rannc_b200.ops.bench_kernels bn --batch 64 --channels 2048 --hw 28      # also bn_bwd, im2col
 
 ``ag_gemm`` / ``gemm_rs`` run the all-gather -> GEMM and GEMM -> reduce-scatter kernels with the group's
 ``--ranks`` shards all placed on this GPU (the peers' buffers are local allocations), ``rs_adam`` runs the
@@ -57,7 +58,9 @@ def _time(fn, iters, warmup, flush):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "attn", "attn_bwd", "ln", "ln_bwd", "adam", "xent", "colsum",
-                                      "ag_gemm", "gemm_rs", "rs_adam"])
+                                      "ag_gemm", "gemm_rs", "rs_adam", "bn", "bn_bwd", "im2col"])
+    ap.add_argument("--channels", type=int, default=2048)
+    ap.add_argument("--hw", type=int, default=28)
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
@@ -205,6 +208,28 @@ def main():
         t = _time(fn, a.iters, a.warmup, not a.no_flush)
         nbytes = n * (4 + 3 * 4 + 3 * 4 + 2)   # grad in; master, m, v in and out; 16-bit parameter out
         out.update(numel=n, ms=t * 1e3, gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / hbm)
+    elif a.kernel in ("bn", "bn_bwd", "im2col"):
+        N, C, HW = a.batch, a.channels, a.hw
+        x4 = torch.randn(N, HW, HW, C, device="cuda", dtype=dt)
+        R = N * HW * HW
+        x2 = x4.view(R, C)
+        if a.kernel == "im2col":
+            fn = lambda: K.im2col(x4, 3, 1, 1)  # noqa: E731
+            nbytes = R * C * 2 * 10          # the input once, nine shifted copies written
+        else:
+            g, b = torch.ones(C, device="cuda"), torch.zeros(C, device="cuda")
+            rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+            res = torch.randn(R, C, device="cuda", dtype=dt)
+            if a.kernel == "bn":
+                fn = lambda: K.bn_fwd(x2, res, g, b, rm, rv, 1e-5, 0.1, True)  # noqa: E731
+                nbytes = R * C * 2 * 4       # x twice (statistics, apply), residual, y
+            else:
+                y, mean, rstd = K.bn_fwd(x2, res, g, b, rm, rv, 1e-5, 0.1, True)
+                dy = torch.randn_like(y)
+                fn = lambda: K.bn_bwd(x2, dy, y, mean, rstd, g, True, True)  # noqa: E731
+                nbytes = R * C * 2 * 8       # x, dy, y twice each (reduce, apply); dx, dres written
+        t = _time(fn, a.iters, a.warmup, not a.no_flush)
+        out.update(N=N, C=C, HW=HW, ms=t * 1e3, gbs=nbytes / t / 1e9, frac_of_peak=nbytes / t / hbm)
     out["device_error_word"] = _lib.read_error()
     print(json.dumps(out))
 

@@ -300,7 +300,7 @@ def bn_bwd(x2d, dy2d, y2d, mean, rstd, gamma32, relu: bool, want_dres: bool):
     R, C = x2d.shape
     dx = torch.empty_like(x2d)
     dres = torch.empty_like(x2d) if want_dres else None
-    part = torch.empty(2, C, dtype=torch.float32, device=x2d.device)
+    part = torch.empty(5, C, dtype=torch.float32, device=x2d.device)   # two sums + three coefficient rows
     _lib.check(_lib.lib().rb_bn_bwd(_lib.vp(x2d), _lib.vp(dy2d), _lib.vp(y2d), _lib.vp(mean), _lib.vp(rstd),
                                     _lib.vp(gamma32), _lib.vp(part), _lib.vp(dx), _lib.vp(dres), c_longlong(R),
                                     c_int(C), c_int(1 if relu else 0), c_int(dt_code(x2d)), _lib.stream_ptr()),
