@@ -277,9 +277,9 @@ static int launch_bwd(const void* dy, const void* z, const void* g, const float*
         case 1: return rb::FN<T, 1, 1>(__VA_ARGS__);    \
         case 2: return rb::FN<T, 2, 1>(__VA_ARGS__);    \
         case 3: return rb::FN<T, 3, 1>(__VA_ARGS__);    \
-        case 4: return rb::FN<T, 4, 1>(__VA_ARGS__);    \
+        case 4: return rb::FN<T, 2, 2>(__VA_ARGS__);    \
         case 6: return rb::FN<T, 3, 2>(__VA_ARGS__);    \
-        case 8: return rb::FN<T, 4, 2>(__VA_ARGS__);    \
+        case 8: return rb::FN<T, 2, 4>(__VA_ARGS__);    \
         case 12: return rb::FN<T, 3, 4>(__VA_ARGS__);   \
         case 16: return rb::FN<T, 4, 4>(__VA_ARGS__);   \
         default: return -2;                             \
