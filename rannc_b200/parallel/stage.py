@@ -18,6 +18,7 @@ import torch.fx as fx
 
 from .. import _core
 from ..ops import functional as RF
+from ..utils.config import conf
 
 aten = torch.ops.aten
 
@@ -74,10 +75,11 @@ def set_dropout(gm: fx.GraphModule, enabled: bool) -> None:
 
 
 class _Saved:
-    __slots__ = ("inputs", "outputs", "rng")
+    __slots__ = ("inputs", "outputs", "rng", "check")
 
     def __init__(self, inputs, outputs, rng):
         self.inputs, self.outputs, self.rng = inputs, outputs, rng
+        self.check = None
 
 
 class StageExec:
@@ -118,6 +120,10 @@ class StageExec:
             with torch.no_grad():
                 outs = self.gm(*args)
             self.saved[split] = _Saved(leaf, None, (rng_state, torch_rng))
+            if bool(conf("verify_recomp")):
+                # self check: the recomputation in backward must reproduce these values
+                # (reference: GraphConnector.cpp:446-451,577-594)
+                self.saved[split].check = [o.detach().clone() if isinstance(o, torch.Tensor) else None for o in outs]
         elif grad_enabled:
             args, leaf = self._args(inputs, True)
             outs = self.gm(*args)
@@ -145,6 +151,14 @@ class StageExec:
             with torch.enable_grad():
                 args, leaf = self._args(sv.inputs, True)
                 outs = dict(zip(self.output_names, self.gm(*args)))
+            chk = getattr(sv, "check", None)
+            if chk is not None:
+                for n, want in zip(self.output_names, chk):
+                    got = outs[n]
+                    if want is not None and not torch.allclose(got.detach().float(), want.float(), rtol=1e-3,
+                                                                atol=1e-3 * float(want.float().abs().max() + 1e-6)):
+                        raise RuntimeError(f"verify_recomp: recomputed value {n} of stage {self.name} differs from "
+                                           f"the one computed in the forward pass")
             RF.rng.set_state(cur_rf)
             torch.set_rng_state(cur_cpu)
             if cur_cuda is not None:

@@ -120,6 +120,12 @@ def test_pp_checkpointing():
                                                 "RANNC_CHECKPOINTING": "true"})
 
 
+def test_pp_checkpointing_with_recompute_self_check():
+    # verify_recomp: every recomputed stage output is compared with the forward pass's
+    run_case(2, {"model": "loss", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2",
+                                                "RANNC_CHECKPOINTING": "true", "RANNC_VERIFY_RECOMP": "true"})
+
+
 def test_grad_accumulation():
     run_case(2, {"model": "loss", "batch": 8, "accum": 2})
 
