@@ -59,9 +59,12 @@ class _DistBackward(torch.autograd.Function):
     (reference: RaNNCTensorBackward, src/comp/Backward.cpp:87-129)."""
 
     @staticmethod
-    def forward(ctx, mod_ref, anchor, *outs):
+    def forward(ctx, mod_ref, anchor, n_out, in_names, *tensors):
+        # tensors = the model outputs followed by the user inputs that require gradients
         ctx.mod_ref = mod_ref
-        ctx.n = len(outs)
+        ctx.n = n_out
+        ctx.in_names = in_names
+        outs = tensors[:n_out]
         return tuple(o.clone() if o.is_floating_point() else o for o in outs)
 
     @staticmethod
@@ -69,8 +72,8 @@ class _DistBackward(torch.autograd.Function):
         mod = ctx.mod_ref()
         if mod is None:
             raise RuntimeError("the RaNNCModule of this output no longer exists")
-        mod._run_backward(grads)
-        return (None, None) + (None,) * ctx.n
+        in_grads = mod._run_backward(grads, ctx.in_names) or {}
+        return (None, None, None, None) + (None,) * ctx.n + tuple(in_grads.get(n) for n in ctx.in_names)
 
 
 class RaNNCModule:
@@ -137,7 +140,11 @@ class RaNNCModule:
         self._dist_barrier()
         outs = self._runtime.forward(args, grad_enabled=torch.is_grad_enabled())
         if torch.is_grad_enabled():
-            outs = list(_DistBackward.apply(weakref.ref(self), self._anchor, *outs))
+            # user inputs that require gradients get them back through the same autograd node
+            names = tuple(n for n, a in zip(self._traced.user_inputs, args)
+                          if isinstance(a, torch.Tensor) and a.requires_grad and a.is_floating_point())
+            extra = tuple(a for a in args if isinstance(a, torch.Tensor) and a.requires_grad and a.is_floating_point())
+            outs = list(_DistBackward.apply(weakref.ref(self), self._anchor, len(outs), names, *outs, *extra))
         if trim:
             outs = [o[: trim * (o.shape[0] // want)] if isinstance(o, torch.Tensor) and o.dim() > 0 and
                     o.shape[0] % want == 0 else o for o in outs]
@@ -533,14 +540,15 @@ class RaNNCModule:
             self._fused_reducer = None
 
     # ------------------------------------------------------------------ backward
-    def _run_backward(self, grads):
-        self._runtime.backward(grads)
+    def _run_backward(self, grads, want_input_grads=()):
+        in_grads = self._runtime.backward(grads, want_input_grads)
         self._dist_barrier()
         if not _delay_grad_allreduce:
             if self.enable_zero:
                 self.allreduce_grads_zero()
             else:
                 self.allreduce_grads()
+        return in_grads
 
     def allreduce_grads(self):
         if self._fused_reducer is not None and self._fused_reducer.handles_reduce:

@@ -221,9 +221,12 @@ class PipelineRuntime:
         return buf if self.rank in dst else None
 
     # ---------------------------------------------------------------- backward
-    def backward(self, out_grads: Sequence[Optional[torch.Tensor]]):
+    def backward(self, out_grads: Sequence[Optional[torch.Tensor]], want_input_grads: Sequence[str] = ()):
+        """Runs the backward pass; returns the gradients of the user inputs named in ``want_input_grads``
+        (this rank's rows; the same names must be asked for on every rank)."""
         comm.check_peers()
         P = self.P
+        input_grads: Dict[str, List[Optional[torch.Tensor]]] = {n: [None] * P for n in want_input_grads}
         offs, _ = self._fwd_state
         gmap = dict(zip(self.user_outputs, out_grads))
         dev = comm.device()
@@ -272,17 +275,36 @@ class PipelineRuntime:
                         got = self._reduce_value(r.ir_value, held, dst_ranks, ranks)
                     if mine and got is not None:
                         og[r.value_name] = got if r.value_name not in og else og[r.value_name] + got
-                if not mine:
-                    continue
-                st = self.stages[sname]
-                _core.trace_begin(_core.func_key("backward", sname, i, True))
-                in_grads = st.backward(i, og)
-                _core.trace_end(_core.func_key("backward", sname, i, True))
-                for r in self.routes.into.get(sname, []):
-                    if r.value_name in in_grads:
-                        self._in_grads[(i, sname, r.value_name)] = in_grads[r.value_name]
+                in_grads: Dict[str, torch.Tensor] = {}
+                if mine:
+                    st = self.stages[sname]
+                    _core.trace_begin(_core.func_key("backward", sname, i, True))
+                    in_grads = st.backward(i, og)
+                    _core.trace_end(_core.func_key("backward", sname, i, True))
+                    for r in self.routes.into.get(sname, []):
+                        if r.value_name in in_grads:
+                            self._in_grads[(i, sname, r.value_name)] = in_grads[r.value_name]
+                # stage -> caller: gradients of the model inputs the caller asked for (every rank takes part in
+                # the move, like for the inputs themselves)
+                for r in self.routes.master_in.get(sname, []):
+                    if r.value_name not in input_grads or not r.ir_value.is_batch:
+                        continue
+                    piece = in_grads.get(r.value_name) if mine else None
+                    if mine and piece is None:
+                        rows = self._rows(ranks, self.rank, i, self._mult(r.ir_value, 0))
+                        piece = torch.zeros([rows] + list(r.ir_value.type.tensor_dim)[1:],
+                                            dtype=_TORCH_DTYPE[r.ir_value.type.tensor_elem_type], device=dev)
+                    got = self._move(r.ir_value, piece, ranks, self.master, i)
+                    if got is not None:
+                        cur = input_grads[r.value_name][i]
+                        input_grads[r.value_name][i] = got if cur is None else cur + got
         self.pending.wait()
         self._in_grads.clear()
+        out = {}
+        for name, pieces in input_grads.items():
+            pieces = [x for x in pieces if x is not None]
+            out[name] = _cat_rows(pieces) if pieces else None
+        return out
 
     def _reduce_value(self, value, t, src: Sequence[int], dst: Sequence[int]):
         """Gradient of a non-batch value: summed over the consumers, delivered to the producers."""

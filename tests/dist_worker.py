@@ -53,6 +53,9 @@ def main():
         for a in range(accum):
             inputs = zoo.inputs(case["model"], B, g)
             local = inputs if whole else tuple(t[rank * lb:(rank + 1) * lb] for t in inputs)
+            if case.get("input_grad"):
+                local = tuple(t.clone().requires_grad_(True) if t.is_floating_point() else t for t in local)
+                inputs = tuple(t.clone().requires_grad_(True) if t.is_floating_point() else t for t in inputs)
             out = wrapped(*local)
             rout = ref(*inputs)
             if out.dim() == 0:
@@ -70,6 +73,13 @@ def main():
                 out.backward((go if whole else go[rank * lb:(rank + 1) * lb]).to(out.dtype))
                 # DDP semantics: gradients are averaged over the ranks
                 rout.backward(go / world)
+                if case.get("input_grad"):
+                    for tl, tf in zip(local, inputs):
+                        if tl.is_floating_point():
+                            want = tf.grad[rank * lb:(rank + 1) * lb] * world
+                            if tl.grad is None or not torch.allclose(tl.grad, want, rtol=tol * 10, atol=tol * 10):
+                                ok = False
+                                msgs.append(f"it {it}: input gradient differs")
         if accum > 1:
             wrapped.allreduce_grads_zero() if case.get("zero") else wrapped.allreduce_grads()
             for p in ref.parameters():

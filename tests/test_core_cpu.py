@@ -524,3 +524,23 @@ def test_checkpoint_reload_into_a_fresh_module():
     assert abs(float(loss) - after[0]) < 1e-5
     assert abs(float(m2(x, y)) - after[1]) < 1e-4
     pyrannc.clear()
+
+
+def test_gradients_of_model_inputs_reach_the_caller():
+    import torch
+
+    import rannc_b200 as pyrannc
+    from rannc_b200.models.mlp import TutorialMLP
+
+    torch.manual_seed(0)
+    net = TutorialMLP(d_in=32, hidden=64, classes=8)
+    ref = TutorialMLP(d_in=32, hidden=64, classes=8)
+    ref.load_state_dict(net.state_dict())
+    model = pyrannc.RaNNCModule(net, torch.optim.SGD(net.parameters(), lr=0.1))
+    x = torch.randn(8, 32, requires_grad=True)
+    xr = x.detach().clone().requires_grad_(True)
+    go = torch.randn(8, 8)
+    model(x).backward(go)
+    ref(xr).backward(go)
+    assert x.grad is not None and torch.allclose(x.grad, xr.grad, atol=1e-5)
+    pyrannc.clear()

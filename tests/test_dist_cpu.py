@@ -115,6 +115,11 @@ def test_dist_param_model_declared_in_shards(env):
     run_case(2, {"model": "deep", "batch": 8, "dist_param": True}, env)
 
 
+def test_input_gradients_dp2_and_pp2():
+    run_case(2, {"model": "deep", "batch": 8, "input_grad": True})
+    run_case(2, {"model": "deep", "batch": 8, "input_grad": True}, {"RANNC_PARTITION_NUM": "2"})
+
+
 def test_pp_checkpointing():
     run_case(2, {"model": "loss", "batch": 8}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2",
                                                 "RANNC_CHECKPOINTING": "true"})
