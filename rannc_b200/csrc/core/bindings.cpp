@@ -131,7 +131,8 @@ PYBIND11_MODULE(_core, m) {
         .def_readwrite("is_batch", &IRValue::is_batch)
         .def_readwrite("is_loss", &IRValue::is_loss)
         .def_readwrite("batch_size", &IRValue::batch_size)
-        .def_readwrite("split_dim", &IRValue::split_dim);
+        .def_readwrite("split_dim", &IRValue::split_dim)
+        .def_readwrite("batch_hint", &IRValue::batch_hint);
 
     py::class_<IRNode>(m, "IRNode")
         .def(py::init<>())

@@ -492,9 +492,13 @@ void guessValueTypes(IRGraph& g) {
     for (auto& kv : g.values) {
         auto it = cls.find(kv.first);
         const VClass c = it == cls.end() ? VClass::CONST_ : it->second;
-        kv.second.is_batch = c == VClass::BATCH;
+        // A tensor computed from batch values whose shape holds no batch dimension (mean over the batch, a
+        // running statistic) stays in the batch flow as far as node ownership goes (its node is placed in
+        // exactly one stage), but the value itself is moved whole, not split into rows.
+        const bool whole = c == VClass::BATCH && kv.second.batch_hint < 0;
+        kv.second.is_batch = c == VClass::BATCH && !whole;
         kv.second.is_loss = c == VClass::LOSS;
-        kv.second.batch_size = (c == VClass::BATCH || c == VClass::LOSS) ? g.batch_size : 0;
+        kv.second.batch_size = ((c == VClass::BATCH && !whole) || c == VClass::LOSS) ? g.batch_size : 0;
     }
 }
 

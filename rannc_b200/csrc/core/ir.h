@@ -72,6 +72,10 @@ struct IRValue {
     int64_t batch_size = 0;
     // not serialised: extra axis a later sequence/context split could use
     int split_dim = 0;
+    // not serialised: what the tracer knows about the first dimension from symbolic shapes.  +1: it is the
+    // (symbolic) batch, -1: the tensor has no batch-sized dimension at all (a reduction over the batch, a
+    // statistic), 0: unknown, the classifier's propagation rule decides.
+    int batch_hint = 0;
 
     mp::Value pack() const;
     static IRValue unpack(const mp::Value& v);

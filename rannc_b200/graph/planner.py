@@ -133,6 +133,12 @@ def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: in
                     f.write(ml.dumps())
         ml_nodes = len(ml.nodes)
         logger.info("Coarsened the graph to %d blocks", ml_nodes)
+        if 0 < ml_nodes < pconf.cfg_partition_num:
+            # a forced stage count cannot exceed the number of blocks there are to distribute
+            logger.warning("partition_num=%d is more than the %d block(s) of this model; using %d",
+                           pconf.cfg_partition_num, ml_nodes, ml_nodes)
+            pconf.cfg_partition_num = ml_nodes
+            pconf.dev_num = max(real_dev, ml_nodes)
         if str(conf("dump_dp_cache")):
             with open(str(conf("dump_dp_cache")), "wb") as f:
                 f.write(_core.dump_dp_cache(ml, ir_graph, node_profiles, pconf))

@@ -144,7 +144,16 @@ def export_model(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], dynamic
     return torch.export.export(model, tuple(args), strict=False), False
 
 
-def fx_to_ir(gm: fx.GraphModule, name: str, param_placeholders, user_inputs, batch_size: int):
+def _batch_hint(val, dynamic_batch: bool) -> int:
+    """+1 if a dimension of the fake tensor is symbolic (derived from the batch symbol), -1 if none is and the
+    tensor is not 0-dim (scalars are left to the loss rule), 0 when the trace has no symbolic batch."""
+    if not dynamic_batch or not isinstance(val, torch.Tensor) or val.dim() == 0:
+        return 0
+    return 1 if any(not isinstance(d, int) for d in val.shape) else -1
+
+
+def fx_to_ir(gm: fx.GraphModule, name: str, param_placeholders, user_inputs, batch_size: int,
+             dynamic_batch: bool = False):
     """Builds the IRGraph: real inputs first, then parameters / buffers / constants."""
     g = _core.IRGraph()
     g.name = name
@@ -165,7 +174,9 @@ def fx_to_ir(gm: fx.GraphModule, name: str, param_placeholders, user_inputs, bat
                 if a.name not in seen:
                     seen.add(a.name)
                     ins.append(a.name)
-            g.add_value(_core.IRValue(n.name, ir_type_of(n.meta.get("val")), False))
+            v = _core.IRValue(n.name, ir_type_of(n.meta.get("val")), False)
+            v.batch_hint = _batch_hint(n.meta.get("val"), dynamic_batch)
+            g.add_value(v)
             g.add_node(_core.IRNode(op_name(n.target), ins, [n.name], n.name))
         elif n.op == "get_attr":
             g.add_input(_core.IRValue(n.name, ir_type_of(n.meta.get("val")), True))
@@ -175,6 +186,34 @@ def fx_to_ir(gm: fx.GraphModule, name: str, param_placeholders, user_inputs, bat
                     g.add_output(a.name)
     g.check()
     return _core.guess_value_types(g)
+
+
+def _materialise_passthrough(gm: fx.GraphModule) -> None:
+    """An output that IS a model input (``forward(x): return x``) has no producing operator, so no stage would
+    own it and a model made only of such outputs would have an empty graph.  Each one gets an ``aten.alias``
+    node: a view, free at run time, that the planner can place like any other operator.  (The reference's
+    test zoo has such a model: test/models.py, IdentityModel.)"""
+    out_node = next(n for n in gm.graph.nodes if n.op == "output")
+    made = {}
+
+    def rec(a):
+        if isinstance(a, fx.Node) and a.op == "placeholder":
+            if a not in made:
+                with gm.graph.inserting_before(out_node):
+                    al = gm.graph.call_function(torch.ops.aten.alias.default, (a,))
+                al.meta = dict(a.meta)
+                made[a] = al
+            return made[a]
+        if isinstance(a, (tuple, list)):
+            return type(a)(rec(x) for x in a)
+        if isinstance(a, dict):
+            return {k: rec(v) for k, v in a.items()}
+        return a
+
+    new_args = rec(out_node.args)
+    if made:
+        out_node.args = new_args
+        gm.recompile()
 
 
 def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: bool = False,
@@ -216,6 +255,7 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
         rewrite.anchor_mutations(gm)
         gm.graph.eliminate_dead_code()
         gm.recompile()
+    _materialise_passthrough(gm)
     # the rewrites may have replaced the nodes that produce the outputs: take the names from the graph
     out_node = next(n for n in gm.graph.nodes if n.op == "output")
     flat_out = _flatten_args_keep_none(out_node.args)
@@ -234,7 +274,7 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
             batch = int(a.shape[0])
             break
     param_like = set(params) | set(buffers) | set(constants)
-    ir = fx_to_ir(gm, name, param_like, user_inputs, batch)
+    ir = fx_to_ir(gm, name, param_like, user_inputs, batch, dynamic_batch=bool(dyn))
     out_spec = getattr(ep.module_call_graph[0].signature, "out_spec", None) if ep.module_call_graph else None
     return TracedModel(gm=gm, ir=ir, user_inputs=user_inputs, params=params, buffers=buffers, constants=constants,
                        user_outputs=user_outputs, buffer_mutations=buffer_mutations, out_spec=out_spec,

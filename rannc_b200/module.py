@@ -138,12 +138,15 @@ class RaNNCModule:
             raise RuntimeError(f"this rank's batch ({local_bs}) is larger than the one the model was deployed "
                                f"with ({want})")
         self._dist_barrier()
-        outs = self._runtime.forward(args, grad_enabled=torch.is_grad_enabled())
-        if torch.is_grad_enabled():
-            # user inputs that require gradients get them back through the same autograd node
-            names = tuple(n for n, a in zip(self._traced.user_inputs, args)
-                          if isinstance(a, torch.Tensor) and a.requires_grad and a.is_floating_point())
-            extra = tuple(a for a in args if isinstance(a, torch.Tensor) and a.requires_grad and a.is_floating_point())
+        # user inputs that require gradients get them back through the same autograd node
+        names = tuple(n for n, a in zip(self._traced.user_inputs, args)
+                      if isinstance(a, torch.Tensor) and a.requires_grad and a.is_floating_point())
+        extra = tuple(a for a in args if isinstance(a, torch.Tensor) and a.requires_grad and a.is_floating_point())
+        # A model without trainable parameters, fed inputs that need no gradient, has nothing to differentiate:
+        # its outputs stay plain tensors, nothing is saved for a backward pass, and none is expected on any rank.
+        need_grad = torch.is_grad_enabled() and (self._trainable or bool(extra))
+        outs = self._runtime.forward(args, grad_enabled=need_grad)
+        if need_grad:
             outs = list(_DistBackward.apply(weakref.ref(self), self._anchor, len(outs), names, *outs, *extra))
         if trim:
             outs = [o[: trim * (o.shape[0] // want)] if isinstance(o, torch.Tensor) and o.dim() > 0 and
@@ -266,6 +269,7 @@ class RaNNCModule:
         self._param_order_by_name = {n: i for i, n in enumerate(self._all_param_names)}
         self._global_param_order = {id(p): self._param_order_by_name[n] for n, p in name_to_param.items()}
         self._param_meta = {n: (tuple(p.shape), p.dtype) for n, p in name_to_param.items()}
+        self._trainable = any(p.requires_grad for p in name_to_param.values())
         owner: Dict[str, set] = {n: set() for n in name_to_param}
         buf_owner: Dict[str, set] = {n: set() for n in name_to_buffer}
         local_stage_names = []

@@ -344,7 +344,7 @@ def gather_optimizer_state_dict(optimizer, root: int = 0, to_cpu: bool = True) -
             target = g.master_params[i] if (g.flat_master is not None and g.master_params) else g.params[i]
             st = optimizer.state.get(target, {}) if target is not None else {}
             if st:
-                items = {k: (("tensor", None) if (torch.is_tensor(v) and v.dim() > 0) else ("value", _plain(v)))
+                items = {k: (("tensor", None) if _per_element(k, v) else ("value", _plain(v)))
                          for k, v in st.items()}
         items = next((x for x in comm.allgather_obj(items) if x), None)
         if not items:
@@ -371,6 +371,12 @@ def gather_optimizer_state_dict(optimizer, root: int = 0, to_cpu: bool = True) -
         idx += len(g["params"])
         groups.append(ng)
     return {"state": state, "param_groups": groups}
+
+
+def _per_element(key, v) -> bool:
+    """True for a state item with one entry per parameter element (moments, momentum buffers), including those
+    of 0-dim parameters; the step counter is a tensor too but describes the whole parameter."""
+    return torch.is_tensor(v) and key != "step"
 
 
 def _plain(v):
@@ -433,7 +439,7 @@ def load_global_optimizer_state(optimizer, sd: dict) -> None:
         st = optimizer.state[target]
         sl = storage.sliced.get(name)
         for k, v in entry.items():
-            if torch.is_tensor(v) and v.dim() > 0:
+            if _per_element(k, v):
                 if sl:
                     ks = v.shape[1] // len(sl)
                     idx = sl.index(comm.get_rank())

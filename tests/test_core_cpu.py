@@ -82,6 +82,48 @@ def test_ir_classification_and_serialisation():
     assert g.param_size_in_byte() == 4 * (16 * 16 + 16) * 4
 
 
+def test_batch_reduced_value_is_owned_but_moved_whole():
+    # mean over the batch: the node stays in the batch flow (one stage owns it), the value is not split in rows
+    g = _core.IRGraph()
+    g.batch_size = 8
+    g.add_input(_core.IRValue("x", _t([8, 16])))
+    stat = _core.IRValue("stat", _t([16]))
+    stat.batch_hint = -1
+    g.add_value(stat)
+    g.add_node(_core.IRNode("aten::mean", ["x"], ["stat"], "mean"))
+    y = _core.IRValue("y", _t([8, 16]))
+    y.batch_hint = 1
+    g.add_value(y)
+    g.add_node(_core.IRNode("aten::div", ["x", "stat"], ["y"], "div"))
+    g.add_output("y")
+    g = _core.guess_value_types(g)
+    nodes = {n.id: n for n in g.nodes}
+    assert nodes["mean"].is_batch and nodes["div"].is_batch
+    assert not g.values["stat"].is_batch and g.values["stat"].batch_size == 0
+    assert g.values["y"].is_batch and g.values["y"].batch_size == 8
+    # without a hint the propagation rule applies, as in the reference (src/graph/ir.cpp, guessValueTypes)
+    h = _core.IRGraph()
+    h.batch_size = 8
+    h.add_input(_core.IRValue("x", _t([8, 16])))
+    h.add_value(_core.IRValue("stat", _t([16])))
+    h.add_node(_core.IRNode("aten::mean", ["x"], ["stat"], "mean"))
+    h.add_output("stat")
+    assert _core.guess_value_types(h).values["stat"].is_batch
+
+
+def test_traced_batch_statistic_carries_no_batch_dimension():
+    import torch
+
+    from rannc_b200.graph import tracer
+    from tests import zoo
+
+    tm = tracer.trace(zoo.build("buffer_rw").train(), (torch.randn(8, 16),))
+    whole = [v for v in tm.ir.values.values() if not v.is_batch and not v.is_param and not v.is_loss and
+             list(v.type.tensor_dim) == [16]]
+    assert whole, "the batch statistic should be classified as a value that is moved whole"
+    assert all(v.is_batch for v in tm.ir.values.values() if len(v.type.tensor_dim) == 2 and not v.is_param)
+
+
 def test_scale_graph_unused_and_shared():
     g = make_mlp_graph(batch=8)
     s = _core.scale_graph(g, 2)

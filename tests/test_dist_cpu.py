@@ -60,6 +60,32 @@ def test_pp2(model):
     assert res["ranks"][0]["stages"] == 2
 
 
+@pytest.mark.parametrize("model", ["small_param", "const_mul", "func_loop", "buffer_ro"])
+def test_zoo_corner_models_dp2_and_pp2(model):
+    # 0-dim and 2-wide parameters, a lifted tensor constant, a layer reused by an unrolled loop, a read-only buffer
+    run_case(2, {"model": model, "batch": 8})
+    res = run_case(2, {"model": model, "batch": 8}, {"RANNC_PARTITION_NUM": "2"})
+    assert res["ranks"][0]["stages"] == 2
+
+
+def test_parameter_free_models():
+    # nothing to place or reduce: forward only, and gradients of the inputs when they are asked for; an output
+    # that is an input gets an alias node, and a forced stage count is clamped to the single block there is
+    run_case(2, {"model": "one_op", "batch": 8})
+    run_case(2, {"model": "one_op", "batch": 8, "input_grad": True}, {"RANNC_PARTITION_NUM": "2"})
+    run_case(2, {"model": "identity", "batch": 8, "input_grad": True})
+    res = run_case(2, {"model": "identity", "batch": 8}, {"RANNC_PARTITION_NUM": "2"})
+    assert res["ranks"][0]["stages"] == 1
+
+
+def test_overwritten_buffer_crosses_a_stage_boundary():
+    # the buffer's new value is a statistic over the batch ([16], no batch dimension): it is computed in the
+    # first stage and read in the second, so it must be moved whole instead of being split into rows
+    run_case(1, {"model": "buffer_rw", "batch": 8})
+    res = run_case(2, {"model": "buffer_rw", "batch": 8}, {"RANNC_PARTITION_NUM": "2"})
+    assert res["ranks"][0]["stages"] == 2
+
+
 def test_pp2_dp2_pipeline2():
     res = run_case(4, {"model": "deep", "batch": 16}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2"})
     assert res["ranks"][0]["stages"] == 2 and res["ranks"][0]["pipeline"] == 2

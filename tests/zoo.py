@@ -1,6 +1,7 @@
 """Small models that each exercise one graph shape the partitioner must cope with: conv + fc, fork/join,
 shared (fan-out) activations, tied weights, scalar-loss output, integer inputs, mixed LayerNorm, BatchNorm
-buffers.  Same coverage as the reference's test zoo (test/models.py), written independently."""
+buffers, tiny parameters, tensor constants, parameter-free graphs, an unrolled helper loop, read-only and
+overwritten buffers.  Same coverage as the reference's test zoo (test/models.py), written independently."""
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -130,7 +131,92 @@ class BNNet(nn.Module):
         return self.fc(x.mean((2, 3)))
 
 
-_MODELS = {"bn": BNNet, "basic": Basic, "forkjoin": ForkJoin, "shared_input": SharedInput, "shared_param": SharedParam,
+class SmallParam(nn.Module):
+    """Parameters far smaller than any alignment or bucket size (a 2-wide bottleneck and a scalar gain)."""
+
+    def __init__(self):
+        super().__init__()
+        self.down = nn.Linear(16, 2)
+        self.up = nn.Linear(2, 16)
+        self.gain = nn.Parameter(torch.ones(()))
+
+    def forward(self, x):
+        return self.up(torch.tanh(self.down(x))) * self.gain
+
+
+class ConstMul(nn.Module):
+    """A plain tensor attribute (neither parameter nor buffer) that the tracer must lift as a constant."""
+
+    def __init__(self):
+        super().__init__()
+        self.l = nn.Linear(16, 16)
+        self.c = torch.linspace(-1.0, 1.0, 16)
+
+    def forward(self, x):
+        return self.l(x) * self.c + 0.5
+
+
+class OneOp(nn.Module):
+    """No parameters at all: nothing to place, nothing to reduce, gradients only flow to the input."""
+
+    def forward(self, x):
+        return torch.tanh(x) * 2.0
+
+
+class Identity(nn.Module):
+    def forward(self, x):
+        return x
+
+
+def _refine(x, layer, steps: int):
+    for i in range(steps):
+        x = x + torch.tanh(layer(x)) * (0.5 / (i + 1))
+    return x
+
+
+class FuncLoop(nn.Module):
+    """A helper with a loop that reuses one layer: the unrolled body reads the same parameter at every trip."""
+
+    def __init__(self):
+        super().__init__()
+        self.inp = nn.Linear(16, 16)
+        self.body = nn.Linear(16, 16)
+
+    def forward(self, x):
+        return _refine(self.inp(x), self.body, 3)
+
+
+class BufferRO(nn.Module):
+    """A buffer that is only read (a fixed mask): it travels with the stage that uses it and is never reduced."""
+
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(16, 16)
+        self.l2 = nn.Linear(16, 16)
+        self.register_buffer("mask", (torch.arange(16) % 2).float())
+
+    def forward(self, x):
+        return self.l2(torch.relu(self.l1(x)) * self.mask)
+
+
+class BufferRW(nn.Module):
+    """A buffer the forward pass overwrites (an exponential average of the activations' scale)."""
+
+    def __init__(self):
+        super().__init__()
+        self.l1 = nn.Linear(16, 16)
+        self.l2 = nn.Linear(16, 16)
+        self.register_buffer("ema", torch.ones(16))
+
+    def forward(self, x):
+        h = torch.relu(self.l1(x))
+        if self.training:
+            self.ema.mul_(0.9).add_(h.detach().abs().mean(0), alpha=0.1)
+        return self.l2(h / (1.0 + self.ema))
+
+
+_MODELS = {"small_param": SmallParam, "const_mul": ConstMul, "one_op": OneOp, "identity": Identity,
+           "func_loop": FuncLoop, "buffer_ro": BufferRO, "buffer_rw": BufferRW, "bn": BNNet, "basic": Basic, "forkjoin": ForkJoin, "shared_input": SharedInput, "shared_param": SharedParam,
            "loss": LossOut, "emb": Emb, "tied": TiedEmb, "layernorm": LayerNormNet, "deep": Deep}
 
 
