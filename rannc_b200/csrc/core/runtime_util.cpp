@@ -50,7 +50,7 @@ const Def kDefs[] = {
     {"display_comm_value", ConfigItem::BOOL, "false"},
     {"display_act_value", ConfigItem::BOOL, "false"},
     {"consolidate_grads", ConfigItem::BOOL, "false"},
-    {"profiling_iter", ConfigItem::INT, "1"},
+    {"profiling_iter", ConfigItem::INT, "3"},
     {"checkpointing", ConfigItem::BOOL, "false"},
     {"checkpointing_no_last", ConfigItem::BOOL, "false"},
     {"disable_balancing", ConfigItem::BOOL, "true"},
@@ -112,7 +112,6 @@ const Def kDefs[] = {
     {"dev_tflops", ConfigItem::FLOAT, "1388"},            // sustained bf16 GEMM throughput for estimates
     {"dev_hbm_gbs", ConfigItem::FLOAT, "6553"},           // copy bandwidth for estimates
     {"prefer_no_checkpointing", ConfigItem::BOOL, "true"},
-    {"grad_bucket_mb", ConfigItem::INT, "128"},
     {"watchdog_period_s", ConfigItem::FLOAT, "10"},
     {"watchdog_stale_s", ConfigItem::FLOAT, "60"},
     {"comm_timeout_s", ConfigItem::FLOAT, "1800"},

@@ -165,3 +165,28 @@ def measured_profiles(gm: fx.GraphModule, device, iters: int = 3) -> Dict[str, "
         except Exception:  # noqa: BLE001 - keep the estimate for operators that cannot run standalone
             continue
     return base
+
+
+def save_profiles(path: str, profiles: Dict[str, "_core.NodeProfile"], batch: int) -> None:
+    """Writes the operator profiles (msgpack: batch size, then per node id the five profile fields).  Counterpart
+    of the reference's profile dump (src/comp/GraphProfiler.cpp, ``save_graph_profile``): a later run with
+    ``load_graph_profile`` plans from the file instead of profiling again."""
+    body = {k: [float(p.fwd_us), float(p.bwd_us), int(p.activation_bytes), int(p.working_bytes),
+                bool(p.scales_with_batch)] for k, p in profiles.items()}
+    with open(path, "wb") as f:
+        f.write(_core.msgpack_pack({"batch": int(batch), "nodes": body}))
+
+
+def load_profiles(path: str, node_ids, batch: int) -> Dict[str, "_core.NodeProfile"]:
+    """Reads a file written by ``save_profiles``.  It must cover exactly the nodes of the traced graph and have
+    been taken at the same batch size; anything else means it belongs to another model or configuration."""
+    with open(path, "rb") as f:
+        raw = _core.msgpack_unpack(f.read())
+    if int(raw["batch"]) != int(batch):
+        raise RuntimeError(f"profile file {path} was taken at batch {raw['batch']}, this run traces batch {batch}")
+    nodes = raw["nodes"]
+    want = set(node_ids)
+    if set(nodes) != want:
+        missing = sorted(want - set(nodes))[:5]
+        raise RuntimeError(f"profile file {path} does not match the traced graph (e.g. missing {missing})")
+    return {k: _core.NodeProfile(v[0], v[1], int(v[2]), int(v[3]), bool(v[4])) for k, v in nodes.items()}

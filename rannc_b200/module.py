@@ -231,10 +231,17 @@ class RaNNCModule:
         ir = _core.scale_graph(tm.ir, global_bs)
 
         logger.info("Running profiler ...")
-        if bool(conf("measure_profiles")) and dev.type == "cuda":
-            node_profiles = profiler.measured_profiles(tm.gm, dev)
+        prof_file = str(conf("graph_profile_file"))
+        if bool(conf("load_graph_profile")) and os.path.exists(prof_file):
+            node_profiles = profiler.load_profiles(prof_file, [n.id for n in tm.ir.nodes], tm.trace_batch)
+            logger.info("Loaded operator profiles from %s", prof_file)
+        elif bool(conf("measure_profiles")) and dev.type == "cuda":
+            node_profiles = profiler.measured_profiles(tm.gm, dev, iters=max(1, int(conf("profiling_iter"))))
         else:
             node_profiles = profiler.analytic_profiles(tm.gm)
+        if bool(conf("save_graph_profile")) and rank == 0:
+            profiler.save_profiles(prof_file, node_profiles, tm.trace_batch)
+            logger.info("Saved operator profiles to %s", prof_file)
         # node times were taken at the traced (local) batch: express them at the global batch
         if global_bs != tm.trace_batch and tm.trace_batch > 0:
             r = global_bs / tm.trace_batch
@@ -674,6 +681,7 @@ class RaNNCModule:
         under every alias); fp32 master values under mixed precision (reference: pyrannc/__init__.py:401-436)."""
         if not self.ready:
             return self.model.state_dict(*args, **kwargs)
+        self._check_device_error()
         keep = comm.get_rank() == 0 or not rank0_only
         out = OrderedDict()
         by_id = {}
@@ -707,8 +715,29 @@ class RaNNCModule:
             with open(path, "wb") as f:
                 f.write(_core.save_deployment(self._dep, comm.get_world_size(), self._dev_mem))
 
+    def _check_device_error(self) -> None:
+        """Every bounded wait inside a kernel of this library records, in a device word, that it gave up (an
+        mbarrier that never completed, a peer flag that was never set).  Reading the word synchronises the
+        device, so the runtime does it where it waits anyway: before parameters are collected for a checkpoint
+        and when the module is taken down.  ``rannc_b200.ops._lib.read_error()`` reads it at any other time."""
+        if self._kernels_on():
+            from .ops import _lib
+
+            err = _lib.read_error()
+            if err > 0:
+                what = {1: "an on-chip barrier wait", 2: "a wait for a peer GPU"}.get(err, f"code {err}")
+                raise RuntimeError(f"a kernel gave up on {what} since the last check (rank {comm.get_rank()}); "
+                                   f"results computed since then are not valid")
+
+    def _kernels_on(self) -> bool:
+        return bool(self.ready and comm.is_cuda() and bool(conf("fused_kernels")))
+
     def undeploy(self) -> None:
         if self._runtime is not None:
+            try:
+                self._check_device_error()
+            except Exception as e:  # taking the module down must not fail (it also runs at interpreter exit)
+                logger.error("%s", e)
             self._runtime.clear()
         self._runtime = None
         self._stages = {}

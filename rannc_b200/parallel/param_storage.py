@@ -238,6 +238,7 @@ class ParamStorage:
                 g.flat_grad.mul_(1.0 / world)
             if g.nranks > 1:
                 comm.allreduce(g.flat_grad, "sum", g.ranks)
+        self._sync_if_asked()
 
     def allreduce_grads_zero(self, only=None):
         """ZeRO baseline: reduce-scatter so each rank holds the reduced gradient of its shard
@@ -254,6 +255,14 @@ class ParamStorage:
                 out = torch.empty(hi - lo, dtype=g.flat_grad.dtype, device=g.device)
                 comm.reduce_scatter_into(out, g.flat_grad, g.ranks)
                 g.flat_grad[lo:hi].copy_(out)
+        self._sync_if_asked()
+
+    @staticmethod
+    def _sync_if_asked():
+        """``sync_allreduce``: the host waits for the reduction before it launches anything else (debugging aid;
+        reference: ParamStorage.cpp, syncStream after the all-reduce)."""
+        if bool(conf("sync_allreduce")) and comm.is_cuda():
+            torch.cuda.synchronize()
 
     def allgather_params_zero(self, only=None):
         """Refreshes the full 16-bit parameters from the updated shards (reference: ParamStorage.cpp:559-596)."""

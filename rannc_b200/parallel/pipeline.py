@@ -22,6 +22,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .. import _core
+from ..utils.config import conf
 from ..utils.log import get_logger
 from . import comm
 from .stage import StageExec
@@ -75,8 +76,20 @@ class PipelineRuntime:
             sets.append(sorted(set(r.sources) | set(r.dests)))
         comm.create_groups(sets)
         self.out_is_loss = {o: bool(dep.graph.value(o).is_loss) for o in user_outputs}
+        # debugging aids of the reference (config items display_comm_value / display_act_value,
+        # src/comp/GraphLauncher.cpp, src/comm/SComm.cpp): log a digest of every value that crosses a stage
+        # boundary / that a stage produces; `profiling` accumulates host-side time per stage and direction
+        self.show_comm = bool(conf("display_comm_value"))
+        self.show_act = bool(conf("display_act_value"))
+        self.timers = _core.TimeCounter(bool(conf("profiling")))
 
     # ---------------------------------------------------------------- helpers
+    def _show(self, what: str, name: str, split: int, t) -> None:
+        if isinstance(t, torch.Tensor) and t.numel() > 0:
+            f = t.detach().float()
+            logger.info("%s %s [micro-batch %d] shape=%s sum=%.6g absmean=%.6g", what, name, split,
+                        tuple(t.shape), float(f.sum()), float(f.abs().mean()))
+
     def _rows(self, ranks: Sequence[int], rank: int, split: int, mult: int = 1) -> int:
         ranks = sorted(ranks)
         if rank not in ranks:
@@ -149,13 +162,20 @@ class PipelineRuntime:
                         got = self._bcast_value(r.ir_value, held, src_ranks, ranks)
                     if mine:
                         ins[r.value_name] = got
+                        if self.show_comm:
+                            self._show("recv", r.value_name, i, got)
                 if not mine:
                     continue
                 st = self.stages[sname]
                 _core.trace_begin(_core.func_key("forward", sname, i, False))
+                self.timers.start("forward " + sname)
                 outs = st.forward(i, ins, self.checkpointing, grad_enabled)
+                self.timers.stop("forward " + sname)
                 _core.trace_end(_core.func_key("forward", sname, i, False))
                 stage_vals[(i, sname)] = outs
+                if self.show_act:
+                    for oname, o in outs.items():
+                        self._show("out", oname, i, o)
                 # stage -> caller
                 for r in self.routes.master_out.get(sname, []):
                     o = outs[r.value_name]
@@ -279,7 +299,9 @@ class PipelineRuntime:
                 if mine:
                     st = self.stages[sname]
                     _core.trace_begin(_core.func_key("backward", sname, i, True))
+                    self.timers.start("backward " + sname)
                     in_grads = st.backward(i, og)
+                    self.timers.stop("backward " + sname)
                     _core.trace_end(_core.func_key("backward", sname, i, True))
                     for r in self.routes.into.get(sname, []):
                         if r.value_name in in_grads:
@@ -323,6 +345,10 @@ class PipelineRuntime:
         return buf if self.rank in dst else None
 
     def clear(self):
+        if bool(conf("profiling")):
+            # host-side time: launches are asynchronous, so set sync_allreduce / CUDA_LAUNCH_BLOCKING for
+            # device-accurate figures, or use trace_events
+            logger.info("time per stage (host side)\n%s", self.timers.summary())
         for st in self.stages.values():
             st.clear()
 

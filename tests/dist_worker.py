@@ -40,6 +40,7 @@ def main():
     opt, ropt = (mk(model.parameters()), mk(ref.parameters())) if has_params else (None, None)
     wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=case.get("amp", False),
                                   enable_zero=case.get("zero", False), check_unused_values=False,
+                                  allreduce_amp_master_params=case.get("ar_master", False),
                                   gather_inputs=case.get("gather_inputs", True))
     whole = not case.get("gather_inputs", True)    # every rank passes (rank 0's copy of) the whole batch
     B = case.get("batch", 8)

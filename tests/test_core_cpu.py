@@ -586,3 +586,46 @@ def test_gradients_of_model_inputs_reach_the_caller():
     ref(xr).backward(go)
     assert x.grad is not None and torch.allclose(x.grad, xr.grad, atol=1e-5)
     pyrannc.clear()
+
+
+def test_operator_profiles_round_trip_and_debug_switches(tmp_path):
+    """save_graph_profile / load_graph_profile, display_act_value, profiling and sync_allreduce on one rank."""
+    import subprocess
+    import sys
+
+    prof = tmp_path / "profiles.bin"
+    code = (
+        "import torch, rannc_b200 as pyrannc\n"
+        "from tests import zoo\n"
+        "torch.manual_seed(0)\n"
+        "m = zoo.build('deep'); o = torch.optim.SGD(m.parameters(), lr=0.1)\n"
+        "w = pyrannc.RaNNCModule(m, o)\n"
+        "out = w(torch.randn(8, 16)); out.sum().backward(); o.step()\n"
+        "print('OUT', float(out.sum()))\n"
+        "pyrannc.clear()\n")
+    base = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", MASTER_ADDR="127.0.0.1", RANNC_FORCE_CPU="1",
+                RANNC_GRAPH_PROFILE_FILE=str(prof), RANNC_LOG_LEVEL="info")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(extra, port):
+        r = subprocess.run([sys.executable, "-c", code], env=dict(base, MASTER_PORT=str(port), **extra), cwd=root,
+                           capture_output=True, text=True, timeout=240)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        return r.stdout + r.stderr
+
+    first = run({"RANNC_SAVE_GRAPH_PROFILE": "true", "RANNC_DISPLAY_ACT_VALUE": "true", "RANNC_PROFILING": "true",
+                 "RANNC_SYNC_ALLREDUCE": "true"}, 29731)
+    assert prof.exists() and "Saved operator profiles" in first
+    assert "absmean=" in first and "time per stage" in first
+    raw = _core.msgpack_unpack(prof.read_bytes())
+    assert raw["batch"] == 8 and len(raw["nodes"]) >= 16
+    second = run({"RANNC_LOAD_GRAPH_PROFILE": "true"}, 29732)
+    assert "Loaded operator profiles" in second
+    out = lambda t: [l for l in t.splitlines() if l.startswith("OUT")]
+    assert out(first) == out(second)
+    # a file taken for another graph is refused
+    raw["nodes"].pop(next(iter(raw["nodes"])))
+    prof.write_bytes(_core.msgpack_pack(raw))
+    r = subprocess.run([sys.executable, "-c", code], env=dict(base, MASTER_PORT="29733", RANNC_LOAD_GRAPH_PROFILE="true"),
+                       cwd=root, capture_output=True, text=True, timeout=240)
+    assert r.returncode != 0 and "does not match the traced graph" in r.stdout + r.stderr

@@ -86,6 +86,13 @@ def test_overwritten_buffer_crosses_a_stage_boundary():
     assert res["ranks"][0]["stages"] == 2
 
 
+def test_amp_gradients_reduced_in_master_precision_with_accumulation():
+    # allreduce_amp_master_params: the fp32 master gradients are what the ranks exchange; four accumulation
+    # steps with the reduction delayed to the last one (reference matrix: test/test_simple.py:37-46)
+    run_case(2, {"model": "layernorm", "batch": 8, "amp": True, "ar_master": True, "accum": 4, "opt": "adam",
+                 "tol": 1e-1})
+
+
 def test_pp2_dp2_pipeline2():
     res = run_case(4, {"model": "deep", "batch": 16}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2"})
     assert res["ranks"][0]["stages"] == 2 and res["ranks"][0]["pipeline"] == 2
