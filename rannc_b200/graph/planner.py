@@ -84,6 +84,36 @@ def _fmt_table(estimates) -> str:
     return "\n".join(rows)
 
 
+def _load_alloc_solution(pconf):
+    """``load_alloc_solutions``: reuse a stage assignment written by ``save_alloc_solutions`` instead of
+    searching again (files ``<alloc_solutions_file_prefix>_s<stages>_p<micro-batches>.bin``).  A forced
+    ``partition_num`` / ``pipeline_num`` selects among several files; otherwise the one with the fewest stages
+    is taken.  Returns None when there is no matching file."""
+    import glob
+    import re
+
+    prefix = str(conf("alloc_solutions_file_prefix"))
+    found = []
+    for path in glob.glob(glob.escape(prefix) + "_s*_p*.bin"):
+        m = re.search(r"_s(\d+)_p(\d+)\.bin$", path)
+        if not m:
+            continue
+        stages, pipe = int(m.group(1)), int(m.group(2))
+        if pconf.cfg_partition_num > 0 and stages != pconf.cfg_partition_num:
+            continue
+        if pconf.cfg_pipeline_num > 0 and pipe != pconf.cfg_pipeline_num:
+            continue
+        found.append((stages, pipe, path))
+    if not found:
+        logger.warning("load_alloc_solutions: no file matches %s_s*_p*.bin; searching instead", prefix)
+        return None
+    found.sort()
+    with open(found[0][2], "rb") as f:
+        sol = _core.AllocSolution.loads(f.read())
+    logger.info("Loaded the stage assignment from %s", found[0][2])
+    return sol
+
+
 def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: int, global_batch: int,
          dev_total_mem: int, use_amp: bool, enable_zero: bool, offload_params: bool, dep_id: str,
          load_deployment: Optional[str] = None) -> Plan:
@@ -142,8 +172,12 @@ def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: in
         if str(conf("dump_dp_cache")):
             with open(str(conf("dump_dp_cache")), "wb") as f:
                 f.write(_core.dump_dp_cache(ml, ir_graph, node_profiles, pconf))
-        sol, estimates, node_json = _core.dp_staging(pm, ml, pconf)
-        if str(conf("dump_dp_node_profiles")):
+        loaded = _load_alloc_solution(pconf) if bool(conf("load_alloc_solutions")) else None
+        if loaded is not None:
+            sol, estimates, node_json = loaded, [], ""
+        else:
+            sol, estimates, node_json = _core.dp_staging(pm, ml, pconf)
+        if str(conf("dump_dp_node_profiles")) and node_json:
             with open(str(conf("dump_dp_node_profiles")), "w") as f:
                 f.write(node_json)
         if bool(conf("save_alloc_solutions")):

@@ -589,7 +589,8 @@ def test_gradients_of_model_inputs_reach_the_caller():
 
 
 def test_operator_profiles_round_trip_and_debug_switches(tmp_path):
-    """save_graph_profile / load_graph_profile, display_act_value, profiling and sync_allreduce on one rank."""
+    """save / load of operator profiles and of the stage assignment, display_act_value, profiling and
+    sync_allreduce on one rank."""
     import subprocess
     import sys
 
@@ -604,7 +605,8 @@ def test_operator_profiles_round_trip_and_debug_switches(tmp_path):
         "print('OUT', float(out.sum()))\n"
         "pyrannc.clear()\n")
     base = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", MASTER_ADDR="127.0.0.1", RANNC_FORCE_CPU="1",
-                RANNC_GRAPH_PROFILE_FILE=str(prof), RANNC_LOG_LEVEL="info")
+                RANNC_GRAPH_PROFILE_FILE=str(prof), RANNC_LOG_LEVEL="info",
+                RANNC_ALLOC_SOLUTIONS_FILE_PREFIX=str(tmp_path / "sols"))
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
     def run(extra, port):
@@ -614,13 +616,14 @@ def test_operator_profiles_round_trip_and_debug_switches(tmp_path):
         return r.stdout + r.stderr
 
     first = run({"RANNC_SAVE_GRAPH_PROFILE": "true", "RANNC_DISPLAY_ACT_VALUE": "true", "RANNC_PROFILING": "true",
-                 "RANNC_SYNC_ALLREDUCE": "true"}, 29731)
+                 "RANNC_SYNC_ALLREDUCE": "true", "RANNC_SAVE_ALLOC_SOLUTIONS": "true"}, 29731)
+    assert (tmp_path / "sols_s1_p1.bin").exists()
     assert prof.exists() and "Saved operator profiles" in first
     assert "absmean=" in first and "time per stage" in first
     raw = _core.msgpack_unpack(prof.read_bytes())
     assert raw["batch"] == 8 and len(raw["nodes"]) >= 16
-    second = run({"RANNC_LOAD_GRAPH_PROFILE": "true"}, 29732)
-    assert "Loaded operator profiles" in second
+    second = run({"RANNC_LOAD_GRAPH_PROFILE": "true", "RANNC_LOAD_ALLOC_SOLUTIONS": "true"}, 29732)
+    assert "Loaded operator profiles" in second and "Loaded the stage assignment" in second
     out = lambda t: [l for l in t.splitlines() if l.startswith("OUT")]
     assert out(first) == out(second)
     # a file taken for another graph is refused
