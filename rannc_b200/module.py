@@ -706,9 +706,41 @@ class RaNNCModule:
         return out if keep else None
 
     def load_state_dict(self, state_dict, strict: bool = True):
-        if self.ready:
-            raise RuntimeError("load_state_dict must be called before the first forward")
-        return self.model.load_state_dict(state_dict, strict)
+        """Before the first forward call the values go into the wrapped model.  Afterwards they are written into
+        the deployed storage on every rank that holds the parameter (working copy and fp32 master copy; shards
+        and column slices are cut out locally), so the partitioning is kept; every rank passes the same
+        ``state_dict``.  (The reference takes the model down and partitions it again:
+        pyrannc/__init__.py:438-451.)  Optimizer state is not touched: load it with
+        ``optimizer.load_state_dict(sd, from_global=True)``."""
+        if not self.ready:
+            return self.model.load_state_dict(state_dict, strict)
+        params = dict(self.model.named_parameters(remove_duplicate=False))
+        canon = {}
+        for n, p in self.model.named_parameters(remove_duplicate=True):
+            canon[id(p)] = n
+        bufs = dict(self.model.named_buffers(remove_duplicate=False))
+        expected = list(self.model.state_dict().keys())
+        unexpected, done = [], set()
+        with torch.no_grad():
+            for k, v in state_dict.items():
+                if k in params:
+                    c = canon[id(params[k])]
+                    if tuple(v.shape) != self._param_meta[c][0]:
+                        raise RuntimeError(f"{k}: shape {tuple(v.shape)} does not match {self._param_meta[c][0]}")
+                    if c not in done:
+                        self._storage.load_param(c, v)
+                        done.add(c)
+                elif k in bufs:
+                    b = bufs[k]
+                    b.data.copy_(v.to(device=b.device, dtype=b.dtype))
+                else:
+                    unexpected.append(k)
+        missing = [k for k in expected if k not in state_dict]
+        if strict and (missing or unexpected):
+            raise RuntimeError(f"load_state_dict: missing keys {missing[:8]}, unexpected keys {unexpected[:8]}")
+        from torch.nn.modules.module import _IncompatibleKeys
+
+        return _IncompatibleKeys(missing, unexpected)
 
     def save_deployment(self, path: str) -> None:
         if comm.get_rank() == 0:

@@ -319,6 +319,32 @@ class ParamStorage:
         return norm
 
     # ---------------------------------------------------------------- access for checkpoints / tests
+    def load_param(self, name: str, value: torch.Tensor) -> bool:
+        """Overwrites a deployed parameter with ``value`` (the full tensor): the 16-bit / working copy in the flat
+        buffer and, under mixed precision, the part of the fp32 master copy this rank keeps.  Every rank that
+        holds the parameter must call it with the same value.  Returns False if this rank does not hold it."""
+        if name not in self.by_name:
+            return False
+        g, i = self.by_name[name]
+        v = value.detach()
+        sl = self.sliced.get(name)
+        if sl:
+            # tensor-partitioned weight: this rank keeps one block of columns
+            ks = v.shape[1] // len(sl)
+            idx = sl.index(comm.get_rank())
+            v = v[:, idx * ks:(idx + 1) * ks]
+        flat = v.contiguous().reshape(-1)
+        o, e = g.param_range(i)
+        if flat.numel() != e - o:
+            raise RuntimeError(f"{name}: got {flat.numel()} elements for a parameter of {e - o}")
+        g.flat_param[o:e].copy_(flat.to(device=g.device, dtype=g.dtype))
+        if g.flat_master is not None:
+            a, b = g.local_range(i)
+            if b > a:
+                lo = g.shard[0]
+                g.flat_master[a - lo:b - lo].copy_(flat[a - o:b - o].to(torch.float32))
+        return True
+
     def _root_of(self, name: str) -> int:
         return self.param_ranks[name][0]
 

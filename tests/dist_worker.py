@@ -136,6 +136,36 @@ def main():
     if opt is not None:
         osd = pyrannc.comm_utils.bcast_obj(osd, 0)
         opt.load_state_dict(osd, from_global=True)
+    if case.get("reload"):
+        # load other values into the DEPLOYED module (every rank passes the same dict), then train one more step
+        # in lockstep with the eager copy
+        sd = pyrannc.comm_utils.bcast_obj(sd, 0)
+        new_sd = {k: (v.float() * 0.5).to(v.dtype) if v.is_floating_point() else v for k, v in sd.items()}
+        wrapped.load_state_dict(new_sd)
+        ref.load_state_dict(new_sd)
+        for n, p in ref.named_parameters():
+            v = wrapped.get_param(n)
+            if not torch.allclose(v.float(), p.detach().float(), rtol=tol * 10, atol=tol * 10):
+                ok = False
+                msgs.append(f"reload: param {n} differs")
+        inputs = zoo.inputs(case["model"], B, g)
+        local = inputs if whole else tuple(t[rank * lb:(rank + 1) * lb] for t in inputs)
+        out, rout = wrapped(*local), ref(*inputs)
+        if out.dim() == 0:
+            out.backward()
+            rout.backward()
+        else:
+            go = torch.randn(rout.shape, generator=g)
+            out.backward((go if whole else go[rank * lb:(rank + 1) * lb]).to(out.dtype))
+            rout.backward(go / world)
+        opt.step()
+        ropt.step()
+        for n, p in ref.named_parameters():
+            v = wrapped.get_param(n)
+            if not torch.allclose(v.float(), p.detach().float(), rtol=tol * 10, atol=tol * 10):
+                ok = False
+                msgs.append(f"reload: param {n} differs after a step by "
+                            f"{(v.float() - p.detach().float()).abs().max().item()}")
     stages = len(wrapped._dep.fwd_graph_order)
     res = {"ok": ok, "msgs": msgs[:8], "stages": stages, "pipeline": wrapped._dep.pipeline_num, "sliced": len(wrapped._storage.sliced),
            "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}}

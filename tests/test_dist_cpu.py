@@ -93,6 +93,15 @@ def test_amp_gradients_reduced_in_master_precision_with_accumulation():
                  "tol": 1e-1})
 
 
+def test_load_state_dict_into_a_deployed_module():
+    # values written into the flat buffers (and fp32 masters / ZeRO shards / column slices) without re-partitioning
+    run_case(2, {"model": "tied", "batch": 8, "reload": True}, {"RANNC_PARTITION_NUM": "2"})
+    run_case(2, {"model": "layernorm", "batch": 8, "amp": True, "zero": True, "opt": "adam", "tol": 1e-1,
+                 "reload": True})
+    run_case(2, {"model": "deep", "batch": 8, "reload": True}, {"RANNC_FORCE_DIST_MATMUL": "true"})
+    run_case(1, {"model": "bn", "batch": 8, "reload": True})
+
+
 def test_pp2_dp2_pipeline2():
     res = run_case(4, {"model": "deep", "batch": 16}, {"RANNC_PARTITION_NUM": "2", "RANNC_PIPELINE_NUM": "2"})
     assert res["ranks"][0]["stages"] == 2 and res["ranks"][0]["pipeline"] == 2
