@@ -112,7 +112,7 @@ class RaNNCModule:
     # ------------------------------------------------------------------ call
     def __call__(self, *args, **kwargs):
         if kwargs:
-            raise RuntimeError("RaNNCModule does not support keyword arguments")
+            args = self._bind_keywords(args, kwargs)
         dev = comm.device()
         if dev.type == "cuda":
             for a in args:
@@ -152,6 +152,33 @@ class RaNNCModule:
             outs = [o[: trim * (o.shape[0] // want)] if isinstance(o, torch.Tensor) and o.dim() > 0 and
                     o.shape[0] % want == 0 else o for o in outs]
         return self._pack_outputs(outs)
+
+    def _bind_keywords(self, args, kwargs):
+        """Keyword arguments are placed by the signature of the wrapped model's ``forward`` (the graph only has
+        positional inputs); parameters skipped in between take their defaults.  The reference refuses keyword
+        arguments (pyrannc/__init__.py, ``RaNNCModule.__call__``)."""
+        import inspect
+
+        sig = inspect.signature(self.model.forward)
+        try:
+            bound = sig.bind(*args, **kwargs)
+        except TypeError as e:
+            raise RuntimeError(f"arguments do not fit the model's forward{sig}: {e}") from None
+        out, last = [], -1
+        params = list(sig.parameters.values())
+        for i, prm in enumerate(params):
+            if prm.kind in (prm.VAR_POSITIONAL, prm.VAR_KEYWORD, prm.KEYWORD_ONLY):
+                if prm.name in bound.arguments and bound.arguments[prm.name]:
+                    raise RuntimeError(f"forward{sig}: only plain positional-or-keyword parameters can be bound")
+                continue
+            if prm.name in bound.arguments:
+                last = i
+        for i, prm in enumerate(params[:last + 1]):
+            if prm.name in bound.arguments:
+                out.append(bound.arguments[prm.name])
+            elif prm.default is not prm.empty:
+                out.append(prm.default)
+        return tuple(out)
 
     @staticmethod
     def _batch_rows(args) -> int:
@@ -223,8 +250,10 @@ class RaNNCModule:
         if tm.rewrite_stats:
             logger.info("Fused operators: %s", str(tm.rewrite_stats))
         if self.check_unused_values:
+            # (an input that is None or a plain Python value is a constant of the trace, not an unused tensor)
+            tensor_inputs = {n for n, a in zip(tm.user_inputs, args) if isinstance(a, torch.Tensor)}
             unused = [v for v in _core.find_unused_values(tm.ir)
-                      if v in tm.params or v in tm.user_inputs]
+                      if v in tm.params or v in tensor_inputs]
             if unused:
                 raise RuntimeError(f"values never used by the model: {unused}; pass check_unused_values=False to "
                                    f"ignore")

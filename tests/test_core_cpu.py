@@ -632,3 +632,38 @@ def test_operator_profiles_round_trip_and_debug_switches(tmp_path):
     r = subprocess.run([sys.executable, "-c", code], env=dict(base, MASTER_PORT="29733", RANNC_LOAD_GRAPH_PROFILE="true"),
                        cwd=root, capture_output=True, text=True, timeout=240)
     assert r.returncode != 0 and "does not match the traced graph" in r.stdout + r.stderr
+
+
+def test_keyword_arguments_are_bound_by_the_forward_signature():
+    import subprocess
+    import sys
+
+    code = (
+        "import torch, torch.nn as nn, rannc_b200 as pyrannc\n"
+        "class M(nn.Module):\n"
+        "    def __init__(self):\n"
+        "        super().__init__(); self.l = nn.Linear(16, 16)\n"
+        "    def forward(self, x, scale=None, shift=None):\n"
+        "        h = self.l(x)\n"
+        "        if scale is not None: h = h * scale\n"
+        "        if shift is not None: h = h + shift\n"
+        "        return h\n"
+        "torch.manual_seed(0)\n"
+        "m = M(); ref = M(); ref.load_state_dict(m.state_dict())\n"
+        "w = pyrannc.RaNNCModule(m, torch.optim.SGD(m.parameters(), lr=0.1))\n"
+        "x, sh = torch.randn(8, 16), torch.randn(8, 16)\n"
+        "out = w(x, shift=sh)\n"
+        "assert torch.allclose(out, ref(x, shift=sh), atol=1e-5), 'mismatch'\n"
+        "out2 = w(x, shift=sh * 2)\n"
+        "assert torch.allclose(out2, ref(x, shift=sh * 2), atol=1e-5), 'mismatch 2'\n"
+        "try:\n"
+        "    w(x, nonsense=1)\n"
+        "    raise SystemExit('no error for an unknown keyword')\n"
+        "except RuntimeError as e:\n"
+        "    assert 'do not fit' in str(e)\n"
+        "print('KW OK'); pyrannc.clear()\n")
+    env = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29741",
+               RANNC_FORCE_CPU="1", RANNC_LOG_LEVEL="warning")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0 and "KW OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
