@@ -65,7 +65,7 @@ def main():
                     ok = False
                     msgs.append(f"it {it}: loss {float(out)} vs {float(rout)}")
                 out.backward()
-                (rout / 1.0).backward()
+                rout.backward()
             else:
                 expect = rout if whole else rout[rank * lb:(rank + 1) * lb]
                 if out.shape != expect.shape or not torch.allclose(out.float(), expect.float(), rtol=tol, atol=tol):
@@ -90,15 +90,11 @@ def main():
                                 msgs.append(f"it {it}: input gradient differs")
         if accum > 1:
             wrapped.allreduce_grads_zero() if case.get("zero") else wrapped.allreduce_grads()
-            for p in ref.parameters():
-                if p.grad is not None:
-                    p.grad /= 1.0
         for n, p in ref.named_parameters():
             if p.grad is None:
                 continue
             gr = wrapped.get_param_grad(n)
-            scale = 1.0 / accum if False else 1.0
-            if not torch.allclose(gr.float(), p.grad.float() * scale, rtol=tol * 10, atol=tol * 10):
+            if not torch.allclose(gr.float(), p.grad.float(), rtol=tol * 10, atol=tol * 10):
                 ok = False
                 msgs.append(f"it {it}: grad {n} differs by {(gr.float() - p.grad.float()).abs().max().item()}")
         if opt is not None:
