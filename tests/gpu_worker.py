@@ -54,8 +54,28 @@ def main():
     torch.cuda.synchronize()
     sd = wrapped.state_dict()
     osd = opt.state_dict(from_global=True)
+    reload_ok = None
+    if case.get("reload"):
+        # other values written into the deployed module (symmetric 16-bit buffers, fp32 master shards), read back
+        # through the same accessor a checkpoint uses, then one more training step on them
+        sd_all = pyrannc.comm_utils.bcast_obj(sd, 0)
+        new_sd = {k: (v.float() * 0.5).to(v.dtype) if v.is_floating_point() else v for k, v in sd_all.items()}
+        wrapped.load_state_dict(new_sd)
+        reload_ok = True
+        for n, _ in list(model.named_parameters())[:12]:
+            got = wrapped.get_param(n, amp_master_param=True).float().cpu()
+            if not torch.allclose(got, new_sd[n].float(), rtol=1e-6, atol=1e-7):
+                reload_ok = False
+        full = (torch.randn(B, 3, 64, 64), torch.randint(0, 10, (B,))) if resnet else synthetic_batch(cfg, B, 128, seed=99)
+        local = tuple(t[rank * lb:(rank + 1) * lb].to(dev) for t in full)
+        loss = wrapped(*local)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        reload_ok = reload_ok and bool(torch.isfinite(loss))
+        torch.cuda.synchronize()
     err = _lib.read_error()
-    info = {"fused": wrapped._fused_reducer is not None, "stages": len(wrapped._dep.fwd_graph_order),
+    info = {"reload_ok": reload_ok, "fused": wrapped._fused_reducer is not None, "stages": len(wrapped._dep.fwd_graph_order),
             "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}, "losses": losses, "err": err,
             "sliced": len(wrapped._storage.sliced)}
     infos = pyrannc._comm.allgather_obj(info)

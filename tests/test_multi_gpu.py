@@ -82,6 +82,12 @@ def test_fused_reduce_matches_nccl_path(tmp_path):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_load_state_dict_into_a_deployed_module_on_the_fused_path(tmp_path):
+    res = _run(2, {"out": str(tmp_path / "r.pt"), "reload": True})
+    assert all(i["fused"] and i["reload_ok"] and i["err"] == 0 for i in res["infos"]), res["infos"]
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_fused_reduce_without_multimem(tmp_path):
     a = _run(2, {"out": str(tmp_path / "a.pt")}, {"RANNC_USE_MULTIMEM": "0"})
     b = _run(2, {"out": str(tmp_path / "b.pt")}, {"RANNC_FUSED_GRAD_ALLREDUCE": "false"})
