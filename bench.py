@@ -18,10 +18,24 @@ Two timed regions of K optimizer steps each, after W warm-up steps:
   * ``e2e``:   every step copies its inputs from pinned host memory and reads the
                loss back to the host.
 Both are the maximum over ranks.  Rank 0 prints one JSON line.
+
+Arms (``--impl``):
+  * ``ours``      (default) this library.  Before its own model is built it also runs the ``eager`` arm for
+                  a few steps (outside every timed region of its own) and reports ``vs_baseline`` = its
+                  samples/s over the eager arm's.
+  * ``eager``     stock PyTorch only: the same ``nn.Module``, ``F.scaled_dot_product_attention``, bf16
+                  autocast, ``torch.optim.Adam(fused=True)``, ``DistributedDataParallel`` when N > 1; none of
+                  this library's kernels, planner or runtime is imported.
+  * ``reference`` the reference implementation itself (prints why it is unavailable here).
+
+Other models: ``--model bert13b`` (256 layers, hidden 2048; parameters declared under
+``DistributeModelParams``, ZeRO, 8 micro-batches), ``--model bert26b`` (128 layers, hidden 4096;
+tensor-partitioned linear layers + pipeline + data parallel, global batch 128), ``--model wide_resnet``.
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
 import os
 import statistics
@@ -30,7 +44,8 @@ import sys
 import threading
 import time
 
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
 
 
 def reference_unavailable():
@@ -92,31 +107,238 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def _plain_bert_module():
+    """The BERT model file is plain ``torch.nn`` code; load it by path so that the eager arm imports nothing
+    else of this library."""
+    spec = importlib.util.spec_from_file_location("_bench_plain_bert", os.path.join(HERE, "rannc_b200", "models",
+                                                                                   "bert.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    return rank, world, local
+
+
+def _max_over_ranks(x: float, dev) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return x
+
+
+def _barrier():
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def run_eager(args, steps: int, warmup: int, want_e2e: bool):
+    """Stock PyTorch arm.  Returns a dict with value / ms_per_step (/ e2e).  The global batch of one optimizer
+    step is the same as in the other arm; when the activations of a rank's whole share do not fit, the share is
+    processed in equal micro-batches with gradient accumulation (``no_sync`` under DDP until the last one)."""
+    import contextlib
+
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = _dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    bert = _plain_bert_module()
+    torch.manual_seed(1234)
+    cfg = bert.BertConfig(hidden_size=args.hidden, num_hidden_layers=args.layers, num_attention_heads=args.heads,
+                          intermediate_size=4 * args.hidden, max_position_embeddings=max(512, args.seq))
+    model = bert.BertForPreTraining(cfg).to(dev)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0, fused=True)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True) \
+        if world > 1 else model
+    lb = args.global_batch // world
+    n_sets = 2
+    host = []
+    for s in range(n_sets):
+        full = bert.synthetic_batch(cfg, args.global_batch, args.seq, seed=100 + s)
+        host.append(tuple(t[rank * lb:(rank + 1) * lb].contiguous().pin_memory() for t in full))
+    dev_sets = [tuple(t.to(dev) for t in hs) for hs in host]
+    micro = [min(lb, args.eager_micro_batch if args.eager_micro_batch > 0 else 64)]
+
+    def one_step(batch):
+        nmb = (lb + micro[0] - 1) // micro[0]
+        total = None
+        for i in range(nmb):
+            sl = tuple(t[i * micro[0]:(i + 1) * micro[0]] for t in batch)
+            last = i == nmb - 1
+            ctx = net.no_sync() if (world > 1 and not last) else contextlib.nullcontext()
+            with ctx:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    loss = net(*sl)
+                (loss * (sl[0].shape[0] / lb)).backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return total / nmb
+
+    # warm-up; a micro-batch that does not fit is halved (every rank takes the same decision)
+    done = 0
+    while done < warmup:
+        try:
+            one_step(dev_sets[done % n_sets])
+            torch.cuda.synchronize()
+            oom = 0
+        except torch.OutOfMemoryError:
+            oom = 1
+        oom = int(_max_over_ranks(float(oom), dev))
+        if oom:
+            opt.zero_grad(set_to_none=True)
+            torch.cuda.empty_cache()
+            if micro[0] <= 1:
+                raise RuntimeError("eager arm: out of memory at micro-batch 1")
+            micro[0] //= 2
+            done = 0
+            continue
+        done += 1
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    _barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(steps):
+        last = one_step(dev_sets[(warmup + i) % n_sets])
+    e1.record()
+    torch.cuda.synchronize()
+    _barrier()
+    ms = _max_over_ranks(e0.elapsed_time(e1), dev)
+    out = {"value": args.global_batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "micro_batch": micro[0],
+           "last_loss": float(last.item()), "params": sum(p.numel() for p in model.parameters())}
+    if want_e2e:
+        h2d = sum(t.numel() * t.element_size() for t in host[0])
+        _barrier()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        e0.record()
+        for i in range(steps):
+            batch = tuple(t.to(dev, non_blocking=True) for t in host[i % n_sets])
+            lv = float(one_step(batch).item())
+        e1.record()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - w0) * 1e3
+        _barrier()
+        e2e_ms = _max_over_ranks(max(e0.elapsed_time(e1), wall), dev)
+        out["e2e"] = {"value": args.global_batch * steps / (e2e_ms / 1e3), "unit": "samples/s",
+                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / steps,
+                      "last_loss": lv}
+    del net, model, opt, dev_sets
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def eager_main(args):
+    import torch
+
+    rank, world, local = _dist_env()
+    if world != args.gpus:
+        if rank == 0:
+            print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch one process per GPU", file=sys.stderr)
+        return 2
+    sampler = ClockSampler(local)
+    sampler.start()
+    r = run_eager(args, args.steps, args.warmup, not args.no_e2e)
+    clocks = sampler.stop()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "BERT samples/s (max over ranks)", "value": r["value"], "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (uniform token ids, 15% MLM labels, Bernoulli NSP), random-init weights",
+            "impl": "eager",
+            "config": {"model": f"BERT {args.layers}L/{args.hidden}H/{args.heads}heads MLM+NSP", "params": r["params"],
+                       "global_batch": args.global_batch, "seq_len": args.seq,
+                       "parallelism": (f"ddp{world}" if world > 1 else "single") + f"_microbatch{r['micro_batch']}",
+                       "optimizer": "torch.optim.Adam(fused=True), bf16 autocast, SDPA",
+                       "l2": "per-step working set far exceeds the 126 MB L2; no flush needed"},
+            "clocks": clocks, "e2e": r.get("e2e"), "gpu_launches": 0,
+            "note": "stock PyTorch kernels only (context number, not this library)"}))
+    _barrier()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours")
-    ap.add_argument("--global-batch", type=int, default=256)
+    ap.add_argument("--impl", default="ours", choices=["ours", "eager", "reference"])
+    ap.add_argument("--global-batch", type=int, default=0, help="0: the model's benchmark definition")
     ap.add_argument("--seq", type=int, default=512)
-    ap.add_argument("--layers", type=int, default=24)
-    ap.add_argument("--hidden", type=int, default=1024)
-    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--hidden", type=int, default=0)
+    ap.add_argument("--heads", type=int, default=0)
     ap.add_argument("--zero", type=int, default=-1, help="-1: on when more than one GPU")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--model", default="bert", choices=["bert", "wide_resnet"],
-                    help="bert: the headline benchmark; wide_resnet: ResNet-152 with every width x --width")
+    ap.add_argument("--no-baseline", action="store_true", help="ours: do not run the eager arm for vs_baseline")
+    ap.add_argument("--baseline-steps", type=int, default=3)
+    ap.add_argument("--eager-micro-batch", type=int, default=0, help="eager arm: rows per micro-batch (0: 64)")
+    ap.add_argument("--model", default="bert", choices=["bert", "bert13b", "bert26b", "wide_resnet"],
+                    help="bert: the headline benchmark; bert13b / bert26b: the enlarged configurations; "
+                         "wide_resnet: ResNet-152 with every width x --width")
     ap.add_argument("--width", type=float, default=8.0)
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--amp-dtype", default="", choices=["", "fp16", "bf16"],
                     help="16-bit compute type (default: bf16 for bert, fp16 for wide_resnet)")
+    ap.add_argument("--dist-params", type=int, default=-1, help="declare the model under DistributeModelParams "
+                                                                "(-1: on for bert13b)")
+    ap.add_argument("--pipeline", type=int, default=0, help="force this many micro-batches (0: planner's choice; "
+                                                            "bert13b defaults to 8)")
+    ap.add_argument("--stages", type=int, default=0, help="force this many pipeline stages (0: planner's choice)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_unavailable()
         return 0
     if args.warmup < 3:
         args.warmup = 3
+    shape = {"bert": (24, 1024, 16, 256), "bert13b": (256, 2048, 32, 256), "bert26b": (128, 4096, 64, 128),
+             "wide_resnet": (24, 1024, 16, 256)}[args.model]
+    args.layers = args.layers or shape[0]
+    args.hidden = args.hidden or shape[1]
+    args.heads = args.heads or shape[2]
+    args.global_batch = args.global_batch or shape[3]
+    if args.impl == "eager":
+        return eager_main(args)
+
+    # ---- baseline context number first, while the device is still empty (stock PyTorch, outside every timed
+    # region of this library's arm)
+    baseline = None
+    if args.model == "bert" and not args.no_baseline and int(os.environ.get("WORLD_SIZE", "1")) == args.gpus:
+        try:
+            baseline = run_eager(args, max(1, args.baseline_steps), 3, False)
+        except Exception as e:  # noqa: BLE001
+            baseline = {"error": f"{type(e).__name__}: {e}"[:200]}
+
+    if args.model == "bert13b" and args.pipeline == 0:
+        args.pipeline = 8
+    if args.pipeline > 0:
+        os.environ.setdefault("RANNC_PIPELINE_NUM", str(args.pipeline))
+    if args.stages > 0:
+        os.environ.setdefault("RANNC_PARTITION_NUM", str(args.stages))
+    if args.model == "bert26b":
+        os.environ.setdefault("RANNC_FORCE_DIST_MATMUL", "true")
 
     import torch
 
@@ -137,12 +359,24 @@ def main():
     lb = args.global_batch // world
     n_sets = 4
     host = []
-    if args.model == "bert":
+    half = False
+    is_bert = args.model.startswith("bert")
+    if is_bert:
         cfg = BertConfig(hidden_size=args.hidden, num_hidden_layers=args.layers, num_attention_heads=args.heads,
                          intermediate_size=4 * args.hidden, max_position_embeddings=max(512, args.seq))
-        model = BertForPreTraining(cfg)
+        dist_params = (args.model == "bert13b") if args.dist_params < 0 else bool(args.dist_params)
+        if dist_params:
+            # every parameter is created as a 1/world shard; full values exist only on the owners after deployment
+            with pyrannc.DistributeModelParams():
+                model = BertForPreTraining(cfg)
+        else:
+            model = BertForPreTraining(cfg)
         optimizer = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0)
-        use_zero = (world > 1) if args.zero < 0 else bool(args.zero)
+        if args.zero < 0:
+            use_zero = world > 1 and args.model != "bert26b"   # tensor-partitioned layers exclude ZeRO
+        else:
+            use_zero = bool(args.zero)
+        n_sets = 4 if args.model == "bert" else 2
         # a few distinct synthetic batches in pinned host memory
         for s in range(n_sets):
             full = synthetic_batch(cfg, args.global_batch, args.seq, seed=100 + s)
@@ -190,6 +424,29 @@ def main():
         losses.append(float(step_device(i).item()))
     torch.cuda.synchronize()
 
+    # value check of the fused gradient path under this very run: one step from the same state down the
+    # fused kernel and down the NCCL collectives (outside the timed regions)
+    fused_err = None
+    red = getattr(wrapped, "_fused_reducer", None)
+    if world > 1 and red is not None:
+        try:
+            from rannc_b200.parallel.fused_reduce import compare_with_collectives
+
+            fused_err = compare_with_collectives(wrapped, optimizer, lambda: step_device(0))
+        except Exception as e:  # noqa: BLE001
+            fused_err = f"{type(e).__name__}: {e}"[:200]
+
+    # host time to enqueue one step, with an idle device and an empty launch queue (no synchronisation inside)
+    enq = []
+    for i in range(3):
+        torch.cuda.synchronize()
+        pyrannc.barrier()
+        t0 = time.perf_counter()
+        step_device(i)
+        enq.append((time.perf_counter() - t0) * 1e3)
+    torch.cuda.synchronize()
+    host_enqueue_ms = _max_over_ranks(statistics.median(enq), dev)
+
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
     pyrannc.barrier()
@@ -229,14 +486,16 @@ def main():
                "last_loss": lv}
     clocks = sampler.stop()
     err = _lib.read_error()
+    peak_mem = torch.tensor([float(torch.cuda.max_memory_allocated(dev))], dtype=torch.float64, device=dev)
+    pyrannc._comm.allreduce(peak_mem, "max")
 
     if rank == 0:
         dep = wrapped._dep
         stages = len(dep.fwd_graph_order)
         repl = [len(dep.allocation[s]) for s in dep.fwd_graph_order]
         par = (f"pp{stages}" if stages > 1 else "") + f"dp{repl[0]}" + (f"_mb{dep.pipeline_num}" if dep.pipeline_num > 1 else "") \
-            + ("_zero" if use_zero else "")
-        if args.model == "bert":
+            + ("_zero" if use_zero else "") + ("_distop" if getattr(wrapped, "_dist_groups", None) else "")
+        if is_bert:
             mname = (f"BERT-Large {args.layers}L/{args.hidden}H/{args.heads}heads MLM+NSP" if
                      (args.layers, args.hidden) == (24, 1024) else
                      f"BERT {args.layers}L/{args.hidden}H/{args.heads}heads MLM+NSP")
@@ -247,18 +506,32 @@ def main():
             data = "synthetic (N(0,1) images, uniform labels over 1000 classes), random-init weights"
             optname = "SGD momentum 0.9 (fused, fp32 master" + (", dynamic loss scale)" if half else ")")
             dtype = "fp16" if half else "bf16"
+        value = args.global_batch * args.steps / (ms / 1e3)
+        plan = getattr(wrapped, "_plan", None)
+        planned_ms = None
+        if plan is not None and getattr(plan, "estimates", None):
+            try:
+                from rannc_b200.graph.planner import planned_step_ms
+
+                planned_ms = planned_step_ms(plan.estimates, dep.pipeline_num)
+            except Exception:  # noqa: BLE001
+                planned_ms = None
         out = {
-            "metric": ("BERT" if args.model == "bert" else "ResNet") + " samples/s (max over ranks)",
-            "value": args.global_batch * args.steps / (ms / 1e3),
+            "metric": ("BERT" if is_bert else "ResNet") + " samples/s (max over ranks)",
+            "value": value,
             "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / baseline["value"]) if baseline and "value" in baseline else None,
+            "baseline_impl": "eager PyTorch in the same process before this arm (bf16 autocast, SDPA, fused Adam"
+                             + (", DDP" if world > 1 else "") + "): see --impl eager" if baseline else None,
+            "baseline": baseline,
             "dtype": dtype, "data": data,
             "impl": "ours",
             "config": {"model": mname,
                        "params": nparams, "global_batch": args.global_batch,
-                       "seq_len": args.seq if args.model == "bert" else None,
+                       "seq_len": args.seq if is_bert else None,
                        "parallelism": par, "stages": stages, "replicas": repl, "micro_batches": dep.pipeline_num,
                        "checkpointing": bool(dep.checkpointing), "optimizer": optname,
                        "l2": "per-step working set (weights 0.67 GB + activations, tens of GB) far exceeds the "
@@ -266,6 +539,14 @@ def main():
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": launches,
+            "launches_per_step": launches / max(1, args.steps),
+            "host_enqueue_ms": host_enqueue_ms,
+            "planned_step_ms": planned_ms,
+            "fused_reduce": bool(red is not None),
+            "multimem": bool(red is not None and red.multimem_active()),
+            "overlap_buckets": int(red.num_buckets()) if red is not None else 0,
+            "fused_vs_nccl_max_rel_err": fused_err,
+            "peak_mem_bytes": int(peak_mem.item()),
             "device_error_word": err,
             "losses": [round(x, 4) for x in losses],
         }

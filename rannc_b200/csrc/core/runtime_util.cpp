@@ -115,6 +115,14 @@ const Def kDefs[] = {
     {"watchdog_period_s", ConfigItem::FLOAT, "10"},
     {"watchdog_stale_s", ConfigItem::FLOAT, "60"},
     {"comm_timeout_s", ConfigItem::FLOAT, "1800"},
+    {"grad_bucket_mb", ConfigItem::FLOAT, "64"},          // gradient bytes per reduction bucket under ZeRO
+    {"overlap_grad_reduce", ConfigItem::BOOL, "true"},    // reduce each bucket while backward still runs
+    {"fused_update_in_backward", ConfigItem::BOOL, "true"},  // the overlapped launches also update + publish
+    {"fused_reduce_ctas", ConfigItem::INT, "32"},         // CTAs of a reduction launch that overlaps backward
+    {"comm_retry", ConfigItem::INT, "1"},                 // retries of a failed collective after re-creating groups
+    {"comm_retry_wait_s", ConfigItem::FLOAT, "1"},
+    {"check_device_error_every_step", ConfigItem::BOOL, "true"},
+    {"cuda_graphs", ConfigItem::BOOL, "false"},           // replay a stage's forward / backward as CUDA graphs
 };
 }  // namespace
 

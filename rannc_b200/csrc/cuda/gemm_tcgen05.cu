@@ -830,6 +830,17 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     }
 }
 
+// Copies the device error word into `host_dst` (pinned host memory) on `stream` without waiting: the caller
+// reads the value once work enqueued before the copy has finished (an event, or the next synchronisation).
+extern "C" int rb_error_peek_async(int* host_dst, void* stream) {
+    int* p = rb::error_word_ptr();
+    if (!p || !host_dst) return -3;
+    return cudaMemcpyAsync(host_dst, p, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)) ==
+                   cudaSuccess
+               ? 0
+               : -4;
+}
+
 // Reads (and clears) the device error word.  Synchronises the device.
 extern "C" int rb_read_error(int clear) {
     int* p = rb::error_word_ptr();

@@ -50,6 +50,8 @@ typedef struct RbGemmArgs {
 int rb_gemm(const RbGemmArgs* args, void* stream);
 // device error word: 0 ok, 1 mbarrier wait ran out, 2 peer wait ran out
 int rb_read_error(int clear);
+// asynchronous copy of the error word into pinned host memory (no synchronisation)
+int rb_error_peek_async(int* host_dst, void* stream);
 
 #ifdef __cplusplus
 }

@@ -92,6 +92,9 @@ struct RsAdamParams {
     const float* ctrl;                      // optional [mul, skip]
     unsigned long long max_polls;
     int* err;
+    int mode;                               // RB_RS_* bits
+    float* own_grad;                        // this rank's gradient buffer (writable)
+    float* sumsq;                           // optional accumulator of the squared reduced gradients
 };
 
 template <typename T16>
@@ -99,14 +102,15 @@ __global__ void __launch_bounds__(512)
     rs_adam_ag_kernel(const RsAdamParams p) {
     __shared__ int s_ok;
     __shared__ int s_last;
+    __shared__ float s_red[16];
     // ---- phase 0: everyone's gradients are complete
-    if (blockIdx.x == 0 && threadIdx.x < p.nranks) {
+    if ((p.mode & RB_RS_BEGIN) && blockIdx.x == 0 && threadIdx.x < p.nranks) {
         __threadfence_system();
         st_release_sys(p.peer_flags[threadIdx.x] + 0 * RB_MAX_PEERS + p.my_idx, p.epoch);
     }
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
-    if (threadIdx.x < p.nranks) {
+    if ((p.mode & RB_RS_BEGIN) && threadIdx.x < p.nranks) {
         if (!wait_flag(p.peer_flags[p.my_idx] + 0 * RB_MAX_PEERS + threadIdx.x, p.epoch, p.max_polls)) {
             s_ok = 0;
             atomicExch(p.err, ERR_PEER_TIMEOUT);
@@ -114,8 +118,10 @@ __global__ void __launch_bounds__(512)
     }
     __syncthreads();
     const bool ok = s_ok != 0;
-    const bool skip = p.ctrl && p.ctrl[1] != 0.f;
-    const float gmul = p.grad_mul * (p.ctrl ? p.ctrl[0] : 1.f);
+    const bool pull = (p.mode & RB_RS_PULL) != 0, update = (p.mode & RB_RS_UPDATE) != 0;
+    const bool skip = update && p.ctrl && p.ctrl[1] != 0.f;
+    const float gmul = p.grad_mul * ((update && p.ctrl) ? p.ctrl[0] : 1.f);
+    float ssq = 0.f;
 
     // ---- phase 1: reduce -> Adam -> scatter the 16-bit result (8 elements = one 16-byte store per step)
     if (ok && !skip) {
@@ -124,24 +130,52 @@ __global__ void __launch_bounds__(512)
              i += static_cast<long long>(gridDim.x) * blockDim.x) {
             const long long e = p.lo + i * 8;
             float g[8];
-            if (p.mc_grad) {
+            if (!pull) {
+                const float4 a = *reinterpret_cast<const float4*>(p.own_grad + e);
+                const float4 b = *reinterpret_cast<const float4*>(p.own_grad + e + 4);
+                g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+                g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+            } else if (p.mc_grad) {
                 const float4 a = multimem_ld_reduce_f32x4(p.mc_grad + e);
                 const float4 b = multimem_ld_reduce_f32x4(p.mc_grad + e + 4);
                 g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
                 g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
             } else {
+                // every peer's 32 bytes are requested before any of them is used, so that the NVLink round trips
+                // overlap; own buffer first, then the peers in a per-rank rotated order
+                float4 a[RB_MAX_PEERS], b[RB_MAX_PEERS];
+#pragma unroll
+                for (int r = 0; r < RB_MAX_PEERS; ++r) {
+                    if (r < p.nranks) {
+                        int src = p.my_idx + r;
+                        if (src >= p.nranks) src -= p.nranks;
+                        a[r] = *reinterpret_cast<const float4*>(p.peer_grad[src] + e);
+                        b[r] = *reinterpret_cast<const float4*>(p.peer_grad[src] + e + 4);
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) g[j] = 0.f;
-#pragma unroll 1
-                for (int r = 0; r < p.nranks; ++r) {
-                    // own buffer first, then the peers in a per-rank rotated order
-                    const int src = (p.my_idx + r) % p.nranks;
-                    const float4 a = *reinterpret_cast<const float4*>(p.peer_grad[src] + e);
-                    const float4 b = *reinterpret_cast<const float4*>(p.peer_grad[src] + e + 4);
-                    g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
-                    g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+#pragma unroll
+                for (int r = 0; r < RB_MAX_PEERS; ++r) {
+                    if (r < p.nranks) {
+                        g[0] += a[r].x; g[1] += a[r].y; g[2] += a[r].z; g[3] += a[r].w;
+                        g[4] += b[r].x; g[5] += b[r].y; g[6] += b[r].z; g[7] += b[r].w;
+                    }
                 }
             }
+            if (p.mode & RB_RS_STORE_GRAD) {
+                // reduction only: the scaled sum goes back into this rank's own buffer (peers read other ranges
+                // of it), the update follows in a later launch
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    g[j] *= gmul;
+                    ssq += g[j] * g[j];
+                }
+                *reinterpret_cast<float4*>(p.own_grad + e) = make_float4(g[0], g[1], g[2], g[3]);
+                *reinterpret_cast<float4*>(p.own_grad + e + 4) = make_float4(g[4], g[5], g[6], g[7]);
+                continue;
+            }
+            if (!update) continue;
             float w[8], mm[8], vv[8];
             const bool sgd = p.adamw == 2;
             *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i * 8);
@@ -200,6 +234,19 @@ __global__ void __launch_bounds__(512)
         }
     }
 
+    if (p.sumsq && (p.mode & RB_RS_STORE_GRAD)) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ssq;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float t = threadIdx.x < (blockDim.x >> 5) ? s_red[threadIdx.x] : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (threadIdx.x == 0) atomicAdd(p.sumsq, t);
+        }
+    }
+    if (!(p.mode & RB_RS_END)) return;   // uniform over the grid: the caller runs rb_peer_barrier instead
     // ---- phase 2: the last CTA publishes completion and waits for the peers
     __threadfence_system();
     __syncthreads();
@@ -267,6 +314,10 @@ extern "C" int rb_rs_adam_ag(const RbRsAdamArgs* a, void* stream) {
     p.max_polls = a->max_polls ? a->max_polls : (1ull << 26);
     p.err = error_word_ptr();
     if (!p.err) return -3;
+    p.mode = a->mode ? a->mode : (RB_RS_BEGIN | RB_RS_END | RB_RS_PULL | RB_RS_UPDATE);
+    if ((p.mode & RB_RS_STORE_GRAD) && (p.mode & RB_RS_UPDATE)) return -2;
+    p.own_grad = const_cast<float*>(p.peer_grad[a->my_idx]);
+    p.sumsq = a->sumsq;
     int grid = a->num_ctas > 0 ? a->num_ctas : 148;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (a->dtype16 == 1)

@@ -27,10 +27,20 @@ typedef struct RbRsAdamArgs {
                                            // eps > 0.5 = Nesterov, bias_corr1 == 0 = first step; v unused)
     int32_t dtype16;                       // 0 fp16, 1 bf16
     int32_t num_ctas;                      // 0: 148
-    int32_t pad_;
+    int32_t mode;                          // 0: everything in one launch (= RB_RS_BEGIN | END | PULL | UPDATE);
+                                           // otherwise a combination of the RB_RS_* bits below
     const float* ctrl;                     // optional [gradient multiplier, skip flag]
     uint64_t max_polls;                    // bound of every flag wait (0: 2^26 polls of >= 100 ns)
+    float* sumsq;                          // optional: += sum of squares of the reduced, scaled gradients
 } RbRsAdamArgs;
+
+// mode bits: a launch may do the reduction alone (during backward, bucket by bucket, after a separate
+// rb_peer_barrier) and leave the update to a later launch that reads the reduced gradients back.
+#define RB_RS_BEGIN 1        // handshake before: every peer's gradients of this range are final
+#define RB_RS_END 2          // handshake after: every peer has finished reading / writing this rank's buffers
+#define RB_RS_PULL 4         // sum the range over all ranks (else: read this rank's own buffer only)
+#define RB_RS_UPDATE 8       // optimizer update of the master shard + write of the 16-bit values to every rank
+#define RB_RS_STORE_GRAD 16  // write the reduced, scaled gradient into this rank's own gradient buffer
 
 // 0 on success.  A wait that runs out sets the device error word to 2 and the kernel returns.
 int rb_rs_adam_ag(const RbRsAdamArgs* args, void* stream);

@@ -202,3 +202,15 @@ def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: in
         with open(str(conf("deployment_file")), "wb") as f:
             f.write(_core.save_deployment(dep, real_dev, dev_mem))
     return Plan(dep, list(estimates), ml_nodes, dev_mem)
+
+
+def planned_step_ms(estimates, pipeline_num: int) -> float:
+    """Step time the stage search expects for its own solution, in ms: the synchronous pipeline runs
+    stages + micro-batches - 1 slots each bounded by the slowest stage (forward and backward), then the
+    slowest gradient reduction (reference: DPStaging::estimateTime, src/graph/DPStaging.cpp:240-276)."""
+    if not estimates:
+        return 0.0
+    fwd = max(float(e.profile.fwd_time) + e.in_comm_us + e.out_comm_us for e in estimates)
+    bwd = max(float(e.profile.bwd_time) + e.in_comm_us + e.out_comm_us for e in estimates)
+    slots = len(estimates) + max(1, int(pipeline_num)) - 1
+    return (slots * (fwd + bwd) + max(e.allreduce_us for e in estimates)) / 1e3

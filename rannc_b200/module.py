@@ -371,13 +371,26 @@ class RaNNCModule:
         if self.offload_params and not self._storage.offload:
             logger.warning("offload_params needs a CUDA device and mixed precision (fp32 master weights); ignored")
         local_params = {n: name_to_param[n] for n in self._used_param_names}
+        # the three projection weights (and biases) of a fused QKV block are laid out back to back so that one
+        # GEMM (forward, dgrad, wgrad) and one column sum serve all three
+        adjacent = []
+        if use_kernels:
+            from .ops import functional as _RF
+
+            for node in tm.gm.graph.nodes:
+                if node.op == "call_function" and node.target is _RF.qkv_attention:
+                    fq = [tm.params.get(a.name) if isinstance(a, torch.fx.Node) else None for a in node.args[1:7]]
+                    if all(f is not None for f in (fq[0], fq[2], fq[4])):
+                        adjacent.append([fq[0], fq[2], fq[4]])
+                    if all(f is not None for f in (fq[1], fq[3], fq[5])):
+                        adjacent.append([fq[1], fq[3], fq[5]])
         want_fused = (self.use_amp_master_params and self.enable_zero and dev.type == "cuda" and world > 1 and
                       not self.offload_params and
                       bool(conf("fused_kernels")) and bool(conf("fused_grad_allreduce")) and
                       type(self.optimizer) in (torch.optim.Adam, torch.optim.AdamW, torch.optim.SGD))
         self._storage.deploy(local_params, {n: sorted(r) for n, r in owner.items()}, opt_group_of, dev,
                              self._param_order_by_name, symmetric=want_fused, sliced=sliced,
-                             symmetric_slices=dist_kernels)
+                             symmetric_slices=dist_kernels, adjacent=adjacent)
         for n in self._used_buffer_names:
             b = name_to_buffer[n]
             b.data = b.data.to(dev)
@@ -578,10 +591,50 @@ class RaNNCModule:
         except Exception as e:  # noqa: BLE001
             logger.warning("fused gradient reduction unavailable (%s); using NCCL collectives", str(e))
             self._fused_reducer = None
+            return
+        red = self._fused_reducer
+        self._storage.reducer = red
+        from .ops import functional as RF
+        from .ops import kernels as K
+
+        RF.set_grad_listener(red.on_grads)
+
+        # a parameter whose gradient reaches it through autograd (an operator without a fused wgrad) is folded
+        # into the fp32 buffer as soon as it is accumulated, and reported like the others
+        def fold(p):
+            mg = getattr(p, "main_grad", None)
+            if mg is None or p.grad is None or p.grad.data_ptr() == mg.data_ptr():
+                return
+            if p.grad.is_cuda and p.grad.dtype in (torch.float16, torch.bfloat16):
+                K.accum_f32(mg, p.grad.contiguous())
+            else:
+                mg.add_(p.grad.float())
+            p.grad = None
+            red.on_grads([p])
+
+        self._grad_hooks = []
+        for g in self._storage.groups:
+            if g.flat_master is None:
+                continue
+            for p in g.params:
+                if p.requires_grad:
+                    self._grad_hooks.append(p.register_post_accumulate_grad_hook(fold))
 
     # ------------------------------------------------------------------ backward
     def _run_backward(self, grads, want_input_grads=()):
-        in_grads = self._runtime.backward(grads, want_input_grads)
+        red = self._fused_reducer
+        if red is not None and red.handles_reduce:
+            # the reducer is told which micro-batch's backward is the last one before the optimizer step: during
+            # that one it launches each bucket's reduction as soon as the bucket's gradients are complete
+            final = not _delay_grad_allreduce
+            self._runtime.split_hook = lambda i, n: red.begin_backward(final and i == n - 1)
+        else:
+            self._runtime.split_hook = None
+        try:
+            in_grads = self._runtime.backward(grads, want_input_grads)
+        finally:
+            if red is not None and red.handles_reduce:
+                red.end_backward()
         self._dist_barrier()
         if not _delay_grad_allreduce:
             if self.enable_zero:
@@ -789,6 +842,25 @@ class RaNNCModule:
                 what = {1: "an on-chip barrier wait", 2: "a wait for a peer GPU"}.get(err, f"code {err}")
                 raise RuntimeError(f"a kernel gave up on {what} since the last check (rank {comm.get_rank()}); "
                                    f"results computed since then are not valid")
+
+    def _after_step(self) -> None:
+        """Called by the patched optimizer step.  Looks at the device error word as it was one step ago (an
+        asynchronous copy, no synchronisation) and raises ``CommError`` when a kernel of this library gave up
+        on a wait since then."""
+        if not self._kernels_on() or not bool(conf("check_device_error_every_step")):
+            return
+        from .ops import _lib
+
+        peek = getattr(self, "_err_peek", None)
+        if peek is None:
+            peek = self._err_peek = _lib.ErrorPeek()
+        err = peek.poll()
+        if err > 0:
+            what = {1: "an on-chip barrier wait", 2: "a wait for a peer GPU", 3: "a bounds check"}.get(
+                err, f"code {err}")
+            _lib.read_error()  # clear
+            raise comm.CommError(f"a kernel gave up on {what} during an earlier step (rank {comm.get_rank()}, "
+                                 f"device error word {err}); results computed since then are not valid")
 
     def _kernels_on(self) -> bool:
         return bool(self.ready and comm.is_cuda() and bool(conf("fused_kernels")))

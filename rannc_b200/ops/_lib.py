@@ -18,7 +18,7 @@ _lib = None
 
 # device kernels launched per C entry point (the optimizer / element-wise entries launch one)
 _KERNELS_PER_CALL = {"rb_bn_fwd": 3, "rb_bn_bwd": 3, "rb_ln_bwd": 2, "rb_xent_fwd": 2, "rb_attn_bwd": 3, "rb_read_error": 0, "rb_ln_supported": 0,
-                     "rb_ln_bwd_grid": 0}
+                     "rb_ln_bwd_grid": 0, "rb_error_peek_async": 0}
 _launches = 0
 
 
@@ -101,3 +101,34 @@ def check(rc: int, what: str) -> None:
 def read_error(clear: bool = True) -> int:
     """Device error word (synchronises): 0 ok, 1 mbarrier wait ran out, 2 peer wait ran out."""
     return int(lib().rb_read_error(1 if clear else 0))
+
+
+class ErrorPeek:
+    """Watches the device error word without synchronising: after every optimizer step an asynchronous copy of
+    the word into pinned host memory is enqueued, and the copy made one step earlier -- complete by then -- is
+    looked at.  A kernel that gave up on a wait is therefore noticed within one step instead of at the next
+    checkpoint (reference: syncWithErrorCheck polls after every forward / backward,
+    src/comm/NCCLWrapper.cpp:575-622)."""
+
+    def __init__(self):
+        self.host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self.events = [None, None]
+        self.k = 0
+
+    def poll(self) -> int:
+        """Enqueues this step's copy; returns the newest completed earlier value (0: no error seen)."""
+        seen = 0
+        for i in (0, 1):
+            ev = self.events[i]
+            if ev is not None and ev.query():
+                seen = max(seen, int(self.host[i]))
+                self.events[i] = None
+        slot = self.k & 1
+        if self.events[slot] is None:
+            rc = lib().rb_error_peek_async(ctypes.c_void_p(self.host.data_ptr() + 4 * slot), stream_ptr())
+            check(rc, "rb_error_peek_async")
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self.events[slot] = ev
+            self.k += 1
+        return seen

@@ -55,6 +55,25 @@ def _main_grad(p):
     return getattr(p, "main_grad", None)
 
 
+# ----------------------------------------------------------------------------- gradient reports
+# The fused operators write weight gradients straight into the flat fp32 buffers, so autograd never sees them
+# and no AccumulateGrad hook fires.  Instead every operator reports, at the END of its backward (after its last
+# kernel that reads the weights was enqueued), which parameters it has just produced gradients for; the
+# gradient reducer uses the reports to launch a bucket's reduction while backward is still running
+# (parallel/fused_reduce.py).  The reference reduces after the whole backward (src/comp/Backward.cpp:100-107).
+_grad_listener = None
+
+
+def set_grad_listener(fn) -> None:
+    global _grad_listener
+    _grad_listener = fn
+
+
+def notify_grads(*params) -> None:
+    if _grad_listener is not None:
+        _grad_listener([p for p in params if p is not None])
+
+
 def _2d(x):
     return x.reshape(-1, x.shape[-1])
 
@@ -119,6 +138,7 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, weight, trans_b=False).view(ctx.x_shape)
         dw = _wgrad(dy2, x2, weight, ctx.w_mg) if ctx.needs_input_grad[1] else None
         db = _bgrad(dy2, ctx.bias_ref, ctx.b_mg) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+        notify_grads(weight if ctx.w_mg is not None else None, ctx.bias_ref if ctx.b_mg is not None else None)
         return dx, dw, db, None
 
 
@@ -162,6 +182,8 @@ class _Mlp(torch.autograd.Function):
         dw1 = _wgrad(dpre, x2, w1, w1_mg)
         db1 = _bgrad(dpre, b1, b1_mg)
         dx = gemm(dpre, w1, trans_b=False).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        notify_grads(w1 if w1_mg is not None else None, b1 if b1_mg is not None else None,
+                     w2 if w2_mg is not None else None, b2 if b2_mg is not None else None)
         return dx, dw1, db1, dw2, db2
 
 
@@ -196,6 +218,7 @@ class _DropoutAddLayerNorm(torch.autograd.Function):
                                   accumulate=use_mg)
         if use_mg:
             dg = db = None
+            notify_grads(ctx.g_ref, ctx.b_ref)
         else:
             dg, db = dg.to(gamma.dtype), db.to(gamma.dtype)
         return dx, (dz if ctx.has_res else None), dg, db, None, None
@@ -268,6 +291,7 @@ class _Embedding(torch.autograd.Function):
         dyc = dy if dy.is_contiguous() else dy.contiguous()
         if ctx.w_mg is not None:
             K.embed_bwd(ids, dyc, ctx.w_mg, ctx.padding_idx)
+            notify_grads(ctx.w_ref)
             return None, None, None
         acc = torch.zeros(ctx.w_ref.shape, dtype=torch.float32, device=dy.device)
         K.embed_bwd(ids, dyc, acc, ctx.padding_idx)
@@ -385,6 +409,39 @@ def _cat_params(tensors):
     return cat
 
 
+_adj_cache = {}
+
+
+def _adjacent_view(tensors):
+    """One [sum of rows, ...] view over tensors that lie back to back in one storage (the parameter storage
+    lays the three projection weights of a QKV block out that way), or None when they do not."""
+    t0 = tensors[0]
+    key = tuple(t.data_ptr() for t in tensors)
+    hit = _adj_cache.get(key)
+    if hit is not None:
+        return hit[0]
+    es = t0.element_size()
+    ok = all(t.is_contiguous() and t.dtype == t0.dtype and t.shape[1:] == t0.shape[1:] for t in tensors)
+    ptr = t0.data_ptr()
+    for t in tensors:
+        ok = ok and t.data_ptr() == ptr
+        ptr += t.numel() * es
+    view = None
+    if ok:
+        try:
+            rows = sum(t.shape[0] for t in tensors)
+            shape = (rows,) + tuple(t0.shape[1:])
+            stride = t0.stride()
+            view = torch.empty(0, dtype=t0.dtype, device=t0.device).set_(
+                t0.detach().untyped_storage(), t0.storage_offset(), shape, stride)
+        except Exception:  # noqa: BLE001
+            view = None
+    if len(_adj_cache) > 4096:
+        _adj_cache.clear()
+    _adj_cache[key] = (view, tensors)   # the tensors stay referenced so their addresses are not reused
+    return view
+
+
 class _QkvAttention(torch.autograd.Function):
     """softmax((x Wq^T)(x Wk^T)^T) (x Wv^T) with ONE projection GEMM over the concatenated weights; the
     attention kernels read q / k / v as strided views of its [B, S, 3, H, D] output and write dq / dk / dv
@@ -396,8 +453,14 @@ class _QkvAttention(torch.autograd.Function):
         x2 = x.reshape(B * S, hid)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        wcat = _cat_params((wq, wk, wv))
-        bcat = _cat_params((bq, bk, bv)) if bq is not None else None
+        wcat = _adjacent_view((wq, wk, wv))
+        if wcat is None:
+            wcat = _cat_params((wq, wk, wv))
+        bcat = None
+        if bq is not None:
+            bcat = _adjacent_view((bq, bk, bv))
+            if bcat is None:
+                bcat = _cat_params((bq, bk, bv))
         Ho = wq.shape[0]
         D = Ho // H
         qkv = gemm(x2, wcat, bias=bcat).view(B, S, 3, H, D)
@@ -421,13 +484,26 @@ class _QkvAttention(torch.autograd.Function):
         K.attn_bwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], o, lse, do4, key_bias, ctx.scale, ctx.p, ctx.seed,
                    ctx.offset, dq=dqkv[:, :, 0], dk=dqkv[:, :, 1], dv=dqkv[:, :, 2])
         d2 = dqkv.view(B * S, 3 * Ho)
-        wcat = _cat_params(ctx.ws)
+        wcat = _adjacent_view(ctx.ws)
+        if wcat is None:
+            wcat = _cat_params(ctx.ws)
         dx = gemm(d2, wcat, trans_b=False).view(B, S, hid) if ctx.needs_input_grad[0] else None
-        grads_w, grads_b = [], []
-        for i in range(3):
-            sl = d2[:, i * Ho:(i + 1) * Ho]
-            grads_w.append(_wgrad(sl, x2, ctx.ws[i], ctx.mgs[i]))
-            grads_b.append(_bgrad(sl, ctx.bs[i], ctx.mgs[3 + i]) if ctx.bs[i] is not None else None)
+        grads_w, grads_b = [None] * 3, [None] * 3
+        # adjacent fp32 gradient buffers: one wgrad GEMM and one column sum serve all three projections
+        wmg = _adjacent_view(ctx.mgs[:3]) if all(m is not None for m in ctx.mgs[:3]) else None
+        if wmg is not None:
+            gemm(d2, x2, trans_a=True, trans_b=False, out=wmg, accumulate=True)
+        else:
+            for i in range(3):
+                grads_w[i] = _wgrad(d2[:, i * Ho:(i + 1) * Ho], x2, ctx.ws[i], ctx.mgs[i])
+        if ctx.bs[0] is not None:
+            bmg = _adjacent_view(ctx.mgs[3:]) if all(m is not None for m in ctx.mgs[3:]) else None
+            if bmg is not None:
+                K.colsum(d2, out=bmg)
+            else:
+                for i in range(3):
+                    grads_b[i] = _bgrad(d2[:, i * Ho:(i + 1) * Ho], ctx.bs[i], ctx.mgs[3 + i])
+        notify_grads(*[t for t, m in zip(ctx.ws + ctx.bs, ctx.mgs) if t is not None and m is not None])
         return (dx, grads_w[0], grads_b[0], grads_w[1], grads_b[1], grads_w[2], grads_b[2], None, None, None, None)
 
 
@@ -537,6 +613,7 @@ class _Conv2d(torch.autograd.Function):
                 else:
                     dw = dwt.to(w.dtype)
         db = _bgrad(dy2, bias, b_mg) if (bias is not None and ctx.needs_input_grad[2]) else None
+        notify_grads(w if w_mg is not None else None, bias if b_mg is not None else None)
         return dx, dw, db, None, None
 
 
@@ -596,6 +673,7 @@ class _BatchNormAct(torch.autograd.Function):
             b_mg.add_(dbeta)
         else:
             db = dbeta.to(beta.dtype)
+        notify_grads(gamma if g_mg is not None else None, beta if b_mg is not None else None)
         return dx, dres, dg, db, None, None, None, None, None
 
 

@@ -130,16 +130,27 @@ def patch_optimizer(module, optimizer):
                 local_of[id(p)] = None  # empty segment on this rank
             else:
                 local_of[id(p)] = p
+    # global order of a parameter = its position in the traversal of the ORIGINAL param groups, which is how
+    # torch numbers ``param_groups[*]['params']`` and how the reference numbers the gathered state
+    # (pyrannc/opt.py, patch_optimizer: global_order counts over param_groups)
+    name_of_id = {id(p): n for n, p in module.model.named_parameters(remove_duplicate=True)}
+    order_by_name: Dict[str, int] = {}
+    for k, p in enumerate(orig_params_flat):
+        n = name_of_id.get(id(p))
+        if n is not None and n not in order_by_name:
+            order_by_name[n] = k
+    optimizer._rannc_order_by_name = order_by_name
     local_to_global: Dict[int, int] = {}
     new_groups = []
+    k = 0
     for gi, g in enumerate(optimizer.param_groups):
         kept = []
         for p in g["params"]:
             lp = local_of.get(id(p), None)
-            if lp is None:
-                continue
-            kept.append(lp)
-            local_to_global[id(lp)] = module._global_param_order[id(p)]
+            if lp is not None:
+                kept.append(lp)
+                local_to_global[id(lp)] = k
+            k += 1
         g["params"] = kept
         new_groups.append(g)
     optimizer.state.clear()
@@ -155,25 +166,31 @@ def patch_optimizer(module, optimizer):
     orig_load_state_dict = optimizer.load_state_dict
 
     def _flat_ranges():
-        """(flat group, optimizer group index, a, b) with [a, b) in flat coordinates, clipped to the shard."""
+        """(flat group, optimizer group index, a, b): maximal runs [a, b) in flat coordinates of consecutive
+        parameters that belong to the same optimizer group and require gradients, clipped to the pieces this
+        rank updates.  Parameters that are frozen or were not handed to the optimizer are in no run, so weight
+        decay never touches them."""
         out = []
         for g in storage.groups:
-            spans: Dict[int, List[int]] = {}
+            runs: List[List[int]] = []
             for i, og in enumerate(g.opt_group):
                 if og < 0 or not g.params[i].requires_grad:
                     continue
                 lo, hi = g.param_range(i)
-                s = spans.setdefault(og, [lo, hi])
-                s[0], s[1] = min(s[0], lo), max(s[1], hi)
-            for og, (lo, hi) in sorted(spans.items()):
-                a, b = max(lo, g.shard[0]), min(hi, g.shard[1])
-                if b > a:
-                    out.append((g, og, a, b))
+                if runs and runs[-1][0] == og and runs[-1][3] == i - 1 and \
+                        g.bucket_of[runs[-1][3]] == g.bucket_of[i]:
+                    runs[-1][2], runs[-1][3] = hi, i
+                else:
+                    runs.append([og, lo, hi, i])
+            for og, lo, hi, _ in runs:
+                for pa, pb, _loc in g.pieces:
+                    a, b = max(lo, pa), min(hi, pb)
+                    if b > a:
+                        out.append((g, og, a, b))
         return out
 
     def _publish_state(g, fs):
         """Per-parameter views of the flat moments in ``optimizer.state`` (torch's own layout)."""
-        lo = g.shard[0]
         for i, p in enumerate(g.params):
             target = g.master_params[i] if (g.flat_master is not None and g.master_params) else p
             if target is None or g.opt_group[i] < 0:
@@ -181,15 +198,16 @@ def patch_optimizer(module, optimizer):
             a, b = g.local_range(i)
             if b <= a:
                 continue
+            la = g.to_local(a)
             st = optimizer.state[target]
             st["step"] = torch.tensor(float(fs.step))
-            # a parameter cut by the shard boundary keeps its state as a flat piece
+            # a parameter cut by a slice boundary keeps its state as a flat piece
             shp = target.shape if (b - a) == target.numel() else (b - a,)
             if optimizer._rannc_kind == "adam":
-                st["exp_avg"] = fs.m[a - lo:b - lo].view(shp)
-                st["exp_avg_sq"] = fs.v[a - lo:b - lo].view(shp)
+                st["exp_avg"] = fs.m[la:la + (b - a)].view(shp)
+                st["exp_avg_sq"] = fs.v[la:la + (b - a)].view(shp)
             else:
-                st["momentum_buffer"] = fs.m[a - lo:b - lo].view(shp)
+                st["momentum_buffer"] = fs.m[la:la + (b - a)].view(shp)
 
     def _offloaded_update(g, fs, hp, og, a, b, kind, ctrl):
         """Streams [a, b) of the host-resident fp32 state through the device in chunks."""
@@ -199,10 +217,10 @@ def patch_optimizer(module, optimizer):
         if win is None:
             chunk = max(1 << 20, int(conf("offload_chunk_numel")))
             win = storage._offload_window = _OffloadWindow(g.device, chunk, 3)
-        lo = g.shard[0]
-        hosts = [g.flat_master[a - lo:b - lo], fs.m[a - lo:b - lo]]
+        la, n = g.to_local(a), b - a
+        hosts = [g.flat_master[la:la + n], fs.m[la:la + n]]
         if kind == "adam":
-            hosts.append(fs.v[a - lo:b - lo])
+            hosts.append(fs.v[la:la + n])
 
         def kernel(off, cnt, dev):
             grad = g.flat_grad[a + off:a + off + cnt]
@@ -227,9 +245,8 @@ def patch_optimizer(module, optimizer):
                 continue
             fs = optimizer._rannc_flat_state.get(id(g))
             if fs is None:
-                n = g.shard[1] - g.shard[0]
                 fs = optimizer._rannc_flat_state[id(g)] = _FlatState(
-                    n, g.device, kind, host=g.flat_master is not None and not g.flat_master.is_cuda and
+                    g.local_len, g.device, kind, host=g.flat_master is not None and not g.flat_master.is_cuda and
                     g.flat_grad.is_cuda)
             fs.step += 1
         for g, og, a, b in _flat_ranges():
@@ -237,21 +254,21 @@ def patch_optimizer(module, optimizer):
                 continue
             fs = optimizer._rannc_flat_state[id(g)]
             hp = optimizer.param_groups[og]
-            lo = g.shard[0]
+            la, n = g.to_local(a), b - a
             is_amp = g.flat_master is not None
             if is_amp and not g.flat_master.is_cuda and g.flat_grad.is_cuda:
                 _offloaded_update(g, fs, hp, og, a, b, kind, ctrl)
                 continue
-            master = g.flat_master[a - lo:b - lo] if is_amp else g.flat_param[a:b]
+            master = g.flat_master[la:la + n] if is_amp else g.flat_param[a:b]
             model16 = g.flat_param[a:b] if is_amp else None
             grad = g.flat_grad[a:b]
             if kind == "adam":
                 b1, b2 = hp["betas"]
-                K.adam_flat(master, grad, fs.m[a - lo:b - lo], fs.v[a - lo:b - lo], model16, float(hp["lr"]), b1,
+                K.adam_flat(master, grad, fs.m[la:la + n], fs.v[la:la + n], model16, float(hp["lr"]), b1,
                             b2, float(hp["eps"]), float(hp["weight_decay"]), fs.step,
                             type(optimizer) is torch.optim.AdamW, ctrl)
             else:
-                K.sgd_flat(master, grad, fs.m[a - lo:b - lo], model16, float(hp["lr"]), float(hp["momentum"]),
+                K.sgd_flat(master, grad, fs.m[la:la + n], model16, float(hp["lr"]), float(hp["momentum"]),
                            float(hp.get("dampening", 0.0)), float(hp["weight_decay"]), bool(hp.get("nesterov")),
                            fs.step == 1, ctrl)
         for g in storage.groups:
@@ -265,24 +282,28 @@ def patch_optimizer(module, optimizer):
         mod = optimizer._rannc_module
         red = getattr(mod, "_fused_reducer", None)
         if red is not None and red.pending and mod._needs_grad_norm():
-            # clipping / fp16 overflow checks need the reduced gradients first (the full-precision groups were
-            # reduced when backward finished)
-            storage.allreduce_grads_zero(only=[g for g in storage.groups if g not in red.plain_groups])
-            red.pending = False
+            # clipping / fp16 overflow checks need the reduced gradients first: the reduction launches that have
+            # not run yet run now, without the update (the full-precision groups were reduced when backward
+            # finished)
+            red.ensure_reduced(sticky=False)
         ctrl = mod._amp_prepare_step() if mod is not None else None
         if ctrl is False:
+            if red is not None and red.pending:
+                red.skip_step()
             return None  # overflow: skipped, scale already lowered
         if red is not None and red.pending:
-            # reduce-scatter + Adam + all-gather in one kernel per rank
+            # reduce-scatter + update + all-gather over peer memory, bucket by bucket (most of it already ran
+            # while backward was in flight)
             plain = list(red.plain_groups)
-            red.step(None)
+            red.step(ctrl if isinstance(ctrl, torch.Tensor) else None)
             red.publish_state()
             if plain:
                 # full-precision groups: gradients were reduced by the collective path, update them here
-                fused_step(None, only=plain)
+                fused_step(ctrl if isinstance(ctrl, torch.Tensor) else None, only=plain)
                 if storage.zero:
                     storage.allgather_params_zero(only=plain)
             RF.bump_param_epoch()
+            mod._after_step()
             return None
         use_fused = optimizer._rannc_kind is not None and all(
             g.flat_grad.is_cuda and g.flat_grad.dtype == torch.float32 for g in storage.groups)
@@ -299,11 +320,12 @@ def patch_optimizer(module, optimizer):
             if amp:
                 for g in storage.groups:
                     if g.flat_master is not None:
-                        lo, hi = g.shard
-                        g.flat_param[lo:hi].copy_(g.flat_master)
+                        g.scatter_local(g.flat_param, g.flat_master)
         if storage.zero:
             storage.allgather_params_zero()
         RF.bump_param_epoch()
+        if mod is not None:
+            mod._after_step()
         return loss
 
     def zero_grad(self, set_to_none: bool = False):
@@ -327,17 +349,20 @@ def patch_optimizer(module, optimizer):
 
 
 def gather_optimizer_state_dict(optimizer, root: int = 0, to_cpu: bool = True) -> Optional[dict]:
-    """Collective over the world.  Returns the global state dict on ``root``, None elsewhere."""
+    """Collective over the world.  Returns the global state dict on ``root``, None elsewhere.  ``state`` is keyed
+    by the parameter's position in the traversal of the original param groups -- the numbers
+    ``param_groups[*]['params']`` hold -- so the dict loads into a plain ``torch.optim`` optimizer built the same
+    way (reference: pyrannc/opt.py:98-157)."""
     mod = optimizer._rannc_module
     storage = mod._storage
     me = comm.get_rank()
     state = {}
-    for name, order in sorted(mod._param_order_by_name.items(), key=lambda kv: kv[1]):
+    for name, order in sorted(optimizer._rannc_order_by_name.items(), key=lambda kv: kv[1]):
         ranks = storage.param_ranks.get(name)
         if ranks is None:
             continue
         # item names and non-tensor items from the first rank that holds state for this parameter (under ZeRO
-        # the lowest owner may hold none of it: the parameter can lie wholly in another rank's shard)
+        # the lowest owner may hold none of it: the parameter can lie wholly in other ranks' slices)
         items = None
         if name in storage.by_name:
             g, i = storage.by_name[name]
@@ -355,8 +380,8 @@ def gather_optimizer_state_dict(optimizer, root: int = 0, to_cpu: bool = True) -
             if kind == "value":
                 entry[k] = val
                 continue
-            # tensor item: assemble from the owner set (shards under ZeRO), then hand to root
-            full = _gather_state_tensor(storage, optimizer, name, k, p_shape)
+            # tensor item: assemble inside the owner set (slices under ZeRO), then hand to root
+            full = _gather_state_tensor(storage, optimizer, name, k, p_shape, root)
             if me == root:
                 entry[k] = full.cpu() if to_cpu else full
         if me == root:
@@ -385,15 +410,22 @@ def _plain(v):
     return v
 
 
-def _gather_state_tensor(storage, optimizer, name: str, key: str, shape) -> torch.Tensor:
-    """Collective over the world: full fp32 tensor of optimizer-state item ``key`` of parameter ``name``."""
+def _gather_state_tensor(storage, optimizer, name: str, key: str, shape, root: int = 0) -> Optional[torch.Tensor]:
+    """Collective over the world: full fp32 tensor of optimizer-state item ``key`` of parameter ``name`` on
+    ``root``.  The pieces are summed inside the parameter's owner set only (one [numel] all-reduce among the
+    ranks that hold it); a rank outside the set takes part only when it is ``root``, by one point-to-point
+    copy from the lowest owner."""
     ranks = storage.param_ranks[name]
     numel = 1
     for d in shape:
         numel *= d
     dev = comm.device()
-    full = torch.zeros(numel, dtype=torch.float32, device=dev)
+    me = comm.get_rank()
     sl = storage.sliced.get(name)
+    holders = tuple(sl) if sl else tuple(ranks)
+    full = None
+    if me in holders or me == root:
+        full = torch.zeros(numel, dtype=torch.float32, device=dev)
     if name in storage.by_name:
         g, i = storage.by_name[name]
         target = g.master_params[i] if (g.flat_master is not None and g.master_params) else g.params[i]
@@ -403,16 +435,18 @@ def _gather_state_tensor(storage, optimizer, name: str, key: str, shape) -> torc
             if sl:
                 # a tensor-partitioned weight: every holder contributes its column block
                 ks = shape[1] // len(sl)
-                idx = sl.index(comm.get_rank())
+                idx = sl.index(me)
                 full.view(shape)[:, idx * ks:(idx + 1) * ks] = \
                     optimizer.state[target][key].reshape(shape[0], ks).to(dev, torch.float32)
-            elif storage.zero or comm.get_rank() == ranks[0]:
+            elif g.zero or me == ranks[0]:
                 full[a - lo:b - lo] = optimizer.state[target][key].reshape(-1).to(dev, torch.float32)
     if comm.get_world_size() > 1:
-        comm.allreduce(full, "sum")
-        if not storage.zero:
-            pass  # only the lowest owner contributed
-    return full.view(shape)
+        if len(holders) > 1 and me in holders:
+            comm.allreduce(full, "sum", holders)
+        if root not in holders:
+            # a checkpoint root outside the owner set gets the assembled tensor from the lowest owner
+            comm.send_recv(full, holders[0], root)
+    return full.view(shape) if full is not None else None
 
 
 def load_global_optimizer_state(optimizer, sd: dict) -> None:
@@ -424,7 +458,7 @@ def load_global_optimizer_state(optimizer, sd: dict) -> None:
         for k, v in hp_new.items():
             if k != "params":
                 hp[k] = v
-    order_to_name = {o: n for n, o in mod._param_order_by_name.items()}
+    order_to_name = {o: n for n, o in optimizer._rannc_order_by_name.items()}
     steps = {}
     for order, entry in sd["state"].items():
         name = order_to_name.get(int(order))
@@ -455,20 +489,21 @@ def load_global_optimizer_state(optimizer, sd: dict) -> None:
     # the fused step keeps flat moments: refill them from the per-parameter entries
     if optimizer._rannc_kind is not None:
         for g in storage.groups:
-            n = g.shard[1] - g.shard[0]
-            fs = _FlatState(n, g.device, optimizer._rannc_kind,
+            fs = _FlatState(g.local_len, g.device, optimizer._rannc_kind,
                             host=g.flat_master is not None and not g.flat_master.is_cuda and g.flat_grad.is_cuda)
             fs.step = steps.get(id(g), 0)
-            lo = g.shard[0]
             for i, p in enumerate(g.params):
                 target = g.master_params[i] if (g.flat_master is not None and g.master_params) else p
                 if target is None or target not in optimizer.state:
                     continue
                 a, b = g.local_range(i)
+                if b <= a:
+                    continue
+                la, n = g.to_local(a), b - a
                 st = optimizer.state[target]
                 if optimizer._rannc_kind == "adam" and "exp_avg" in st:
-                    fs.m[a - lo:b - lo] = st["exp_avg"].reshape(-1)
-                    fs.v[a - lo:b - lo] = st["exp_avg_sq"].reshape(-1)
+                    fs.m[la:la + n] = st["exp_avg"].reshape(-1)
+                    fs.v[la:la + n] = st["exp_avg_sq"].reshape(-1)
                 elif "momentum_buffer" in st and st["momentum_buffer"] is not None:
-                    fs.m[a - lo:b - lo] = st["momentum_buffer"].reshape(-1)
+                    fs.m[la:la + n] = st["momentum_buffer"].reshape(-1)
             optimizer._rannc_flat_state[id(g)] = fs

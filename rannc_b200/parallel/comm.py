@@ -279,6 +279,17 @@ def reduce_scatter_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Se
     dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=g)
 
 
+def send_recv(t: Optional[torch.Tensor], src: int, dst: int) -> None:
+    """One point-to-point copy of ``t`` from rank ``src`` to rank ``dst``; every other rank returns at once."""
+    if get_world_size() == 1 or src == dst:
+        return
+    me = get_rank()
+    if me == src:
+        dist.send(t.contiguous(), dst)
+    elif me == dst:
+        dist.recv(t, src)
+
+
 class PendingOps:
     """Handles of posted sends; buffers stay referenced until ``wait``."""
 

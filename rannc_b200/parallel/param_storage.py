@@ -39,7 +39,17 @@ def _align(n: int, unit: int) -> int:
 
 
 class FlatGroup:
-    """All parameters of one (owner rank set, dtype)."""
+    """All parameters of one (owner rank set, dtype).
+
+    The flat buffer is a sequence of *buckets*: runs of whole parameters, each padded so that it splits into
+    equal 16-byte aligned slices, one per rank.  Without ZeRO there is one bucket and every rank updates all of
+    it.  With ZeRO rank r updates slice r of EVERY bucket (``pieces``), so that each bucket can be reduced as
+    soon as backward has produced its gradients, with every rank taking an equal part of the work; the fp32
+    master copy and the optimizer moments of a rank are the concatenation of its slices (``local_len``
+    elements, ``to_local`` maps flat coordinates into it).  Because buckets end at parameter boundaries a
+    parameter meets this rank's slices in at most one contiguous piece (``local_range``).
+    (Reference: 128 MiB reduce-scatter buckets, src/comp/ParamStorage.cpp:21,396-520; per-parameter aligned
+    segments, src/comp/DistributedGradLocator.cpp:10-86.)"""
 
     def __init__(self, ranks: Tuple[int, ...], dtype: torch.dtype, device: torch.device):
         self.ranks = ranks
@@ -50,12 +60,17 @@ class FlatGroup:
         self.offsets: List[int] = []
         self.numels: List[int] = []
         self.opt_group: List[int] = []          # optimizer param_group index per param (-1: none)
+        self.units: List[Optional[str]] = []    # parameters with the same key stay adjacent in one bucket
         self.total = 0                           # aligned flat length
         self.flat_param: Optional[torch.Tensor] = None
         self.flat_grad: Optional[torch.Tensor] = None
-        self.flat_master: Optional[torch.Tensor] = None  # fp32, full or shard
+        self.flat_master: Optional[torch.Tensor] = None  # fp32, full or this rank's slices
         self.master_params: List[Optional[torch.nn.Parameter]] = []
-        self.shard: Tuple[int, int] = (0, 0)     # [lo, hi) of the flat buffer this rank updates
+        self.buckets: List[Tuple[int, int]] = []          # [lo, hi) in flat coordinates
+        self.bucket_of: List[int] = []                    # bucket index per parameter
+        self.pieces: List[Tuple[int, int, int]] = []      # (flat lo, flat hi, local offset) this rank updates
+        self.local_len = 0
+        self.zero = False
         self.symm = None                         # symmetric-memory handles of the fused gradient path
         self.slice_ranks: Optional[Tuple[int, ...]] = None  # tensor-partitioned weights: ranks holding the slices
 
@@ -67,22 +82,40 @@ class FlatGroup:
     def my_index(self) -> int:
         return self.ranks.index(comm.get_rank())
 
-    def add(self, name: str, p: torch.nn.Parameter, opt_group: int):
+    @property
+    def shard(self) -> Tuple[int, int]:
+        """[lo, hi) this rank updates when that is ONE interval (no ZeRO, or a single bucket)."""
+        if len(self.pieces) != 1:
+            raise RuntimeError("this rank's part of the flat buffer is not one interval; use pieces / to_local")
+        return self.pieces[0][0], self.pieces[0][1]
+
+    def add(self, name: str, p: torch.nn.Parameter, opt_group: int, unit: Optional[str] = None):
         self.names.append(name)
         self.params.append(p)
         self.opt_group.append(opt_group)
+        self.units.append(unit)
 
-    def finalize(self, amp: bool, zero: bool, symmetric: bool = False):
+    def finalize(self, amp: bool, zero: bool, symmetric: bool = False, bucket_numel: int = 0):
         # 16-byte aligned slots so every parameter view can feed TMA / vector loads
         es = torch.empty((), dtype=self.dtype).element_size()
         unit = max(1, 16 // es)
-        off = 0
-        for p in self.params:
+        balign = unit * self.nranks * 8          # a bucket divides into equal 16-byte aligned slices
+        self.zero = bool(zero)
+        off, bstart = 0, 0
+        n = len(self.params)
+        for i, p in enumerate(self.params):
             self.offsets.append(off)
             self.numels.append(p.numel())
+            self.bucket_of.append(len(self.buckets))
             off += _align(p.numel(), unit)
-        # whole buffer divisible into equal 16-byte aligned shards
-        self.total = _align(max(off, 1), unit * self.nranks * 8)
+            same_unit = i + 1 < n and self.units[i] is not None and self.units[i + 1] == self.units[i]
+            if zero and bucket_numel > 0 and off - bstart >= bucket_numel and not same_unit and i + 1 < n:
+                off = bstart + _align(off - bstart, balign)
+                self.buckets.append((bstart, off))
+                bstart = off
+        off = bstart + _align(max(off - bstart, 1), balign)
+        self.buckets.append((bstart, off))
+        self.total = off
         gdtype = torch.float32 if amp else self.dtype
         self.symmetric = bool(symmetric and (self.nranks > 1 or self.slice_ranks) and self.device.type == "cuda")
         if self.symmetric:
@@ -94,13 +127,22 @@ class FlatGroup:
         else:
             self.flat_param = torch.zeros(self.total, dtype=self.dtype, device=self.device)
             self.flat_grad = torch.zeros(self.total, dtype=gdtype, device=self.device)
-        seg = self.total // self.nranks
-        self.shard = (seg * self.my_index, seg * (self.my_index + 1)) if zero else (0, self.total)
-        for p, o, n in zip(self.params, self.offsets, self.numels):
-            view = self.flat_param[o:o + n].view(p.shape)
+        if zero:
+            loc = 0
+            for lo, hi in self.buckets:
+                seg = (hi - lo) // self.nranks
+                a = lo + seg * self.my_index
+                self.pieces.append((a, a + seg, loc))
+                loc += seg
+            self.local_len = loc
+        else:
+            self.pieces = [(0, self.total, 0)]
+            self.local_len = self.total
+        for p, o, n_ in zip(self.params, self.offsets, self.numels):
+            view = self.flat_param[o:o + n_].view(p.shape)
             view.copy_(p.data.to(device=self.device, dtype=self.dtype))
             p.data = view
-            gview = self.flat_grad[o:o + n].view(p.shape)
+            gview = self.flat_grad[o:o + n_].view(p.shape)
             if amp:
                 p.main_grad = gview
                 p.grad = None
@@ -111,9 +153,32 @@ class FlatGroup:
         return self.offsets[i], self.offsets[i] + self.numels[i]
 
     def local_range(self, i: int) -> Tuple[int, int]:
-        """Intersection of parameter i with this rank's shard, in flat coordinates (may be empty)."""
+        """Intersection of parameter i with the part this rank updates, in flat coordinates (may be empty)."""
         lo, hi = self.param_range(i)
-        return max(lo, self.shard[0]), max(max(lo, self.shard[0]), min(hi, self.shard[1]))
+        if not self.zero:
+            return lo, hi
+        a, b, _ = self.pieces[self.bucket_of[i]]
+        return max(lo, a), max(max(lo, a), min(hi, b))
+
+    def to_local(self, x: int) -> int:
+        """Index into this rank's master / moment buffers of flat coordinate ``x`` (inside, or at the end of,
+        one of its pieces)."""
+        for a, b, loc in self.pieces:
+            if a <= x <= b:
+                return loc + (x - a)
+        raise IndexError(f"flat offset {x} is not in this rank's part of the buffer")
+
+    def gather_local(self, flat: torch.Tensor) -> torch.Tensor:
+        """This rank's pieces of a flat buffer, concatenated (the layout of the master / moment buffers)."""
+        if len(self.pieces) == 1:
+            a, b, _ = self.pieces[0]
+            return flat[a:b]
+        return torch.cat([flat[a:b] for a, b, _ in self.pieces])
+
+    def scatter_local(self, flat: torch.Tensor, local: torch.Tensor) -> None:
+        """Inverse of ``gather_local``: writes a local buffer into this rank's pieces of ``flat``."""
+        for a, b, loc in self.pieces:
+            flat[a:b].copy_(local[loc:loc + (b - a)])
 
 
 class ParamStorage:
@@ -137,20 +202,40 @@ class ParamStorage:
     def deploy(self, named_params: Dict[str, torch.nn.Parameter], owner_ranks: Dict[str, Sequence[int]],
                opt_group_of: Dict[int, int], device: torch.device, global_order: Dict[str, int],
                symmetric: bool = False, sliced: Optional[Dict[str, Sequence[int]]] = None,
-               symmetric_slices: bool = False):
+               symmetric_slices: bool = False, adjacent: Optional[Sequence[Sequence[str]]] = None):
         """``sliced``: fqn -> ranks for weights stored as column slices (tensor-partitioned linear layers);
         such a parameter's local slice belongs to a flat buffer only this rank reduces and updates.
         ``named_params``: parameters used on this rank (fqn -> Parameter, tied names deduplicated);
         ``owner_ranks``: fqn -> ranks of every stage using it (for ALL parameters of the model, so that every
-        rank can create the same communicators in the same order)."""
+        rank can create the same communicators in the same order).
+        ``adjacent``: lists of fqns to lay out back to back, in the given order (the three projection weights of
+        a fused QKV block, so that one GEMM serves them); honoured when the parameters share a group."""
         me = comm.get_rank()
         self.global_order = dict(global_order)
         self.param_ranks = {k: tuple(sorted(set(v))) for k, v in owner_ranks.items()}
         self.sliced = {k: tuple(sorted(set(v))) for k, v in (sliced or {}).items()}
         comm.create_groups(list(self.param_ranks.values()) + list(self.sliced.values()))
         keyed: Dict[tuple, FlatGroup] = {}
-        order = sorted(named_params.items(),
-                       key=lambda kv: (opt_group_of.get(id(kv[1]), 1 << 30), global_order.get(kv[0], 0)))
+        unit_of: Dict[str, Tuple[str, int, int]] = {}     # fqn -> (unit key, order of the unit's first member, pos)
+        for names in (adjacent or ()):
+            names = [n for n in names if n in named_params]
+            ogs = {opt_group_of.get(id(named_params[n]), 1 << 30) for n in names}
+            dts = {named_params[n].dtype for n in names}
+            if len(names) < 2 or len(ogs) != 1 or len(dts) != 1 or any(n in unit_of for n in names):
+                continue
+            first = min(global_order.get(n, 0) for n in names)
+            for pos, n in enumerate(names):
+                unit_of[n] = ("u:" + names[0], first, pos)
+
+        def sort_key(kv):
+            name, p = kv
+            u = unit_of.get(name)
+            og = opt_group_of.get(id(p), 1 << 30)
+            if u is not None:
+                return (og, u[1], 0, u[2])
+            return (og, global_order.get(name, 0), 1, 0)
+
+        order = sorted(named_params.items(), key=sort_key)
         for name, p in order:
             ranks = self.param_ranks[name]
             if me not in ranks:
@@ -161,12 +246,16 @@ class ParamStorage:
             if key not in keyed:
                 keyed[key] = FlatGroup(key[0], dtype, device)
                 keyed[key].slice_ranks = sl
-            keyed[key].add(name, p, opt_group_of.get(id(p), -1))
+            keyed[key].add(name, p, opt_group_of.get(id(p), -1), unit_of[name][0] if name in unit_of else None)
         # deterministic group order on every rank: smaller rank sets first
         self.groups = [keyed[k] for k in sorted(keyed, key=lambda k: (len(k[0]), k[0], str(k[1]), k[2]))]
+        bucket_bytes = float(conf("grad_bucket_mb")) * (1 << 20)
         for g in self.groups:
-            g.finalize(self.amp and g.dtype in (torch.float16, torch.bfloat16), self.zero,
-                       symmetric_slices if g.slice_ranks else symmetric)
+            g_amp = self.amp and g.dtype in (torch.float16, torch.bfloat16)
+            ges = 4 if g_amp else torch.empty((), dtype=g.dtype).element_size()
+            g.finalize(g_amp, self.zero and not g.slice_ranks,
+                       symmetric_slices if g.slice_ranks else symmetric,
+                       bucket_numel=int(bucket_bytes // ges) if g.nranks > 1 else 0)
             for i, n in enumerate(g.names):
                 self.by_name[n] = (g, i)
         if self.sync_on_init:
@@ -179,13 +268,12 @@ class ParamStorage:
                 comm.bcast(g.flat_param, g.ranks[0], g.ranks)
 
     def setup_master(self):
-        """fp32 master copies (whole buffer, or this rank's shard under ZeRO)."""
+        """fp32 master copies (whole buffer, or this rank's slices of every bucket under ZeRO)."""
         for g in self.groups:
             if g.dtype not in (torch.float16, torch.bfloat16) or not self.amp:
                 g.master_params = [None] * len(g.params)
                 continue
-            lo, hi = g.shard
-            g.flat_master = g.flat_param[lo:hi].float()
+            g.flat_master = g.gather_local(g.flat_param).float()
             host = self.offload and g.flat_master.is_cuda
             if host:
                 g.flat_master = g.flat_master.cpu().pin_memory()
@@ -196,7 +284,8 @@ class ParamStorage:
                     g.master_params.append(None)
                     continue
                 full = (a, b) == g.param_range(i)
-                mview = g.flat_master[a - lo:b - lo]
+                la = g.to_local(a)
+                mview = g.flat_master[la:la + (b - a)]
                 mp = torch.nn.Parameter(mview.view(p.shape) if full else mview, requires_grad=p.requires_grad)
                 if not host:
                     mp.grad = g.flat_grad[a:b].view(mp.shape)
@@ -241,7 +330,7 @@ class ParamStorage:
         self._sync_if_asked()
 
     def allreduce_grads_zero(self, only=None):
-        """ZeRO baseline: reduce-scatter so each rank holds the reduced gradient of its shard
+        """ZeRO baseline: reduce-scatter, bucket by bucket, so each rank holds the reduced gradient of its slices
         (reference: bucketed ncclReduceScatter, ParamStorage.cpp:396-520).  ``only``: a subset of the groups."""
         world = comm.get_world_size()
         self.fold_model_grads()
@@ -250,11 +339,13 @@ class ParamStorage:
                 continue
             if world > 1:
                 g.flat_grad.mul_(1.0 / world)
-            if g.nranks > 1:
-                lo, hi = g.shard
-                out = torch.empty(hi - lo, dtype=g.flat_grad.dtype, device=g.device)
-                comm.reduce_scatter_into(out, g.flat_grad, g.ranks)
-                g.flat_grad[lo:hi].copy_(out)
+            if g.nranks > 1 and g.zero:
+                for (lo, hi), (a, b, _) in zip(g.buckets, g.pieces):
+                    out = torch.empty(b - a, dtype=g.flat_grad.dtype, device=g.device)
+                    comm.reduce_scatter_into(out, g.flat_grad[lo:hi], g.ranks)
+                    g.flat_grad[a:b].copy_(out)
+            elif g.nranks > 1:
+                comm.allreduce(g.flat_grad, "sum", g.ranks)
         self._sync_if_asked()
 
     @staticmethod
@@ -265,13 +356,13 @@ class ParamStorage:
             torch.cuda.synchronize()
 
     def allgather_params_zero(self, only=None):
-        """Refreshes the full 16-bit parameters from the updated shards (reference: ParamStorage.cpp:559-596)."""
+        """Refreshes the full 16-bit parameters from the updated slices (reference: ParamStorage.cpp:559-596)."""
         for g in self.groups:
             if only is not None and g not in only:
                 continue
-            if g.nranks > 1 and self.zero:
-                lo, hi = g.shard
-                comm.allgather_into(g.flat_param, g.flat_param[lo:hi].clone(), g.ranks)
+            if g.nranks > 1 and g.zero:
+                for (lo, hi), (a, b, _) in zip(g.buckets, g.pieces):
+                    comm.allgather_into(g.flat_param[lo:hi], g.flat_param[a:b].clone(), g.ranks)
 
     # ---------------------------------------------------------------- norms
     def _norm_bufs(self, device):
@@ -281,27 +372,38 @@ class ParamStorage:
             self._norm = torch.zeros(1, dtype=torch.float32, device=device)
         return self._sumsq, self._ctrl, self._norm
 
+    def _ensure_reduced(self) -> None:
+        """The fused gradient path reduces inside (or right before) the optimizer step; anything that reads
+        gradients earlier first makes sure the reduction has happened."""
+        red = getattr(self, "reducer", None)
+        if red is not None:
+            red.ensure_reduced()
+
     def grad_sumsq(self) -> torch.Tensor:
         """Sum of squares of the gradients this rank is responsible for, as a device scalar.  Each element is
-        counted once across the job: a rank counts its shard under ZeRO, otherwise the lowest owner counts."""
+        counted once across the job: a rank counts its slices under ZeRO, otherwise the lowest owner counts."""
+        self._ensure_reduced()
         me = comm.get_rank()
         dev = self.groups[0].device if self.groups else comm.device()
         ss, _, _ = self._norm_bufs(dev)
         ss.zero_()
+        red = getattr(self, "reducer", None)
         for g in self.groups:
-            if self.zero:
-                lo, hi = g.shard
+            if red is not None and red.adds_sumsq(g, ss):
+                continue   # the reduction kernels already summed the squares of this group's reduced gradients
+            if g.zero:
+                segs = [g.flat_grad[a:b] for a, b, _ in g.pieces]
             elif g.ranks[0] == me:
-                lo, hi = 0, g.total
+                segs = [g.flat_grad]
             else:
                 continue
-            seg = g.flat_grad[lo:hi]
-            if seg.is_cuda:
-                from ..ops import kernels as K
+            for seg in segs:
+                if seg.is_cuda:
+                    from ..ops import kernels as K
 
-                K.sumsq(seg, ss)
-            else:
-                ss.add_(seg.float().pow(2).sum())
+                    K.sumsq(seg, ss)
+                else:
+                    ss.add_(seg.float().pow(2).sum())
         if comm.get_world_size() > 1:
             comm.allreduce(ss, "sum")
         return ss
@@ -310,6 +412,7 @@ class ParamStorage:
         return float(self.grad_sumsq().sqrt().item())
 
     def clip_grad_norm(self, max_norm: float) -> float:
+        """Global L2 norm of the reduced gradients, then scale them (reference: ParamStorage.cpp:721-819)."""
         ss = self.grad_sumsq()
         norm = float(ss.sqrt().item())
         coef = max_norm / (norm + 1e-6)
@@ -341,8 +444,8 @@ class ParamStorage:
         if g.flat_master is not None:
             a, b = g.local_range(i)
             if b > a:
-                lo = g.shard[0]
-                g.flat_master[a - lo:b - lo].copy_(flat[a - o:b - o].to(torch.float32))
+                la = g.to_local(a)
+                g.flat_master[la:la + (b - a)].copy_(flat[a - o:b - o].to(torch.float32))
         return True
 
     def _root_of(self, name: str) -> int:
@@ -371,15 +474,16 @@ class ParamStorage:
             g, i = self.by_name[name]
             lo, hi = g.param_range(i)
             if grad:
-                if self.zero and g.nranks > 1:
-                    full = self._gather_sharded(g, g.flat_grad, lo, hi)
+                self._ensure_reduced()
+                if g.zero and g.nranks > 1:
+                    full = self._gather_sharded(g, i, g.flat_grad)
                 else:
                     full = g.flat_grad[lo:hi]
             elif use_master and g.flat_master is not None:
-                if self.zero and g.nranks > 1:
-                    full = self._gather_sharded(g, None, lo, hi, master=True)
+                if g.zero and g.nranks > 1:
+                    full = self._gather_sharded(g, i, None)
                 else:
-                    full = g.flat_master[lo - g.shard[0]:hi - g.shard[0]]
+                    full = g.flat_master[lo:hi]
             else:
                 full = g.flat_param[lo:hi]
             if sl:
@@ -405,11 +509,19 @@ class ParamStorage:
             comm.bcast(val, root)
         return val.cpu()
 
-    def _gather_sharded(self, g: FlatGroup, flat: Optional[torch.Tensor], lo: int, hi: int, master: bool = False):
-        """All-gather of the shards of a ZeRO-sharded buffer inside the owner set, then the [lo, hi) slice."""
-        seg = g.total // g.nranks
-        slo, shi = g.shard
-        mine = (g.flat_master if master else flat[slo:shi]).float().contiguous()
-        full = torch.empty(g.total, dtype=torch.float32, device=g.device)
-        comm.allgather_into(full, mine, g.ranks)
-        return full[lo:hi]
+    def _gather_sharded(self, g: FlatGroup, i: int, flat: Optional[torch.Tensor]) -> torch.Tensor:
+        """Parameter i of a ZeRO-sharded group, assembled inside the owner set: every rank contributes the part
+        of the parameter that lies in its slice of the parameter's bucket (``flat`` = a full-length buffer such
+        as the gradients; None = the fp32 master slices).  Only the parameter's own range travels: an
+        all-reduce of a zero-filled [numel] buffer (reference: gatherParamZero, ParamStorage.cpp:1143-1232)."""
+        lo, hi = g.param_range(i)
+        a, b = g.local_range(i)
+        out = torch.zeros(hi - lo, dtype=torch.float32, device=g.device)
+        if b > a:
+            if flat is None:
+                la = g.to_local(a)
+                out[a - lo:b - lo] = g.flat_master[la:la + (b - a)].to(g.device, torch.float32)
+            else:
+                out[a - lo:b - lo] = flat[a:b].float()
+        comm.allreduce(out, "sum", g.ranks)
+        return out

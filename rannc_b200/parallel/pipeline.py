@@ -71,6 +71,7 @@ class PipelineRuntime:
         self.master = self.all_ranks if gather_inputs else [0]
         self._fwd_state = None
         self._in_grads: Dict = {}
+        self.split_hook = None      # called as split_hook(i, P) before the backward of micro-batch i starts
         sets = [self.all_ranks] + list(self.alloc.values())
         for r in list(dep.fwd_routes):
             sets.append(sorted(set(r.sources) | set(r.dests)))
@@ -252,6 +253,8 @@ class PipelineRuntime:
         dev = comm.device()
         recv_grads: Dict[Tuple[int, str], Dict[str, torch.Tensor]] = {}
         for i in range(P):
+            if self.split_hook is not None:
+                self.split_hook(i, P)
             for sname in reversed(self.order):
                 ranks = self.alloc[sname]
                 mine = sname in self.stages

@@ -37,7 +37,17 @@ def main():
     mk = (lambda ps: torch.optim.SGD(ps, lr=lr, momentum=0.9)) if case.get("opt", "sgd") == "sgd" else \
         (lambda ps: torch.optim.Adam(ps, lr=0.01))
     has_params = any(True for _ in model.parameters())
-    opt, ropt = (mk(model.parameters()), mk(ref.parameters())) if has_params else (None, None)
+    if case.get("two_groups"):
+        # biases first (no decay), then the matrices (decay): not the model's parameter order
+        def groups(m):
+            ps = list(m.named_parameters())
+            return [{"params": [p for n, p in ps if p.dim() < 2], "weight_decay": 0.0},
+                    {"params": [p for n, p in ps if p.dim() >= 2], "weight_decay": 0.01}]
+
+        mk2 = lambda gs: torch.optim.Adam(gs, lr=0.01)  # noqa: E731
+        opt, ropt = mk2(groups(model)), mk2(groups(ref))
+    else:
+        opt, ropt = (mk(model.parameters()), mk(ref.parameters())) if has_params else (None, None)
     wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=case.get("amp", False),
                                   enable_zero=case.get("zero", False), check_unused_values=False,
                                   allreduce_amp_master_params=case.get("ar_master", False),
@@ -97,6 +107,12 @@ def main():
             if not torch.allclose(gr.float(), p.grad.float(), rtol=tol * 10, atol=tol * 10):
                 ok = False
                 msgs.append(f"it {it}: grad {n} differs by {(gr.float() - p.grad.float()).abs().max().item()}")
+        if case.get("clip"):
+            got = wrapped.clip_grad_norm(case["clip"])
+            want = float(torch.nn.utils.clip_grad_norm_(ref.parameters(), case["clip"]))
+            if abs(got - want) > tol * 10 * max(1.0, want):
+                ok = False
+                msgs.append(f"it {it}: grad norm {got} vs {want}")
         if opt is not None:
             opt.step()
             ropt.step()
@@ -129,6 +145,17 @@ def main():
                     elif not torch.allclose(osd["state"][k][item].float(), v.float(), rtol=tol * 10, atol=tol * 10):
                         ok = False
                         msgs.append(f"optimizer state {k}/{item} differs")
+    if opt is not None and case.get("two_groups") and rank == 0:
+        # the gathered dict must load into a plain optimizer over the eager copy and carry the same moments
+        fresh = torch.optim.Adam(groups(ref), lr=0.01)
+        fresh.load_state_dict(osd)
+        for gi, g_ in enumerate(fresh.param_groups):
+            for p in g_["params"]:
+                a = fresh.state[p]["exp_avg"].float()
+                b = ropt.state[p]["exp_avg"].float()
+                if a.shape != b.shape or not torch.allclose(a, b, rtol=tol * 10, atol=tol * 10):
+                    ok = False
+                    msgs.append(f"two_groups: exp_avg of a parameter of group {gi} differs after loading into torch")
     if opt is not None:
         osd = pyrannc.comm_utils.bcast_obj(osd, 0)
         opt.load_state_dict(osd, from_global=True)
@@ -163,7 +190,8 @@ def main():
                 msgs.append(f"reload: param {n} differs after a step by "
                             f"{(v.float() - p.detach().float()).abs().max().item()}")
     stages = len(wrapped._dep.fwd_graph_order)
-    res = {"ok": ok, "msgs": msgs[:8], "stages": stages, "pipeline": wrapped._dep.pipeline_num, "sliced": len(wrapped._storage.sliced),
+    res = {"ok": ok, "msgs": msgs[:8], "stages": stages,
+           "buckets": max([len(g_.buckets) for g_ in wrapped._storage.groups] or [0]), "pipeline": wrapped._dep.pipeline_num, "sliced": len(wrapped._storage.sliced),
            "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}}
     all_res = pyrannc._comm.allgather_obj(res)
     if rank == 0:

@@ -152,6 +152,35 @@ def test_mixed_precision_with_zero_sharding_dp2():
     run_case(2, {"model": "deep", "batch": 8, "amp": True, "zero": True, "accum": 2, "tol": 1e-1})
 
 
+def test_zero_sharding_over_several_buckets():
+    # a bucket of a few hundred bytes: every flat buffer splits into many buckets and each rank owns a slice of
+    # each, so a rank's master / moment buffers are the concatenation of non-adjacent slices; gradients,
+    # updates, state_dict, the gathered optimizer state and load_state_dict into the deployed module must agree
+    env = {"RANNC_GRAD_BUCKET_MB": "0.0005"}
+    res = run_case(2, {"model": "layernorm", "batch": 8, "amp": True, "zero": True, "opt": "adam", "tol": 1e-1,
+                       "reload": True, "want_buckets": 2}, env)
+    assert min(r["buckets"] for r in res["ranks"]) >= 2
+    run_case(2, {"model": "deep", "batch": 8, "amp": True, "zero": True, "accum": 2, "tol": 1e-1}, env)
+    run_case(3, {"model": "deep", "batch": 12, "amp": True, "zero": True, "opt": "adam", "tol": 1e-1},
+             dict(env, RANNC_LIMIT_DEV_NUM_POT="false", RANNC_PARTITION_NUM="1", RANNC_REPLICA_NUM="3"))
+
+
+def test_clip_grad_norm_matches_eager_under_zero():
+    # the norm is taken over the reduced gradients (each element once across the ranks) and the clipped
+    # update follows eager's clip_grad_norm_ on the full batch
+    run_case(2, {"model": "deep", "batch": 8, "clip": 0.05})
+    run_case(2, {"model": "deep", "batch": 8, "amp": True, "zero": True, "clip": 0.05, "tol": 1e-1},
+             {"RANNC_GRAD_BUCKET_MB": "0.0005"})
+
+
+def test_two_param_groups_checkpoint_loads_into_plain_torch():
+    # decay / no-decay groups listed in an order that differs from the model's: the gathered state is keyed by
+    # the optimizer's own numbering, so a fresh torch.optim.Adam built the same way accepts it as is
+    run_case(2, {"model": "deep", "batch": 8, "opt": "adam", "two_groups": True})
+    run_case(2, {"model": "deep", "batch": 8, "opt": "adam", "two_groups": True, "amp": True, "zero": True,
+                 "tol": 1e-1})
+
+
 @pytest.mark.parametrize("env", [{}, {"RANNC_PARTITION_NUM": "2"}])
 def test_dist_param_model_declared_in_shards(env):
     run_case(2, {"model": "deep", "batch": 8, "dist_param": True}, env)
