@@ -96,11 +96,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         *abort_flag = 0;
         fence_mbar_init();
     }
+    int any_bias = FAST ? 0 : 1;
     if (FAST) {
         // per-key tables for the whole (padded) sequence: -inf bias masks the keys past its end
         const float* kb = p.key_bias ? p.key_bias + static_cast<long long>(b) * p.S : nullptr;
         for (int i = threadIdx.x; i < nchunks * AK; i += ATT_THREADS) {
-            s_kb[i] = i < p.S ? (kb ? kb[i] * 1.4426950408889634f : 0.f) : -INFINITY;
+            const float v = i < p.S ? (kb ? kb[i] * 1.4426950408889634f : 0.f) : -INFINITY;
+            any_bias |= (v != 0.f);
+            s_kb[i] = v;
             s_kh[i] = drop_key_hash(p.seed, i);
         }
     }
@@ -109,7 +112,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         tmem_relinquish();
     }
     tc_fence_before();
-    __syncthreads();
+    // an all-zero bias (no padding in this batch row, sequence a multiple of the chunk) takes the loops
+    // without the per-key add: the row maximum is then taken over the raw scores
+    const bool has_bias = __syncthreads_or(any_bias) != 0 || !(p.scale_log2 > 0.f);
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -221,19 +226,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             // the current one is processed.
             float cm = -INFINITY;
             const uint32_t s_addr = col_s + lane_addr + half * 64;
+            const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
             {
                 uint32_t va[16], vb[16];
                 auto max16 = [&](const uint32_t(&v)[16], int colbase) {
+                    if (has_bias) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        float4 kb;
-                        uint4 kh = make_uint4(0, 0, 0, 0);
-                        cols4(key0 + colbase + g * 4, kb, kh);
-                        const float s0 = fmaf(__uint_as_float(v[g * 4]), p.scale_log2, kb.x);
-                        const float s1 = fmaf(__uint_as_float(v[g * 4 + 1]), p.scale_log2, kb.y);
-                        const float s2 = fmaf(__uint_as_float(v[g * 4 + 2]), p.scale_log2, kb.z);
-                        const float s3 = fmaf(__uint_as_float(v[g * 4 + 3]), p.scale_log2, kb.w);
-                        cm = fmaxf(fmaxf(cm, s0), fmaxf(s1, fmaxf(s2, s3)));
+                        for (int g = 0; g < 4; ++g) {
+                            float4 kb;
+                            uint4 kh = make_uint4(0, 0, 0, 0);
+                            cols4(key0 + colbase + g * 4, kb, kh);
+                            float s0, s1, s2, s3;
+                            f2_unpack(f2_fma(f2_pack_bits(v[g * 4], v[g * 4 + 1]), scale2, f2_pack(kb.x, kb.y)), s0, s1);
+                            f2_unpack(f2_fma(f2_pack_bits(v[g * 4 + 2], v[g * 4 + 3]), scale2, f2_pack(kb.z, kb.w)), s2,
+                                      s3);
+                            cm = fmax3(cm, s0, s1);
+                            cm = fmax3(cm, s2, s3);
+                        }
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            cm = fmax3(cm, __uint_as_float(v[g * 2]), __uint_as_float(v[g * 2 + 1]));
                     }
                 };
                 tmem_ld16(s_addr, va);
@@ -249,6 +262,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 tmem_ld_wait();
                 max16(vb, 48);
             }
+            if (!has_bias) cm *= p.scale_log2;   // scale > 0: the maximum of the raw scores, scaled
             float* xch = xbase + (j & 1) * 256;
             xch[half * 128 + r] = cm;
             bar_sync_named(1 + t, GROUP);
@@ -283,27 +297,49 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
             // pass 2: probabilities -> shared memory (16-bit, swizzled K-major).  Dropped entries are
             // zeroed here; the 1 / (1 - p) factor is applied once to the finished row.
-            float rs = 0.f;
+            uint64_t rs2 = f2_pack(0.f, 0.f);
             {
                 uint32_t va[16], vb[16];
+                const uint64_t negm2 = f2_pack(-m_use, -m_use);
                 auto prob16 = [&](const uint32_t(&v)[16], int colbase) {
 #pragma unroll
                     for (int g = 0; g < 2; ++g) {
                         float pr[8];
 #pragma unroll
                         for (int hq = 0; hq < 2; ++hq) {
-                            float4 kb;
+                            float4 kb = make_float4(0.f, 0.f, 0.f, 0.f);
                             uint4 kh = make_uint4(0, 0, 0, 0);
-                            cols4(key0 + colbase + g * 8 + hq * 4, kb, kh);
-                            const float kbv[4] = {kb.x, kb.y, kb.z, kb.w};
-                            const uint32_t khv[4] = {kh.x, kh.y, kh.z, kh.w};
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float e =
-                                    exp2f(fmaf(__uint_as_float(v[g * 8 + hq * 4 + i]), p.scale_log2, kbv[i]) - m_use);
-                                rs += e;
-                                pr[hq * 4 + i] = (!p.thr32 || drop_keep(row_hash, khv[i], p.thr32)) ? e : 0.f;
+                            if (has_bias) {
+                                cols4(key0 + colbase + g * 8 + hq * 4, kb, kh);
+                            } else if (p.thr32) {
+                                if (FAST) {
+                                    kh = *reinterpret_cast<const uint4*>(s_kh + key0 + colbase + g * 8 + hq * 4);
+                                } else {
+                                    cols4(key0 + colbase + g * 8 + hq * 4, kb, kh);
+                                }
                             }
+                            const uint32_t khv[4] = {kh.x, kh.y, kh.z, kh.w};
+                            const int e0 = g * 8 + hq * 4;
+                            uint64_t x01, x23;
+                            if (has_bias) {
+                                x01 = f2_add(f2_fma(f2_pack_bits(v[e0], v[e0 + 1]), scale2, f2_pack(kb.x, kb.y)), negm2);
+                                x23 = f2_add(f2_fma(f2_pack_bits(v[e0 + 2], v[e0 + 3]), scale2, f2_pack(kb.z, kb.w)),
+                                             negm2);
+                            } else {
+                                x01 = f2_fma(f2_pack_bits(v[e0], v[e0 + 1]), scale2, negm2);
+                                x23 = f2_fma(f2_pack_bits(v[e0 + 2], v[e0 + 3]), scale2, negm2);
+                            }
+                            float x[4];
+                            f2_unpack(x01, x[0], x[1]);
+                            f2_unpack(x23, x[2], x[3]);
+                            float e[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) e[i] = ex2_approx(x[i]);
+                            rs2 = f2_add(rs2, f2_pack(e[0], e[1]));
+                            rs2 = f2_add(rs2, f2_pack(e[2], e[3]));
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                pr[hq * 4 + i] = (!p.thr32 || drop_keep(row_hash, khv[i], p.thr32)) ? e[i] : 0.f;
                         }
                         uint4 qv;
                         qv.x = pack2<T>(pr[0], pr[1]);
@@ -329,6 +365,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 mbar_arrive(&s_free[t]);
                 prob16(vb, 48);
             }
+            float rs_lo, rs_hi;
+            f2_unpack(rs2, rs_lo, rs_hi);
+            const float rs = rs_lo + rs_hi;
             l = l * alpha + rs;
             m = m_new == -INFINITY ? -INFINITY : m_use;
             fence_proxy_async();

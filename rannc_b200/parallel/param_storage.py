@@ -11,9 +11,9 @@ pack/unpack copy around a collective, one collective (or one fused kernel)
 covers a whole rank set, and gradient accumulation over micro-batches writes
 straight into it.  Under mixed precision an fp32 master copy and the optimizer
 moments sit in further flat buffers; with ``enable_zero`` each rank keeps only
-its contiguous 1/n shard of those (aligned to 16 bytes x ranks, like the
-reference's segments) and the optimizer sees the per-parameter intersections
-with that shard.
+one 1/n slice of every gradient bucket of those (aligned to 16 bytes x ranks,
+like the reference's segments) and the optimizer sees the per-parameter
+intersections with its slices.
 
 Semantics kept from the reference: a parameter's owner set is the union of the
 rank sets of the stages that use it; gradients are summed over the owner set
@@ -372,17 +372,18 @@ class ParamStorage:
             self._norm = torch.zeros(1, dtype=torch.float32, device=device)
         return self._sumsq, self._ctrl, self._norm
 
-    def _ensure_reduced(self) -> None:
+    def _ensure_reduced(self, sticky: bool = True) -> None:
         """The fused gradient path reduces inside (or right before) the optimizer step; anything that reads
-        gradients earlier first makes sure the reduction has happened."""
+        gradients earlier first makes sure the reduction has happened.  ``sticky``: the request comes from user
+        code (``clip_grad_norm``, ``get_param_grad``), which will ask again in later steps."""
         red = getattr(self, "reducer", None)
         if red is not None:
-            red.ensure_reduced()
+            red.ensure_reduced(sticky)
 
-    def grad_sumsq(self) -> torch.Tensor:
+    def grad_sumsq(self, sticky: bool = False) -> torch.Tensor:
         """Sum of squares of the gradients this rank is responsible for, as a device scalar.  Each element is
         counted once across the job: a rank counts its slices under ZeRO, otherwise the lowest owner counts."""
-        self._ensure_reduced()
+        self._ensure_reduced(sticky)
         me = comm.get_rank()
         dev = self.groups[0].device if self.groups else comm.device()
         ss, _, _ = self._norm_bufs(dev)
@@ -409,11 +410,11 @@ class ParamStorage:
         return ss
 
     def calc_grad_norm(self) -> float:
-        return float(self.grad_sumsq().sqrt().item())
+        return float(self.grad_sumsq(sticky=True).sqrt().item())
 
     def clip_grad_norm(self, max_norm: float) -> float:
         """Global L2 norm of the reduced gradients, then scale them (reference: ParamStorage.cpp:721-819)."""
-        ss = self.grad_sumsq()
+        ss = self.grad_sumsq(sticky=True)
         norm = float(ss.sqrt().item())
         coef = max_norm / (norm + 1e-6)
         if coef < 1.0:

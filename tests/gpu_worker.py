@@ -20,6 +20,8 @@ def main():
     torch.manual_seed(0)
     RF.manual_seed(5)
     resnet = case.get("model", "bert") == "resnet"
+    if case.get("fp16"):
+        pyrannc.amp.initialize(None, None, dtype=torch.float16)
     if resnet:
         from rannc_b200.models.resnet import ResNetWithLoss, tiny_resnet
 
@@ -35,10 +37,12 @@ def main():
         opt = torch.optim.Adam(model.parameters(), lr=1e-3)
     wrapped = pyrannc.RaNNCModule(model, opt, enable_apex_amp=True, enable_zero=case.get("zero", True),
                                   offload_params=case.get("offload", False))
+    if case.get("max_grad_norm"):
+        wrapped.max_grad_norm = float(case["max_grad_norm"])
     B = case.get("batch", 16)
     lb = B // world
     dev = pyrannc._comm.device()
-    losses = []
+    losses, norms, skipped = [], [], []
     for it in range(case.get("iters", 3)):
         if resnet:
             g = torch.Generator().manual_seed(it)
@@ -46,10 +50,25 @@ def main():
         else:
             full = synthetic_batch(cfg, B, 128, seed=it)
         local = tuple(t[rank * lb:(rank + 1) * lb].to(dev) for t in full)
+        saved_scale = None
+        if case.get("inject_inf") == it:
+            # an overflow made on the host: an absurd loss scale for this one step turns the fp16 gradients
+            # into inf; the step must be skipped on every rank
+            sc = pyrannc.amp.get_scaler()
+            saved_scale, sc._loss_scale = sc._loss_scale, 2.0 ** 60
         loss = wrapped(*local)
-        loss.backward()
+        if case.get("fp16"):
+            with pyrannc.amp.scale_loss(loss) as scaled:
+                scaled.backward()
+        else:
+            loss.backward()
+        if case.get("clip"):
+            norms.append(wrapped.clip_grad_norm(float(case["clip"])))
         opt.step()
         opt.zero_grad()
+        if saved_scale is not None:
+            skipped.append(pyrannc.amp.get_scaler().loss_scale() < 2.0 ** 60)
+            pyrannc.amp.get_scaler()._loss_scale = saved_scale
         losses.append(float(loss))
     torch.cuda.synchronize()
     sd = wrapped.state_dict()
@@ -75,7 +94,11 @@ def main():
         reload_ok = reload_ok and bool(torch.isfinite(loss))
         torch.cuda.synchronize()
     err = _lib.read_error()
-    info = {"reload_ok": reload_ok, "fused": wrapped._fused_reducer is not None, "stages": len(wrapped._dep.fwd_graph_order),
+    red = wrapped._fused_reducer
+    info = {"reload_ok": reload_ok, "fused": red is not None, "norms": norms,
+            "buckets": red.num_buckets() if red is not None else 0,
+            "in_backward": red.launched_in_backward if red is not None else 0,
+            "scale": pyrannc.amp.get_scaler().loss_scale(), "skipped": skipped, "stages": len(wrapped._dep.fwd_graph_order),
             "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}, "losses": losses, "err": err,
             "sliced": len(wrapped._storage.sliced)}
     infos = pyrannc._comm.allgather_obj(info)

@@ -81,6 +81,63 @@ def test_fused_reduce_matches_nccl_path(tmp_path):
     assert fused["opt"]["state"][k0]["exp_avg"].shape == plain["opt"]["state"][k0]["exp_avg"].shape
 
 
+def _tight(a, b, rel, what=""):
+    """Every weight of every tensor: |a - b| <= rel * max|b| of that tensor (no key is skipped)."""
+    for k in a["sd"]:
+        x, y = a["sd"][k].float(), b["sd"][k].float()
+        assert torch.isfinite(x).all(), k
+        assert (x - y).abs().max().item() <= rel * (y.abs().max().item() + 1e-3), (what, k)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("multimem", ["1", "0"])
+def test_bucketed_reduce_overlapping_backward_matches_nccl(tmp_path, multimem):
+    """Buckets of 256 KiB: the 4-layer model splits into many buckets, each rank owns a slice of each, and from
+    the second step on every bucket is reduced and updated on the side stream while backward still runs.  SGD
+    with momentum, so that a mis-reduced element shows up at its own size (Adam would hide it behind +-lr)."""
+    case = {"opt": "sgd", "layers": 4, "iters": 5}
+    env = {"RANNC_GRAD_BUCKET_MB": "0.25", "RANNC_USE_MULTIMEM": multimem}
+    a = _run(2, dict(case, out=str(tmp_path / "a.pt")), env)
+    b = _run(2, dict(case, out=str(tmp_path / "b.pt")), dict(env, RANNC_FUSED_GRAD_ALLREDUCE="false"))
+    assert all(i["fused"] and i["err"] == 0 for i in a["infos"]), a["infos"]
+    assert all(i["buckets"] >= 4 for i in a["infos"]), a["infos"]
+    # 4 of the 5 steps ran with the launches inside backward
+    assert all(i["in_backward"] >= 4 * (i["buckets"] - 1) for i in a["infos"]), a["infos"]
+    for la, lb in zip(a["infos"][0]["losses"], b["infos"][0]["losses"]):
+        assert abs(la - lb) < 2e-2 * abs(lb)
+    _tight(a, b, 2e-2, "bucketed")
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_reduce_with_gradient_clipping(tmp_path):
+    """clip_grad_norm between backward and the step (the reducer then keeps reduction and update apart and
+    the norm comes from the reduction launches), and the same clipping done inside the step via max_grad_norm;
+    both against the NCCL path."""
+    case = {"opt": "sgd", "layers": 2, "iters": 4}
+    env = {"RANNC_GRAD_BUCKET_MB": "0.25"}
+    a = _run(2, dict(case, clip=0.5, out=str(tmp_path / "a.pt")), env)
+    b = _run(2, dict(case, clip=0.5, out=str(tmp_path / "b.pt")), dict(env, RANNC_FUSED_GRAD_ALLREDUCE="false"))
+    c = _run(2, dict(case, max_grad_norm=0.5, out=str(tmp_path / "c.pt")), env)
+    assert all(i["fused"] and i["err"] == 0 for i in a["infos"] + c["infos"])
+    for na, nb in zip(a["infos"][0]["norms"], b["infos"][0]["norms"]):
+        assert nb > 0.5 and abs(na - nb) < 2e-2 * nb, (na, nb)   # the clip is active and the norms agree
+    _tight(a, b, 2e-2, "clip_grad_norm")
+    _tight(c, b, 2e-2, "max_grad_norm")
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_reduce_with_fp16_loss_scaling_and_an_overflow(tmp_path):
+    """fp16 with the dynamic loss scale on the fused path; in step 1 an absurd loss scale set on the host makes
+    the gradients overflow: every rank must skip that step and lower the scale, like the NCCL path does."""
+    case = {"opt": "sgd", "layers": 2, "iters": 4, "fp16": True, "inject_inf": 1}
+    a = _run(2, dict(case, out=str(tmp_path / "a.pt")))
+    b = _run(2, dict(case, out=str(tmp_path / "b.pt")), {"RANNC_FUSED_GRAD_ALLREDUCE": "false"})
+    assert all(i["fused"] and i["err"] == 0 for i in a["infos"])
+    assert all(i["skipped"] == [True] for i in a["infos"] + b["infos"]), (a["infos"], b["infos"])
+    assert a["infos"][0]["scale"] == b["infos"][0]["scale"] and a["infos"][1]["scale"] == b["infos"][0]["scale"]
+    _tight(a, b, 3e-2, "fp16")
+
+
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_load_state_dict_into_a_deployed_module_on_the_fused_path(tmp_path):
     res = _run(2, {"out": str(tmp_path / "r.pt"), "reload": True})
