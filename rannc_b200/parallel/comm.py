@@ -50,6 +50,9 @@ class _State:
         self.cpu_group = None
         self.watchdog = None
         self.failed_peer = -1
+        self.p2p_stream = None
+        self.inject_failures = 0     # test hook: the next N guarded collectives raise on the host
+        self.retries_done = 0
 
 
 _S = _State()
@@ -242,41 +245,104 @@ def bcast_bytes(data: bytes, root: int = 0) -> bytes:
     return bcast_obj(data, root)
 
 
+# ---------------------------------------------------------------- failure handling
+def inject_collective_failures(n: int) -> None:
+    """Test hook: the next ``n`` guarded collectives of this process raise before anything is issued (a failure
+    made on the host, as a transport error would surface)."""
+    _S.inject_failures = int(n)
+
+
+def retries_done() -> int:
+    return _S.retries_done
+
+
+def _with_retry(what: str, fn):
+    """Runs a collective; when it raises (a transport error, an aborted communicator, a process-group timeout)
+    every communicator is re-created and the call is tried again, ``comm_retry`` times, before ``CommError`` is
+    raised (reference: commWithRetry / recreateAllCommunicators, src/comm/NCCLWrapper.cpp:667-739).  All ranks
+    of the collective see the failure (a failed rank makes the others' call fail or time out), so all of them
+    take part in the re-creation."""
+    attempts = max(0, int(conf("comm_retry")))
+    for attempt in range(attempts + 1):
+        try:
+            if _S.inject_failures > 0:
+                _S.inject_failures -= 1
+                raise RuntimeError(f"injected failure in {what}")
+            return fn()
+        except CommError:
+            raise
+        except (RuntimeError, ValueError) as e:
+            if attempt >= attempts:
+                raise CommError(f"{what} failed after {attempt} retr{'y' if attempt == 1 else 'ies'}: {e}") from e
+            logger.warning("%s failed (%s); re-creating the communicators and retrying", what, str(e)[:200])
+            import time
+
+            time.sleep(float(conf("comm_retry_wait_s")))
+            recreate_all_communicators()
+            _S.retries_done += 1
+
+
+def sync_with_error_check(timeout_s: float = 0.0) -> None:
+    """Waits for the work enqueued so far WITHOUT blocking inside the driver: polls an event and, while it is
+    not complete, looks for a failed peer (heartbeat watchdog), so that a rank whose peer died raises instead
+    of hanging in a synchronise (reference: syncWithErrorCheck, src/comm/NCCLWrapper.cpp:575-622, which polls
+    cudaStreamQuery and ncclCommGetAsyncError; here torch's own NCCL watchdog turns an asynchronous NCCL error
+    into an exception of the next call, which ``_with_retry`` handles)."""
+    import time
+
+    check_peers()
+    if not is_cuda():
+        return
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream())
+    t0 = time.monotonic()
+    limit = timeout_s if timeout_s > 0 else float(conf("comm_timeout_s"))
+    while not ev.query():
+        check_peers()
+        if time.monotonic() - t0 > limit:
+            raise CommError(f"work on the device did not finish within {limit:.0f} s")
+        time.sleep(0.0005)
+
+
 # ---------------------------------------------------------------- tensors
 def allreduce(t: torch.Tensor, op: str = "sum", ranks: Optional[Sequence[int]] = None, async_op: bool = False):
     if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
         return None
     rop = {"sum": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op]
-    return dist.all_reduce(t, op=rop, group=group(ranks), async_op=async_op)
+    return _with_retry("all-reduce", lambda: dist.all_reduce(t, op=rop, group=group(ranks), async_op=async_op))
 
 
 def bcast(t: torch.Tensor, root: int, ranks: Optional[Sequence[int]] = None) -> None:
     if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
         return
-    dist.broadcast(t, src=root, group=group(ranks))
+    _with_retry("broadcast", lambda: dist.broadcast(t, src=root, group=group(ranks)))
 
 
 def allgather_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Sequence[int]] = None) -> None:
     if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
         out.view(-1)[: inp.numel()].copy_(inp.view(-1))
         return
-    dist.all_gather_into_tensor(out, inp, group=group(ranks))
+    _with_retry("all-gather", lambda: dist.all_gather_into_tensor(out, inp, group=group(ranks)))
 
 
 def reduce_scatter_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Sequence[int]] = None) -> None:
     if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
         out.copy_(inp.view(-1)[: out.numel()].view_as(out))
         return
-    g = group(ranks)
     if _S.backend == "gloo":
         # gloo has no reduce-scatter: all-reduce a copy and keep this rank's piece (CPU rank harness only)
-        full = inp.clone()
-        dist.all_reduce(full, op=dist.ReduceOp.SUM, group=g)
-        n = out.numel()
-        i = dist.get_rank(g)
-        out.copy_(full.view(-1)[i * n:(i + 1) * n].view_as(out))
+        def via_allreduce():
+            g = group(ranks)
+            full = inp.clone()
+            dist.all_reduce(full, op=dist.ReduceOp.SUM, group=g)
+            n = out.numel()
+            i = dist.get_rank(g)
+            out.copy_(full.view(-1)[i * n:(i + 1) * n].view_as(out))
+
+        _with_retry("reduce-scatter", via_allreduce)
         return
-    dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=g)
+    _with_retry("reduce-scatter",
+                lambda: dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=group(ranks)))
 
 
 def send_recv(t: Optional[torch.Tensor], src: int, dst: int) -> None:
@@ -296,10 +362,16 @@ class PendingOps:
     def __init__(self):
         self.reqs = []
         self.keep = []
+        self.events = []      # completion events of sends issued from the transfer stream
 
     def wait(self):
         for r in self.reqs:
             r.wait()
+        if self.events:
+            cur = torch.cuda.current_stream()
+            for ev in self.events:
+                cur.wait_event(ev)
+            self.events.clear()
         self.reqs.clear()
         self.keep.clear()
 
@@ -334,6 +406,9 @@ def redist(src_rows: Optional[torch.Tensor], args, recv_rows: int, like: Optiona
             ops.append(dist.P2POp(dist.irecv, wire(out[args.rdispls[r]: args.rdispls[r] + rc]), r))
             is_send.append(False)
     if ops:
+        if is_cuda():
+            _redist_on_side_stream(ops, is_send, out, pending)
+            return out
         reqs = dist.batch_isend_irecv(ops)
         if pending is not None and len(reqs) == len(ops):
             # one request per operation (gloo): receives are needed now, sends may finish later
@@ -343,7 +418,40 @@ def redist(src_rows: Optional[torch.Tensor], args, recv_rows: int, like: Optiona
                 else:
                     q.wait()
         else:
-            # one coalesced request (NCCL): waiting only orders the current stream after it
             for q in reqs:
                 q.wait()
     return out
+
+
+def p2p_stream() -> "torch.cuda.Stream":
+    """The stream pipeline transfers are issued from (one per process)."""
+    if getattr(_S, "p2p_stream", None) is None:
+        _S.p2p_stream = torch.cuda.Stream(device=_S.device)
+    return _S.p2p_stream
+
+
+def _redist_on_side_stream(ops, is_send, out, pending) -> None:
+    """NCCL send / recv of one route, issued from a dedicated stream: the transfer starts once the data is ready
+    on the compute stream (an event), and the compute stream waits only when this rank RECEIVES something -- a
+    stage that has sent its outputs goes straight on with the next micro-batch, whether or not the receiver has
+    posted its receive yet.  (The reference orders sends behind a delay for the same purpose:
+    src/comp/GraphConnector.cpp:53-96,363-374; its NCCL p2p runs on the compute stream,
+    src/comm/NCCLWrapper.cpp:501-533.)"""
+    cur = torch.cuda.current_stream()
+    side = p2p_stream()
+    ready = torch.cuda.Event()
+    ready.record(cur)
+    for op in ops:
+        # the tensors were allocated on the compute stream and are used on the side stream
+        op.tensor.record_stream(side)
+    with torch.cuda.stream(side):
+        side.wait_event(ready)
+        reqs = dist.batch_isend_irecv(ops)
+        for q in reqs:
+            q.wait()          # orders the side stream behind NCCL's own stream; the host does not block
+        done = torch.cuda.Event()
+        done.record(side)
+    if not all(is_send):
+        cur.wait_event(done)
+    elif pending is not None:
+        pending.events.append(done)

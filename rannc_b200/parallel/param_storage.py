@@ -353,7 +353,7 @@ class ParamStorage:
         """``sync_allreduce``: the host waits for the reduction before it launches anything else (debugging aid;
         reference: ParamStorage.cpp, syncStream after the all-reduce)."""
         if bool(conf("sync_allreduce")) and comm.is_cuda():
-            torch.cuda.synchronize()
+            comm.sync_with_error_check()
 
     def allgather_params_zero(self, only=None):
         """Refreshes the full 16-bit parameters from the updated slices (reference: ParamStorage.cpp:559-596)."""

@@ -232,3 +232,21 @@ def test_peer_failure_is_detected_on_the_host(tmp_path):
     outs = [p.communicate(timeout=180)[0] for p in procs]
     assert "LEFT" in outs[1], outs[1][-2000:]
     assert "DETECTED" in outs[0] and "NOT DETECTED" not in outs[0], outs[0][-2000:]
+
+
+def test_failed_collective_is_retried_after_recreating_the_communicators():
+    """A collective that raises on the host (failure injected before anything is issued) is followed by
+    re-creation of every communicator and one retry; training continues with unchanged numbers, and a failure
+    that persists beyond the configured retries surfaces as CommError."""
+    port = _free_port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ)
+        env.update({"RANK": str(r), "WORLD_SIZE": "2", "LOCAL_RANK": str(r), "MASTER_ADDR": "127.0.0.1",
+                    "MASTER_PORT": str(port), "RANNC_FORCE_CPU": "1", "OMP_NUM_THREADS": "1",
+                    "RANNC_LOG_LEVEL": "error", "RANNC_COMM_RETRY": "1", "RANNC_COMM_RETRY_WAIT_S": "0.05"})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "retry_worker.py")], env=env,
+                                      cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    for o in outs:
+        assert "RETRY_OK" in o, o[-3000:]
