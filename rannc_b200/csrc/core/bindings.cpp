@@ -200,6 +200,8 @@ PYBIND11_MODULE(_core, m) {
         .def_readwrite("name", &GraphProfile::name)
         .def_readwrite("fwd_time", &GraphProfile::fwd_time)
         .def_readwrite("bwd_time", &GraphProfile::bwd_time)
+        .def_readwrite("fwd_cpu_time", &GraphProfile::fwd_cpu_time)
+        .def_readwrite("bwd_cpu_time", &GraphProfile::bwd_cpu_time)
         .def_readwrite("fwd_cuda_time", &GraphProfile::fwd_cuda_time)
         .def_readwrite("bwd_cuda_time", &GraphProfile::bwd_cuda_time)
         .def_readwrite("max_allocated_mem", &GraphProfile::max_allocated_mem)
@@ -265,7 +267,22 @@ PYBIND11_MODULE(_core, m) {
         .def_readwrite("link", &PartitioningConf::link);
     py::class_<ProfileModel>(m, "ProfileModel")
         .def(py::init<const IRGraph&, std::unordered_map<std::string, NodeProfile>, LinkModel>())
-        .def("profile", &ProfileModel::profile);
+        .def("profile", &ProfileModel::profile)
+        .def("set_subgraph_measure",
+             [](ProfileModel& pm, py::function fn, int limit) {
+                 // fn(node_ids, batch, checkpointing) -> GraphProfile or None; may be called from the stage
+                 // search, which runs without the interpreter lock
+                 pm.setSubgraphMeasure(
+                     [fn](const std::vector<std::string>& ids, int64_t bs, bool ckpt, GraphProfile* out) {
+                         py::gil_scoped_acquire gil;
+                         py::object r = fn(ids, bs, ckpt);
+                         if (r.is_none()) return false;
+                         *out = r.cast<GraphProfile>();
+                         return true;
+                     },
+                     limit);
+             })
+        .def("measured_count", &ProfileModel::measuredCount);
     m.def("calc_comm_time", &calcCommTime);
     m.def("calc_allreduce_time", &calcAllReduceTime);
     m.def("get_opt_mem_size", &getOptMemSize);
@@ -302,18 +319,31 @@ PYBIND11_MODULE(_core, m) {
     py::class_<MLNode>(m, "MLNode")
         .def_readonly("id", &MLNode::id)
         .def_readonly("graph", &MLNode::graph)
-        .def_readonly("sub_nodes", &MLNode::sub_nodes);
+        .def_readonly("sub_nodes", &MLNode::sub_nodes)
+        .def_readonly("children", &MLNode::children)
+        .def_readonly("level", &MLNode::level);
     py::class_<MLEdge>(m, "MLEdge").def_readonly("src_id", &MLEdge::src_id).def_readonly("tgt_id", &MLEdge::tgt_id);
     py::class_<MLGraph>(m, "MLGraph")
         .def(py::init<>())
         .def_readonly("nodes", &MLGraph::nodes)
         .def_readonly("edges", &MLGraph::edges)
+        .def("level", &MLGraph::level)
         .def("dumps", [](const MLGraph& g) { return py::bytes(mp::pack(g.pack())); })
         .def_static("loads", [](const std::string& d) { return MLGraph::unpack(mp::unpack(d)); });
     m.def("ml_partition", [](const ProfileModel& pm, const PartitioningConf& conf) {
         MLPartitioner p(pm, conf);
         return p.partition();
     });
+    // the same, with what the passes did: (graph, coarsening levels, boundary moves, cut bytes before / after
+    // the uncoarsening)
+    m.def("ml_partition_stats", [](const ProfileModel& pm, const PartitioningConf& conf) {
+        MLPartitioner p(pm, conf);
+        MLGraph g = p.partition();
+        return py::make_tuple(g, p.levels(), p.moves(), p.cutBefore(), p.cutAfter());
+    });
+    m.def("ml_to_lower_level", &toLowerLevel);
+    m.def("ml_lift_up", &liftUp);
+    m.def("ml_cut_bytes", &cutBytes);
     py::class_<AllocSolution>(m, "AllocSolution")
         .def(py::init<>())
         .def_readwrite("graphs", &AllocSolution::graphs)

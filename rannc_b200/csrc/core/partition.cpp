@@ -4,6 +4,7 @@
 #include <cmath>
 #include <functional>
 #include <limits>
+#include <map>
 #include <numeric>
 #include <queue>
 #include <set>
@@ -32,18 +33,47 @@ MLEdge MLEdge::unpack(const mp::Value& v) {
     return e;
 }
 mp::Value MLNode::pack() const {
-    // field order: id, graph, sub_nodes, sub_edges (reference: MLGraph.h:14-39); lower levels are
-    // recorded by id only
-    return mp::Value::array({mp::Value::str(id), graph.pack(), packStrings(sub_nodes), mp::Value::array({})});
+    // field order: id, graph, sub_nodes, sub_edges (reference: MLGraph.h:14-39).  sub_nodes holds the nodes of
+    // the level below as nested records; an atomic block lists the ids of its operators instead.
+    mp::Value subs;
+    if (!children.empty()) {
+        mp::Array cs;
+        for (const auto& c : children) cs.push_back(c.pack());
+        subs = mp::Value::array(std::move(cs));
+    } else {
+        subs = packStrings(sub_nodes);
+    }
+    return mp::Value::array({mp::Value::str(id), graph.pack(), std::move(subs), mp::Value::array({})});
 }
+namespace {
+void collectOps(const MLNode& n, std::vector<std::string>* out) {
+    if (n.children.empty()) {
+        out->insert(out->end(), n.sub_nodes.begin(), n.sub_nodes.end());
+        return;
+    }
+    for (const auto& c : n.children) collectOps(c, out);
+}
+}  // namespace
 MLNode MLNode::unpack(const mp::Value& v) {
     MLNode n;
     n.id = v.at(0).as_str();
     n.graph = IRGraph::unpack(v.at(1));
     const mp::Value& sn = v.at(2);
-    for (const auto& s : sn.as_array())
-        if (s.kind == mp::Value::STR) n.sub_nodes.push_back(s.as_str());
+    for (const auto& s : sn.as_array()) {
+        if (s.kind == mp::Value::STR) {
+            n.sub_nodes.push_back(s.as_str());
+        } else {
+            n.children.push_back(MLNode::unpack(s));
+            n.level = std::max(n.level, n.children.back().level + 1);
+        }
+    }
+    if (!n.children.empty()) collectOps(n, &n.sub_nodes);
     return n;
+}
+int MLGraph::level() const {
+    int l = 0;
+    for (const auto& n : nodes) l = std::max(l, n.level);
+    return l;
 }
 mp::Value MLGraph::pack() const {
     mp::Array ns, es;
@@ -319,6 +349,71 @@ std::vector<int> topoOrder(const BlockGraph& bg) {
 
 }  // namespace
 
+namespace {
+
+// Skeleton of the multi-level hierarchy: which blocks of the level below a block was merged from.
+struct Skel {
+    int level = 0;
+    std::vector<int> own;        // operator indices (sorted)
+    std::vector<Skel> kids;
+};
+
+using Adj = std::vector<std::unordered_map<int, int64_t>>;
+
+// Group-level adjacency (bytes of the values that go from group a to group b) for a node -> group labelling.
+void buildAdjacency(const GraphIndex& idx, const std::vector<int>& group_of, int ngroups, double ratio, Adj* succ,
+                    Adj* pred) {
+    const IRGraph& g = idx.g;
+    succ->assign(ngroups, {});
+    pred->assign(ngroups, {});
+    for (size_t i = 0; i < g.nodes.size(); ++i) {
+        if (!idx.owned_kind[i] || group_of[i] < 0) continue;
+        for (const auto& o : g.nodes[i].output_names) {
+            auto cit = idx.consumer.find(o);
+            if (cit == idx.consumer.end()) continue;
+            const int64_t bytes = static_cast<int64_t>(g.value(o).type.sizeInByte() * ratio);
+            std::set<int> targets;
+            for (size_t c : cit->second) {
+                if (idx.owned_kind[c]) targets.insert(group_of[c]);
+                else
+                    for (int d : idx.dependants[c]) targets.insert(group_of[d]);
+            }
+            for (int t : targets) {
+                if (t < 0 || t == group_of[i]) continue;
+                (*succ)[group_of[i]][t] += bytes;
+                (*pred)[t][group_of[i]] += bytes;
+            }
+        }
+    }
+}
+
+bool reaches(const Adj& succ, int from, int to) {
+    if (from == to) return true;
+    std::vector<int> stack{from};
+    std::unordered_set<int> seen;
+    while (!stack.empty()) {
+        const int v = stack.back();
+        stack.pop_back();
+        if (v == to) return true;
+        if (!seen.insert(v).second) continue;
+        for (const auto& kv : succ[v]) stack.push_back(kv.first);
+    }
+    return false;
+}
+
+MLNode skelToNode(const GraphIndex& idx, const Skel& s, const std::string& id, bool with_graph, bool last) {
+    MLNode n;
+    n.id = id;
+    n.level = s.level;
+    if (with_graph) n.graph = idx.extract(s.own, id, last);
+    for (int i : s.own) n.sub_nodes.push_back(idx.g.nodes[i].id);
+    for (size_t k = 0; k < s.kids.size(); ++k)
+        n.children.push_back(skelToNode(idx, s.kids[k], id + "_" + std::to_string(k), false, false));
+    return n;
+}
+
+}  // namespace
+
 MLGraph MLPartitioner::partition() {
     const IRGraph& g = pm_.graph();
     GraphIndex idx(g);
@@ -330,46 +425,44 @@ MLGraph MLPartitioner::partition() {
     const int64_t plan_bs =
         std::max<int64_t>(1, conf_.batch_size / std::max(1, conf_.dev_num) / std::max(1, conf_.max_pipeline));
     const double ratio = static_cast<double>(plan_bs) / std::max<int64_t>(1, g.batch_size);
+    std::vector<double> node_time(n, 0.0);
+    std::vector<int64_t> node_mem(n, 0);
     for (int i = 0; i < n; ++i) {
         if (!idx.owned_kind[i]) continue;
         Block b;
         b.own = {i};
         const NodeProfile* np = pm_.nodeProfile(g.nodes[i].id);
         if (np) {
-            b.eval = (np->fwd_us + np->bwd_us) * (np->scales_with_batch ? ratio : 1.0);
+            node_time[i] = (np->fwd_us + np->bwd_us) * (np->scales_with_batch ? ratio : 1.0);
             b.mem = static_cast<int64_t>(np->activation_bytes * ratio);
         }
         for (const auto& in : g.nodes[i].input_names)
             if (g.hasValue(in) && g.value(in).is_param) b.mem += g.value(in).type.sizeInByte();
+        node_mem[i] = b.mem;
+        // what a block is weighed by: its time, or (coarsen_by_time = false) the memory it needs
+        // (reference: Partitioner.cpp:44-55)
+        b.eval = conf_.coarsen_by_time ? node_time[i] : static_cast<double>(b.mem);
         bg.block_of[i] = static_cast<int>(bg.blocks.size());
         bg.blocks.push_back(std::move(b));
     }
     const int nb = static_cast<int>(bg.blocks.size());
-    bg.succ.assign(nb, {});
-    bg.pred.assign(nb, {});
-    auto addEdge = [&](int pa, int pb, int64_t bytes) {
-        if (pa == pb || pa < 0 || pb < 0) return;
-        bg.succ[pa][pb] += bytes;
-        bg.pred[pb][pa] += bytes;
-    };
-    for (int i = 0; i < n; ++i) {
-        if (!idx.owned_kind[i]) continue;
-        for (const auto& o : g.nodes[i].output_names) {
-            auto cit = idx.consumer.find(o);
-            if (cit == idx.consumer.end()) continue;
-            const int64_t bytes = static_cast<int64_t>(g.value(o).type.sizeInByte() * ratio);
-            std::set<int> targets;
-            for (size_t c : cit->second) {
-                if (idx.owned_kind[c]) targets.insert(bg.block_of[c]);
-                else
-                    for (int d : idx.dependants[c]) targets.insert(bg.block_of[d]);
-            }
-            for (int t : targets) addEdge(bg.block_of[i], t, bytes);
-        }
-    }
+    buildAdjacency(idx, bg.block_of, nb, ratio, &bg.succ, &bg.pred);
+    std::vector<Skel> skel(nb);
+    for (int b = 0; b < nb; ++b) skel[b].own = bg.blocks[b].own;
 
     const int min_parts = std::max(1, std::min(conf_.max_partition_num,
                                                std::max(conf_.min_partition_num, 2 * conf_.dev_num)));
+    auto mergeSkel = [&](int a, int b, int level) {
+        Skel m;
+        m.level = level;
+        m.kids.push_back(std::move(skel[a]));
+        m.kids.push_back(std::move(skel[b]));
+        m.own = m.kids[0].own;
+        m.own.insert(m.own.end(), m.kids[1].own.begin(), m.kids[1].own.end());
+        std::sort(m.own.begin(), m.own.end());
+        skel[a] = std::move(m);
+        skel[b] = Skel{};
+    };
     levels_ = 0;
     if (conf_.do_coarsening) {
         int last = -1;
@@ -405,7 +498,20 @@ MLGraph MLPartitioner::partition() {
                     if (order.size() > 8 && merged_eval > mean + 2 * sigma && merged_eval > 2.5 * mean) continue;
                     if (conf_.dev_mem > 0 && bg.blocks[v].mem + bg.blocks[adj].mem > conf_.dev_mem) continue;
                     if (reachableWithout(bg, v, adj)) continue;  // merge would not be convex
-                    const double imprv = calcCommTime(pm_.link(), kv.second);
+                    // gain of the merge = t(v) + t(adj) + comm(v -> adj) - t(merged)
+                    // (reference: Partitioner.cpp:90-238).  The merged time comes from a measurement of the
+                    // merged subgraph when the profile model has one (measured subgraph profiles), and is
+                    // the sum of the two otherwise, which leaves the saved transfer as the gain.
+                    double imprv = calcCommTime(pm_.link(), kv.second);
+                    if (conf_.coarsen_by_time) {
+                        std::vector<int> both = bg.blocks[v].own;
+                        both.insert(both.end(), bg.blocks[adj].own.begin(), bg.blocks[adj].own.end());
+                        std::vector<std::string> ids;
+                        for (int i : both) ids.push_back(g.nodes[i].id);
+                        double t_merged = 0;
+                        if (pm_.measuredSubgraphTime(ids, plan_bs, &t_merged))
+                            imprv += merged_eval - t_merged;
+                    }
                     if (imprv > best_imprv) {
                         best_imprv = imprv;
                         best = adj;
@@ -414,11 +520,188 @@ MLGraph MLPartitioner::partition() {
                 if (best >= 0) {
                     matched[v] = matched[best] = true;
                     mergeInto(bg, v, best);
+                    mergeSkel(v, best, levels_ + 1);
                     --remaining;
                 }
             }
             ++levels_;
         }
+    }
+
+    // uncoarsening: walk the hierarchy back down; at every level the blocks of the level below that sit at a
+    // boundary may change sides when that shrinks the cut and keeps the block sizes in bounds
+    // (reference: uncoarsen / adjustBoundaries, Partitioner.cpp:511-771)
+    moves_ = 0;
+    cut_before_ = cut_after_ = 0;
+    for (int b = 0; b < nb; ++b)
+        if (bg.blocks[b].alive)
+            for (const auto& kv : bg.succ[b]) cut_before_ += kv.second;
+    cut_after_ = cut_before_;
+    if (conf_.do_uncoarsening && conf_.do_coarsening && levels_ > 0) {
+        // parts = the alive blocks; units = pieces of the hierarchy, refined level by level
+        std::vector<int> part_ids;
+        for (int b = 0; b < nb; ++b)
+            if (bg.blocks[b].alive) part_ids.push_back(b);
+        struct Unit {
+            Skel skel;
+            int part;
+        };
+        std::vector<Unit> units;
+        for (int b : part_ids) {
+            if (skel[b].kids.empty()) units.push_back({skel[b], b});
+            else
+                for (auto& k : skel[b].kids) units.push_back({k, b});
+        }
+        auto unitEval = [&](const Skel& s) {
+            double e = 0;
+            for (int i : s.own) e += conf_.coarsen_by_time ? node_time[i] : static_cast<double>(node_mem[i]);
+            return e;
+        };
+        auto unitMem = [&](const Skel& s) {
+            int64_t m = 0;
+            for (int i : s.own) m += node_mem[i];
+            return m;
+        };
+        for (int level = levels_; level >= 1; --level) {
+            for (int pass = 0; pass < 2; ++pass) {
+                int moved_this_pass = 0;
+                const int nu = static_cast<int>(units.size());
+                std::vector<int> unit_of(n, -1), part_of_node(n, -1);
+                for (int u = 0; u < nu; ++u)
+                    for (int i : units[u].skel.own) {
+                        unit_of[i] = u;
+                        part_of_node[i] = units[u].part;
+                    }
+                Adj usucc, upred, psucc, ppred;
+                buildAdjacency(idx, unit_of, nu, ratio, &usucc, &upred);
+                buildAdjacency(idx, part_of_node, nb, ratio, &psucc, &ppred);
+                std::vector<double> part_eval(nb, 0.0);
+                std::vector<int64_t> part_mem(nb, 0);
+                std::vector<int> part_units(nb, 0);
+                for (int u = 0; u < nu; ++u) {
+                    part_eval[units[u].part] += unitEval(units[u].skel);
+                    part_mem[units[u].part] += unitMem(units[u].skel);
+                    part_units[units[u].part] += 1;
+                }
+                double sum = 0, sq = 0, mx = 0;
+                for (int b : part_ids) {
+                    sum += part_eval[b];
+                    mx = std::max(mx, part_eval[b]);
+                }
+                const double mean = sum / part_ids.size();
+                for (int b : part_ids) sq += (part_eval[b] - mean) * (part_eval[b] - mean);
+                const double limit = std::max(mx, mean + 2 * std::sqrt(sq / part_ids.size()));
+                for (int u = 0; u < nu; ++u) {
+                    const int A = units[u].part;
+                    if (part_units[A] < 2) continue;
+                    bool succ_in_A = false, pred_in_A = false;
+                    std::unordered_map<int, int64_t> to_part, from_part;
+                    for (const auto& kv : usucc[u]) {
+                        if (units[kv.first].part == A) succ_in_A = true;
+                        else to_part[units[kv.first].part] += kv.second;
+                    }
+                    int64_t from_A = 0, to_A = 0;
+                    for (const auto& kv : upred[u]) {
+                        if (units[kv.first].part == A) {
+                            pred_in_A = true;
+                            from_A += kv.second;
+                        } else {
+                            from_part[units[kv.first].part] += kv.second;
+                        }
+                    }
+                    for (const auto& kv : usucc[u])
+                        if (units[kv.first].part == A) to_A += kv.second;
+                    const double ue = unitEval(units[u].skel);
+                    const int64_t um = unitMem(units[u].skel);
+                    int best = -1;
+                    int64_t best_gain = 0;
+                    auto fits = [&](int B) {
+                        if (part_eval[B] + ue > limit) return false;
+                        if (conf_.dev_mem > 0 && part_mem[B] + um > conf_.dev_mem) return false;
+                        return true;
+                    };
+                    if (!succ_in_A) {
+                        // a sink of its part: may move forward into a part it feeds
+                        for (const auto& kv : to_part) {
+                            const int B = kv.first;
+                            if (!fits(B)) continue;
+                            bool cyc = false;
+                            for (const auto& o : to_part)
+                                if (o.first != B && reaches(psucc, o.first, B)) cyc = true;
+                            if (cyc) continue;
+                            const int64_t gain = kv.second - from_A;
+                            if (gain > best_gain) {
+                                best_gain = gain;
+                                best = B;
+                            }
+                        }
+                    }
+                    if (!pred_in_A) {
+                        // a source of its part: may move backward into a part that feeds it
+                        for (const auto& kv : from_part) {
+                            const int B = kv.first;
+                            if (!fits(B)) continue;
+                            bool cyc = false;
+                            for (const auto& o : from_part)
+                                if (o.first != B && reaches(psucc, B, o.first)) cyc = true;
+                            if (cyc) continue;
+                            const int64_t gain = kv.second - to_A;
+                            if (gain > best_gain) {
+                                best_gain = gain;
+                                best = B;
+                            }
+                        }
+                    }
+                    if (best < 0) continue;
+                    units[u].part = best;
+                    part_eval[A] -= ue;
+                    part_eval[best] += ue;
+                    part_mem[A] -= um;
+                    part_mem[best] += um;
+                    part_units[A] -= 1;
+                    part_units[best] += 1;
+                    for (int i : units[u].skel.own) part_of_node[i] = best;
+                    buildAdjacency(idx, part_of_node, nb, ratio, &psucc, &ppred);
+                    ++moves_;
+                    ++moved_this_pass;
+                }
+                if (!moved_this_pass) break;
+            }
+            if (level > 1) {
+                // one level down: every unit is replaced by the blocks it was merged from
+                std::vector<Unit> lower;
+                for (auto& u : units) {
+                    if (u.skel.kids.empty()) lower.push_back(std::move(u));
+                    else
+                        for (auto& k : u.skel.kids) lower.push_back({k, u.part});
+                }
+                units = std::move(lower);
+            }
+        }
+        // rebuild the blocks from the final assignment
+        for (int b : part_ids) {
+            bg.blocks[b].own.clear();
+            bg.blocks[b].eval = 0;
+            bg.blocks[b].mem = 0;
+            skel[b] = Skel{};
+            skel[b].level = levels_;
+        }
+        for (auto& u : units) {
+            Block& B = bg.blocks[u.part];
+            B.own.insert(B.own.end(), u.skel.own.begin(), u.skel.own.end());
+            B.eval += unitEval(u.skel);
+            B.mem += unitMem(u.skel);
+            skel[u.part].kids.push_back(std::move(u.skel));
+        }
+        for (int b : part_ids) {
+            std::sort(bg.blocks[b].own.begin(), bg.blocks[b].own.end());
+            skel[b].own = bg.blocks[b].own;
+            for (int i : bg.blocks[b].own) bg.block_of[i] = b;
+        }
+        buildAdjacency(idx, bg.block_of, nb, ratio, &bg.succ, &bg.pred);
+        cut_after_ = 0;
+        for (int b : part_ids)
+            for (const auto& kv : bg.succ[b]) cut_after_ += kv.second;
     }
 
     // mergeSmall: cheapest block joins its cheaper convex neighbour until <= max_partition_num
@@ -450,8 +733,13 @@ MLGraph MLPartitioner::partition() {
             best = other;
             best_is_succ = true;
         }
-        if (best_is_succ) mergeInto(bg, cheapest, best);
-        else mergeInto(bg, best, cheapest);
+        if (best_is_succ) {
+            mergeInto(bg, cheapest, best);
+            mergeSkel(cheapest, best, std::max(skel[cheapest].level, skel[best].level) + 1);
+        } else {
+            mergeInto(bg, best, cheapest);
+            mergeSkel(best, cheapest, std::max(skel[cheapest].level, skel[best].level) + 1);
+        }
     }
 
     // emit in topological order (reference: sortMLGraph)
@@ -460,11 +748,8 @@ MLGraph MLPartitioner::partition() {
     std::unordered_map<int, std::string> id_of;
     for (size_t k = 0; k < order.size(); ++k) id_of[order[k]] = "ML_" + std::to_string(k);
     for (size_t k = 0; k < order.size(); ++k) {
-        MLNode node;
-        node.id = id_of[order[k]];
-        node.graph = idx.extract(bg.blocks[order[k]].own, node.id, k + 1 == order.size());
-        for (int i : bg.blocks[order[k]].own) node.sub_nodes.push_back(g.nodes[i].id);
-        out.nodes.push_back(std::move(node));
+        skel[order[k]].own = bg.blocks[order[k]].own;
+        out.nodes.push_back(skelToNode(idx, skel[order[k]], id_of[order[k]], true, k + 1 == order.size()));
     }
     for (int b : order) {
         for (const auto& kv : bg.succ[b]) {
@@ -489,6 +774,101 @@ MLGraph MLPartitioner::partition() {
         }
     }
     return out;
+}
+
+namespace {
+// edges (with value-level base edges) of an ML graph whose nodes carry operator ids
+void rebuildEdges(const IRGraph& g, MLGraph* ml) {
+    GraphIndex idx(g);
+    std::unordered_map<std::string, int> pos;
+    for (size_t i = 0; i < g.nodes.size(); ++i) pos[g.nodes[i].id] = static_cast<int>(i);
+    std::vector<int> group_of(g.nodes.size(), -1);
+    for (size_t k = 0; k < ml->nodes.size(); ++k)
+        for (const auto& id : ml->nodes[k].sub_nodes) {
+            auto it = pos.find(id);
+            if (it != pos.end() && idx.owned_kind[it->second]) group_of[it->second] = static_cast<int>(k);
+        }
+    ml->edges.clear();
+    std::unordered_map<std::string, int> producer_node;
+    for (size_t k = 0; k < ml->nodes.size(); ++k)
+        for (const auto& o : ml->nodes[k].graph.output_names) producer_node[o] = static_cast<int>(k);
+    std::map<std::pair<int, int>, std::vector<std::string>> found;
+    for (size_t k = 0; k < ml->nodes.size(); ++k)
+        for (const auto& in : ml->nodes[k].graph.input_names) {
+            auto it = producer_node.find(in);
+            if (it != producer_node.end() && it->second != static_cast<int>(k))
+                found[{it->second, static_cast<int>(k)}].push_back(in);
+        }
+    for (const auto& kv : found) {
+        MLEdge e;
+        e.src_id = ml->nodes[kv.first.first].id;
+        e.tgt_id = ml->nodes[kv.first.second].id;
+        for (const auto& v : kv.second) e.base_edges.push_back({e.src_id, e.tgt_id, v});
+        ml->edges.push_back(std::move(e));
+    }
+}
+
+std::vector<int> opsOf(const IRGraph& g, const GraphIndex& idx, const MLNode& n) {
+    std::unordered_map<std::string, int> pos;
+    for (size_t i = 0; i < g.nodes.size(); ++i) pos[g.nodes[i].id] = static_cast<int>(i);
+    std::vector<int> own;
+    for (const auto& id : n.sub_nodes) {
+        auto it = pos.find(id);
+        if (it != pos.end() && idx.owned_kind[it->second]) own.push_back(it->second);
+    }
+    std::sort(own.begin(), own.end());
+    return own;
+}
+}  // namespace
+
+MLGraph toLowerLevel(const IRGraph& g, const MLGraph& ml) {
+    GraphIndex idx(g);
+    MLGraph out;
+    for (const auto& node : ml.nodes) {
+        if (node.children.empty()) {
+            out.nodes.push_back(node);
+            continue;
+        }
+        for (const auto& c : node.children) out.nodes.push_back(c);
+    }
+    for (size_t k = 0; k < out.nodes.size(); ++k)
+        out.nodes[k].graph = idx.extract(opsOf(g, idx, out.nodes[k]), out.nodes[k].id, false);
+    rebuildEdges(g, &out);
+    return out;
+}
+
+MLGraph liftUp(const IRGraph& g, const MLGraph& ml, const std::vector<std::vector<int>>& groups) {
+    GraphIndex idx(g);
+    std::vector<bool> used(ml.nodes.size(), false);
+    MLGraph out;
+    for (size_t k = 0; k < groups.size(); ++k) {
+        MLNode up;
+        up.id = "ML_" + std::to_string(k);
+        for (int i : groups[k]) {
+            if (i < 0 || i >= static_cast<int>(ml.nodes.size()) || used[i])
+                throw std::invalid_argument("liftUp: the groups must partition the nodes");
+            used[i] = true;
+            MLNode child = ml.nodes[i];
+            child.graph = IRGraph{};
+            up.level = std::max(up.level, child.level + 1);
+            up.sub_nodes.insert(up.sub_nodes.end(), child.sub_nodes.begin(), child.sub_nodes.end());
+            up.children.push_back(std::move(child));
+        }
+        up.graph = idx.extract(opsOf(g, idx, up), up.id, k + 1 == groups.size());
+        out.nodes.push_back(std::move(up));
+    }
+    if (std::find(used.begin(), used.end(), false) != used.end())
+        throw std::invalid_argument("liftUp: the groups must partition the nodes");
+    rebuildEdges(g, &out);
+    return out;
+}
+
+int64_t cutBytes(const IRGraph& g, const MLGraph& ml) {
+    int64_t total = 0;
+    for (const auto& e : ml.edges)
+        for (const auto& b : e.base_edges)
+            if (g.hasValue(b.value)) total += g.value(b.value).type.sizeInByte();
+    return total;
 }
 
 // ---------------------------------------------------------------- stage search
@@ -589,14 +969,18 @@ bool DPStaging::runOnce(int S, int P, bool ckpt, AllocSolution* sol, std::vector
         ev.e.name = sg.name;
         ev.e.repl = repl;
         ev.e.micro_batch = mb;
-        ev.e.profile = pm_.profile(sg, mb, ckpt);
+        // checkpointing_no_last: the last stage keeps its activations instead of recomputing them when they
+        // fit (its backward is the first to run, so its recomputation would sit on the critical path)
+        // (reference: config item checkpointing_no_last)
+        const bool stage_ckpt = ckpt && !(conf_.checkpointing_no_last && b1 == L);
+        ev.e.profile = pm_.profile(sg, mb, stage_ckpt);
         IRGraph scaled = scaleGraph(sg, mb);
         ev.e.in_comm_us = calcCommTime(pm_.link(), scaled.inputSizeInByte());
         ev.e.out_comm_us = calcCommTime(pm_.link(), scaled.outputSizeInByte());
         ev.e.allreduce_us = calcAllReduceTime(pm_.link(), sg.paramSizeInByte(), repl);
         ev.e.opt_mem = getOptMemSize(sg, conf_, repl);
         ev.e.comm_mem = scaled.commBufSize();
-        ev.e.total_mem = calcGraphMem(scaled, ev.e.profile, conf_, repl, P, ckpt);
+        ev.e.total_mem = calcGraphMem(scaled, ev.e.profile, conf_, repl, P, stage_ckpt);
         ev.ok = conf_.dev_mem <= 0 || ev.e.total_mem < conf_.dev_mem;
         return evals.emplace(key, std::move(ev)).first->second;
     };

@@ -28,17 +28,29 @@ struct MLEdge {
 };
 struct MLNode {
     std::string id;
-    IRGraph graph;                        // operators of this node
-    std::vector<std::string> sub_nodes;   // ids of the lower-level nodes merged into it
+    IRGraph graph;                        // operators of this node (empty for the nodes of lower levels)
+    std::vector<std::string> sub_nodes;   // ids of the operators merged into it
+    std::vector<MLNode> children;         // the nodes of the level below that were merged into this one
+    int level = 0;                        // 0: an atomic block (one batch / criterion operator)
     mp::Value pack() const;
     static MLNode unpack(const mp::Value& v);
 };
 struct MLGraph {
     std::vector<MLNode> nodes;  // topological order after sortMLGraph
     std::vector<MLEdge> edges;
+    int level() const;          // the highest level among the nodes
     mp::Value pack() const;
     static MLGraph unpack(const mp::Value& v);
 };
+
+// One level down: every node is replaced by its children (a node without children stays); edges are
+// rebuilt from the operator graph `g` (reference: toLowerLevel, src/graph/MLGraph.cpp).
+MLGraph toLowerLevel(const IRGraph& g, const MLGraph& ml);
+// One level up: `groups[k]` lists the indices of the nodes of `ml` that become node k of the result, which
+// keeps them as its children (reference: liftUp, src/graph/MLGraph.cpp).  The groups must partition the nodes.
+MLGraph liftUp(const IRGraph& g, const MLGraph& ml, const std::vector<std::vector<int>>& groups);
+// Sum over the edges of the bytes of the values that cross between nodes.
+int64_t cutBytes(const IRGraph& g, const MLGraph& ml);
 
 // Cuts `g` by a node -> part label into per-part IRGraphs.  Non-batch nodes are
 // copied into every part that consumes them (reference: fixNonBatchRanks,
@@ -54,11 +66,16 @@ public:
     MLPartitioner(const ProfileModel& pm, const PartitioningConf& conf) : pm_(pm), conf_(conf) {}
     MLGraph partition();  // atomic blocks -> coarsen -> (uncoarsen) -> sort -> mergeSmall
     int levels() const { return levels_; }
+    int moves() const { return moves_; }          // boundary moves made by the uncoarsening passes
+    int64_t cutBefore() const { return cut_before_; }
+    int64_t cutAfter() const { return cut_after_; }
 
 private:
     const ProfileModel& pm_;
     PartitioningConf conf_;
     int levels_ = 0;
+    int moves_ = 0;
+    int64_t cut_before_ = 0, cut_after_ = 0;
 };
 
 // ---- stage search ---------------------------------------------------------

@@ -70,6 +70,42 @@ const NodeProfile* ProfileModel::nodeProfile(const std::string& id) const {
     return it == np_.end() ? nullptr : &it->second;
 }
 
+bool ProfileModel::measured(const std::vector<std::string>& ids, int64_t bs, bool checkpointing,
+                            GraphProfile* out) const {
+    if (!measure_ || ids.empty()) return false;
+    std::vector<std::string> sorted = ids;
+    std::sort(sorted.begin(), sorted.end());
+    std::string key = std::to_string(bs) + (checkpointing ? "|c|" : "|n|");
+    for (const auto& s : sorted) {
+        key += s;
+        key += ',';
+    }
+    auto it = measure_cache_.find(key);
+    if (it != measure_cache_.end()) {
+        if (it->second.first) *out = it->second.second;
+        return it->second.first;
+    }
+    if (measured_ >= measure_limit_) return false;
+    GraphProfile gp;
+    bool ok = false;
+    try {
+        ok = measure_(sorted, bs, checkpointing, &gp);
+    } catch (...) {
+        ok = false;
+    }
+    ++measured_;
+    measure_cache_[key] = {ok, gp};
+    if (ok) *out = gp;
+    return ok;
+}
+
+bool ProfileModel::measuredSubgraphTime(const std::vector<std::string>& ids, int64_t bs, double* us) const {
+    GraphProfile gp;
+    if (!measured(ids, bs, false, &gp)) return false;
+    *us = static_cast<double>(gp.fwd_time + gp.bwd_time);
+    return true;
+}
+
 GraphProfile ProfileModel::profile(const IRGraph& sub, int64_t bs, bool checkpointing) const {
     GraphProfile p;
     p.name = sub.name;
@@ -102,6 +138,27 @@ GraphProfile ProfileModel::profile(const IRGraph& sub, int64_t bs, bool checkpoi
     p.activation_size = static_cast<int64_t>(act);
     p.working_mem = static_cast<int64_t>(work);
     p.max_allocated_mem = p.param_size + p.input_size + p.output_size + p.activation_size + p.working_mem;
+    if (measure_) {
+        // a measurement of this very subgraph replaces the sums of operator figures: times, and the memory
+        // the allocator really needed
+        std::vector<std::string> ids;
+        for (const auto& n : sub.nodes)
+            if (n.is_batch || n.is_criterion) ids.push_back(n.id);
+        GraphProfile m;
+        if (measured(ids, bs, checkpointing, &m)) {
+            p.fwd_time = m.fwd_time;
+            p.bwd_time = m.bwd_time;
+            p.fwd_cuda_time = m.fwd_cuda_time ? m.fwd_cuda_time : m.fwd_time;
+            p.bwd_cuda_time = m.bwd_cuda_time ? m.bwd_cuda_time : m.bwd_time;
+            p.fwd_cpu_time = m.fwd_cpu_time;
+            p.bwd_cpu_time = m.bwd_cpu_time;
+            if (m.activation_size > 0) p.activation_size = m.activation_size;
+            if (m.working_mem > 0) p.working_mem = m.working_mem;
+            if (m.max_allocated_mem > 0)
+                p.max_allocated_mem = std::max<int64_t>(m.max_allocated_mem + p.param_size,
+                                                        p.param_size + p.input_size + p.output_size);
+        }
+    }
     return p;
 }
 

@@ -10,6 +10,7 @@
 // what NVLink 5 / NVSwitch delivers on an 8 x B200 box and are configurable.
 #pragma once
 #include <cstdint>
+#include <functional>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -80,10 +81,32 @@ public:
     const LinkModel& link() const { return link_; }
     const NodeProfile* nodeProfile(const std::string& id) const;
 
+    // Measurement of a whole candidate subgraph (reference: GraphProfiler::computeGraph,
+    // src/comp/GraphProfiler.cpp:245-415): given the ids of its operators, the micro-batch size and whether it
+    // recomputes, the callback runs forward + backward on the device and fills times (microseconds), the
+    // allocator peak, activation and working bytes.  It returns false when it cannot measure (no device, too
+    // large), and the additive estimate is used.  Results are cached per (operators, batch, checkpointing), at
+    // most `limit` subgraphs are measured per model.
+    using SubgraphMeasure =
+        std::function<bool(const std::vector<std::string>& node_ids, int64_t bs, bool checkpointing, GraphProfile*)>;
+    void setSubgraphMeasure(SubgraphMeasure f, int limit) {
+        measure_ = std::move(f);
+        measure_limit_ = limit;
+    }
+    bool hasSubgraphMeasure() const { return static_cast<bool>(measure_); }
+    int measuredCount() const { return measured_; }
+    // fwd + bwd microseconds of the operators `ids` run as one graph; false: no measurement available
+    bool measuredSubgraphTime(const std::vector<std::string>& ids, int64_t bs, double* us) const;
+
 private:
+    bool measured(const std::vector<std::string>& ids, int64_t bs, bool checkpointing, GraphProfile* out) const;
     IRGraph g_;
     std::unordered_map<std::string, NodeProfile> np_;
     LinkModel link_;
+    SubgraphMeasure measure_;
+    int measure_limit_ = 0;
+    mutable int measured_ = 0;
+    mutable std::unordered_map<std::string, std::pair<bool, GraphProfile>> measure_cache_;
 };
 
 // microseconds to move `bytes` between two stages / to all-reduce `bytes` over n ranks

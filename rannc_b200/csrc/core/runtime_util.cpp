@@ -106,7 +106,9 @@ const Def kDefs[] = {
     // --- items of this runtime (no counterpart in the reference) ---
     {"fused_kernels", ConfigItem::BOOL, "true"},          // false: stock ATen ops + NCCL collectives
     {"fused_grad_allreduce", ConfigItem::BOOL, "true"},   // peer-memory reduce-scatter + Adam + all-gather
-    {"measure_profiles", ConfigItem::BOOL, "false"},      // time operators with CUDA events when planning
+    {"measure_profiles", ConfigItem::BOOL, "true"},       // on a CUDA device: time operators and blocks when planning
+    {"measure_subgraphs", ConfigItem::BOOL, "false"},     // the stage search measures its candidate stages
+    {"max_measured_subgraphs", ConfigItem::INT, "64"},
     {"p2p_gbs", ConfigItem::FLOAT, "770"},                // stage <-> stage bandwidth, GB/s
     {"allreduce_gbs", ConfigItem::FLOAT, "725"},          // all-reduce bus bandwidth, GB/s
     {"dev_tflops", ConfigItem::FLOAT, "1388"},            // sustained bf16 GEMM throughput for estimates

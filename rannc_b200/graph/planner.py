@@ -84,6 +84,31 @@ def _fmt_table(estimates) -> str:
     return "\n".join(rows)
 
 
+def _calibrate(pm, ml, ir_graph, node_profiles, pconf, sp):
+    """One measurement per block of the coarsened graph (forward + backward on the device at the micro-batch
+    size a pure data-parallel plan would use); the operator profiles of the block are scaled to it.  With
+    ``measure_subgraphs`` the stage search additionally measures the stages it considers, up to
+    ``max_measured_subgraphs`` of them (reference: every candidate is profiled, GraphProfiler.cpp:245-415)."""
+    owned = {n.id for n in ir_graph.nodes if n.is_batch or n.is_criterion}
+    bs = max(1, int(pconf.batch_size) // max(1, int(pconf.dev_num)))
+    blocks = [(n.id, [i for i in n.sub_nodes if i in owned], n.graph) for n in ml.nodes]
+    graphs = {n.id: n.graph for n in ml.nodes}
+
+    def additive(name):
+        p = pm.profile(graphs[name], bs, False)
+        return float(p.fwd_time), float(p.bwd_time), float(p.activation_size)
+
+    new_profiles, report = sp.calibrate(node_profiles, blocks, bs, additive)
+    if report:
+        logger.info("Measured %d block(s) at micro-batch %d: measured / estimated (fwd, bwd, kept bytes) %s", len(report),
+                    bs, ", ".join(f"{n}: {rf:.2f} {rb:.2f} {ra:.2f}" for n, _, rf, rb, ra in report))
+    pm2 = _core.ProfileModel(ir_graph, new_profiles, pconf.link)
+    if bool(conf("measure_subgraphs")):
+        pm2.set_subgraph_measure(lambda ids, b, ckpt: sp.measure(list(ids), int(b), bool(ckpt)),
+                                 int(conf("max_measured_subgraphs")))
+    return pm2, new_profiles
+
+
 def _load_alloc_solution(pconf):
     """``load_alloc_solutions``: reuse a stage assignment written by ``save_alloc_solutions`` instead of
     searching again (files ``<alloc_solutions_file_prefix>_s<stages>_p<micro-batches>.bin``).  A forced
@@ -116,8 +141,11 @@ def _load_alloc_solution(pconf):
 
 def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: int, global_batch: int,
          dev_total_mem: int, use_amp: bool, enable_zero: bool, offload_params: bool, dep_id: str,
-         load_deployment: Optional[str] = None) -> Plan:
-    """``ir_graph`` must already be scaled to the global batch size."""
+         load_deployment: Optional[str] = None, subgraph_profiler=None) -> Plan:
+    """``ir_graph`` must already be scaled to the global batch size.  ``subgraph_profiler``
+    (``profiler.SubgraphProfiler``): when given, every block of the coarsened graph is measured once and the
+    operator profiles are calibrated to it; with ``measure_subgraphs`` the stage search measures its candidate
+    stages themselves."""
     if dev_total_mem == 0 and int(conf("partitioning_dry_run_np")) > 0 and int(conf("mem_limit_gb")) <= 0:
         # a dry run on a machine without the target device plans for a B200's 180 GB unless told otherwise
         dev_total_mem = 180 * 10 ** 9
@@ -163,6 +191,8 @@ def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: in
                     f.write(ml.dumps())
         ml_nodes = len(ml.nodes)
         logger.info("Coarsened the graph to %d blocks", ml_nodes)
+        if subgraph_profiler is not None:
+            pm, node_profiles = _calibrate(pm, ml, ir_graph, node_profiles, pconf, subgraph_profiler)
         if 0 < ml_nodes < pconf.cfg_partition_num:
             # a forced stage count cannot exceed the number of blocks there are to distribute
             logger.warning("partition_num=%d is more than the %d block(s) of this model; using %d",

@@ -7,9 +7,19 @@ Two modes:
   taken from the configuration (defaults are the rates measured on B200);
 * measured (``measure_profiles``): every operator of the rewritten graph is
   timed on the device with CUDA events, forward and backward, on fake-shaped
-  random inputs -- the counterpart of the reference's GraphProfiler
-  (src/comp/GraphProfiler.cpp:245-415), but per operator instead of per
-  candidate subgraph, and on the device clock instead of the host's.
+  random inputs, and ``SubgraphProfiler`` runs whole candidate subgraphs --
+  forward + backward at a given micro-batch size, with or without
+  recomputation -- and reports device time (CUDA events), host enqueue time,
+  the allocator peak, and the bytes kept for backward: the counterpart of the
+  reference's GraphProfiler (src/comp/GraphProfiler.cpp:245-415), on the device
+  clock instead of the host's.  The planner uses it in two ways: to calibrate
+  the operator figures block by block (one measurement per block of the
+  coarsened graph), and -- ``measure_subgraphs`` -- as the profile source of the
+  stage search itself, one measurement per candidate stage like the reference.
+
+Profiles are kept in the reference's ``ProfileDB`` file layout
+(src/comp/GraphProfiler.h:54-57,133-160): ``save_graph_profile`` /
+``load_graph_profile`` / ``graph_profile_file``.
 """
 from __future__ import annotations
 
@@ -167,26 +177,341 @@ def measured_profiles(gm: fx.GraphModule, device, iters: int = 3) -> Dict[str, "
     return base
 
 
-def save_profiles(path: str, profiles: Dict[str, "_core.NodeProfile"], batch: int) -> None:
-    """Writes the operator profiles (msgpack: batch size, then per node id the five profile fields).  Counterpart
-    of the reference's profile dump (src/comp/GraphProfiler.cpp, ``save_graph_profile``): a later run with
-    ``load_graph_profile`` plans from the file instead of profiling again."""
-    body = {k: [float(p.fwd_us), float(p.bwd_us), int(p.activation_bytes), int(p.working_bytes),
-                bool(p.scales_with_batch)] for k, p in profiles.items()}
+_OP_ITER = 1          # ``iteration`` field of the ProfileDB key under which operator profiles are filed
+
+
+def _key_graphs(ir_graph):
+    """The traced graph under a fixed name (its own name carries the module's random id), as the ``ir_graphs``
+    part of a ProfileDB key."""
+    if ir_graph is None:
+        return {}
+    g = _core.IRGraph.loads(ir_graph.dumps())
+    g.name = "model"
+    return {"model": g}
+
+
+def _as_graph_profile(name: str, p: "_core.NodeProfile") -> "_core.GraphProfile":
+    gp = _core.GraphProfile()
+    gp.name = name
+    # microseconds, rounded up so that an operator that takes time never reads as free
+    gp.fwd_time = int(-(-p.fwd_us // 1)) if p.fwd_us > 0 else 0
+    gp.bwd_time = int(-(-p.bwd_us // 1)) if p.bwd_us > 0 else 0
+    gp.fwd_cuda_time, gp.bwd_cuda_time = gp.fwd_time, gp.bwd_time
+    gp.activation_size = int(p.activation_bytes)
+    gp.working_mem = int(p.working_bytes)
+    return gp
+
+
+def save_profiles(path: str, profiles: Dict[str, "_core.NodeProfile"], batch: int, ir_graph=None,
+                  db: "_core.ProfileDB" = None) -> None:
+    """Writes the operator profiles in the reference's ``ProfileDB`` layout: one item whose key holds the traced
+    graph and the batch size and whose result maps every operator id to a ``GraphProfile`` record
+    (src/comp/GraphProfiler.h:54-57,133-160; config ``save_graph_profile``).  ``db``: a database that already
+    holds subgraph measurements to be written along."""
+    db = db if db is not None else _core.ProfileDB()
+    graphs = _key_graphs(ir_graph)
+    db.add(graphs, int(batch), _OP_ITER, False, {k: _as_graph_profile(k, p) for k, p in profiles.items()})
     with open(path, "wb") as f:
-        f.write(_core.msgpack_pack({"batch": int(batch), "nodes": body}))
+        f.write(db.dumps())
 
 
-def load_profiles(path: str, node_ids, batch: int) -> Dict[str, "_core.NodeProfile"]:
-    """Reads a file written by ``save_profiles``.  It must cover exactly the nodes of the traced graph and have
-    been taken at the same batch size; anything else means it belongs to another model or configuration."""
+def load_profiles(path: str, node_ids, batch: int, ir_graph=None) -> Dict[str, "_core.NodeProfile"]:
+    """Reads a file written by ``save_profiles``.  It must hold an item for this traced graph and batch size that
+    covers exactly the graph's operators; anything else means it belongs to another model or configuration."""
+    db = _core.ProfileDB()
     with open(path, "rb") as f:
-        raw = _core.msgpack_unpack(f.read())
-    if int(raw["batch"]) != int(batch):
-        raise RuntimeError(f"profile file {path} was taken at batch {raw['batch']}, this run traces batch {batch}")
-    nodes = raw["nodes"]
+        db.loads(f.read())
+    graphs = _key_graphs(ir_graph)
+    found = db.get(graphs, int(batch), _OP_ITER, False)
+    if found is None:
+        raise RuntimeError(f"profile file {path} has no entry for this graph at batch {batch}")
     want = set(node_ids)
-    if set(nodes) != want:
-        missing = sorted(want - set(nodes))[:5]
+    if set(found) != want:
+        missing = sorted(want - set(found))[:5]
         raise RuntimeError(f"profile file {path} does not match the traced graph (e.g. missing {missing})")
-    return {k: _core.NodeProfile(v[0], v[1], int(v[2]), int(v[3]), bool(v[4])) for k, v in nodes.items()}
+    return {k: _core.NodeProfile(float(v.fwd_time), float(v.bwd_time), int(v.activation_size), int(v.working_mem),
+                                 bool(v.fwd_time or v.bwd_time or v.activation_size))
+            for k, v in found.items()}
+
+
+class SubgraphProfiler:
+    """Runs a set of operators of the traced graph as one graph on the device and measures it.
+
+    ``measure(ids, batch, checkpointing)`` cuts the operators ``ids`` (plus the batch-independent operators
+    they read from: views of parameters, constants, size arithmetic) out of the traced FX graph, feeds it
+    random tensors of the right shapes with the batch dimension scaled to ``batch``, and runs forward +
+    backward ``profiling_iter`` times after one warm-up.  Returns a ``GraphProfile``: forward / backward device
+    time from CUDA events (``*_time`` and ``*_cuda_time``, microseconds), host time to enqueue them
+    (``*_cpu_time``; with ``enable_kineto`` the split comes from ``torch.profiler`` instead), the allocator peak
+    over the run, the bytes still held after the forward (kept for backward) and the transient remainder.
+    Counterpart of GraphProfiler::computeGraph (src/comp/GraphProfiler.cpp:245-415) and of KinetoWrapper
+    (src/comp/KinetoWrapper.cpp:9-40).  Measurements are kept in a ``ProfileDB`` (reference file layout)."""
+
+    def __init__(self, tm, device, iters: int = 1, max_bytes: int = 0):
+        self.tm = tm
+        self.device = device
+        self.iters = max(1, int(iters))
+        self.db = _core.ProfileDB()
+        self.by_name = {n.name: n for n in tm.gm.graph.nodes}
+        self.owned = {n.id for n in tm.ir.nodes if n.is_batch or n.is_criterion}
+        self.order = {n.name: i for i, n in enumerate(tm.gm.graph.nodes)}
+        self.max_bytes = int(max_bytes)
+        self.use_kineto = bool(conf("enable_kineto"))
+        self.count = 0
+
+    # ---------------------------------------------------------------- graph cutting
+    def _cut(self, ids):
+        inset = set(ids)
+        stack = list(ids)
+        while stack:
+            n = self.by_name[stack.pop()]
+            for a in n.all_input_nodes:
+                if a.op == "call_function" and a.name not in inset and a.name not in self.owned:
+                    inset.add(a.name)
+                    stack.append(a.name)
+        g = fx.Graph()
+        env, inputs = {}, []
+
+        def arg(a):
+            if a.name not in env:
+                ph = g.placeholder(a.name)
+                ph.meta = dict(a.meta)
+                env[a.name] = ph
+                inputs.append(a)
+            return env[a.name]
+
+        outs = []
+        for name in sorted(inset, key=lambda k: self.order[k]):
+            src = self.by_name[name]
+            for a in src.all_input_nodes:
+                if a.name not in env and a.name not in inset:
+                    arg(a)
+            env[name] = g.node_copy(src, lambda x: env[x.name] if x.name in env else arg(x))
+            val = src.meta.get("val")
+            if name in self.owned and isinstance(val, torch.Tensor) and val.is_floating_point() and \
+                    any(u.name not in inset for u in src.users):
+                outs.append(env[name])
+        if not outs:
+            last = [env[n] for n in sorted(inset, key=lambda k: self.order[k]) if
+                    isinstance(self.by_name[n].meta.get("val"), torch.Tensor) and
+                    self.by_name[n].meta["val"].is_floating_point()]
+            outs = last[-1:]
+        g.output(tuple(outs))
+        # placeholders first (fx requires it): node_copy appended them in order of first use, which is fine
+        # because every placeholder was created before the node that uses it; reorder to the front
+        gm = fx.GraphModule(self.tm.gm, _placeholders_first(g))
+        return gm, inputs
+
+    def _make_input(self, node, ratio: float):
+        val = node.meta.get("val")
+        name = node.name
+        if isinstance(val, torch.Tensor):
+            shp = _shape(val)
+            is_param = name in self.tm.params or name in self.tm.buffers or name in self.tm.constants
+            if not is_param and shp and self.tm.trace_batch > 0 and shp[0] % self.tm.trace_batch == 0 and \
+                    self.tm.ir.has_value(name) and self.tm.ir.value(name).is_batch:
+                shp = [max(1, int(round(shp[0] * ratio)))] + shp[1:]
+            if val.is_floating_point():
+                t = torch.randn(shp, dtype=val.dtype, device=self.device) * 0.02
+                return t.requires_grad_(True)
+            return torch.zeros(shp, dtype=val.dtype, device=self.device)
+        if isinstance(val, (int, torch.SymInt)):
+            h = int(getattr(getattr(val, "node", None), "hint", val)) if not isinstance(val, int) else val
+            if self.tm.trace_batch > 0 and not isinstance(val, int) and h % self.tm.trace_batch == 0:
+                return max(1, int(round(h * ratio)))
+            return h
+        return val
+
+    # ---------------------------------------------------------------- measurement
+    def measure(self, ids, batch: int, checkpointing: bool = False):
+        ids = [i for i in ids if i in self.by_name]
+        if not ids:
+            return None
+        ratio = float(batch) / max(1, self.tm.trace_batch)
+        try:
+            gm, inputs = self._cut(ids)
+            est = sum(_numel_bytes(self.by_name[i].meta.get("val")) for i in ids) * ratio
+            if self.max_bytes and est * 3 > self.max_bytes:
+                return None
+            args = [self._make_input(n, ratio) for n in inputs]
+            return self._run(gm, args, checkpointing, "+".join(ids[:2]) + f"..({len(ids)})")
+        except torch.OutOfMemoryError:
+            torch.cuda.empty_cache()
+            return None
+        except Exception:  # noqa: BLE001 - a subgraph that cannot run standalone keeps its estimate
+            return None
+
+    def _run(self, gm, args, checkpointing: bool, name: str):
+        if self.device.type != "cuda":
+            return self._run_host(gm, args, checkpointing, name)
+        import time
+
+        dev = self.device
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ft = bt = fcpu = bcpu = 0.0
+        peak = kept = 0
+        for it in range(self.iters + 1):
+            for a in args:
+                if isinstance(a, torch.Tensor) and a.grad is not None:
+                    a.grad = None
+            torch.cuda.synchronize(dev)
+            torch.cuda.reset_peak_memory_stats(dev)
+            base = torch.cuda.memory_allocated(dev)
+            t0 = time.perf_counter()
+            ev[0].record()
+            if checkpointing:
+                with torch.no_grad():
+                    outs = gm(*args)
+                held = torch.cuda.memory_allocated(dev) - base
+                outs = gm(*args)      # the recomputation, charged to the backward like the runtime does
+                ev[1].record()
+                t1 = time.perf_counter()
+            else:
+                outs = gm(*args)
+                ev[1].record()
+                t1 = time.perf_counter()
+                held = torch.cuda.memory_allocated(dev) - base
+            outs = [o for o in (outs if isinstance(outs, (tuple, list)) else (outs,))
+                    if isinstance(o, torch.Tensor) and o.requires_grad]
+            if outs:
+                torch.autograd.backward(outs, [torch.ones_like(o) for o in outs])
+            ev[2].record()
+            t2 = time.perf_counter()
+            torch.cuda.synchronize(dev)
+            if it > 0:
+                f, b = ev[0].elapsed_time(ev[1]) * 1e3, ev[1].elapsed_time(ev[2]) * 1e3
+                if checkpointing:
+                    # forward without grad + recomputation were timed together: half is the forward
+                    f, b = f / 2, b + f / 2
+                ft, bt = ft + f, bt + b
+                fcpu, bcpu = fcpu + (t1 - t0) * 1e6, bcpu + (t2 - t1) * 1e6
+                peak = max(peak, torch.cuda.max_memory_allocated(dev) - base)
+                kept = max(kept, held)
+            del outs
+        n = self.iters
+        out_bytes = 0
+        gp = _core.GraphProfile()
+        gp.name = name
+        gp.fwd_time, gp.bwd_time = int(ft / n + 0.5), int(bt / n + 0.5)
+        gp.fwd_cuda_time, gp.bwd_cuda_time = gp.fwd_time, gp.bwd_time
+        gp.fwd_cpu_time, gp.bwd_cpu_time = int(fcpu / n + 0.5), int(bcpu / n + 0.5)
+        if self.use_kineto:
+            self._kineto_split(gm, args, gp)
+        gp.max_allocated_mem = int(peak)
+        gp.activation_size = int(max(0, kept - out_bytes))
+        gp.working_mem = int(max(0, peak - kept))
+        gp.checkpointing = bool(checkpointing)
+        self.count += 1
+        return gp
+
+    def _run_host(self, gm, args, checkpointing: bool, name: str):
+        """Without a CUDA device (CPU ranks): host clock, and the bytes of the tensors the forward returns and
+        saves are approximated by the outputs'."""
+        import time
+
+        ft = bt = 0.0
+        kept = 0
+        for it in range(self.iters + 1):
+            for a in args:
+                if isinstance(a, torch.Tensor) and a.grad is not None:
+                    a.grad = None
+            t0 = time.perf_counter()
+            if checkpointing:
+                with torch.no_grad():
+                    gm(*args)
+            outs = gm(*args)
+            t1 = time.perf_counter()
+            outs = [o for o in (outs if isinstance(outs, (tuple, list)) else (outs,))
+                    if isinstance(o, torch.Tensor) and o.requires_grad]
+            kept = sum(o.numel() * o.element_size() for o in outs)
+            if outs:
+                torch.autograd.backward(outs, [torch.ones_like(o) for o in outs])
+            t2 = time.perf_counter()
+            if it > 0:
+                f, b = (t1 - t0) * 1e6, (t2 - t1) * 1e6
+                if checkpointing:
+                    f, b = f / 2, b + f / 2
+                ft, bt = ft + f, bt + b
+        gp = _core.GraphProfile()
+        gp.name = name
+        gp.fwd_time, gp.bwd_time = max(1, int(ft / self.iters + 0.5)), max(1, int(bt / self.iters + 0.5))
+        gp.fwd_cpu_time, gp.bwd_cpu_time = gp.fwd_time, gp.bwd_time
+        gp.activation_size = int(kept)
+        gp.max_allocated_mem = int(kept)
+        gp.checkpointing = bool(checkpointing)
+        self.count += 1
+        return gp
+
+    def _kineto_split(self, gm, args, gp) -> None:
+        """``enable_kineto``: host and device time of one more forward + backward from ``torch.profiler``
+        (reference: KinetoWrapper, src/comp/KinetoWrapper.cpp:9-40)."""
+        try:
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+                outs = gm(*args)
+                outs = [o for o in (outs if isinstance(outs, (tuple, list)) else (outs,))
+                        if isinstance(o, torch.Tensor) and o.requires_grad]
+                if outs:
+                    torch.autograd.backward(outs, [torch.ones_like(o) for o in outs])
+                torch.cuda.synchronize(self.device)
+            cpu = sum(e.self_cpu_time_total for e in prof.key_averages())
+            cuda = sum(getattr(e, "self_device_time_total", 0) for e in prof.key_averages())
+            total = max(1, gp.fwd_time + gp.bwd_time)
+            gp.fwd_cpu_time = int(cpu * gp.fwd_time / total)
+            gp.bwd_cpu_time = int(cpu * gp.bwd_time / total)
+            gp.fwd_cuda_time = int(cuda * gp.fwd_time / total)
+            gp.bwd_cuda_time = int(cuda * gp.bwd_time / total)
+        except Exception:  # noqa: BLE001
+            pass
+
+    # ---------------------------------------------------------------- calibration of the operator profiles
+    def calibrate(self, node_profiles, blocks, batch: int, additive):
+        """``blocks``: (block name, operator ids, IRGraph) per block of the coarsened graph.  Each block is
+        measured once at micro-batch ``batch``; the operator profiles inside it are scaled so that their sum
+        matches the measurement (time forward, time backward, bytes kept for backward).  ``additive(name)``
+        returns the (fwd, bwd, activation) sums the current profiles give for the block at that batch.
+        Returns (new profiles, list of (block, measured / estimated) for the log)."""
+        out = dict(node_profiles)
+        report = []
+        for name, ids, graph in blocks:
+            cached = self.db.get({name: graph}, int(batch), self.iters, False)
+            gp = cached.get(name) if cached else None
+            if gp is None:
+                gp = self.measure(ids, batch, False)
+                if gp is None:
+                    continue
+                self.db.add({name: graph}, int(batch), self.iters, False, {name: gp})
+            ef, eb, ea = additive(name)
+            rf = gp.fwd_time / ef if ef > 0 and gp.fwd_time > 0 else 1.0
+            rb = gp.bwd_time / eb if eb > 0 and gp.bwd_time > 0 else 1.0
+            ra = gp.activation_size / ea if ea > 0 and gp.activation_size > 0 else 1.0
+            # a single measurement can be off: keep the correction within a factor of four
+            rf, rb, ra = (min(4.0, max(0.25, r)) for r in (rf, rb, ra))
+            for i in ids:
+                p = out.get(i)
+                if p is None:
+                    continue
+                out[i] = _core.NodeProfile(p.fwd_us * rf, p.bwd_us * rb, int(p.activation_bytes * ra),
+                                           p.working_bytes, p.scales_with_batch)
+            report.append((name, len(ids), rf, rb, ra))
+        return out, report
+
+
+def _placeholders_first(g: fx.Graph) -> fx.Graph:
+    """A copy of ``g`` with its placeholders moved in front of every other node."""
+    out = fx.Graph()
+    env = {}
+    for n in g.nodes:
+        if n.op == "placeholder":
+            env[n] = out.placeholder(n.name)
+            env[n].meta = dict(n.meta)
+    for n in g.nodes:
+        if n.op == "placeholder":
+            continue
+        if n.op == "output":
+            out.output(torch.fx.node.map_arg(n.args[0], lambda x: env[x]))
+        else:
+            env[n] = out.node_copy(n, lambda x: env[x])
+    out.lint()
+    return out

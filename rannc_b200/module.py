@@ -261,15 +261,20 @@ class RaNNCModule:
 
         logger.info("Running profiler ...")
         prof_file = str(conf("graph_profile_file"))
+        measuring = bool(conf("measure_profiles")) and dev.type == "cuda" and use_kernels and \
+            not any(p.is_meta for p in model.parameters())
+        sub_prof = None
         if bool(conf("load_graph_profile")) and os.path.exists(prof_file):
-            node_profiles = profiler.load_profiles(prof_file, [n.id for n in tm.ir.nodes], tm.trace_batch)
+            node_profiles = profiler.load_profiles(prof_file, [n.id for n in tm.ir.nodes], tm.trace_batch, tm.ir)
             logger.info("Loaded operator profiles from %s", prof_file)
-        elif bool(conf("measure_profiles")) and dev.type == "cuda":
+        elif measuring and rank == 0:
             node_profiles = profiler.measured_profiles(tm.gm, dev, iters=max(1, int(conf("profiling_iter"))))
         else:
             node_profiles = profiler.analytic_profiles(tm.gm)
+        if (measuring or bool(conf("measure_subgraphs"))) and rank == 0:
+            sub_prof = profiler.SubgraphProfiler(tm, dev, iters=max(1, int(conf("profiling_iter"))))
         if bool(conf("save_graph_profile")) and rank == 0:
-            profiler.save_profiles(prof_file, node_profiles, tm.trace_batch)
+            profiler.save_profiles(prof_file, node_profiles, tm.trace_batch, tm.ir)
             logger.info("Saved operator profiles to %s", prof_file)
         # node times were taken at the traced (local) batch: express them at the global batch
         if global_bs != tm.trace_batch and tm.trace_batch > 0:
@@ -286,7 +291,15 @@ class RaNNCModule:
         if rank == 0:
             logger.info("Partitioning the model for %d device(s), global batch %d ...", world, global_bs)
             self._plan = planner.plan(ir, node_profiles, world, global_bs, total_mem, self.use_amp_master_params,
-                                      self.enable_zero, self.offload_params, self.id, self.load_deployment)
+                                      self.enable_zero, self.offload_params, self.id, self.load_deployment,
+                                      subgraph_profiler=sub_prof)
+            if sub_prof is not None:
+                if bool(conf("save_graph_profile")) and sub_prof.count:
+                    # the measured blocks / stages go into the same file as the operator profiles
+                    profiler.save_profiles(prof_file, node_profiles, tm.trace_batch, tm.ir, db=sub_prof.db)
+                del sub_prof
+                if dev.type == "cuda":
+                    torch.cuda.empty_cache()
             dep_bytes = bytes(_core.save_deployment(self._plan.deployment, world, self._plan.dev_mem))
         dry = int(conf("partitioning_dry_run_np"))
         if dry > 0:

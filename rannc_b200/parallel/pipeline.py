@@ -63,6 +63,8 @@ class PipelineRuntime:
         self.all_ranks = list(range(self.world))
         self.calc = _core.BatchSizeCalculator(self.P, self.B)
         self.checkpointing = bool(dep.checkpointing)
+        # checkpointing_no_last: the last stage keeps its activations (same rule as the stage search)
+        self.no_ckpt_stage = self.order[-1] if (bool(conf("checkpointing_no_last")) and len(self.order) > 1) else None
         self.pending = comm.PendingOps()
         self.gather_inputs = gather_inputs
         # the ranks that hand inputs in and take outputs back: every rank with its slice of the batch, or
@@ -170,7 +172,7 @@ class PipelineRuntime:
                 st = self.stages[sname]
                 _core.trace_begin(_core.func_key("forward", sname, i, False))
                 self.timers.start("forward " + sname)
-                outs = st.forward(i, ins, self.checkpointing, grad_enabled)
+                outs = st.forward(i, ins, self.checkpointing and sname != self.no_ckpt_stage, grad_enabled)
                 self.timers.stop("forward " + sname)
                 _core.trace_end(_core.func_key("forward", sname, i, False))
                 stage_vals[(i, sname)] = outs

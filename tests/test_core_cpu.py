@@ -257,6 +257,176 @@ def test_forced_stage_and_pipeline_counts_and_dry_run():
     assert s3.pipeline_num == 4 and s3.boundaries == sol.boundaries
 
 
+def _residual_ffn_graph(layers=24, h=64, batch=8):
+    """x -> [linear(h -> 4h) -> gelu -> linear(4h -> h) -> add(x)] x layers: wide values inside a block, narrow
+    ones (two of them: the sum and the skip) between blocks."""
+    g = _core.IRGraph()
+    g.name = "res"
+    g.batch_size = batch
+    g.add_input(_core.IRValue("x", _t([batch, h])))
+    for i in range(layers):
+        g.add_input(_core.IRValue(f"w{i}a", _t([4 * h, h], rg=True), True))
+        g.add_input(_core.IRValue(f"w{i}b", _t([h, 4 * h], rg=True), True))
+    prev = "x"
+    for i in range(layers):
+        g.add_value(_core.IRValue(f"u{i}", _t([batch, 4 * h])))
+        g.add_node(_core.IRNode("aten::linear", [prev, f"w{i}a"], [f"u{i}"], f"up{i}"))
+        g.add_value(_core.IRValue(f"g{i}", _t([batch, 4 * h])))
+        g.add_node(_core.IRNode("aten::gelu", [f"u{i}"], [f"g{i}"], f"act{i}"))
+        g.add_value(_core.IRValue(f"d{i}", _t([batch, h])))
+        g.add_node(_core.IRNode("aten::linear", [f"g{i}", f"w{i}b"], [f"d{i}"], f"down{i}"))
+        g.add_value(_core.IRValue(f"r{i}", _t([batch, h])))
+        g.add_node(_core.IRNode("aten::add", [f"d{i}", prev], [f"r{i}"], f"add{i}"))
+        prev = f"r{i}"
+    g.add_output(prev)
+    g.check()
+    return _core.guess_value_types(g)
+
+
+def test_uncoarsening_moves_boundaries_to_a_smaller_cut():
+    """Multi-level partitioning: coarsening records which blocks a block was merged from; uncoarsening walks the
+    levels back down and lets boundary blocks change sides when that shrinks the cut.  The result must still be
+    a partition of all operators into a DAG of convex blocks that the stage search accepts."""
+    import random
+
+    g = _residual_ffn_graph()
+    random.seed(0)
+    np_ = {n.id: _core.NodeProfile(50.0 + random.random() * 100, 100.0 + random.random() * 200, 1 << 16, 0, True)
+           for n in g.nodes}
+    conf = _conf(4, 8)
+    conf.min_partition_num = 8
+    pm = _core.ProfileModel(g, np_, conf.link)
+    conf.do_uncoarsening = False
+    coarse, levels, moves, cut0, cut1 = _core.ml_partition_stats(pm, conf)
+    assert levels >= 2 and moves == 0 and cut0 == cut1 and coarse.level() == levels
+    conf.do_uncoarsening = True
+    fine, levels2, moves2, before, after = _core.ml_partition_stats(pm, conf)
+    assert levels2 == levels and moves2 > 0 and after < before == cut0
+    assert _core.ml_cut_bytes(g, fine) < _core.ml_cut_bytes(g, coarse)
+    assert len(fine.nodes) == len(coarse.nodes)
+    # still a partition of the operators ...
+    ops = sorted(o for n in fine.nodes for o in n.sub_nodes)
+    assert ops == sorted(n.id for n in g.nodes)
+    # ... whose blocks, in the emitted order, only feed later blocks
+    pos = {n.id: k for k, n in enumerate(fine.nodes)}
+    assert all(pos[e.src_id] < pos[e.tgt_id] for e in fine.edges)
+    sol, est, _ = _core.dp_staging(pm, fine, conf)
+    owned = sorted(n.id for sg in sol.graphs for n in sg.nodes if n.is_batch)
+    assert owned == sorted(n.id for n in g.nodes if n.is_batch)
+    # hierarchy: one level down there are more, smaller nodes covering the same operators; lifting them back
+    # up in pairs restores a coarser graph; the file format keeps the nesting
+    low = _core.ml_to_lower_level(g, coarse)
+    assert len(low.nodes) > len(coarse.nodes) and low.level() == coarse.level() - 1
+    assert sorted(o for n in low.nodes for o in n.sub_nodes) == ops
+    groups = [[i, i + 1] if i + 1 < len(low.nodes) else [i] for i in range(0, len(low.nodes), 2)]
+    up = _core.ml_lift_up(g, low, groups)
+    assert len(up.nodes) == len(groups) and up.level() == low.level() + 1
+    back = _core.MLGraph.loads(coarse.dumps())
+    assert back.level() == coarse.level() and [len(n.children) for n in back.nodes] == \
+        [len(n.children) for n in coarse.nodes]
+    raw = _core.msgpack_unpack(coarse.dumps())
+    node0 = raw[0][0]                      # MLNode: id, graph, sub_nodes, sub_edges
+    assert node0[0] == "ML_0" and isinstance(node0[2][0], list) and node0[2][0][0].startswith("ML_0_")
+
+
+def test_coarsening_by_memory_and_checkpointing_no_last():
+    g = make_mlp_graph(layers=16, hidden=256, batch=32, with_loss=False)
+    # one operator is heavy in memory but cheap in time
+    np_ = {n.id: _core.NodeProfile(100.0, 200.0, (64 << 20) if n.id == "lin8" else (1 << 20), 0, True)
+           for n in g.nodes}
+    conf = _conf(2, 32)
+    conf.min_partition_num = 6
+    pm = _core.ProfileModel(g, np_, conf.link)
+    by_time = _core.ml_partition(pm, conf)
+    conf.coarsen_by_time = False
+    by_mem = _core.ml_partition(pm, conf)
+    size_of = lambda ml: [len(n.sub_nodes) for n in ml.nodes if "lin8" in n.sub_nodes][0]  # noqa: E731
+    # weighed by memory, the heavy operator's block stays small (it is the outlier nothing merges with)
+    assert size_of(by_mem) < size_of(by_time)
+    # checkpointing_no_last: with recomputation forced, the last stage is planned without it
+    conf = _conf(2, 32)
+    conf.cfg_partition_num, conf.cfg_pipeline_num, conf.checkpointing = 2, 2, True
+    pm = _core.ProfileModel(g, np_, conf.link)
+    ml = _core.ml_partition(pm, conf)
+    _, est, _ = _core.dp_staging(pm, ml, conf)
+    assert est[0].profile.checkpointing and est[1].profile.checkpointing
+    conf.checkpointing_no_last = True
+    _, est2, _ = _core.dp_staging(pm, ml, conf)
+    assert est2[0].profile.checkpointing and not est2[1].profile.checkpointing
+    assert est2[1].profile.bwd_time < est[1].profile.bwd_time
+
+
+def test_measured_subgraph_profiles_replace_the_additive_estimate():
+    """The profile model asks a callback to measure whole candidate subgraphs (time and allocator peak); what it
+    returns is what the stage search plans with, each subgraph is measured once, and a callback that declines
+    leaves the additive estimate in place."""
+    g = make_mlp_graph(layers=8, hidden=64, batch=16, with_loss=False)
+    np_ = _profiles(g)
+    conf = _conf(2, 16)
+    pm = _core.ProfileModel(g, np_, conf.link)
+    calls = []
+
+    def measure(ids, bs, ckpt):
+        calls.append((tuple(ids), bs, ckpt))
+        if len(ids) > 12:
+            return None
+        p = _core.GraphProfile()
+        p.fwd_time, p.bwd_time = 7 * len(ids), 11 * len(ids)
+        p.max_allocated_mem, p.activation_size, p.working_mem = 12345 * len(ids), 1000 * len(ids), 10
+        return p
+
+    pm.set_subgraph_measure(measure, 1000)
+    ml = _core.ml_partition(pm, conf)
+    sol, est, _ = _core.dp_staging(pm, ml, conf)
+    assert calls and pm.measured_count() == len(set(calls)) == len(calls)
+    for e in est:
+        n_ops = sum(1 for n in sol.graphs[0].nodes if n.is_batch)
+        if n_ops <= 12:
+            assert e.profile.fwd_time == 7 * n_ops and e.profile.bwd_time == 11 * n_ops
+            assert e.profile.activation_size == 1000 * n_ops
+        else:
+            assert e.profile.fwd_time > 7 * n_ops      # the additive estimate (100 us per operator)
+
+
+def test_subgraph_profiler_measures_blocks_and_files_them_in_the_profile_db(tmp_path):
+    """The measuring profiler cuts operator sets out of the traced graph, runs them forward + backward at a
+    given micro-batch size (here on the host clock), calibrates the operator profiles block by block, and its
+    measurements travel in the reference's ProfileDB layout together with the operator profiles."""
+    import torch
+
+    from rannc_b200.graph import planner, profiler, tracer
+    from tests import zoo
+
+    torch.manual_seed(0)
+    m = zoo.build("deep")
+    x = zoo.inputs("deep", 8, torch.Generator().manual_seed(1))
+    tm = tracer.trace(m, x, use_kernels=False, name="t")
+    sp = profiler.SubgraphProfiler(tm, torch.device("cpu"), iters=1)
+    ids = [n.id for n in tm.ir.nodes if n.is_batch or n.is_criterion]
+    gp = sp.measure(ids[:4], 4, False)
+    assert gp.fwd_time > 0 and gp.bwd_time > 0 and gp.activation_size == 4 * 16 * 4 and not gp.checkpointing
+    gp2 = sp.measure(ids, 8, True)
+    assert gp2.checkpointing and gp2.bwd_time > gp2.fwd_time
+    assert sp.measure(["no_such_operator"], 4, False) is None
+    np_ = profiler.analytic_profiles(tm.gm)
+    ir = _core.scale_graph(tm.ir, 8)
+    n0 = sp.count
+    plan = planner.plan(ir, np_, 2, 8, 0, False, False, False, "x", None, subgraph_profiler=sp)
+    assert sp.count - n0 == plan.ml_nodes and len(sp.db) == plan.ml_nodes
+    path = str(tmp_path / "profiles.bin")
+    profiler.save_profiles(path, np_, tm.trace_batch, tm.ir, db=sp.db)
+    back = profiler.load_profiles(path, [n.id for n in tm.ir.nodes], tm.trace_batch, tm.ir)
+    assert set(back) == set(np_)
+    db = _core.ProfileDB()
+    db.loads(open(path, "rb").read())
+    assert len(db) == plan.ml_nodes + 1
+    raw = _core.msgpack_unpack(open(path, "rb").read())        # map: hash -> ProfileItem(key, profile)
+    item = next(iter(raw.values()))
+    assert len(item) == 2 and len(item[0]) == 5 and len(item[1]) == 2
+    with pytest.raises(RuntimeError):
+        profiler.load_profiles(path, ["other"], tm.trace_batch, tm.ir)
+
+
 def test_subgraph_cut_replicates_non_batch_nodes():
     g = _core.IRGraph()
     g.batch_size = 4
@@ -620,15 +790,19 @@ def test_operator_profiles_round_trip_and_debug_switches(tmp_path):
     assert (tmp_path / "sols_s1_p1.bin").exists()
     assert prof.exists() and "Saved operator profiles" in first
     assert "absmean=" in first and "time per stage" in first
+    # the reference's ProfileDB layout: {hash: [key, result]}; key = [ir_graphs, batch_size, repl_nums,
+    # iteration, checkpointing], result = [node_profiles, value_types]
     raw = _core.msgpack_unpack(prof.read_bytes())
-    assert raw["batch"] == 8 and len(raw["nodes"]) >= 16
+    (key, result), = raw.values()
+    assert key[1] == 8 and len(result[0]) >= 16
     second = run({"RANNC_LOAD_GRAPH_PROFILE": "true", "RANNC_LOAD_ALLOC_SOLUTIONS": "true"}, 29732)
     assert "Loaded operator profiles" in second and "Loaded the stage assignment" in second
     out = lambda t: [l for l in t.splitlines() if l.startswith("OUT")]
     assert out(first) == out(second)
     # a file taken for another graph is refused
-    raw["nodes"].pop(next(iter(raw["nodes"])))
-    prof.write_bytes(_core.msgpack_pack(raw))
+    h, = raw.keys()
+    result[0].pop(next(iter(result[0])))
+    prof.write_bytes(_core.msgpack_pack({h: [key, result]}))
     r = subprocess.run([sys.executable, "-c", code], env=dict(base, MASTER_PORT="29733", RANNC_LOAD_GRAPH_PROFILE="true"),
                        cwd=root, capture_output=True, text=True, timeout=240)
     assert r.returncode != 0 and "does not match the traced graph" in r.stdout + r.stderr
