@@ -49,8 +49,12 @@ def _run(cmd):
     return r.stdout
 
 
-def build_kernels(verbose: bool = False) -> Path:
-    out = HERE / "_kernels.so"
+def build_kernels(verbose: bool = False, debug: bool = False) -> Path:
+    """``debug``: the checked build (``_kernels_debug.so``, -DRB_DEBUG_BOUNDS): data-dependent indices are
+    range-checked on the device before the kernels that use them run, and a violation is recorded in the device
+    error word instead of trapping (see csrc/cuda/debug_check.cuh).  Loaded instead of the regular library when
+    RANNC_KERNEL_DEBUG=1."""
+    out = HERE / ("_kernels_debug.so" if debug else "_kernels.so")
     srcs = sorted(CUDA_SRC.glob("*.cu"))
     hdrs = sorted(CUDA_SRC.glob("*.cuh")) + sorted(CUDA_SRC.glob("*.h"))
     if _newer(out, srcs + hdrs):
@@ -59,10 +63,11 @@ def build_kernels(verbose: bool = False) -> Path:
     objs = []
 
     def compile_one(src: Path):
-        obj = BUILD_DIR / (src.stem + ".o")
+        obj = BUILD_DIR / (src.stem + ("_dbg.o" if debug else ".o"))
         if _newer(obj, [src] + hdrs):
             return obj
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CUDA_SRC), "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(["-DRB_DEBUG_BOUNDS"] if debug else []), "-I", str(CUDA_SRC), "-c", str(src),
+               "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -105,11 +110,36 @@ def build_core(verbose: bool = False) -> Path:
     return out
 
 
+def build_selftest(sanitize: str = "address,undefined") -> Path:
+    """The native core (everything but the Python bindings) linked into a stand-alone self-test program
+    (``csrc/core/selftest.cpp``) with the host sanitizers switched on: ``address,undefined`` (default) or
+    ``thread``.  The program exercises the msgpack codec, the IR, the partitioner and stage search, deployment,
+    batch arithmetic, the event recorder from several threads and the watchdog; a sanitizer report makes it exit
+    non-zero.  This is how the host code is checked for memory errors, undefined behaviour and data races."""
+    tag = sanitize.replace(",", "_")
+    out = BUILD_DIR / f"core_selftest_{tag}"
+    srcs = [p for p in sorted(CORE_SRC.glob("*.cpp")) if p.name != "bindings.cpp"]
+    hdrs = sorted(CORE_SRC.glob("*.h"))
+    if _newer(out, srcs + hdrs):
+        return out
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    flags = ["-O1", "-g", "-std=c++17", "-fno-omit-frame-pointer", f"-fsanitize={sanitize}", "-pthread", "-Wall",
+             "-Wno-sign-compare", "-DRANNC_SELFTEST"]
+    _run(["g++", *flags, "-I", str(CORE_SRC), *map(str, srcs), "-o", str(out)])
+    return out
+
+
 def build_all(verbose: bool = False):
     return build_core(verbose), build_kernels(verbose)
 
 
 if __name__ == "__main__":
-    c, k = build_all(verbose="-v" in sys.argv)
-    print("built", c)
-    print("built", k)
+    if "--debug" in sys.argv:
+        print("built", build_kernels(verbose="-v" in sys.argv, debug=True))
+    elif "--selftest" in sys.argv:
+        print("built", build_selftest("address,undefined"))
+        print("built", build_selftest("thread"))
+    else:
+        c, k = build_all(verbose="-v" in sys.argv)
+        print("built", c)
+        print("built", k)

@@ -404,11 +404,14 @@ bool reaches(const Adj& succ, int from, int to) {
 MLNode skelToNode(const GraphIndex& idx, const Skel& s, const std::string& id, bool with_graph, bool last) {
     MLNode n;
     n.id = id;
-    n.level = s.level;
     if (with_graph) n.graph = idx.extract(s.own, id, last);
     for (int i : s.own) n.sub_nodes.push_back(idx.g.nodes[i].id);
-    for (size_t k = 0; k < s.kids.size(); ++k)
+    // the level of a node is the height of the hierarchy below it (what a reader of the file can recompute)
+    n.level = 0;
+    for (size_t k = 0; k < s.kids.size(); ++k) {
         n.children.push_back(skelToNode(idx, s.kids[k], id + "_" + std::to_string(k), false, false));
+        n.level = std::max(n.level, n.children.back().level + 1);
+    }
     return n;
 }
 

@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "debug_check.cuh"
 #include "philox.cuh"
 #include "tc_common.cuh"
 
@@ -318,7 +319,9 @@ extern "C" int rb_embed_fwd(const long long* ids, const void* table, void* out, 
                             long long vocab, int dtype, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows <= 0) return 0;
+    RB_DEBUG_ARG(H % 8 == 0, "rb_embed_fwd: H must be a multiple of 8");
     if (H % 8) return -2;
+    RB_DEBUG_RANGE(ids, rows, 0, vocab, -1 - vocab, st);
     const int g = (rows * 32 + 255) / 256;
     if (dtype == 1)
         embed_fwd_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(
@@ -334,6 +337,7 @@ extern "C" int rb_embed_bwd(const long long* ids, const void* dout, float* dtabl
                             long long vocab, long long padding_idx, int dtype, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows <= 0) return 0;
+    RB_DEBUG_RANGE(ids, rows, 0, vocab, padding_idx, st);
     const int g = (rows * 32 + 255) / 256;
     if (dtype == 1)
         embed_bwd_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(
@@ -349,6 +353,12 @@ extern "C" int rb_rowcopy(const void* src, void* dst, long long rows, long long 
                           long long src_stride_bytes, long long dst_stride_bytes, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows <= 0 || bytes_per_row <= 0) return 0;
+    RB_DEBUG_ARG(((bytes_per_row | src_stride_bytes | dst_stride_bytes) & 15) == 0,
+                 "rb_rowcopy: row length and strides must be multiples of 16 bytes");
+    RB_DEBUG_ARG(((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0,
+                 "rb_rowcopy: both buffers must be 16-byte aligned");
+    RB_DEBUG_ARG(src_stride_bytes >= bytes_per_row && dst_stride_bytes >= bytes_per_row,
+                 "rb_rowcopy: a row stride shorter than the row makes rows overlap");
     if ((bytes_per_row | src_stride_bytes | dst_stride_bytes) & 15) return -2;
     if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) return -2;
     const long long vpr = bytes_per_row / 16;

@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "debug_check.cuh"
 #include "tc_common.cuh"
 
 namespace rb {
@@ -146,6 +147,7 @@ extern "C" int rb_xent_fwd(const void* logits, const long long* labels, float* l
                            float* loss, int rows, int V, long long ld, long long ignore_index,
                            float weight, int dtype, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RB_DEBUG_RANGE(labels, rows, 0, V, ignore_index, st);
     if (rows > 0) {
         if (dtype == 1)
             xent_fwd_kernel<__nv_bfloat16><<<rows, XT, 0, st>>>(

@@ -360,22 +360,26 @@ extern "C" int rb_ln_bwd(const void* dy, const void* z, const void* gamma, const
 // ---------------------------------------------------------------------------
 // Allocation-free variant of rb_ln_bwd (declared and documented in norm_noalloc.h)
 // ---------------------------------------------------------------------------
+#include <atomic>
+
 #include "norm_noalloc.h"
 
 // Scratch for the per-CTA partial sums of dgamma / dbeta.  In host code this name is only a
 // stand-in for the symbol: kernels must be given the address cudaGetSymbolAddress returns.
 static __device__ __align__(256) float g_ln_noalloc_scratch[RB_LN_NOALLOC_MAX_FLOATS];
 
+// One cached address per device.  The slots are atomics: two host threads that make their first call on a
+// device at the same time both resolve the symbol and store the same value, which is harmless.
 static float* ln_noalloc_scratch_ptr() {
-    static float* ptrs[64] = {nullptr};
+    static std::atomic<float*> ptrs[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!ptrs[dev]) {
-        float* p = nullptr;
+    float* p = ptrs[dev].load(std::memory_order_acquire);
+    if (!p) {
         if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_noalloc_scratch) != cudaSuccess) return nullptr;
-        ptrs[dev] = p;
+        ptrs[dev].store(p, std::memory_order_release);
     }
-    return ptrs[dev];
+    return p;
 }
 
 extern "C" const char* rb_ln_bwd_noalloc_strerror(int code) {

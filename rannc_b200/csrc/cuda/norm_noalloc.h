@@ -20,7 +20,10 @@
 //     rejected with RB_LN_NOALLOC_BAD_WIDTH).
 //   * The first call on a device looks up the device address of the array
 //     (cudaGetSymbolAddress, with that device current) and remembers it.  Make
-//     that first call before any stream capture begins.
+//     that first call before any stream capture begins.  The address that is
+//     used is the CURRENT device's: make the device that owns `stream` current
+//     before calling, as for any launch.  The lookup may run on several host
+//     threads at once (the cached addresses are atomics).
 //   * All calls on one device share the one array.  Nothing in it has to start
 //     at zero -- every word a call reads was written by the same call -- but two
 //     calls that overlap on the GPU (different streams, no ordering between

@@ -62,12 +62,15 @@ def lib() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        path = _HERE / "_kernels.so"
+        import os
+
+        debug = os.environ.get("RANNC_KERNEL_DEBUG", "0") == "1"
+        path = _HERE / ("_kernels_debug.so" if debug else "_kernels.so")
         if not path.exists():
             from .. import build
 
             try:
-                build.build_kernels()
+                build.build_kernels(debug=debug)
             except Exception as e:  # noqa: BLE001
                 raise KernelLibraryError(f"cannot build {path}: {e}") from e
         try:

@@ -63,3 +63,22 @@ def test_ln_bwd_noalloc_matches_regular_entry_point():
                                ctypes.c_int(1000), ctypes.c_int(4096), ctypes.c_float(0.0), ctypes.c_uint64(0),
                                ctypes.c_uint64(0), ctypes.c_int(0), ctypes.c_int(1), stream)
     assert rc == -7 and b"scratch" in lib.rb_ln_bwd_noalloc_strerror(rc)
+    # the limit itself: at H = 3072 the built-in scratch serves 394 rows and refuses 395
+    H = 3072
+    x = torch.randn(395, H, device="cuda", dtype=torch.bfloat16)
+    g = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(H, device="cuda", dtype=torch.bfloat16)
+    y, z, mean, rstd = K.ln_fwd(x, None, g, b, 1e-5, 0.0, 0, 0)
+    dy = torch.randn_like(x)
+    dz = torch.empty_like(z)
+    dg = torch.empty(H, device="cuda", dtype=torch.float32)
+    db = torch.empty(H, device="cuda", dtype=torch.float32)
+    for rows, want in ((394, 0), (395, -7)):
+        rc = lib.rb_ln_bwd_noalloc(vp(dy), vp(z), vp(g), vp(mean), vp(rstd), vp(dz), vp(None), vp(dg), vp(db),
+                                   ctypes.c_int(rows), ctypes.c_int(H), ctypes.c_float(0.0), ctypes.c_uint64(0),
+                                   ctypes.c_uint64(0), ctypes.c_int(0), ctypes.c_int(1), stream)
+        assert rc == want, (rows, rc, lib.rb_ln_bwd_noalloc_strerror(rc))
+    torch.cuda.synchronize()
+    ref_dz, _, ref_dg, _ = K.ln_bwd(dy[:394], z[:394], g, mean[:394], rstd[:394])
+    _close(dz[:394], ref_dz)
+    _close(dg, ref_dg)
