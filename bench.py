@@ -365,10 +365,26 @@ def main():
         cfg = BertConfig(hidden_size=args.hidden, num_hidden_layers=args.layers, num_attention_heads=args.heads,
                          intermediate_size=4 * args.hidden, max_position_embeddings=max(512, args.seq))
         dist_params = (args.model == "bert13b") if args.dist_params < 0 else bool(args.dist_params)
-        if dist_params:
-            # every parameter is created as a 1/world shard; full values exist only on the owners after deployment
+        big = args.model in ("bert13b", "bert26b")
+        if big:
+            # tens of billions of parameters: they are created on the device, in the 16-bit compute type, with
+            # the layers' own default initialisation (a host-side fp32 copy per rank would not fit the host)
+            import contextlib
+
+            os.environ.setdefault("RANNC_MEASURE_PROFILES", "false")
+            prev_dtype = torch.get_default_dtype()
+            torch.set_default_dtype(torch.bfloat16)
+            ctx = pyrannc.DistributeModelParams() if dist_params else contextlib.nullcontext()
+            try:
+                with torch.device(dev), ctx:
+                    # with dist_params every parameter is cut to this rank's 1/world shard as soon as its
+                    # layer exists; full values are assembled on the owners at deployment
+                    model = BertForPreTraining(cfg, init_weights=False)
+            finally:
+                torch.set_default_dtype(prev_dtype)
+        elif dist_params:
             with pyrannc.DistributeModelParams():
-                model = BertForPreTraining(cfg)
+                model = BertForPreTraining(cfg, init_weights=False)
         else:
             model = BertForPreTraining(cfg)
         optimizer = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0)

@@ -127,18 +127,31 @@ def analytic_profiles(gm: fx.GraphModule) -> Dict[str, "_core.NodeProfile"]:
     return out
 
 
-def measured_profiles(gm: fx.GraphModule, device, iters: int = 3) -> Dict[str, "_core.NodeProfile"]:
-    """Times every call_function node on ``device`` with CUDA events (forward and backward)."""
+def _with_main_grad(t: torch.Tensor) -> torch.Tensor:
+    """A stand-in for a deployed 16-bit parameter: it carries the fp32 gradient buffer the fused operators
+    accumulate into (and split K for), so that what is timed is what training runs."""
+    if t.dtype in (torch.float16, torch.bfloat16):
+        t.main_grad = torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+    return t
+
+
+def measured_profiles(gm: fx.GraphModule, device, iters: int = 3, param_names=()) -> Dict[str, "_core.NodeProfile"]:
+    """Times every call_function node on ``device`` with CUDA events (forward and backward).  ``param_names``:
+    placeholders that are parameters (their stand-ins get an fp32 gradient buffer like deployed ones)."""
     base = analytic_profiles(gm)
     if not torch.cuda.is_available():
         return base
     from .tracer import op_name
 
+    param_names = set(param_names)
+    cur = [None]
+
     def real(v):
         if isinstance(v, torch.Tensor):
             shp = _shape(v)
             if v.is_floating_point():
-                return torch.randn(shp, dtype=v.dtype, device=device).requires_grad_(True)
+                t = torch.randn(shp, dtype=v.dtype, device=device).requires_grad_(True)
+                return _with_main_grad(t) if cur[0] in param_names else t
             return torch.zeros(shp, dtype=v.dtype, device=device)
         return v
 
@@ -148,6 +161,7 @@ def measured_profiles(gm: fx.GraphModule, device, iters: int = 3) -> Dict[str, "
         try:
             def conv(a):
                 if isinstance(a, fx.Node):
+                    cur[0] = a.name
                     return real(a.meta.get("val"))
                 if isinstance(a, (list, tuple)):
                     return type(a)(conv(x) for x in a)
@@ -312,8 +326,8 @@ class SubgraphProfiler:
                     self.tm.ir.has_value(name) and self.tm.ir.value(name).is_batch:
                 shp = [max(1, int(round(shp[0] * ratio)))] + shp[1:]
             if val.is_floating_point():
-                t = torch.randn(shp, dtype=val.dtype, device=self.device) * 0.02
-                return t.requires_grad_(True)
+                t = (torch.randn(shp, dtype=val.dtype, device=self.device) * 0.02).requires_grad_(True)
+                return _with_main_grad(t) if (name in self.tm.params and self.device.type == "cuda") else t
             return torch.zeros(shp, dtype=val.dtype, device=self.device)
         if isinstance(val, (int, torch.SymInt)):
             h = int(getattr(getattr(val, "node", None), "hint", val)) if not isinstance(val, int) else val
@@ -348,9 +362,9 @@ class SubgraphProfiler:
 
         dev = self.device
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        ft = bt = fcpu = bcpu = 0.0
+        ft = bt = fcpu = bcpu = float("inf")
         peak = kept = 0
-        for it in range(self.iters + 1):
+        for it in range(max(2, self.iters) + 1):
             for a in args:
                 if isinstance(a, torch.Tensor) and a.grad is not None:
                     a.grad = None
@@ -383,12 +397,13 @@ class SubgraphProfiler:
                 if checkpointing:
                     # forward without grad + recomputation were timed together: half is the forward
                     f, b = f / 2, b + f / 2
-                ft, bt = ft + f, bt + b
-                fcpu, bcpu = fcpu + (t1 - t0) * 1e6, bcpu + (t2 - t1) * 1e6
+                # the fastest of the timed runs: allocator warm-up and clock ramps only ever add time
+                ft, bt = min(ft, f), min(bt, b)
+                fcpu, bcpu = min(fcpu, (t1 - t0) * 1e6), min(bcpu, (t2 - t1) * 1e6)
                 peak = max(peak, torch.cuda.max_memory_allocated(dev) - base)
                 kept = max(kept, held)
             del outs
-        n = self.iters
+        n = 1
         out_bytes = 0
         gp = _core.GraphProfile()
         gp.name = name

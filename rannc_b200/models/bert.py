@@ -138,7 +138,9 @@ class BertModel(nn.Module):
 class BertForPreTraining(nn.Module):
     """Returns the scalar pre-training loss: masked-LM cross entropy + next-sentence cross entropy."""
 
-    def __init__(self, cfg: BertConfig):
+    def __init__(self, cfg: BertConfig, init_weights: bool = True):
+        """``init_weights=False`` keeps the layers' own default initialisation (needed when the parameters no
+        longer hold their full values at this point, e.g. when they are sharded as they are constructed)."""
         super().__init__()
         self.cfg = cfg
         self.bert = BertModel(cfg)
@@ -146,7 +148,8 @@ class BertForPreTraining(nn.Module):
         self.transform_ln = nn.LayerNorm(cfg.hidden_size, eps=cfg.layer_norm_eps)
         self.decoder_bias = nn.Parameter(torch.zeros(cfg.padded_vocab_size))
         self.seq_relationship = nn.Linear(cfg.hidden_size, 2)
-        self.apply(self._init)
+        if init_weights:
+            self.apply(self._init)
 
     def _init(self, m):
         if isinstance(m, nn.Linear):

@@ -268,7 +268,8 @@ class RaNNCModule:
             node_profiles = profiler.load_profiles(prof_file, [n.id for n in tm.ir.nodes], tm.trace_batch, tm.ir)
             logger.info("Loaded operator profiles from %s", prof_file)
         elif measuring and rank == 0:
-            node_profiles = profiler.measured_profiles(tm.gm, dev, iters=max(1, int(conf("profiling_iter"))))
+            node_profiles = profiler.measured_profiles(tm.gm, dev, iters=max(1, int(conf("profiling_iter"))),
+                                                       param_names=tm.params.keys())
         else:
             node_profiles = profiler.analytic_profiles(tm.gm)
         if (measuring or bool(conf("measure_subgraphs"))) and rank == 0:
