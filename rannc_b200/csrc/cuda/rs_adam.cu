@@ -97,6 +97,84 @@ struct RsAdamParams {
     float* sumsq;                           // optional accumulator of the squared reduced gradients
 };
 
+// What happens to one group of 8 reduced gradient elements (index i within this rank's slice): either the
+// scaled sum goes back into this rank's own gradient buffer (reduction-only launch; returns its sum of
+// squares), or the optimizer updates master / moments and the 16-bit result is written to every rank.
+template <typename T16>
+__device__ __forceinline__ float apply_group(const RsAdamParams& p, long long i, float (&g)[8], float gmul,
+                                             bool update) {
+    const long long e = p.lo + i * 8;
+    if (p.mode & RB_RS_STORE_GRAD) {
+        float ssq = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            g[j] *= gmul;
+            ssq += g[j] * g[j];
+        }
+        *reinterpret_cast<float4*>(p.own_grad + e) = make_float4(g[0], g[1], g[2], g[3]);
+        *reinterpret_cast<float4*>(p.own_grad + e + 4) = make_float4(g[4], g[5], g[6], g[7]);
+        return ssq;
+    }
+    if (!update) return 0.f;
+    float w[8], mm[8], vv[8];
+    const bool sgd = p.adamw == 2;
+    *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i * 8);
+    *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(p.master + i * 8 + 4);
+    *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(p.m + i * 8);
+    *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(p.m + i * 8 + 4);
+    if (!sgd) {
+        *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(p.v + i * 8);
+        *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(p.v + i * 8 + 4);
+    }
+    uint4 packed;
+    T16* o = reinterpret_cast<T16*>(&packed);
+    if (sgd) {
+        // SGD with momentum (torch.optim.SGD): beta1 = momentum, beta2 = dampening, eps > 0.5 = Nesterov,
+        // bias_corr1 == 0 marks the first step (the buffer starts as the gradient)
+        const bool first = p.bias_corr1 == 0.f, nesterov = p.eps > 0.5f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float gg = g[j] * gmul;
+            if (p.weight_decay != 0.f) gg += p.weight_decay * w[j];
+            mm[j] = first ? gg : p.beta1 * mm[j] + (1.f - p.beta2) * gg;
+            const float u = nesterov ? gg + p.beta1 * mm[j] : mm[j];
+            w[j] -= p.lr * u;
+            o[j] = from_f32<T16>(w[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float gg = g[j] * gmul;
+            if (!p.adamw && p.weight_decay != 0.f) gg += p.weight_decay * w[j];
+            mm[j] = p.beta1 * mm[j] + (1.f - p.beta1) * gg;
+            vv[j] = p.beta2 * vv[j] + (1.f - p.beta2) * gg * gg;
+            float u = (mm[j] / p.bias_corr1) / (sqrtf(vv[j] / p.bias_corr2) + p.eps);
+            if (p.adamw && p.weight_decay != 0.f) u += p.weight_decay * w[j];
+            w[j] -= p.lr * u;
+            o[j] = from_f32<T16>(w[j]);
+        }
+    }
+    *reinterpret_cast<float4*>(p.master + i * 8) = *reinterpret_cast<float4*>(w);
+    *reinterpret_cast<float4*>(p.master + i * 8 + 4) = *reinterpret_cast<float4*>(w + 4);
+    *reinterpret_cast<float4*>(p.m + i * 8) = *reinterpret_cast<float4*>(mm);
+    *reinterpret_cast<float4*>(p.m + i * 8 + 4) = *reinterpret_cast<float4*>(mm + 4);
+    if (!sgd) {
+        *reinterpret_cast<float4*>(p.v + i * 8) = *reinterpret_cast<float4*>(vv);
+        *reinterpret_cast<float4*>(p.v + i * 8 + 4) = *reinterpret_cast<float4*>(vv + 4);
+    }
+    if (p.mc_param) {
+        multimem_st_b128(reinterpret_cast<T16*>(p.mc_param) + e, packed);
+    } else {
+#pragma unroll 1
+        for (int r = 0; r < p.nranks; ++r) {
+            int dst = p.my_idx + r;
+            if (dst >= p.nranks) dst -= p.nranks;
+            *reinterpret_cast<uint4*>(reinterpret_cast<T16*>(p.peer_param[dst]) + e) = packed;
+        }
+    }
+    return 0.f;
+}
+
 template <typename T16>
 __global__ void __launch_bounds__(512)
     rs_adam_ag_kernel(const RsAdamParams p) {
@@ -126,110 +204,64 @@ __global__ void __launch_bounds__(512)
     // ---- phase 1: reduce -> Adam -> scatter the 16-bit result (8 elements = one 16-byte store per step)
     if (ok && !skip) {
         const long long nvec = p.len / 8;
-        for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-             i += static_cast<long long>(gridDim.x) * blockDim.x) {
-            const long long e = p.lo + i * 8;
-            float g[8];
-            if (!pull) {
-                const float4 a = *reinterpret_cast<const float4*>(p.own_grad + e);
-                const float4 b = *reinterpret_cast<const float4*>(p.own_grad + e + 4);
-                g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
-                g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
-            } else if (p.mc_grad) {
-                const float4 a = multimem_ld_reduce_f32x4(p.mc_grad + e);
-                const float4 b = multimem_ld_reduce_f32x4(p.mc_grad + e + 4);
-                g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
-                g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
-            } else {
-                // every peer's 32 bytes are requested before any of them is used, so that the NVLink round trips
-                // overlap; own buffer first, then the peers in a per-rank rotated order
-                float4 a[RB_MAX_PEERS], b[RB_MAX_PEERS];
+        const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+        const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+        if (pull && p.mc_grad) {
+            // In-switch reduction: one multimem.ld_reduce returns the sum over all ranks.  Its round trip through
+            // the switch is long, so every thread keeps UNROLL groups (2 x 16 bytes each) in flight.
+            constexpr int UNROLL = 4;
+            for (long long i0 = first; i0 < nvec; i0 += stride * UNROLL) {
+                float4 ga[UNROLL], gb[UNROLL];
 #pragma unroll
-                for (int r = 0; r < RB_MAX_PEERS; ++r) {
-                    if (r < p.nranks) {
-                        int src = p.my_idx + r;
-                        if (src >= p.nranks) src -= p.nranks;
-                        a[r] = *reinterpret_cast<const float4*>(p.peer_grad[src] + e);
-                        b[r] = *reinterpret_cast<const float4*>(p.peer_grad[src] + e + 4);
+                for (int u = 0; u < UNROLL; ++u) {
+                    const long long i = i0 + u * stride;
+                    if (i < nvec) {
+                        ga[u] = multimem_ld_reduce_f32x4(p.mc_grad + p.lo + i * 8);
+                        gb[u] = multimem_ld_reduce_f32x4(p.mc_grad + p.lo + i * 8 + 4);
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) g[j] = 0.f;
-#pragma unroll
-                for (int r = 0; r < RB_MAX_PEERS; ++r) {
-                    if (r < p.nranks) {
-                        g[0] += a[r].x; g[1] += a[r].y; g[2] += a[r].z; g[3] += a[r].w;
-                        g[4] += b[r].x; g[5] += b[r].y; g[6] += b[r].z; g[7] += b[r].w;
+                for (int u = 0; u < UNROLL; ++u) {
+                    const long long i = i0 + u * stride;
+                    if (i < nvec) {
+                        float g[8] = {ga[u].x, ga[u].y, ga[u].z, ga[u].w, gb[u].x, gb[u].y, gb[u].z, gb[u].w};
+                        ssq += apply_group<T16>(p, i, g, gmul, update);
                     }
                 }
             }
-            if (p.mode & RB_RS_STORE_GRAD) {
-                // reduction only: the scaled sum goes back into this rank's own buffer (peers read other ranges
-                // of it), the update follows in a later launch
+        } else {
+            for (long long i = first; i < nvec; i += stride) {
+                const long long e = p.lo + i * 8;
+                float g[8];
+                if (!pull) {
+                    const float4 a = *reinterpret_cast<const float4*>(p.own_grad + e);
+                    const float4 b = *reinterpret_cast<const float4*>(p.own_grad + e + 4);
+                    g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+                    g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+                } else {
+                    // every peer's 32 bytes are requested before any of them is used, so that the NVLink round
+                    // trips overlap; own buffer first, then the peers in a per-rank rotated order
+                    float4 a[RB_MAX_PEERS], b[RB_MAX_PEERS];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    g[j] *= gmul;
-                    ssq += g[j] * g[j];
-                }
-                *reinterpret_cast<float4*>(p.own_grad + e) = make_float4(g[0], g[1], g[2], g[3]);
-                *reinterpret_cast<float4*>(p.own_grad + e + 4) = make_float4(g[4], g[5], g[6], g[7]);
-                continue;
-            }
-            if (!update) continue;
-            float w[8], mm[8], vv[8];
-            const bool sgd = p.adamw == 2;
-            *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i * 8);
-            *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(p.master + i * 8 + 4);
-            *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(p.m + i * 8);
-            *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(p.m + i * 8 + 4);
-            if (!sgd) {
-                *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(p.v + i * 8);
-                *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(p.v + i * 8 + 4);
-            }
-            uint4 packed;
-            T16* o = reinterpret_cast<T16*>(&packed);
-            if (sgd) {
-                // SGD with momentum (torch.optim.SGD): beta1 = momentum, beta2 = dampening, eps > 0.5 = Nesterov,
-                // bias_corr1 == 0 marks the first step (the buffer starts as the gradient)
-                const bool first = p.bias_corr1 == 0.f, nesterov = p.eps > 0.5f;
+                    for (int r = 0; r < RB_MAX_PEERS; ++r) {
+                        if (r < p.nranks) {
+                            int src = p.my_idx + r;
+                            if (src >= p.nranks) src -= p.nranks;
+                            a[r] = *reinterpret_cast<const float4*>(p.peer_grad[src] + e);
+                            b[r] = *reinterpret_cast<const float4*>(p.peer_grad[src] + e + 4);
+                        }
+                    }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float gg = g[j] * gmul;
-                    if (p.weight_decay != 0.f) gg += p.weight_decay * w[j];
-                    mm[j] = first ? gg : p.beta1 * mm[j] + (1.f - p.beta2) * gg;
-                    const float u = nesterov ? gg + p.beta1 * mm[j] : mm[j];
-                    w[j] -= p.lr * u;
-                    o[j] = from_f32<T16>(w[j]);
-                }
-            } else {
+                    for (int j = 0; j < 8; ++j) g[j] = 0.f;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float gg = g[j] * gmul;
-                    if (!p.adamw && p.weight_decay != 0.f) gg += p.weight_decay * w[j];
-                    mm[j] = p.beta1 * mm[j] + (1.f - p.beta1) * gg;
-                    vv[j] = p.beta2 * vv[j] + (1.f - p.beta2) * gg * gg;
-                    float u = (mm[j] / p.bias_corr1) / (sqrtf(vv[j] / p.bias_corr2) + p.eps);
-                    if (p.adamw && p.weight_decay != 0.f) u += p.weight_decay * w[j];
-                    w[j] -= p.lr * u;
-                    o[j] = from_f32<T16>(w[j]);
+                    for (int r = 0; r < RB_MAX_PEERS; ++r) {
+                        if (r < p.nranks) {
+                            g[0] += a[r].x; g[1] += a[r].y; g[2] += a[r].z; g[3] += a[r].w;
+                            g[4] += b[r].x; g[5] += b[r].y; g[6] += b[r].z; g[7] += b[r].w;
+                        }
+                    }
                 }
-            }
-            *reinterpret_cast<float4*>(p.master + i * 8) = *reinterpret_cast<float4*>(w);
-            *reinterpret_cast<float4*>(p.master + i * 8 + 4) = *reinterpret_cast<float4*>(w + 4);
-            *reinterpret_cast<float4*>(p.m + i * 8) = *reinterpret_cast<float4*>(mm);
-            *reinterpret_cast<float4*>(p.m + i * 8 + 4) = *reinterpret_cast<float4*>(mm + 4);
-            if (!sgd) {
-                *reinterpret_cast<float4*>(p.v + i * 8) = *reinterpret_cast<float4*>(vv);
-                *reinterpret_cast<float4*>(p.v + i * 8 + 4) = *reinterpret_cast<float4*>(vv + 4);
-            }
-            if (p.mc_param) {
-                multimem_st_b128(reinterpret_cast<T16*>(p.mc_param) + e, packed);
-            } else {
-#pragma unroll 1
-                for (int r = 0; r < p.nranks; ++r) {
-                    const int dst = (p.my_idx + r) % p.nranks;
-                    *reinterpret_cast<uint4*>(reinterpret_cast<T16*>(p.peer_param[dst]) + e) = packed;
-                }
+                ssq += apply_group<T16>(p, i, g, gmul, update);
             }
         }
     }

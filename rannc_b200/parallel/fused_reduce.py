@@ -109,7 +109,10 @@ class FusedGradReducer:
         self.handles_reduce = True
         self.pending = False                # local gradients are final, (part of) the reduction is still to come
         self.plain_groups = []
-        self.use_multimem = bool(int(os.environ.get("RANNC_USE_MULTIMEM", "1")))
+        # multimem.ld_reduce / multimem.st through the switch, or plain peer loads / stores.  Measured on two and
+        # on eight B200s the peer-load path is the faster one for this access pattern (every thread keeps
+        # 2 x nranks 16-byte loads in flight), so it is the default; RANNC_USE_MULTIMEM=1 selects the other.
+        self.use_multimem = bool(int(os.environ.get("RANNC_USE_MULTIMEM", "0")))
         self.stream: Optional[torch.cuda.Stream] = None
         self.overlap = bool(conf("overlap_grad_reduce"))
         self.update_in_backward = bool(conf("fused_update_in_backward"))
