@@ -124,7 +124,7 @@ const Def kDefs[] = {
     {"comm_retry", ConfigItem::INT, "1"},                 // retries of a failed collective after re-creating groups
     {"comm_retry_wait_s", ConfigItem::FLOAT, "1"},
     {"check_device_error_every_step", ConfigItem::BOOL, "true"},
-    {"cuda_graphs", ConfigItem::BOOL, "false"},           // replay a stage's forward / backward as CUDA graphs
+    {"keep_dist_params_sharded", ConfigItem::BOOL, "false"},  // dist_param weights of linear layers stay sliced
 };
 }  // namespace
 

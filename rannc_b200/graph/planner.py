@@ -46,7 +46,7 @@ def make_partitioning_conf(world_size: int, batch_size: int, dev_mem: int, use_a
     c.use_amp_master_params = use_amp
     c.enable_zero = enable_zero
     c.offload_params = offload_params
-    c.force_dist_matmul = bool(conf("force_dist_matmul"))
+    c.force_dist_matmul = bool(conf("force_dist_matmul")) or bool(conf("keep_dist_params_sharded"))
     c.opt_param_factor = int(conf("opt_param_factor"))
     c.min_pipeline = int(conf("min_pipeline"))
     c.max_pipeline = int(conf("max_pipeline"))

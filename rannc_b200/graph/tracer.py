@@ -247,7 +247,14 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
 
         from ..utils.config import conf
 
-        stats = rewrite.fuse(gm, training=model.training, keep_linear=bool(conf("force_dist_matmul")))
+        # linear layers that will run tensor-partitioned stay nodes of their own: all of them under
+        # force_dist_matmul, and under keep_dist_params_sharded when the model was declared in shards
+        keep = bool(conf("force_dist_matmul"))
+        if not keep and bool(conf("keep_dist_params_sharded")):
+            from .. import dist_param as _dp
+
+            keep = any(_dp.dist_param_registered(id(p)) for p in model.parameters())
+        stats = rewrite.fuse(gm, training=model.training, keep_linear=keep)
     else:
         from . import rewrite
 

@@ -347,21 +347,40 @@ class RaNNCModule:
             self._verify_partitioning(tm, dep, args, name_to_param, name_to_buffer)
         # tensor-partitioned linear layers: which nodes, which weights, over which ranks
         dist_kernels = dev.type == "cuda" and bool(conf("fused_kernels")) and self.use_amp_master_params
-        dist_nodes, sliced = self._select_dist_linears(tm, dep, name_to_param, owner, 256 if dist_kernels else 1) \
-            if bool(conf("force_dist_matmul")) else ({}, {})
+        # force_dist_matmul: every eligible linear layer.  keep_dist_params_sharded: the linear layers whose weight
+        # was declared in shards (DistributeModelParams) -- such a weight is never kept whole: each replica of
+        # its stage stores one column slice, and the layer's GEMM gathers the slices from the peers in its
+        # prologue (forward and input gradient) and scatters the weight gradient in its epilogue.
+        force = bool(conf("force_dist_matmul"))
+        keep_sharded = bool(conf("keep_dist_params_sharded")) and not force
+        if force or keep_sharded:
+            only = {id(p) for p in name_to_param.values() if _dp.dist_param_registered(id(p))} if keep_sharded \
+                else None
+            dist_nodes, sliced = self._select_dist_linears(tm, dep, name_to_param, owner,
+                                                           256 if dist_kernels else 1, only_params=only)
+        else:
+            dist_nodes, sliced = {}, {}
         for fq, ranks in sliced.items():
             p = name_to_param[fq]
-            if _dp.dist_param_registered(id(p)):
-                raise RuntimeError(f"{fq}: a parameter cannot be both a dist_param and tensor-partitioned")
-            if _sync_params_on_init:
+            was_dist = _dp.dist_param_registered(id(p))
+            if was_dist:
+                # assembled once (collective over the world, every rank in the same order), cut into the column
+                # slice this rank keeps, and dropped again: the peak is one parameter, not the model
+                full = _dp.load_dist_param(id(p), dev)
+                _dp.remove_dist_param(id(p))
+            if _sync_params_on_init and not was_dist:
                 comm.create_groups([ranks])
             if rank in ranks:
-                full = p.data.to(dev)
-                if _sync_params_on_init:
-                    comm.bcast(full, ranks[0], ranks)
+                if not was_dist:
+                    full = p.data.to(dev)
+                    if _sync_params_on_init:
+                        comm.bcast(full, ranks[0], ranks)
                 ks = full.shape[1] // len(ranks)
                 i = ranks.index(rank)
                 p.data = full[:, i * ks:(i + 1) * ks].contiguous()
+            elif was_dist:
+                p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+            full = None
         unused_params = [n for n, r in owner.items() if not r]
         for n in unused_params:
             owner[n] = {0}
@@ -509,7 +528,7 @@ class RaNNCModule:
 
     # ------------------------------------------------------------------ tensor-partitioned linear layers
     @staticmethod
-    def _select_dist_linears(tm, dep, name_to_param, owner, col_unit: int = 1):
+    def _select_dist_linears(tm, dep, name_to_param, owner, col_unit: int = 1, only_params=None):
         """Every ``linear`` whose stage has more than one replica and whose weight is a plain 2-D parameter
         used by that node alone is partitioned along its input dimension over the replicas
         (reference: src/distop/PartitionTensor.cpp:230-298, config force_dist_matmul).  Deterministic: every
@@ -544,6 +563,8 @@ class RaNNCModule:
                 fq = tm.params[w.name]
                 p = name_to_param.get(fq)
                 if p is None or p.dim() != 2 or use_count.get(w.name, 0) != 1 or set(owner[fq]) != set(ranks):
+                    continue
+                if only_params is not None and id(p) not in only_params:
                     continue
                 if p.shape[1] % (col_unit * n):   # the kernels move slices in 256-column tiles
                     continue

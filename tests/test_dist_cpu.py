@@ -186,6 +186,16 @@ def test_dist_param_model_declared_in_shards(env):
     run_case(2, {"model": "deep", "batch": 8, "dist_param": True}, env)
 
 
+def test_dist_param_weights_stay_sliced_through_training():
+    # keep_dist_params_sharded: the linear weights declared in shards are re-cut into column slices over the
+    # replicas and never exist whole; everything else of the run must still match eager on the full batch
+    res = run_case(2, {"model": "deep", "batch": 8, "dist_param": True}, {"RANNC_KEEP_DIST_PARAMS_SHARDED": "true"})
+    assert res["ranks"][0]["sliced"] > 0
+    res = run_case(4, {"model": "deep", "batch": 16, "dist_param": True, "opt": "adam"},
+                   {"RANNC_KEEP_DIST_PARAMS_SHARDED": "true", "RANNC_PARTITION_NUM": "2"})
+    assert res["ranks"][0]["sliced"] > 0 and res["ranks"][0]["stages"] == 2
+
+
 def test_input_gradients_dp2_and_pp2():
     run_case(2, {"model": "deep", "batch": 8, "input_grad": True})
     run_case(2, {"model": "deep", "batch": 8, "input_grad": True}, {"RANNC_PARTITION_NUM": "2"})
