@@ -14,10 +14,18 @@ def _ref(a, b, trans_a, trans_b):
     return a32 @ b32
 
 
-def _check(out, ref, tol=2e-2):
-    err = (out.float() - ref).abs().max().item()
+def _check(out, ref, tol=2e-2, elementwise=True):
+    """Two criteria.  The largest error relative to the largest reference value (catches a wrong tile), and --
+    for outputs that were rounded once to 16 bits from an fp32 accumulator -- every element on its own:
+    |err| <= atol + rtol * |ref| with atol a tenth of the first criterion's, so that an error confined to
+    small-magnitude outputs does not hide behind the large ones."""
+    d = (out.float() - ref).abs()
     scale = ref.abs().max().item() + 1e-6
-    assert err / scale < tol, f"rel err {err / scale}"
+    assert d.max().item() / scale < tol, f"rel err {d.max().item() / scale}"
+    if elementwise:
+        bound = 0.1 * tol * scale + tol * ref.abs()
+        bad = d > bound
+        assert not bad.any(), f"{int(bad.sum())} element(s) outside atol + rtol|ref|, worst {float((d - bound).max())}"
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
