@@ -82,7 +82,16 @@ def lib() -> ctypes.CDLL:
         return _lib
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_cur_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream_ptr() -> ctypes.c_void_p:
+    """The current stream of the current device.  Asked of the C layer directly: ``torch.cuda.current_stream``
+    spends some 15 us per call on device-index bookkeeping, which at hundreds of launches per step was a third
+    of the host time of a step."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(_cur_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

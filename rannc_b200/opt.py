@@ -190,7 +190,18 @@ def patch_optimizer(module, optimizer):
         return out
 
     def _publish_state(g, fs):
-        """Per-parameter views of the flat moments in ``optimizer.state`` (torch's own layout)."""
+        """Per-parameter views of the flat moments in ``optimizer.state`` (torch's own layout).  The views are
+        made once: the moment buffers live as long as the optimizer, so later steps only refresh the step
+        count (one tensor shared by the group's entries) unless the entries were replaced meanwhile."""
+        probe = getattr(fs, "published", None)
+        if probe is not None:
+            st = optimizer.state.get(probe[0])
+            if st is not None and st.get(probe[1]) is probe[2] and probe[3] == fs.m.data_ptr():
+                fs.step_t.fill_(float(fs.step))
+                return
+        fs.step_t = torch.tensor(float(fs.step))
+        key = "exp_avg" if optimizer._rannc_kind == "adam" else "momentum_buffer"
+        fs.published = None
         for i, p in enumerate(g.params):
             target = g.master_params[i] if (g.flat_master is not None and g.master_params) else p
             if target is None or g.opt_group[i] < 0:
@@ -200,14 +211,18 @@ def patch_optimizer(module, optimizer):
                 continue
             la = g.to_local(a)
             st = optimizer.state[target]
-            st["step"] = torch.tensor(float(fs.step))
             # a parameter cut by a slice boundary keeps its state as a flat piece
             shp = target.shape if (b - a) == target.numel() else (b - a,)
             if optimizer._rannc_kind == "adam":
+                st["step"] = fs.step_t
                 st["exp_avg"] = fs.m[la:la + (b - a)].view(shp)
                 st["exp_avg_sq"] = fs.v[la:la + (b - a)].view(shp)
             else:
                 st["momentum_buffer"] = fs.m[la:la + (b - a)].view(shp)
+            if fs.published is None:
+                fs.published = (target, key, st[key], fs.m.data_ptr())
+
+    optimizer._rannc_publish_state = _publish_state
 
     def _offloaded_update(g, fs, hp, og, a, b, kind, ctrl):
         """Streams [a, b) of the host-resident fp32 state through the device in chunks."""

@@ -465,19 +465,7 @@ class FusedGradReducer:
         for g in self.storage.groups:
             if g.flat_master is None:
                 continue
-            fs = self._moments(g)
-            for i, mp in enumerate(g.master_params):
-                if mp is None or g.opt_group[i] < 0:
-                    continue
-                a, b = g.local_range(i)
-                la, n = g.to_local(a), b - a
-                s = self.optimizer.state[mp]
-                if fs.v is None:
-                    s["momentum_buffer"] = fs.m[la:la + n].view(mp.shape)
-                    continue
-                s["step"] = torch.tensor(float(fs.step))
-                s["exp_avg"] = fs.m[la:la + n].view(mp.shape)
-                s["exp_avg_sq"] = fs.v[la:la + n].view(mp.shape)
+            self.optimizer._rannc_publish_state(g, self._moments(g))
 
 
 def compare_with_collectives(module, optimizer, run_step) -> float:

@@ -30,7 +30,18 @@ def main():
     else:
         cfg = BertConfig.tiny(hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
                               num_hidden_layers=case.get("layers", 2))
-        model = BertForPreTraining(cfg)
+        if case.get("dist_param"):
+            # declared in shards: every rank keeps 1/world of each parameter until deployment
+            full = BertForPreTraining(cfg)
+            torch.manual_seed(0)
+            with pyrannc.DistributeModelParams():
+                model = BertForPreTraining(cfg, init_weights=False)
+            with torch.no_grad():
+                for (_, p), (_, q) in zip(model.named_parameters(), full.named_parameters()):
+                    pyrannc.set_dist_param(id(p), q)
+            del full
+        else:
+            model = BertForPreTraining(cfg)
     if case.get("opt", "adam") == "sgd":
         opt = torch.optim.SGD(model.parameters(), lr=0.02, momentum=0.9, weight_decay=1e-4)
     else:

@@ -180,6 +180,23 @@ def test_force_dist_matmul_over_two_gpus(tmp_path):
     _compare(a, b, 3e-2)
 
 
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_dist_param_weights_stay_sliced_on_the_kernels(tmp_path):
+    """A model declared under DistributeModelParams with keep_dist_params_sharded: its linear weights are never
+    assembled whole -- each GPU keeps one column slice, the GEMM gathers the peers' slices in its prologue and
+    scatters the weight gradient in its epilogue -- and training matches the run with whole weights."""
+    env = {"NCCL_NVLS_ENABLE": "0", "RANNC_USE_MULTIMEM": "0"}
+    case = {"opt": "sgd", "zero": False, "iters": 3}
+    a = _run(2, dict(case, dist_param=True, out=str(tmp_path / "a.pt")),
+             dict(env, RANNC_KEEP_DIST_PARAMS_SHARDED="true"))
+    b = _run(2, dict(case, out=str(tmp_path / "b.pt")), env)
+    assert a["infos"][0]["sliced"] > 0 and b["infos"][0]["sliced"] == 0
+    assert all(i["err"] == 0 for i in a["infos"])
+    for la, lb in zip(a["infos"][0]["losses"], b["infos"][0]["losses"]):
+        assert abs(la - lb) < 3e-2 * abs(lb)
+    _tight(a, b, 3e-2, "keep_dist_params_sharded")
+
+
 @pytest.mark.skipif(_ngpu() < 1, reason="needs a GPU")
 def test_offloaded_optimizer_state_matches_resident(tmp_path):
     # fp32 master weights and Adam moments in pinned host memory, streamed through the device in chunks
