@@ -20,6 +20,7 @@ from torch.export import Dim
 from torch.export.graph_signature import InputKind, OutputKind
 
 from .. import _core
+from ..utils.config import conf
 
 logger = logging.getLogger("rannc")
 
@@ -92,6 +93,7 @@ class TracedModel:
     dynamic_batch: bool = True
     rewrite_stats: Dict[str, int] = field(default_factory=dict)
     trace_batch: int = 0
+    dim_names: Dict[str, List[str]] = field(default_factory=dict)   # use_named_tensors: value -> name per dim
 
 
 def _flatten_args_keep_none(args) -> list:
@@ -150,6 +152,26 @@ def _batch_hint(val, dynamic_batch: bool) -> int:
     if not dynamic_batch or not isinstance(val, torch.Tensor) or val.dim() == 0:
         return 0
     return 1 if any(not isinstance(d, int) for d in val.shape) else -1
+
+
+def trace_dim_names(gm: fx.GraphModule) -> Dict[str, List[str]]:
+    """Name of every dimension of every tensor value of a trace made with a symbolic batch: ``"N"`` where the
+    extent derives from the batch symbol, ``<value>_D<i>`` otherwise.
+
+    The reference learns the same thing by running every node once on named tensors and reading the names that
+    come out (``use_named_tensors``; src/comp/GraphProfiler.cpp:135-243, names built as in ``createDimnames``
+    :149-170); here the symbolic shapes ``torch.export`` attaches to each node already carry it, so nothing
+    is executed."""
+    import re
+
+    out: Dict[str, List[str]] = {}
+    for n in gm.graph.nodes:
+        val = n.meta.get("val")
+        if not isinstance(val, torch.Tensor):
+            continue
+        base = re.sub(r"_+", "_", re.sub(r"[_:\[\]\.]+", "_", n.name))
+        out[n.name] = ["N" if not isinstance(d, int) else f"{base}_D{i}" for i, d in enumerate(val.shape)]
+    return out
 
 
 def fx_to_ir(gm: fx.GraphModule, name: str, param_placeholders, user_inputs, batch_size: int,
@@ -245,8 +267,6 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
     if use_kernels:
         from . import rewrite
 
-        from ..utils.config import conf
-
         # linear layers that will run tensor-partitioned stay nodes of their own: all of them under
         # force_dist_matmul, and under keep_dist_params_sharded when the model was declared in shards
         keep = bool(conf("force_dist_matmul"))
@@ -283,6 +303,14 @@ def trace(model: torch.nn.Module, args: Tuple[torch.Tensor, ...], use_kernels: b
     param_like = set(params) | set(buffers) | set(constants)
     ir = fx_to_ir(gm, name, param_like, user_inputs, batch, dynamic_batch=bool(dyn))
     out_spec = getattr(ep.module_call_graph[0].signature, "out_spec", None) if ep.module_call_graph else None
+    names: Dict[str, List[str]] = {}
+    if dyn and bool(conf("use_named_tensors")):
+        names = trace_dim_names(gm)
+        off0 = [v for v, dn in names.items() if "N" in dn[1:] and v not in param_like]
+        if off0:
+            # micro-batches and replicas split dimension 0; a value that carries the batch elsewhere still
+            # works (it is produced and consumed inside one stage or moved whole) but is worth knowing about
+            logger.info("values whose batch dimension is not the first one: %s", ", ".join(off0[:8]))
     return TracedModel(gm=gm, ir=ir, user_inputs=user_inputs, params=params, buffers=buffers, constants=constants,
                        user_outputs=user_outputs, buffer_mutations=buffer_mutations, out_spec=out_spec,
-                       dynamic_batch=dyn, rewrite_stats=stats, trace_batch=batch)
+                       dynamic_batch=dyn, rewrite_stats=stats, trace_batch=batch, dim_names=names)

@@ -859,6 +859,12 @@ class RaNNCModule:
 
         return _IncompatibleKeys(missing, unexpected)
 
+    def dim_names(self) -> Dict[str, List[str]]:
+        """With ``use_named_tensors``: traced value -> a name per dimension, ``"N"`` for the batch
+        (reference: the names its profiler puts on tensors, src/comp/GraphProfiler.cpp:149-170).  Empty before
+        the first call of the module or when the switch is off."""
+        return dict(self._traced.dim_names) if self._traced is not None else {}
+
     def save_deployment(self, path: str) -> None:
         if comm.get_rank() == 0:
             with open(path, "wb") as f:

@@ -305,10 +305,36 @@ def sync_with_error_check(timeout_s: float = 0.0) -> None:
 
 
 # ---------------------------------------------------------------- tensors
-def allreduce(t: torch.Tensor, op: str = "sum", ranks: Optional[Sequence[int]] = None, async_op: bool = False):
-    if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
+def _premul_sum(scale: float):
+    """NCCL's PreMulSum reduction operator (every contribution is multiplied by ``scale`` on its way into the sum,
+    inside the collective); None where the backend has none (reference: ncclRedOpCreatePreMulSum,
+    src/comm/NCCLWrapper.cpp:340-372)."""
+    if _S.backend != "nccl" or scale == 1.0:
         return None
-    rop = {"sum": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op]
+    make = getattr(dist, "_make_nccl_premul_sum", None)
+    if make is None:
+        return None
+    try:
+        return make(float(scale))
+    except Exception:  # noqa: BLE001 -- a build of torch without the operator
+        return None
+
+
+def allreduce(t: torch.Tensor, op: str = "sum", ranks: Optional[Sequence[int]] = None, async_op: bool = False,
+              scale: float = 1.0):
+    """``scale`` (with ``op="sum"``): every rank's contribution is multiplied by it first -- inside the
+    collective where the backend can (PreMulSum), by one extra pass over ``t`` otherwise."""
+    if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
+        if scale != 1.0:
+            t.mul_(scale)
+        return None
+    if scale != 1.0 and op == "sum":
+        rop = _premul_sum(scale)
+        if rop is None:
+            t.mul_(scale)
+            rop = dist.ReduceOp.SUM
+    else:
+        rop = {"sum": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op]
     return _with_retry("all-reduce", lambda: dist.all_reduce(t, op=rop, group=group(ranks), async_op=async_op))
 
 
@@ -325,9 +351,13 @@ def allgather_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Sequenc
     _with_retry("all-gather", lambda: dist.all_gather_into_tensor(out, inp, group=group(ranks)))
 
 
-def reduce_scatter_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Sequence[int]] = None) -> None:
+def reduce_scatter_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Sequence[int]] = None,
+                        scale: float = 1.0) -> None:
+    """``scale``: as for :func:`allreduce`; ``inp`` is left unscaled when the collective applies it."""
     if get_world_size() == 1 or (ranks is not None and len(_key(ranks)) <= 1):
         out.copy_(inp.view(-1)[: out.numel()].view_as(out))
+        if scale != 1.0:
+            out.mul_(scale)
         return
     if _S.backend == "gloo":
         # gloo has no reduce-scatter: all-reduce a copy and keep this rank's piece (CPU rank harness only)
@@ -338,11 +368,18 @@ def reduce_scatter_into(out: torch.Tensor, inp: torch.Tensor, ranks: Optional[Se
             n = out.numel()
             i = dist.get_rank(g)
             out.copy_(full.view(-1)[i * n:(i + 1) * n].view_as(out))
+            if scale != 1.0:
+                out.mul_(scale)
 
         _with_retry("reduce-scatter", via_allreduce)
         return
-    _with_retry("reduce-scatter",
-                lambda: dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=group(ranks)))
+    rop = _premul_sum(scale) if scale != 1.0 else dist.ReduceOp.SUM
+    post = 1.0
+    if rop is None:
+        rop, post = dist.ReduceOp.SUM, scale
+    _with_retry("reduce-scatter", lambda: dist.reduce_scatter_tensor(out, inp, op=rop, group=group(ranks)))
+    if post != 1.0:
+        out.mul_(post)
 
 
 def send_recv(t: Optional[torch.Tensor], src: int, dst: int) -> None:

@@ -323,10 +323,9 @@ class ParamStorage:
         world = comm.get_world_size()
         self.fold_model_grads()
         for g in self.groups:
-            if world > 1:
-                g.flat_grad.mul_(1.0 / world)
-            if g.nranks > 1:
-                comm.allreduce(g.flat_grad, "sum", g.ranks)
+            # the divisor is the world size whatever the size of the owner set: every rank saw its share of
+            # the global batch.  The scaling rides inside the collective where NCCL's PreMulSum is available.
+            comm.allreduce(g.flat_grad, "sum", g.ranks, scale=1.0 / world)
         self._sync_if_asked()
 
     def allreduce_grads_zero(self, only=None):
@@ -337,15 +336,14 @@ class ParamStorage:
         for g in self.groups:
             if only is not None and g not in only:
                 continue
-            if world > 1:
-                g.flat_grad.mul_(1.0 / world)
+            scale = 1.0 / world
             if g.nranks > 1 and g.zero:
                 for (lo, hi), (a, b, _) in zip(g.buckets, g.pieces):
                     out = torch.empty(b - a, dtype=g.flat_grad.dtype, device=g.device)
-                    comm.reduce_scatter_into(out, g.flat_grad[lo:hi], g.ranks)
+                    comm.reduce_scatter_into(out, g.flat_grad[lo:hi], g.ranks, scale=scale)
                     g.flat_grad[a:b].copy_(out)
-            elif g.nranks > 1:
-                comm.allreduce(g.flat_grad, "sum", g.ranks)
+            else:
+                comm.allreduce(g.flat_grad, "sum", g.ranks, scale=scale)
         self._sync_if_asked()
 
     @staticmethod

@@ -841,3 +841,80 @@ def test_keyword_arguments_are_bound_by_the_forward_signature():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0 and "KW OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+# ----------------------------------------------------------------------------- byte-level goldens
+def test_serialised_bytes_match_an_independent_msgpack_encoder():
+    """The files this library writes are meant to be readable by the reference's loaders, whose classes are
+    serialised positionally by msgpack-c (src/graph/ir.h:225-227,381,458-459,603-604;
+    src/comp/GraphProfiler.h:54-57).  The positional structures below are written out by hand from those field
+    lists and encoded with the ``msgpack`` Python package; the native encoder must produce the same bytes, and
+    bytes frozen in this file must still load."""
+    import msgpack
+
+    SIZE_MAX = 2 ** 64 - 1
+    g = _core.IRGraph()
+    g.name, g.batch_size = "g", 4
+    g.add_input(_core.IRValue("x", _t([4, 3])))
+    g.add_value(_core.IRValue("y", _t([4, 3], _core.IRTensorElemType.HALF, True)))
+    g.add_node(_core.IRNode("aten::relu", ["x"], ["y"], "relu_1"))
+    g.add_output("y")
+
+    def ir_type(elem, dims, rg):
+        # base_type (TENSOR = 1), scalar_type (NONE = 0), tensor_dim, tensor_elem_type, requires_grad,
+        # list_type (not meaningful for a tensor; this library writes GENERIC = 4), compound_types, list_size,
+        # func_name
+        return [1, 0, dims, elem, rg, 4, [], SIZE_MAX, ""]
+
+    def ir_value(name, ty):
+        return [name, ty, False, False, False, 0]      # name, type, is_param, is_batch, is_loss, batch_size
+
+    want = ["g",
+            [["aten::relu", ["x"], ["y"], "relu_1", False, False, 0]],   # name, inputs, outputs, id, flags, batch
+            {"x": ir_value("x", ir_type(3, [4, 3], False)), "y": ir_value("y", ir_type(4, [4, 3], True))},
+            ["x"], ["y"], True, 4]
+    assert g.dumps() == msgpack.packb(want)
+    frozen = bytes.fromhex(
+        "97a1679197aa6174656e3a3a72656c7591a17891a179a672656c755f31c2c20082a17896a17899010092040303c20490cfffff"
+        "ffffffffffffa0c2c2c200a17996a17999010092040304c30490cfffffffffffffffffa0c2c2c20091a17891a179c304")
+    assert g.dumps() == frozen
+    g2 = _core.IRGraph.loads(frozen)
+    assert str(g2) == str(g) and g2.dumps() == frozen
+    assert g2.values["y"].type.requires_grad and g2.values["y"].type.tensor_dim == [4, 3]
+
+    p = _core.GraphProfile()
+    p.name, p.fwd_time, p.bwd_time, p.max_allocated_mem = "g", 11, 22, 33
+    # name, fwd_time, fwd_cpu_time, fwd_cuda_time, bwd_time, bwd_cpu_time, bwd_cuda_time, max_allocated_mem,
+    # param_size, input_size, output_size, working_mem, activation_size, checkpointing
+    assert p.dumps() == msgpack.packb(["g", 11, 0, 0, 22, 0, 0, 33, 0, 0, 0, 0, 0, False])
+    assert p.dumps() == bytes.fromhex("9ea1670b0000160000210000000000c2")
+
+
+def test_dimension_names_follow_the_batch_through_the_trace(monkeypatch):
+    """``use_named_tensors``: the batch dimension is named "N" wherever it ends up, other dimensions after the
+    value (reference: src/comp/GraphProfiler.cpp:149-170)."""
+    import torch
+
+    from rannc_b200.graph import tracer
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = torch.nn.Linear(8, 4)
+
+        def forward(self, x):
+            return self.lin(x).transpose(0, 1).sum(1)
+
+    monkeypatch.setenv("RANNC_USE_NAMED_TENSORS", "true")
+    _core.config_reload()
+    try:
+        tm = tracer.trace(M(), (torch.randn(4, 8),), use_kernels=False, name="m")
+    finally:
+        monkeypatch.delenv("RANNC_USE_NAMED_TENSORS")
+        _core.config_reload()
+    assert tm.dim_names["x"] == ["N", "x_D1"]
+    assert tm.dim_names["linear"] == ["N", "linear_D1"]
+    assert tm.dim_names["transpose"] == ["transpose_D0", "N"]
+    assert "N" not in tm.dim_names["sum_1"] and "N" not in tm.dim_names["p_lin_weight"]
+    tm2 = tracer.trace(M(), (torch.randn(4, 8),), use_kernels=False, name="m")
+    assert tm2.dim_names == {}
