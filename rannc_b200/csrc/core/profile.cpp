@@ -1,5 +1,7 @@
 #include "profile.h"
 
+#include "runtime_util.h"
+
 #include <algorithm>
 #include <cmath>
 #include <functional>
@@ -174,8 +176,16 @@ double calcAllReduceTime(const LinkModel& l, int64_t bytes, int nranks) {
     return l.latency_us + static_cast<double>(bytes) * factor / l.allreduce_bytes_per_us;
 }
 
+// Bytes of the device window through which 16-bit parameters and their gradients are streamed from host memory
+// (offload_params with offload_param_window_mb > 0); 0: they are resident.
+static int64_t paramWindowBytes(const PartitioningConf& conf) {
+    if (!conf.offload_params || !conf.use_amp_master_params) return 0;
+    return std::max<int64_t>(0, Config::get().getInt("offload_param_window_mb")) << 20;
+}
+
 int64_t getOptMemSize(const IRGraph& g, const PartitioningConf& conf, int zero_ranks) {
     const int z = conf.enable_zero ? std::max(1, zero_ranks) : 1;
+    const bool streamed = paramWindowBytes(conf) > 0;
     int64_t total = 0;
     for (const auto& n : g.input_names) {
         const IRValue& v = g.value(n);
@@ -187,7 +197,7 @@ int64_t getOptMemSize(const IRGraph& g, const PartitioningConf& conf, int zero_r
             // fp32 gradient buffer (whole), fp32 master copy and optimizer state (sharded under ZeRO);
             // with offload_params the master copy and the optimizer state live in pinned host memory and
             // only a fixed staging window is on the device
-            total += 2 * sz;
+            if (!streamed) total += 2 * sz;   // streamed: the gradients live on the host too
             if (!conf.offload_params) {
                 total += (2 * sz) / z;
                 total += (static_cast<int64_t>(conf.opt_param_factor) * 2 * sz) / z;
@@ -204,6 +214,18 @@ int64_t calcGraphMem(const IRGraph& g, const GraphProfile& prof, const Partition
                      int pipeline_num, bool checkpointing) {
     const int64_t opt = getOptMemSize(g, conf, repl);
     const int64_t P = std::max(1, pipeline_num);
+    const int64_t window = paramWindowBytes(conf);
+    if (window > 0 && prof.param_size > 0) {
+        // streamed parameters: two segments' parameters (half a window each) and one segment's fp32 gradients
+        // are on the device; the stage recomputes segment by segment, keeping the inputs of every segment for
+        // every micro-batch in flight
+        const int64_t half = std::max<int64_t>(1, window / 2);
+        const int64_t nseg = std::max<int64_t>(1, (prof.param_size + half - 1) / half);
+        const int64_t params = std::min(prof.param_size, window) + std::min(2 * prof.param_size, window);
+        const int64_t act_s = P * prof.input_size * nseg + prof.activation_size / nseg;
+        IRGraph scaled_s = g;
+        return params + act_s + prof.working_mem + opt + scaled_s.commBufSize() * std::min<int64_t>(P, 2);
+    }
     int64_t act;
     if (checkpointing) {
         // stage inputs of every in-flight micro-batch + one micro-batch's activations

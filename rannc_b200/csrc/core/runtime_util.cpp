@@ -99,6 +99,7 @@ const Def kDefs[] = {
     {"watchdog_lockfile_dir", ConfigItem::STRING, ""},
     {"force_dist_matmul", ConfigItem::BOOL, "false"},
     {"offload_chunk_numel", ConfigItem::INT, "33554432"},
+    {"offload_param_window_mb", ConfigItem::INT, "0"},
     {"use_named_tensors", ConfigItem::BOOL, "false"},
     {"profiler_cache_size", ConfigItem::INT, "0"},
     {"enable_kineto", ConfigItem::BOOL, "false"},

@@ -401,7 +401,13 @@ class RaNNCModule:
         self._storage = ParamStorage(self.use_amp_master_params, self.enable_zero, self.allreduce_amp_master_params)
         self._storage.sync_on_init = _sync_params_on_init
         self._storage.offload = bool(self.offload_params) and dev.type == "cuda" and self.use_amp_master_params
-        if self.offload_params and not self._storage.offload:
+        # offload_param_window_mb > 0: the 16-bit parameters and their gradients leave the device too and are
+        # streamed through a window of that size, segment by segment (parallel/param_stream.py)
+        window_mb = int(conf("offload_param_window_mb"))
+        self._storage.stream16 = bool(self.offload_params) and self.use_amp_master_params and window_mb > 0
+        if self._storage.stream16 and (bool(conf("force_dist_matmul")) or bool(conf("keep_dist_params_sharded"))):
+            raise RuntimeError("offload_param_window_mb does not combine with tensor-partitioned linear layers")
+        if self.offload_params and not self._storage.offload and not self._storage.stream16:
             logger.warning("offload_params needs a CUDA device and mixed precision (fp32 master weights); ignored")
         local_params = {n: name_to_param[n] for n in self._used_param_names}
         # the three projection weights (and biases) of a fused QKV block are laid out back to back so that one
@@ -417,6 +423,10 @@ class RaNNCModule:
                         adjacent.append([fq[0], fq[2], fq[4]])
                     if all(f is not None for f in (fq[1], fq[3], fq[5])):
                         adjacent.append([fq[1], fq[3], fq[5]])
+        if self._storage.stream16:
+            from .parallel.param_stream import ParamStreamer
+
+            self._storage.streamer = ParamStreamer(dev)
         want_fused = (self.use_amp_master_params and self.enable_zero and dev.type == "cuda" and world > 1 and
                       not self.offload_params and
                       bool(conf("fused_kernels")) and bool(conf("fused_grad_allreduce")) and
@@ -449,7 +459,12 @@ class RaNNCModule:
             if sname in dist_nodes:
                 self._install_dist_linears(gm, sname, dist_nodes[sname], tuple(dep.allocation[sname]), name_to_param,
                                            dist_kernels, dev)
-            st = StageExec(sname, gm, sg, tensors)
+            if self._storage.stream16 and any(hasattr(t, "_rannc_host") for t in tensors.values()):
+                from .parallel.param_stream import StreamedStage
+
+                st = StreamedStage(sname, gm, sg, tensors, self._storage.streamer, window_mb << 20)
+            else:
+                st = StageExec(sname, gm, sg, tensors)
             st.keep_graph = _keep_graph
             stages[sname] = st
         self._stages = stages

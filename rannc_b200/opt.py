@@ -51,6 +51,13 @@ def _fusable(opt) -> Optional[str]:
     return None
 
 
+def _state_on_host(g) -> bool:
+    """fp32 master weights and moments of the group are kept in host memory and streamed through the device by
+    the update (``offload_params``; with streamed 16-bit parameters the gradients are host-resident too)."""
+    return g.flat_master is not None and not g.flat_master.is_cuda and \
+        (g.flat_grad.is_cuda or (getattr(g, "streamed", False) and g.device.type == "cuda"))
+
+
 class _FlatState:
     """Moment buffers of one flat group, indexed like its master buffer (the shard under ZeRO)."""
 
@@ -78,28 +85,45 @@ class _OffloadWindow:
         self.bufs = [[torch.empty(chunk, dtype=torch.float32, device=device) for _ in range(n_state)]
                      for _ in range(2)]
         self.free = [None, None]
+        self.extra = {}
 
-    def run(self, host_tensors, n: int, kernel):
-        """``kernel(off, cnt, dev_tensors)`` updates ``cnt`` elements at offset ``off`` in place on the device."""
+    def _extra(self, k: int, j: int, dtype, device):
+        key = (k, j, dtype)
+        buf = self.extra.get(key)
+        if buf is None:
+            buf = self.extra[key] = torch.empty(self.chunk, dtype=dtype, device=device)
+        return buf
+
+    def run(self, host_tensors, n: int, kernel, ins=(), outs=()):
+        """``kernel(off, cnt, dev_tensors, dev_ins, dev_outs)`` updates ``cnt`` elements at offset ``off`` in
+        place on the device.  ``host_tensors`` travel both ways; ``ins`` (e.g. host-resident gradients) only
+        to the device, ``outs`` (e.g. host-resident 16-bit parameters) only back."""
         cur = torch.cuda.current_stream()
+        dev = self.bufs[0][0].device
         k = 0
         for off in range(0, n, self.chunk):
             cnt = min(self.chunk, n - off)
             set_ = self.bufs[k & 1]
+            d_in = [self._extra(k & 1, j, h.dtype, dev) for j, h in enumerate(ins)]
+            d_out = [self._extra(k & 1, len(ins) + j, h.dtype, dev) for j, h in enumerate(outs)]
             with torch.cuda.stream(self.stream):
                 if self.free[k & 1] is not None:
                     self.stream.wait_event(self.free[k & 1])
                 for h, d in zip(host_tensors, set_):
                     d[:cnt].copy_(h[off:off + cnt], non_blocking=True)
+                for h, d in zip(ins, d_in):
+                    d[:cnt].copy_(h[off:off + cnt], non_blocking=True)
                 ready = torch.cuda.Event()
                 ready.record(self.stream)
             cur.wait_event(ready)
-            kernel(off, cnt, [d[:cnt] for d in set_])
+            kernel(off, cnt, [d[:cnt] for d in set_], [d[:cnt] for d in d_in], [d[:cnt] for d in d_out])
             done = torch.cuda.Event()
             done.record(cur)
             with torch.cuda.stream(self.stream):
                 self.stream.wait_event(done)
                 for h, d in zip(host_tensors, set_):
+                    h[off:off + cnt].copy_(d[:cnt], non_blocking=True)
+                for h, d in zip(outs, d_out):
                     h[off:off + cnt].copy_(d[:cnt], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.stream)
@@ -237,9 +261,11 @@ def patch_optimizer(module, optimizer):
         if kind == "adam":
             hosts.append(fs.v[la:la + n])
 
-        def kernel(off, cnt, dev):
-            grad = g.flat_grad[a + off:a + off + cnt]
-            model16 = g.flat_param[a + off:a + off + cnt]
+        streamed = getattr(g, "streamed", False)
+
+        def kernel(off, cnt, dev, dev_in, dev_out):
+            grad = dev_in[0] if streamed else g.flat_grad[a + off:a + off + cnt]
+            model16 = dev_out[0] if streamed else g.flat_param[a + off:a + off + cnt]
             if kind == "adam":
                 b1, b2 = hp["betas"]
                 K.adam_flat(dev[0], grad, dev[1], dev[2], model16, float(hp["lr"]), b1, b2, float(hp["eps"]),
@@ -249,6 +275,11 @@ def patch_optimizer(module, optimizer):
                            float(hp.get("dampening", 0.0)), float(hp["weight_decay"]), bool(hp.get("nesterov")),
                            fs.step == 1, ctrl)
 
+        if streamed:
+            # gradients come from and the new 16-bit values go to host memory as well
+            storage.wait_streamed()
+            win.run(hosts, b - a, kernel, ins=[g.flat_grad[a:b]], outs=[g.flat_param[a:b]])
+            return
         win.run(hosts, b - a, kernel)
 
     def fused_step(ctrl=None, only=None):
@@ -261,8 +292,7 @@ def patch_optimizer(module, optimizer):
             fs = optimizer._rannc_flat_state.get(id(g))
             if fs is None:
                 fs = optimizer._rannc_flat_state[id(g)] = _FlatState(
-                    g.local_len, g.device, kind, host=g.flat_master is not None and not g.flat_master.is_cuda and
-                    g.flat_grad.is_cuda)
+                    g.local_len, g.device, kind, host=_state_on_host(g))
             fs.step += 1
         for g, og, a, b in _flat_ranges():
             if only is not None and g not in only:
@@ -271,7 +301,7 @@ def patch_optimizer(module, optimizer):
             hp = optimizer.param_groups[og]
             la, n = g.to_local(a), b - a
             is_amp = g.flat_master is not None
-            if is_amp and not g.flat_master.is_cuda and g.flat_grad.is_cuda:
+            if _state_on_host(g):
                 _offloaded_update(g, fs, hp, og, a, b, kind, ctrl)
                 continue
             master = g.flat_master[la:la + n] if is_amp else g.flat_param[a:b]
@@ -321,7 +351,9 @@ def patch_optimizer(module, optimizer):
             mod._after_step()
             return None
         use_fused = optimizer._rannc_kind is not None and all(
-            g.flat_grad.is_cuda and g.flat_grad.dtype == torch.float32 for g in storage.groups)
+            (g.flat_grad.is_cuda or (g.streamed and g.device.type == "cuda")) and g.flat_grad.dtype == torch.float32
+            for g in storage.groups)
+        storage.wait_streamed(host=not use_fused)
         if use_fused:
             fused_step(ctrl if isinstance(ctrl, torch.Tensor) else None)
             loss = None
@@ -504,8 +536,7 @@ def load_global_optimizer_state(optimizer, sd: dict) -> None:
     # the fused step keeps flat moments: refill them from the per-parameter entries
     if optimizer._rannc_kind is not None:
         for g in storage.groups:
-            fs = _FlatState(g.local_len, g.device, optimizer._rannc_kind,
-                            host=g.flat_master is not None and not g.flat_master.is_cuda and g.flat_grad.is_cuda)
+            fs = _FlatState(g.local_len, g.device, optimizer._rannc_kind, host=_state_on_host(g))
             fs.step = steps.get(id(g), 0)
             for i, p in enumerate(g.params):
                 target = g.master_params[i] if (g.flat_master is not None and g.master_params) else p

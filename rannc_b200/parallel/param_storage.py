@@ -34,6 +34,12 @@ from . import comm
 logger = get_logger("ParamStorage")
 
 
+def _host_zeros(n: int, dtype: torch.dtype) -> torch.Tensor:
+    """Host buffer the device can copy from / to asynchronously (pinned when there is a CUDA device)."""
+    t = torch.zeros(n, dtype=dtype)
+    return t.pin_memory() if torch.cuda.is_available() else t
+
+
 def _align(n: int, unit: int) -> int:
     return (n + unit - 1) // unit * unit
 
@@ -73,6 +79,9 @@ class FlatGroup:
         self.zero = False
         self.symm = None                         # symmetric-memory handles of the fused gradient path
         self.slice_ranks: Optional[Tuple[int, ...]] = None  # tensor-partitioned weights: ranks holding the slices
+        # streamed: the 16-bit parameters and their fp32 gradients live in (pinned) host memory and only the
+        # operators about to run have theirs on the device (parallel/param_stream.py)
+        self.streamed = False
 
     @property
     def nranks(self) -> int:
@@ -95,7 +104,8 @@ class FlatGroup:
         self.opt_group.append(opt_group)
         self.units.append(unit)
 
-    def finalize(self, amp: bool, zero: bool, symmetric: bool = False, bucket_numel: int = 0):
+    def finalize(self, amp: bool, zero: bool, symmetric: bool = False, bucket_numel: int = 0,
+                 streamed: bool = False):
         # 16-byte aligned slots so every parameter view can feed TMA / vector loads
         es = torch.empty((), dtype=self.dtype).element_size()
         unit = max(1, 16 // es)
@@ -117,8 +127,13 @@ class FlatGroup:
         self.buckets.append((bstart, off))
         self.total = off
         gdtype = torch.float32 if amp else self.dtype
-        self.symmetric = bool(symmetric and (self.nranks > 1 or self.slice_ranks) and self.device.type == "cuda")
-        if self.symmetric:
+        self.streamed = bool(streamed and amp and not self.slice_ranks)
+        self.symmetric = bool(symmetric and (self.nranks > 1 or self.slice_ranks) and self.device.type == "cuda"
+                              and not self.streamed)
+        if self.streamed:
+            self.flat_param = _host_zeros(self.total, self.dtype)
+            self.flat_grad = _host_zeros(self.total, gdtype)
+        elif self.symmetric:
             # peers read / write these buffers directly (fused gradient path)
             from .fused_reduce import symm_empty
 
@@ -140,6 +155,18 @@ class FlatGroup:
             self.local_len = self.total
         for p, o, n_ in zip(self.params, self.offsets, self.numels):
             view = self.flat_param[o:o + n_].view(p.shape)
+            if self.streamed:
+                view.copy_(p.data.to(dtype=self.dtype))
+                # the Parameter keeps its identity (the optimizer and the stage graphs refer to it); between
+                # uses it holds no device memory.  ``fetch`` / ``release`` of the streamer swap the data in and out.
+                p._rannc_host = view
+                p._rannc_host_grad = self.flat_grad[o:o + n_].view(p.shape)
+                p._rannc_shape = tuple(p.shape)
+                p._rannc_grad_valid = False
+                p.data = torch.empty(0, dtype=self.dtype, device=self.device)
+                p.main_grad = None
+                p.grad = None
+                continue
             view.copy_(p.data.to(device=self.device, dtype=self.dtype))
             p.data = view
             gview = self.flat_grad[o:o + n_].view(p.shape)
@@ -194,6 +221,8 @@ class ParamStorage:
         self.global_order: Dict[str, int] = {}
         self.sync_on_init = True
         self.offload = False     # fp32 master copies and optimizer state in pinned host memory
+        self.stream16 = False    # ... and the 16-bit parameters + fp32 gradients too (offload_param_window_mb > 0)
+        self.streamer = None     # parallel/param_stream.ParamStreamer when stream16
         self._sumsq = None
         self._ctrl = None
         self._norm = None
@@ -255,7 +284,8 @@ class ParamStorage:
             ges = 4 if g_amp else torch.empty((), dtype=g.dtype).element_size()
             g.finalize(g_amp, self.zero and not g.slice_ranks,
                        symmetric_slices if g.slice_ranks else symmetric,
-                       bucket_numel=int(bucket_bytes // ges) if g.nranks > 1 else 0)
+                       bucket_numel=int(bucket_bytes // ges) if g.nranks > 1 else 0,
+                       streamed=self.stream16)
             for i, n in enumerate(g.names):
                 self.by_name[n] = (g, i)
         if self.sync_on_init:
@@ -264,8 +294,26 @@ class ParamStorage:
     def sync_params_from_root(self):
         """Every owner starts from the lowest owner rank's values (reference: ParamStorage.cpp:1024-1057)."""
         for g in self.groups:
-            if g.nranks > 1:
+            if g.nranks > 1 and g.streamed:
+                for lo, hi in self._chunks(0, g.total):
+                    d = g.flat_param[lo:hi].to(g.device)
+                    comm.bcast(d, g.ranks[0], g.ranks)
+                    g.flat_param[lo:hi].copy_(d)
+            elif g.nranks > 1:
                 comm.bcast(g.flat_param, g.ranks[0], g.ranks)
+
+    @staticmethod
+    def _chunks(lo: int, hi: int):
+        """[lo, hi) in pieces of at most ``offload_chunk_numel`` elements (device staging of host buffers)."""
+        step = max(1 << 16, int(conf("offload_chunk_numel")))
+        for a in range(lo, hi, step):
+            yield a, min(hi, a + step)
+
+    def wait_streamed(self, host: bool = False) -> None:
+        """Copies of streamed gradients / parameters still in flight are ordered before what the current stream
+        does next (``host``: before what the host does next)."""
+        if self.streamer is not None:
+            self.streamer.wait(host)
 
     def setup_master(self):
         """fp32 master copies (whole buffer, or this rank's slices of every bucket under ZeRO)."""
@@ -277,6 +325,8 @@ class ParamStorage:
             host = self.offload and g.flat_master.is_cuda
             if host:
                 g.flat_master = g.flat_master.cpu().pin_memory()
+            elif g.streamed and torch.cuda.is_available():
+                g.flat_master = g.flat_master.pin_memory()
             g.master_params = []
             for i, p in enumerate(g.params):
                 a, b = g.local_range(i)
@@ -286,7 +336,7 @@ class ParamStorage:
                 full = (a, b) == g.param_range(i)
                 la = g.to_local(a)
                 mview = g.flat_master[la:la + (b - a)]
-                mp = torch.nn.Parameter(mview.view(p.shape) if full else mview, requires_grad=p.requires_grad)
+                mp = torch.nn.Parameter(mview.view(getattr(p, "_rannc_shape", p.shape)) if full else mview, requires_grad=p.requires_grad)
                 if not host:
                     mp.grad = g.flat_grad[a:b].view(mp.shape)
                 g.master_params.append(mp)
@@ -294,6 +344,12 @@ class ParamStorage:
     # ---------------------------------------------------------------- gradients
     def zero_grad(self):
         for g in self.groups:
+            if g.streamed:
+                # nothing is cleared on the host: the first gradient written for a parameter in the next
+                # backward overwrites, later ones (further micro-batches) accumulate
+                for p in g.params:
+                    p._rannc_grad_valid = False
+                continue
             g.flat_grad.zero_()
             for p in g.params:
                 if not self.amp or g.flat_master is None:
@@ -309,6 +365,8 @@ class ParamStorage:
         for g in self.groups:
             if g.flat_master is None and not (self.amp and g.dtype in (torch.float16, torch.bfloat16)):
                 continue
+            if g.streamed:
+                continue    # folded segment by segment, while the gradient window is on the device
             for p in g.params:
                 if p.grad is not None and p.grad.data_ptr() != p.main_grad.data_ptr():
                     if p.grad.is_cuda and p.grad.dtype in (torch.float16, torch.bfloat16):
@@ -325,8 +383,32 @@ class ParamStorage:
         for g in self.groups:
             # the divisor is the world size whatever the size of the owner set: every rank saw its share of
             # the global batch.  The scaling rides inside the collective where NCCL's PreMulSum is available.
+            if g.streamed:
+                self._reduce_streamed(g, 1.0 / world)
+                continue
             comm.allreduce(g.flat_grad, "sum", g.ranks, scale=1.0 / world)
         self._sync_if_asked()
+
+    def _reduce_streamed(self, g: FlatGroup, scale: float) -> None:
+        """Host-resident gradients: chunk by chunk onto the device, all-reduce there, and back.  Under ZeRO only
+        the slices this rank updates are written back (the rest of the host buffer is not read again)."""
+        self.wait_streamed()
+        if g.nranks == 1 and scale == 1.0:
+            return
+        spans = g.buckets if g.zero else [(0, g.total)]
+        for bi, (blo, bhi) in enumerate(spans):
+            for lo, hi in self._chunks(blo, bhi):
+                d = g.flat_grad[lo:hi].to(g.device, non_blocking=True)
+                comm.allreduce(d, "sum", g.ranks, scale=scale)
+                if g.zero:
+                    a, b, _ = g.pieces[bi]
+                    a, b = max(a, lo), min(b, hi)
+                    if b > a:
+                        g.flat_grad[a:b].copy_(d[a - lo:b - lo], non_blocking=True)
+                else:
+                    g.flat_grad[lo:hi].copy_(d, non_blocking=True)
+        if g.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()   # the optimizer (host or device) reads the host buffer next
 
     def allreduce_grads_zero(self, only=None):
         """ZeRO baseline: reduce-scatter, bucket by bucket, so each rank holds the reduced gradient of its slices
@@ -337,7 +419,9 @@ class ParamStorage:
             if only is not None and g not in only:
                 continue
             scale = 1.0 / world
-            if g.nranks > 1 and g.zero:
+            if g.streamed:
+                self._reduce_streamed(g, scale)
+            elif g.nranks > 1 and g.zero:
                 for (lo, hi), (a, b, _) in zip(g.buckets, g.pieces):
                     out = torch.empty(b - a, dtype=g.flat_grad.dtype, device=g.device)
                     comm.reduce_scatter_into(out, g.flat_grad[lo:hi], g.ranks, scale=scale)
@@ -358,7 +442,15 @@ class ParamStorage:
         for g in self.groups:
             if only is not None and g not in only:
                 continue
-            if g.nranks > 1 and g.zero:
+            if g.nranks > 1 and g.zero and g.streamed:
+                # host-resident parameters: each bucket is assembled on the device and copied back whole
+                for (lo, hi), (a, b, _) in zip(g.buckets, g.pieces):
+                    out = torch.empty(hi - lo, dtype=g.dtype, device=g.device)
+                    comm.allgather_into(out, g.flat_param[a:b].to(g.device, non_blocking=True), g.ranks)
+                    g.flat_param[lo:hi].copy_(out, non_blocking=True)
+                if g.device.type == "cuda":
+                    torch.cuda.current_stream().synchronize()
+            elif g.nranks > 1 and g.zero:
                 for (lo, hi), (a, b, _) in zip(g.buckets, g.pieces):
                     comm.allgather_into(g.flat_param[lo:hi], g.flat_param[a:b].clone(), g.ranks)
 
@@ -382,6 +474,7 @@ class ParamStorage:
         """Sum of squares of the gradients this rank is responsible for, as a device scalar.  Each element is
         counted once across the job: a rank counts its slices under ZeRO, otherwise the lowest owner counts."""
         self._ensure_reduced(sticky)
+        self.wait_streamed(host=True)
         me = comm.get_rank()
         dev = self.groups[0].device if self.groups else comm.device()
         ss, _, _ = self._norm_bufs(dev)
