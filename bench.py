@@ -416,6 +416,14 @@ def main():
             host.append((x, y))
     nparams = sum(p.numel() for p in model.parameters())
     wrapped = pyrannc.RaNNCModule(model, optimizer, enable_apex_amp=True, enable_zero=use_zero)
+    t_start = time.perf_counter()
+
+    def progress(what):
+        # large models spend minutes before the first step: say where (stderr, rank 0)
+        if rank == 0 and args.model != "bert":
+            print(f"[bench] +{time.perf_counter() - t_start:.1f}s {what}", file=sys.stderr, flush=True)
+
+    progress(f"model built ({nparams / 1e9:.2f} B parameters)")
 
     h2d_bytes = sum(t.numel() * t.element_size() for t in host[0])
     dev_sets = [tuple(t.to(dev) for t in hs) for hs in host]
@@ -438,6 +446,7 @@ def main():
     losses = []
     for i in range(args.warmup):
         losses.append(float(step_device(i).item()))
+        progress(f"warm-up step {i} done (the first one traces, plans and deploys)")
     torch.cuda.synchronize()
 
     # value check of the fused gradient path under this very run: one step from the same state down the

@@ -6,7 +6,9 @@
 #include <algorithm>
 #include <cctype>
 #include <cstdio>
+#include <chrono>
 #include <cstdlib>
+#include <ctime>
 #include <fstream>
 #include <iostream>
 #include <sstream>
@@ -278,10 +280,25 @@ bool Logger::enabled(LogLevel lv) const {
 }
 void Logger::log(LogLevel lv, const std::string& msg) const {
     if (!enabled(lv)) return;
+    // one write per line (ranks share the terminal), wall-clock time first as spdlog's default pattern does in
+    // the reference
+    const auto now = std::chrono::system_clock::now();
+    const std::time_t tt = std::chrono::system_clock::to_time_t(now);
+    const int ms = static_cast<int>(
+        std::chrono::duration_cast<std::chrono::milliseconds>(now.time_since_epoch()).count() % 1000);
+    std::tm tmv{};
+    localtime_r(&tt, &tmv);
+    char stamp[40];
+    std::snprintf(stamp, sizeof stamp, "[%04d-%02d-%02d %02d:%02d:%02d.%03d] ", tmv.tm_year + 1900, tmv.tm_mon + 1,
+                  tmv.tm_mday, tmv.tm_hour, tmv.tm_min, tmv.tm_sec, ms);
+    std::ostringstream line;
+    line << stamp << "[" << name_ << "] [" << levelName(lv) << "]";
+    if (g_log_rank >= 0) line << " [rank " << g_log_rank << "]";
+    line << " " << msg << "\n";
+    const std::string text = line.str();
     std::lock_guard<std::mutex> lk(g_log_mu);
-    std::cerr << "[" << name_ << "] [" << levelName(lv) << "]";
-    if (g_log_rank >= 0) std::cerr << " [rank " << g_log_rank << "]";
-    std::cerr << " " << msg << std::endl;
+    std::cerr.write(text.data(), static_cast<std::streamsize>(text.size()));
+    std::cerr.flush();
 }
 Logger& getLogger(const std::string& name) {
     std::lock_guard<std::mutex> lk(g_log_mu);

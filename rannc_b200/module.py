@@ -388,6 +388,16 @@ class RaNNCModule:
         self._used_buffer_names = [n for n in name_to_buffer if rank in buf_owner[n] or not buf_owner[n]]
         self._buffer_root = {n: (min(r) if r else 0) for n, r in buf_owner.items()}
 
+        # a model that was built on the device: what this rank does not use would otherwise stay in its memory
+        # for good (a model built on the host, as the reference requires, leaves those values on the host)
+        released = 0
+        for n, p in name_to_param.items():
+            if rank not in owner[n] and p.device.type == "cuda" and p.numel() > 0 and \
+                    not _dp.dist_param_registered(id(p)):
+                released += p.numel() * p.element_size()
+                p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+        if released:
+            logger.info("released %.1f GB of device-resident parameters that other ranks own", released / 1e9)
         # parameters sharded at construction are assembled on their owners only (collective, global order)
         for n, p in name_to_param.items():
             if _dp.dist_param_registered(id(p)):
