@@ -400,12 +400,14 @@ def bump_param_epoch() -> None:
 def _cat_params(tensors):
     """Concatenation of a few parameters along dim 0, cached until the parameters next change."""
     key = tuple(id(t) for t in tensors)
-    hit = _cat_cache.get(key)
+    volatile = any(getattr(t, "_rannc_host", None) is not None for t in tensors)
+    hit = None if volatile else _cat_cache.get(key)
     if hit is not None and hit[0] == param_epoch and hit[2] == tuple(t.data_ptr() for t in tensors):
         return hit[1]
     with torch.no_grad():
         cat = torch.cat([t.detach() for t in tensors], 0)
-    _cat_cache[key] = (param_epoch, cat, tuple(t.data_ptr() for t in tensors))
+    if not volatile:
+        _cat_cache[key] = (param_epoch, cat, tuple(t.data_ptr() for t in tensors))
     return cat
 
 
@@ -413,29 +415,42 @@ _adj_cache = {}
 
 
 def _adjacent_view(tensors):
-    """One [sum of rows, ...] view over tensors that lie back to back in one storage (the parameter storage
-    lays the three projection weights of a QKV block out that way), or None when they do not."""
+    """One [sum of rows, ...] view over tensors that lie back to back in ONE storage (the parameter storage
+    lays the three projection weights of a QKV block out that way), or None when they do not.  Tensors that
+    merely have consecutive addresses in different allocations do not qualify: the view must stay inside the
+    first tensor's storage."""
     t0 = tensors[0]
+    # windows of streamed parameters / gradients come and go: their views are made afresh and never cached
+    volatile = any(getattr(t, "_rannc_host", None) is not None or getattr(t, "_rannc_window", False)
+                   for t in tensors)
     key = tuple(t.data_ptr() for t in tensors)
-    hit = _adj_cache.get(key)
-    if hit is not None:
-        return hit[0]
+    if not volatile:
+        hit = _adj_cache.get(key)
+        if hit is not None:
+            return hit[0]
     es = t0.element_size()
     ok = all(t.is_contiguous() and t.dtype == t0.dtype and t.shape[1:] == t0.shape[1:] for t in tensors)
     ptr = t0.data_ptr()
+    total = 0
     for t in tensors:
         ok = ok and t.data_ptr() == ptr
         ptr += t.numel() * es
+        total += t.numel()
     view = None
     if ok:
         try:
-            rows = sum(t.shape[0] for t in tensors)
-            shape = (rows,) + tuple(t0.shape[1:])
-            stride = t0.stride()
-            view = torch.empty(0, dtype=t0.dtype, device=t0.device).set_(
-                t0.detach().untyped_storage(), t0.storage_offset(), shape, stride)
+            st = t0.detach().untyped_storage()
+            inside = st.nbytes() >= (t0.storage_offset() + total) * es and \
+                all(t.untyped_storage().data_ptr() == st.data_ptr() for t in tensors)
+            if inside:
+                rows = sum(t.shape[0] for t in tensors)
+                shape = (rows,) + tuple(t0.shape[1:])
+                view = torch.empty(0, dtype=t0.dtype, device=t0.device).set_(st, t0.storage_offset(), shape,
+                                                                             t0.stride())
         except Exception:  # noqa: BLE001
             view = None
+    if volatile:
+        return view
     if len(_adj_cache) > 4096:
         _adj_cache.clear()
     _adj_cache[key] = (view, tensors)   # the tensors stay referenced so their addresses are not reused

@@ -162,6 +162,7 @@ class FlatGroup:
                 p._rannc_host = view
                 p._rannc_host_grad = self.flat_grad[o:o + n_].view(p.shape)
                 p._rannc_shape = tuple(p.shape)
+                p._rannc_flat = (self, o, n_)     # where it lives in the host buffers
                 p._rannc_grad_valid = False
                 p.data = torch.empty(0, dtype=self.dtype, device=self.device)
                 p.main_grad = None

@@ -33,10 +33,32 @@ logger = get_logger("ParamStream")
 
 
 class _Window:
-    __slots__ = ("params", "bufs", "ready")
+    __slots__ = ("params", "views", "bufs", "ready", "nbytes")
 
-    def __init__(self, params, bufs, ready):
-        self.params, self.bufs, self.ready = params, bufs, ready
+    def __init__(self, params, views, bufs, ready, nbytes):
+        self.params, self.views, self.bufs, self.ready, self.nbytes = params, views, bufs, ready, nbytes
+
+
+def _runs(params):
+    """Groups parameters that lie back to back in a host flat buffer: [(group, lo, hi, [(param, offset, numel)])].
+    One run is one device allocation and one copy; parameters the storage laid out adjacently (the three
+    projection weights of a QKV block) stay adjacent on the device, so the single-GEMM paths keep working."""
+    by_group = {}
+    for p in params:
+        g, o, n = p._rannc_flat
+        by_group.setdefault(id(g), (g, []))[1].append((o, n, p))
+    out = []
+    for g, items in by_group.values():
+        items.sort(key=lambda t: t[0])
+        cur = None
+        for o, n, p in items:
+            if cur is not None and 0 <= o - cur[2] < 64:
+                cur[2] = o + n
+                cur[3].append((p, o, n))
+            else:
+                cur = [g, o, o + n, [(p, o, n)]]
+                out.append(cur)
+    return out
 
 
 class ParamStreamer:
@@ -54,15 +76,15 @@ class ParamStreamer:
     # ------------------------------------------------------------------ parameters
     def prefetch(self, params: Sequence[torch.nn.Parameter]) -> _Window:
         """Starts the host -> device copies of ``params`` on the copy stream."""
-        bufs = []
+        bufs, views, plist = [], [], []
         nbytes = 0
         if self.cuda:
             # the device blocks come from the compute stream's pool: the copy stream may write them only after
             # everything the compute stream has been given so far (their previous user is among it)
             self.stream.wait_stream(torch.cuda.current_stream())
-        for p in params:
-            h = p._rannc_host
-            d = torch.empty(h.shape, dtype=h.dtype, device=self.device)
+        for g, lo, hi, items in _runs(params):
+            h = g.flat_param[lo:hi]
+            d = torch.empty(hi - lo, dtype=h.dtype, device=self.device)
             if self.cuda:
                 with torch.cuda.stream(self.stream):
                     d.copy_(h, non_blocking=True)
@@ -71,6 +93,9 @@ class ParamStreamer:
                 d.copy_(h)
             bufs.append(d)
             nbytes += h.numel() * h.element_size()
+            for p, o, n in items:
+                plist.append(p)
+                views.append(d[o - lo:o - lo + n].view(p._rannc_shape))
         ready = None
         if self.cuda:
             ready = torch.cuda.Event()
@@ -78,67 +103,78 @@ class ParamStreamer:
         self.resident += nbytes
         self.fetched_bytes += nbytes
         self.peak_resident = max(self.peak_resident, self.resident)
-        return _Window(list(params), bufs, ready)
+        return _Window(plist, views, bufs, ready, nbytes)
 
     def attach(self, w: _Window) -> None:
         """The parameters of the window become usable on the current stream."""
         if w.ready is not None:
             torch.cuda.current_stream().wait_event(w.ready)
-        for p, d in zip(w.params, w.bufs):
-            p.data = d
+        for p, v in zip(w.params, w.views):
+            p.data = v
 
     def release(self, w: _Window) -> None:
-        for p, d in zip(w.params, w.bufs):
-            if p.data.data_ptr() == d.data_ptr():
-                p.data = torch.empty(0, dtype=d.dtype, device=self.device)
+        for p, v in zip(w.params, w.views):
+            if p.data.data_ptr() == v.data_ptr():
+                p.data = torch.empty(0, dtype=v.dtype, device=self.device)
             p.main_grad = None
             p.grad = None
-            self.resident -= d.numel() * d.element_size()
-        w.bufs = []
+        self.resident -= w.nbytes
+        w.nbytes = 0
+        w.bufs, w.views = [], []
 
     # ------------------------------------------------------------------ gradients
-    def open_grads(self, params: Sequence[torch.nn.Parameter]) -> List[torch.Tensor]:
-        """fp32 gradient windows on the device; a parameter that already has gradients from an earlier
-        micro-batch (or an earlier segment: tied weights) starts from them."""
+    def open_grads(self, params: Sequence[torch.nn.Parameter]):
+        """fp32 gradient windows on the device, laid out like the host buffer; a parameter that already has
+        gradients from an earlier micro-batch (or an earlier segment: tied weights) starts from them."""
         self.wait()
-        outs = []
-        for p in params:
-            hg = p._rannc_host_grad
-            if p._rannc_grad_valid:
-                d = hg.to(self.device, non_blocking=True)
+        runs = []
+        for g, lo, hi, items in _runs(params):
+            valid = [p._rannc_grad_valid for p, _, _ in items]
+            if all(valid):
+                d = g.flat_grad[lo:hi].to(self.device, non_blocking=True)
             else:
-                d = torch.zeros(hg.shape, dtype=hg.dtype, device=self.device)
-            p.main_grad = d
-            p.grad = None
-            outs.append(d)
-        return outs
+                d = torch.zeros(hi - lo, dtype=g.flat_grad.dtype, device=self.device)
+                for (p, o, n), ok in zip(items, valid):
+                    if ok:
+                        d[o - lo:o - lo + n].copy_(g.flat_grad[o:o + n], non_blocking=True)
+            for p, o, n in items:
+                v = d[o - lo:o - lo + n].view(p._rannc_shape)
+                v._rannc_window = True
+                p.main_grad = v
+                p.grad = None
+            runs.append((g, lo, hi, items, d))
+        return runs
 
-    def flush_grads(self, params: Sequence[torch.nn.Parameter], wins: List[torch.Tensor]) -> None:
+    def flush_grads(self, runs) -> None:
         """Gradients autograd left in ``p.grad`` join the window, the window goes to the host."""
         from ..ops import kernels as K
 
-        for p, d in zip(params, wins):
-            if p.grad is not None and p.grad.data_ptr() != d.data_ptr():
-                if p.grad.is_cuda and p.grad.dtype in (torch.float16, torch.bfloat16):
-                    K.accum_f32(d, p.grad.contiguous())
-                else:
-                    d.add_(p.grad.float())
-            p.grad = None
-            p.main_grad = None
+        for g, lo, hi, items, d in runs:
+            for p, o, n in items:
+                mg = p.main_grad
+                if p.grad is not None and mg is not None and p.grad.data_ptr() != mg.data_ptr():
+                    if p.grad.is_cuda and p.grad.dtype in (torch.float16, torch.bfloat16):
+                        K.accum_f32(mg, p.grad.contiguous())
+                    else:
+                        mg.add_(p.grad.float())
+                p.grad = None
+                p.main_grad = None
         if self.cuda:
             self.stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.stream):
-                for p, d in zip(params, wins):
-                    p._rannc_host_grad.copy_(d, non_blocking=True)
+                for g, lo, hi, items, d in runs:
+                    # the padding between two parameters of a run is zero on both sides
+                    g.flat_grad[lo:hi].copy_(d, non_blocking=True)
                     d.record_stream(self.stream)
                 ev = torch.cuda.Event()
                 ev.record(self.stream)
             self.last_flush = ev
         else:
-            for p, d in zip(params, wins):
-                p._rannc_host_grad.copy_(d)
-        for p in params:
-            p._rannc_grad_valid = True
+            for g, lo, hi, items, d in runs:
+                g.flat_grad[lo:hi].copy_(d)
+        for g, lo, hi, items, d in runs:
+            for p, _, _ in items:
+                p._rannc_grad_valid = True
 
     def wait(self, host: bool = False) -> None:
         if self.last_flush is None:
@@ -334,7 +370,7 @@ class StreamedStage(StageExec):
             if not wanted:
                 st.release(win)
                 continue
-            gwins = st.open_grads(trainable)
+            gruns = st.open_grads(trainable)
             self._set_rng_state(sv.rng)
             with torch.enable_grad():
                 args, leaf = self._seg_args(seg, sv.inputs, True)
@@ -356,7 +392,7 @@ class StreamedStage(StageExec):
                 else:
                     grads[nm] = t.grad
                 t.grad = None
-            st.flush_grads(trainable, gwins)
+            st.flush_grads(gruns)
             del outs, tensors, gs, leaf, args
             st.release(win)
         self._set_rng_state(cur)
