@@ -227,7 +227,12 @@ int64_t calcGraphMem(const IRGraph& g, const GraphProfile& prof, const Partition
         return params + act_s + prof.working_mem + opt + scaled_s.commBufSize() * std::min<int64_t>(P, 2);
     }
     int64_t act;
-    if (checkpointing) {
+    const int64_t segs = Config::get().getInt("checkpoint_segments");
+    if (checkpointing && segs > 1) {
+        // recomputation segment by segment: the values at the segment boundaries (about a stage input each) of
+        // every in-flight micro-batch + one segment's activations of one micro-batch
+        act = P * segs * prof.input_size + prof.activation_size / segs;
+    } else if (checkpointing) {
         // stage inputs of every in-flight micro-batch + one micro-batch's activations
         act = P * prof.input_size + prof.activation_size;
     } else {

@@ -102,6 +102,7 @@ const Def kDefs[] = {
     {"force_dist_matmul", ConfigItem::BOOL, "false"},
     {"offload_chunk_numel", ConfigItem::INT, "33554432"},
     {"offload_param_window_mb", ConfigItem::INT, "0"},
+    {"checkpoint_segments", ConfigItem::INT, "0"},
     {"use_named_tensors", ConfigItem::BOOL, "false"},
     {"profiler_cache_size", ConfigItem::INT, "0"},
     {"enable_kineto", ConfigItem::BOOL, "false"},

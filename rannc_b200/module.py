@@ -469,10 +469,16 @@ class RaNNCModule:
             if sname in dist_nodes:
                 self._install_dist_linears(gm, sname, dist_nodes[sname], tuple(dep.allocation[sname]), name_to_param,
                                            dist_kernels, dev)
+            nseg = int(conf("checkpoint_segments"))
             if self._storage.stream16 and any(hasattr(t, "_rannc_host") for t in tensors.values()):
                 from .parallel.param_stream import StreamedStage
 
                 st = StreamedStage(sname, gm, sg, tensors, self._storage.streamer, window_mb << 20)
+            elif nseg > 1:
+                # activation recomputation segment by segment instead of stage by stage
+                from .parallel.param_stream import StreamedStage
+
+                st = StreamedStage(sname, gm, sg, tensors, None, 0, segments=nseg)
             else:
                 st = StageExec(sname, gm, sg, tensors)
             st.keep_graph = _keep_graph

@@ -197,9 +197,18 @@ class _Segment:
         self.nbytes = nbytes
 
 
-def split_into_segments(gm: fx.GraphModule, params: Dict[str, torch.Tensor], max_bytes: int) -> List[_Segment]:
+def _pbytes(t) -> int:
+    h = getattr(t, "_rannc_host", None)
+    if h is not None:
+        return h.numel() * h.element_size()
+    return t.numel() * t.element_size()
+
+
+def split_into_segments(gm: fx.GraphModule, params: Dict[str, torch.Tensor], max_bytes: int,
+                        resident: bool = False) -> List[_Segment]:
     """Cuts a stage graph into consecutive runs of operators whose streamed parameters take at most ``max_bytes``
-    (one operator's parameters may exceed it: it then forms a segment of its own)."""
+    (one operator's parameters may exceed it: it then forms a segment of its own).  ``resident``: every
+    parameter counts, streamed or not (segments for recomputation only)."""
     nodes = [n for n in gm.graph.nodes if n.op == "call_function"]
     out_node = next(n for n in gm.graph.nodes if n.op == "output")
     stage_outs = [a.name for a in out_node.all_input_nodes]
@@ -208,7 +217,8 @@ def split_into_segments(gm: fx.GraphModule, params: Dict[str, torch.Tensor], max
         res = []
         for a in n.all_input_nodes:
             t = params.get(a.name) if a.op == "placeholder" else None
-            if t is not None and hasattr(t, "_rannc_host"):
+            if t is not None and (hasattr(t, "_rannc_host") or
+                                  (resident and isinstance(t, torch.nn.Parameter))):
                 res.append((a.name, t))
         return res
 
@@ -217,12 +227,12 @@ def split_into_segments(gm: fx.GraphModule, params: Dict[str, torch.Tensor], max
     size = 0
     for n in nodes:
         mine = [(nm, t) for nm, t in streamed_of(n) if nm not in seen]
-        add = sum(t._rannc_host.numel() * t._rannc_host.element_size() for _, t in mine)
+        add = sum(_pbytes(t) for _, t in mine)
         if groups[-1] and size > 0 and size + add > max_bytes:
             groups.append([])
             seen, size = set(), 0
             mine = streamed_of(n)
-            add = sum(t._rannc_host.numel() * t._rannc_host.element_size() for _, t in mine)
+            add = sum(_pbytes(t) for _, t in mine)
         groups[-1].append(n)
         seen.update(nm for nm, _ in mine)
         size += add
@@ -258,7 +268,8 @@ def split_into_segments(gm: fx.GraphModule, params: Dict[str, torch.Tensor], max
             if hasattr(t, "_rannc_host") and id(t) not in ids:
                 ids.add(id(t))
                 streamed.append(t)
-        nbytes = sum(t._rannc_host.numel() * t._rannc_host.element_size() for t in streamed)
+        nbytes = sum(_pbytes(t) for t in (ptens.values() if resident else streamed)
+                     if isinstance(t, torch.Tensor))
         segs.append(_Segment(sub, inputs, outs, ptens, streamed, nbytes))
     return segs
 
@@ -271,15 +282,27 @@ class _SegSaved:
 
 
 class StreamedStage(StageExec):
-    """A stage that runs segment by segment with its parameters streamed from the host.  Same interface as
-    :class:`StageExec`; activation recomputation is built in (per segment), so the ``checkpointing`` argument of
-    ``forward`` makes no difference."""
+    """A stage that runs segment by segment.  Same interface as :class:`StageExec`.
+
+    With a ``streamer`` the parameters of a segment are on the device only while the segment runs and activation
+    recomputation is built in, whatever the ``checkpointing`` argument of ``forward`` says.  Without one
+    (``checkpoint_segments``) the parameters are resident and the class only refines recomputation: where the
+    plain stage recomputes its whole forward in backward and so holds a whole stage's activations of one
+    micro-batch, this one keeps the values at the segment boundaries and recomputes one segment at a time, so
+    the peak is one SEGMENT's activations -- same arithmetic, a fraction of the memory, which buys larger
+    micro-batches for deep stages (the reference recomputes stage by stage, GraphConnector.cpp:395-457)."""
 
     def __init__(self, name: str, gm: fx.GraphModule, sub_ir, params: Dict[str, torch.Tensor],
-                 streamer: ParamStreamer, window_bytes: int):
+                 streamer: Optional[ParamStreamer], window_bytes: int, segments: int = 0):
         super().__init__(name, gm, sub_ir, params)
         self.streamer = streamer
-        self.segments = split_into_segments(gm, params, max(1, window_bytes // 2))
+        if streamer is not None:
+            self.segments = split_into_segments(gm, params, max(1, window_bytes // 2))
+        else:
+            total = sum(_pbytes(t) for t in {id(t): t for t in params.values()
+                                             if isinstance(t, torch.nn.Parameter)}.values())
+            self.segments = split_into_segments(gm, params, max(1, total // max(1, segments)), resident=True)
+        self.mode: Dict[int, bool] = {}     # micro-batch -> ran segment by segment
         out_node = next(n for n in gm.graph.nodes if n.op == "output")
         # a stage output that is a stage input (pass-through) is produced by no segment
         self._out_nodes = [a.name for a in out_node.args[0]] if isinstance(out_node.args[0], (tuple, list)) \
@@ -324,21 +347,28 @@ class StreamedStage(StageExec):
     def forward(self, split: int, inputs: Dict[str, torch.Tensor], checkpointing: bool,
                 grad_enabled: bool = True) -> Dict[str, torch.Tensor]:
         st = self.streamer
+        if st is None and not (checkpointing and grad_enabled):
+            # resident parameters and nothing to recompute: the plain stage
+            self.mode[split] = False
+            return super().forward(split, inputs, checkpointing, grad_enabled)
+        self.mode[split] = True
         env: Dict[str, object] = {n: inputs[n] for n in self.batch_input_names}
         saved: List[_SegSaved] = []
-        nxt = st.prefetch(self.segments[0].streamed) if self.segments else None
+        nxt = st.prefetch(self.segments[0].streamed) if (st is not None and self.segments) else None
         keep = set(self.output_names)
         for i, seg in enumerate(self.segments):
             win = nxt
-            st.attach(win)
-            nxt = st.prefetch(self.segments[i + 1].streamed) if i + 1 < len(self.segments) else None
+            if st is not None:
+                st.attach(win)
+                nxt = st.prefetch(self.segments[i + 1].streamed) if i + 1 < len(self.segments) else None
             rng = self._rng_state() if grad_enabled else None
             args, _ = self._seg_args(seg, env, False)
             with torch.no_grad():
                 outs = seg.gm(*args)
             if grad_enabled:
                 saved.append(_SegSaved({nm: env[nm] for nm in seg.inputs if nm not in seg.params}, rng))
-            st.release(win)
+            if st is not None:
+                st.release(win)
             for nm, o in zip(seg.outputs, outs):
                 env[nm] = o
             for nm in seg.inputs:
@@ -355,22 +385,25 @@ class StreamedStage(StageExec):
     # ------------------------------------------------------------------ backward
     def backward(self, split: int, out_grads: Dict[str, Optional[torch.Tensor]]) -> Dict[str, torch.Tensor]:
         st = self.streamer
+        if not (self.mode.get(split, True) if self.keep_graph else self.mode.pop(split, True)):
+            return super().backward(split, out_grads)
         saved = self.seg_saved[split] if self.keep_graph else self.seg_saved.pop(split)
         grads: Dict[str, torch.Tensor] = {n: g for n, g in out_grads.items() if g is not None}
         cur = self._rng_state()
         last = len(self.segments) - 1
-        nxt = st.prefetch(self.segments[last].streamed) if self.segments else None
+        nxt = st.prefetch(self.segments[last].streamed) if (st is not None and self.segments) else None
         for i in range(last, -1, -1):
             seg, sv = self.segments[i], saved[i]
             win = nxt
-            st.attach(win)
-            nxt = st.prefetch(self.segments[i - 1].streamed) if i > 0 else None
+            if st is not None:
+                st.attach(win)
+                nxt = st.prefetch(self.segments[i - 1].streamed) if i > 0 else None
             wanted = [nm for nm in seg.outputs if nm in grads]
-            trainable = [p for p in seg.streamed if p.requires_grad]
             if not wanted:
-                st.release(win)
+                if st is not None:
+                    st.release(win)
                 continue
-            gruns = st.open_grads(trainable)
+            gruns = st.open_grads([p for p in seg.streamed if p.requires_grad]) if st is not None else None
             self._set_rng_state(sv.rng)
             with torch.enable_grad():
                 args, leaf = self._seg_args(seg, sv.inputs, True)
@@ -392,12 +425,15 @@ class StreamedStage(StageExec):
                 else:
                     grads[nm] = t.grad
                 t.grad = None
-            st.flush_grads(gruns)
+            if st is not None:
+                st.flush_grads(gruns)
             del outs, tensors, gs, leaf, args
-            st.release(win)
+            if st is not None:
+                st.release(win)
         self._set_rng_state(cur)
         return {n: grads[n] for n in self.batch_input_names if n in grads}
 
     def clear(self):
         super().clear()
         self.seg_saved.clear()
+        self.mode.clear()

@@ -17,11 +17,15 @@ from rannc_b200 import _core  # noqa: E402
 from rannc_b200.models.bert import BertConfig, BertForPreTraining, synthetic_batch  # noqa: E402
 
 
-def run(case, window_mb):
+def run(case, window_mb, segments=0):
     if window_mb:
         os.environ["RANNC_OFFLOAD_PARAM_WINDOW_MB"] = str(window_mb)
     else:
         os.environ.pop("RANNC_OFFLOAD_PARAM_WINDOW_MB", None)
+    if segments:
+        os.environ["RANNC_CHECKPOINT_SEGMENTS"] = str(segments)
+    else:
+        os.environ.pop("RANNC_CHECKPOINT_SEGMENTS", None)
     _core.config_reload()
     rank, world = pyrannc.get_rank(), pyrannc.get_world_size()
     torch.manual_seed(0)
@@ -48,6 +52,10 @@ def run(case, window_mb):
     sd = m.state_dict()
     info = {}
     st = m._storage.streamer
+    if segments:
+        stages = list(m._stages.values())
+        info = {"segments": sum(len(s.segments) for s in stages), "checkpointing": m.is_checkpointing_enabled(),
+                "segmented_runs": sum(1 for s in stages if hasattr(s, "seg_saved"))}
     if window_mb:
         stages = list(m._stages.values())
         info = {"segments": sum(len(s.segments) for s in stages), "peak_resident": st.peak_resident,
@@ -63,7 +71,11 @@ def main():
     case = json.loads(sys.argv[1])
     rank = pyrannc.get_rank()
     la, sda, _ = run(case, 0)
-    lb_, sdb, info = run(case, case.get("window_mb", 1))
+    if case.get("segments"):
+        # recomputation segment by segment against recomputation of the whole stage (parameters resident)
+        lb_, sdb, info = run(case, 0, case["segments"])
+    else:
+        lb_, sdb, info = run(case, case.get("window_mb", 1))
     ok, msgs = True, []
     for i, (x, y) in enumerate(zip(la, lb_)):
         if abs(x - y) > 2e-3 * max(1.0, abs(x)):
@@ -75,7 +87,11 @@ def main():
         if worst > 2e-2:
             ok = False
             msgs.append(f"parameters differ by {worst}")
-    if info.get("segments", 0) < 3 or info.get("held", 1) != 0 or info.get("resident_after", 1) != 0 or \
+    if case.get("segments"):
+        if info.get("segments", 0) < 3 or not info.get("checkpointing"):
+            ok = False
+            msgs.append(f"segments: {info}")
+    elif info.get("segments", 0) < 3 or info.get("held", 1) != 0 or info.get("resident_after", 1) != 0 or \
             not info.get("host_grads") or info.get("peak_resident", 1 << 40) > (case.get("window_mb", 1) << 20):
         ok = False
         msgs.append(f"residency: {info}")

@@ -278,3 +278,15 @@ def test_parameters_streamed_from_host_memory(world, case, env):
     run with everything resident (reference: per-operator offload hooks, src/torch/TorchDriver.cpp:318-374)."""
     res = run_case(world, case, env, timeout=600, worker="stream_worker.py", every_rank=True)
     assert res["info"]["segments"] >= 3 and res["info"]["streamed_groups"] >= 1
+
+
+@pytest.mark.parametrize("world,case,env", [
+    (1, {"batch": 8, "segments": 4}, {"RANNC_CHECKPOINTING": "true", "RANNC_PIPELINE_NUM": "2"}),
+    (2, {"batch": 8, "segments": 3, "zero": True}, {"RANNC_CHECKPOINTING": "true", "RANNC_PARTITION_NUM": "2",
+                                                     "RANNC_PIPELINE_NUM": "2"}),
+])
+def test_recomputation_segment_by_segment_matches_stage_recomputation(world, case, env):
+    """checkpoint_segments: a checkpointed stage keeps the values at its segment boundaries and recomputes one
+    segment at a time in backward; same dropout masks, same gradients as recomputing the whole stage."""
+    res = run_case(world, case, env, timeout=600, worker="stream_worker.py", every_rank=True)
+    assert res["info"]["segments"] >= 3
