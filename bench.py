@@ -462,7 +462,9 @@ def main():
         except Exception as e:  # noqa: BLE001
             fused_err = f"{type(e).__name__}: {e}"[:200]
 
-    # host time to enqueue one step, with an idle device and an empty launch queue (no synchronisation inside)
+    # host time to enqueue one step, with an idle device and an empty launch queue (no synchronisation inside).
+    # A step of tens of thousands of launches fills the launch queue, after which the host advances at the
+    # device's pace: for the enlarged models this figure is an upper bound of the host's own work, not a measure.
     enq = []
     for i in range(1 if args.model in ("bert13b", "bert26b") else 3):
         torch.cuda.synchronize()
