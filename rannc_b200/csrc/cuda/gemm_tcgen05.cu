@@ -76,6 +76,10 @@ struct GemmKernelParams {
     float alpha;
     int flags;
     int* err;
+    // implicit-GEMM convolution: see RbGemmArgs
+    int conv_kb_per_tap, conv_b_tap_cols, b_row_shift;
+    int map_hp, map_wp, map_h, map_w, map_pad;
+    int conv_shift[49];
 };
 
 __device__ __forceinline__ void tile_coords(const GemmKernelParams& p, int tile, int& mb, int& nb,
@@ -262,12 +266,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
                     uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
                     const int k0 = kb * BK;
+                    // A (K-major) reads columns ax of rows ay..; B (MN-major) reads columns +bx of rows bk..
+                    int ax = k0, ay = m0, bx = 0, bk = k0 + p.b_row_shift;
+                    if (p.conv_kb_per_tap > 0) {
+                        const int tap = kb / p.conv_kb_per_tap;
+                        ax = (kb - tap * p.conv_kb_per_tap) * BK;
+                        ay = m0 + p.conv_shift[tap];
+                        if (p.b_major != 0) {
+                            bx = tap * p.conv_b_tap_cols;
+                            bk = ax;
+                        }
+                    }
                     if constexpr (PAIR) {
                         // both CTAs' bytes are counted on the first CTA's barrier
                         if (crank == 0) mbar_arrive_expect_tx(&full[stage], 2 * STAGE_BYTES);
                         const uint32_t fb = mapa_shared(smem_u32(&full[stage]), 0);
                         if (p.a_major == 0) {
-                            tma_load_3d_pair(a_dst, &tmA, fb, k0, m0, b);
+                            tma_load_3d_pair(a_dst, &tmA, fb, ax, ay, b);
                         } else {
 #pragma unroll
                             for (int c = 0; c < BM / 64; ++c)
@@ -278,12 +293,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         } else {
 #pragma unroll
                             for (int c = 0; c < Cfg<PAIR>::B_ROWS / 64; ++c)
-                                tma_load_3d_pair(b_dst + c * (BK * 128), &tmB, fb, n0 + c * 64, k0, b);
+                                tma_load_3d_pair(b_dst + c * (BK * 128), &tmB, fb, n0 + bx + c * 64, bk, b);
                         }
                     } else {
                         mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
                         if (p.a_major == 0) {
-                            tma_load_3d(a_dst, &tmA, &full[stage], k0, m0, b);
+                            tma_load_3d(a_dst, &tmA, &full[stage], ax, ay, b);
                         } else {
 #pragma unroll
                             for (int c = 0; c < BM / 64; ++c)
@@ -295,8 +310,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         } else {
 #pragma unroll
                             for (int c = 0; c < BN / 64; ++c)
-                                tma_load_3d(b_dst + c * (BK * 128), &tmB, &full[stage], n0 + c * 64,
-                                            k0, b);
+                                tma_load_3d(b_dst + c * (BK * 128), &tmB, &full[stage], n0 + bx + c * 64,
+                                            bk, b);
                         }
                     }
                     if (++stage == STAGES) {
@@ -421,10 +436,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) break;
             tc_fence_after();
-            const int row = mb * TILE_M + static_cast<int>(crank) * BM + row_in_tile;
-            const bool row_ok = row < p.M;
+            int row = mb * TILE_M + static_cast<int>(crank) * BM + row_in_tile;
+            bool row_ok = row < p.M;
+            if (p.map_hp > 0 && row_ok) {
+                // rows are positions of a zero-padded image grid: only the interior is stored
+                const int per_img = p.map_hp * p.map_wp;
+                const int img = row / per_img;
+                const int rem = row - img * per_img;
+                const int yy = rem / p.map_wp - p.map_pad;
+                const int xx = rem - (rem / p.map_wp) * p.map_wp - p.map_pad;
+                row_ok = yy >= 0 && yy < p.map_h && xx >= 0 && xx < p.map_w;
+                row = (img * p.map_h + yy) * p.map_w + xx;
+            }
             const long long row_off = static_cast<long long>(b) * p.strideD +
-                                      static_cast<long long>(row) * p.ldd;
+                                      static_cast<long long>(row_ok ? row : 0) * p.ldd;
 #pragma unroll 1
             for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
                 const int col = nb * BN + c * 32;
@@ -799,18 +824,45 @@ extern "C" int rb_gemm(const RbGemmArgs* a, void* stream_) {
     p.flags = a->flags;
     p.err = error_word_ptr();
     if (!p.err) return -3;
+    p.conv_kb_per_tap = 0;
+    p.conv_b_tap_cols = 0;
+    p.b_row_shift = a->b_major != 0 ? a->b_row_shift : 0;
+    p.map_hp = a->map_hp;
+    p.map_wp = a->map_wp;
+    p.map_h = a->map_h;
+    p.map_w = a->map_w;
+    p.map_pad = a->map_pad;
+    for (int t = 0; t < 49; ++t) p.conv_shift[t] = 0;
+    if (a->conv_taps > 0) {
+        // A must be K-major with conv_c (a multiple of the k step) columns; no batch, gather or scatter
+        if (a->conv_taps > 49 || a->a_major != 0 || a->conv_c % BK || a->lda != a->conv_c || a->batch != 1 ||
+            a->K != static_cast<int64_t>(a->conv_taps) * a->conv_c || a->ag_nranks > 1 || a->rs_nranks > 1 ||
+            (a->b_major != 0 && a->conv_b_tap_cols % 8))
+            return -7;
+        p.conv_kb_per_tap = a->conv_c / BK;
+        p.conv_b_tap_cols = a->conv_b_tap_cols;
+        for (int t = 0; t < a->conv_taps; ++t) p.conv_shift[t] = a->conv_shift[t];
+    }
+    if (a->map_hp > 0 && (a->batch != 1 || a->rs_nranks > 1 || a->map_wp <= 0)) return -7;
 
     CUtensorMap tmA, tmB;
     int rc;
     const uint64_t sA = a->batch > 1 ? a->strideA * 2 : (a->a_major == 0 ? a->M : a->K) * a->lda * 2;
     const uint64_t sB = a->batch > 1 ? a->strideB * 2 : (a->b_major == 0 ? a->N : a->K) * a->ldb * 2;
-    if (a->a_major == 0)
+    if (a->conv_taps > 0)
+        rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->conv_c, a->M, 1, a->lda * 2, a->M * a->lda * 2, BK, BM, 1);
+    else if (a->a_major == 0)
         rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->K, a->M, a->batch, a->lda * 2, sA, BK, BM, 1);
     else
         rc = make_tmap_3d(&tmA, a->A, a->in_dtype, a->M, a->K, a->batch, a->lda * 2, sA, 64, BK, 1);
     if (rc) return rc;
     if (a->b_major == 0)
         rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->K, a->N, a->batch, a->ldb * 2, sB, BK, pair ? BN / 2 : BN, 1);
+    else if (a->conv_taps > 0)
+        // the stored matrix is [conv_c rows, conv_taps * conv_b_tap_cols columns]: tap t's [conv_c, N] block
+        // starts at column t * conv_b_tap_cols
+        rc = make_tmap_3d(&tmB, a->B, a->in_dtype, static_cast<uint64_t>(a->conv_taps) * a->conv_b_tap_cols,
+                          a->conv_c, 1, a->ldb * 2, static_cast<uint64_t>(a->conv_c) * a->ldb * 2, 64, BK, 1);
     else
         rc = make_tmap_3d(&tmB, a->B, a->in_dtype, a->N, a->K, a->batch, a->ldb * 2, sB, 64, BK, 1);
     if (rc) return rc;

@@ -44,6 +44,17 @@ typedef struct RbGemmArgs {
     int32_t ag_nranks, ag_my_idx, ag_rows, ag_cols;
     void* ag_flags;        // 8 x uint32 of local device memory (cleared by the call)
     const void* ag_src[8];
+    // implicit-GEMM convolution (conv_taps > 0).  A is the zero-padded channels-last activation seen as
+    // [rows = N * Hp * Wp, conv_c] (lda = conv_c); the K dimension runs over conv_taps x conv_c: k-block kb reads
+    // channels (kb mod conv_c/64) * 64 of the rows m + conv_shift[kb / (conv_c/64)] -- rows outside the matrix
+    // read as zero.  With B stored [K, N] (b_major = 1) tap t's block starts conv_b_tap_cols * t columns further
+    // right and its rows are the tap's own channel range.  No filter-sized copy of the activation exists.
+    int32_t conv_taps, conv_c, conv_b_tap_cols;
+    int32_t b_row_shift;   // b_major = 1: the rows of B that k-block kb reads start at kb * 64 + b_row_shift
+    int32_t conv_shift[49];
+    // output rows are positions of the padded grid: only the interior (map_pad <= y < map_pad + map_h, same for
+    // x) is stored, at row (n * map_h + y - map_pad) * map_w + (x - map_pad) of D.  map_hp = 0: rows are rows.
+    int32_t map_hp, map_wp, map_h, map_w, map_pad;
 } RbGemmArgs;
 
 // returns 0 on success, <0 on a host-side error (-2: operand not 16 B aligned)

@@ -16,6 +16,7 @@ from __future__ import annotations
 import torch
 
 from . import kernels as K
+from ..utils.config import conf
 from .gemm import gemm
 
 
@@ -562,11 +563,12 @@ def _conv_weight(w):
         return w.detach().reshape(Co, Ci)
     key = ("conv", id(w))
     hit = _cat_cache.get(key)
-    if hit is not None and hit[0] == param_epoch and hit[2] == w.data_ptr():
+    if hit is not None and hit[0] == param_epoch and hit[2] == (w.data_ptr(), tuple(w.shape)):
         return hit[1]
     with torch.no_grad():
         w2 = w.detach().permute(0, 2, 3, 1).reshape(Co, kh * kw * Ci).contiguous()
-    _cat_cache[key] = (param_epoch, w2, w.data_ptr())
+    # (an id and an address can both recur once the earlier tensor is gone: the shape is part of the check)
+    _cat_cache[key] = (param_epoch, w2, (w.data_ptr(), tuple(w.shape)))
     return w2
 
 
@@ -585,24 +587,88 @@ class _Conv2d(torch.autograd.Function):
         return K.im2col(x4, k, s, pad)
 
     @staticmethod
+    def _implicit(k, stride, padding, Ci, Co, H=0, W=0) -> bool:
+        """Stride-1 "same" convolutions with a filter larger than 1x1 can run as an implicit GEMM: the producer of
+        the GEMM reads the zero-padded activation tap by tap (a row shift per tap), so neither the k*k-fold
+        ``im2col`` matrix nor its adjoint is ever written.  The product is taken over the PADDED grid (border
+        positions are computed and dropped), so small feature maps pay more in extra arithmetic than the gather
+        costs in traffic: ``conv_implicit_max_overhead`` bounds (Hp * Wp) / (H * W)."""
+        if not (k > 1 and k % 2 == 1 and stride == 1 and padding == (k - 1) // 2 and Ci % 64 == 0 and Co % 64 == 0
+                and k * k <= 49 and bool(conf("conv_implicit_gemm"))):
+            return False
+        if H > 0 and W > 0:
+            over = (H + 2 * padding) * (W + 2 * padding) / float(H * W)
+            return over <= float(conf("conv_implicit_max_overhead"))
+        return True
+
+    @staticmethod
+    def _padded(x4, pad):
+        """[N * Hp * Wp, C] rows of the zero-padded channels-last image."""
+        xp = torch.nn.functional.pad(x4, (0, 0, pad, pad, pad, pad))
+        return xp.reshape(-1, x4.shape[-1])
+
+    @staticmethod
+    def _shifts(k, pad, Wp):
+        return [(r - pad) * Wp + (s - pad) for r in range(k) for s in range(k)]
+
+    @staticmethod
     def forward(ctx, x, w, bias, stride, padding):
         N, C, H, W = x.shape
         Co, _, k, _ = w.shape
         x4 = _nhwc(x)
-        a = _Conv2d._operand(x4, k, stride, padding)
-        y2 = gemm(a, _conv_weight(w), bias=bias)
         Ho, Wo = K.conv_out_size(H, k, stride, padding), K.conv_out_size(W, k, stride, padding)
+        implicit = _Conv2d._implicit(k, stride, padding, C, Co, H, W)
+        if implicit:
+            Hp, Wp = H + 2 * padding, W + 2 * padding
+            y2 = torch.empty(N * H * W, Co, dtype=x.dtype, device=x.device)
+            gemm(_Conv2d._padded(x4, padding), _conv_weight(w), bias=bias, out=y2,
+                 conv={"taps": k * k, "shifts": _Conv2d._shifts(k, padding, Wp)},
+                 row_map=(Hp, Wp, H, W, padding))
+        else:
+            a = _Conv2d._operand(x4, k, stride, padding)
+            y2 = gemm(a, _conv_weight(w), bias=bias)
         ctx.save_for_backward(x4, w)
-        ctx.meta = (stride, padding, bias, _main_grad(w), _main_grad(bias) if bias is not None else None)
+        ctx.meta = (stride, padding, bias, _main_grad(w), _main_grad(bias) if bias is not None else None, implicit)
         return y2.view(N, Ho, Wo, Co).permute(0, 3, 1, 2)
 
     @staticmethod
     def backward(ctx, dy):
         x4, w = ctx.saved_tensors
-        stride, padding, bias, w_mg, b_mg = ctx.meta
+        stride, padding, bias, w_mg, b_mg, implicit = ctx.meta
         N, H, W, C = x4.shape
         Co, Ci, k, _ = w.shape
-        dy2 = _nhwc(dy).reshape(-1, Co)
+        dy4 = _nhwc(dy)
+        dy2 = dy4.reshape(-1, Co)
+        if implicit:
+            Hp, Wp = H + 2 * padding, W + 2 * padding
+            shifts = _Conv2d._shifts(k, padding, Wp)
+            dyp = _Conv2d._padded(dy4, padding)                 # zero where the padded grid has no output
+            dx = None
+            if ctx.needs_input_grad[0]:
+                # dx[j] = sum_t dy[j - shift_t] W_t : the same kernel with the shifts negated and tap t's
+                # [Co, Ci] block of the weight matrix as the [K, N] operand
+                dx2 = torch.empty(N * H * W, C, dtype=dy2.dtype, device=dy2.device)
+                gemm(dyp, _conv_weight(w), trans_b=False, out=dx2,
+                     conv={"taps": k * k, "shifts": [-v for v in shifts], "b_tap_cols": Ci, "n": Ci},
+                     row_map=(Hp, Wp, H, W, padding))
+                dx = dx2.view(N, H, W, C).permute(0, 3, 1, 2)
+            dw = None
+            if ctx.needs_input_grad[1]:
+                # dW_t = dy^T x[. + shift_t]: one GEMM per tap over the padded rows, the activation read with
+                # the tap's row shift
+                xp = _Conv2d._padded(x4, padding)
+                dw2 = torch.zeros(Co, k * k * Ci, dtype=torch.float32, device=dy2.device)
+                for t, sh in enumerate(shifts):
+                    gemm(dyp, xp, trans_a=True, trans_b=False, out=dw2[:, t * Ci:(t + 1) * Ci], accumulate=True,
+                         b_row_shift=sh)
+                dwt = dw2.view(Co, k, k, Ci).permute(0, 3, 1, 2)
+                if w_mg is not None:
+                    w_mg.add_(dwt)
+                else:
+                    dw = dwt.to(w.dtype)
+            db = _bgrad(dy2, bias, b_mg) if (bias is not None and ctx.needs_input_grad[2]) else None
+            notify_grads(w if w_mg is not None else None, bias if b_mg is not None else None)
+            return dx, dw, db, None, None
         dx = None
         if ctx.needs_input_grad[0]:
             da = gemm(dy2, _conv_weight(w), trans_b=False)

@@ -25,6 +25,10 @@ class _Args(ctypes.Structure):
         ("rs_peer", ctypes.c_void_p * 8),
         ("ag_nranks", ctypes.c_int32), ("ag_my_idx", ctypes.c_int32), ("ag_rows", ctypes.c_int32),
         ("ag_cols", ctypes.c_int32), ("ag_flags", ctypes.c_void_p), ("ag_src", ctypes.c_void_p * 8),
+        ("conv_taps", ctypes.c_int32), ("conv_c", ctypes.c_int32), ("conv_b_tap_cols", ctypes.c_int32),
+        ("b_row_shift", ctypes.c_int32), ("conv_shift", ctypes.c_int32 * 49),
+        ("map_hp", ctypes.c_int32), ("map_wp", ctypes.c_int32), ("map_h", ctypes.c_int32),
+        ("map_w", ctypes.c_int32), ("map_pad", ctypes.c_int32),
     ]
 
 
@@ -67,17 +71,38 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
          bias=None, residual=None, aux_in=None, aux_out=None, gelu: bool = False,
          dgelu: bool = False, out: torch.Tensor | None = None, accumulate: bool = False,
          out_dtype: torch.dtype | None = None, alpha: float = 1.0, max_ctas: int = 0,
-         rs_peers=None, rs_ld: int = 0, gather=None) -> torch.Tensor:
+         rs_peers=None, rs_ld: int = 0, gather=None, conv=None, b_row_shift: int = 0,
+         row_map=None) -> torch.Tensor:
     """``out = epilogue(alpha * op(a) @ op(b))``.
 
     ``a`` is stored ``[M, K]`` (``trans_a=False``) or ``[K, M]`` (``trans_a=True``).
     ``b`` is stored ``[N, K]`` (``trans_b=True``, the ``nn.Linear`` weight layout) or
     ``[K, N]`` (``trans_b=False``).  A leading batch dimension is allowed on both.
+
+    ``conv = {"taps": T, "shifts": [...], "b_tap_cols": n}``: implicit-GEMM convolution.  ``a`` is the padded
+    channels-last activation as ``[rows, C]``; the product runs over K = T x C, k-block by k-block reading the
+    rows shifted by ``shifts[tap]`` (rows outside ``a`` read as zero).  ``b`` is ``[N, T*C]`` (``trans_b=True``) or
+    ``[C, T*b_tap_cols]`` with tap t's ``[C, N]`` block at column ``t * b_tap_cols`` (``trans_b=False``).
+    ``b_row_shift`` (``trans_b=False`` only): the rows of ``b`` a k-block reads are shifted by this many.
+    ``row_map = (Hp, Wp, H, W, pad)``: the M rows are positions of a padded image grid; only the interior is
+    stored, at the un-padded row index (``out`` has N_img * H * W rows).
     """
     a, ar, ac, lda, ba, sa = _mat(a)
     b, br, bc, ldb, bb, sb = _mat(b)
     M, K = (ac, ar) if trans_a else (ar, ac)
     N, Kb = (br, bc) if trans_b else (bc, br)
+    if conv is not None:
+        T = int(conv["taps"])
+        if trans_a or a.dim() != 2 or b.dim() != 2 or len(conv["shifts"]) != T or lda != ac:
+            raise ValueError("gemm: a convolution wants a contiguous 2-D [rows, C] activation")
+        if trans_b:
+            if bc != T * ac:
+                raise ValueError(f"gemm: weight matrix has {bc} columns, expected {T} x {ac}")
+        else:
+            N = int(conv["n"])
+            if br != ac or bc < (T - 1) * int(conv["b_tap_cols"]) + N:
+                raise ValueError("gemm: weight matrix does not hold the taps' blocks")
+        K = Kb = T * ac
     if K != Kb:
         raise ValueError(f"gemm: inner dimensions differ ({K} vs {Kb})")
     batch = max(ba, bb)
@@ -89,6 +114,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         sb = 0
     odt = out_dtype or (out.dtype if out is not None else a.dtype)
     if out is None:
+        if row_map is not None:
+            raise ValueError("gemm: row_map needs an explicit output")
         shape = (M, N) if batch == 1 and a.dim() == 2 and b.dim() == 2 else (batch, M, N)
         out = torch.empty(shape, dtype=odt, device=a.device)
     ldd = out.stride(-2)
@@ -126,6 +153,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         args.ag_flags = gather["flags"]
         for i, ptr in enumerate(gather["src"]):
             args.ag_src[i] = int(ptr)
+    if conv is not None:
+        args.conv_taps = int(conv["taps"])
+        args.conv_c = ac
+        args.conv_b_tap_cols = int(conv.get("b_tap_cols", 0))
+        for i, sh in enumerate(conv["shifts"]):
+            args.conv_shift[i] = int(sh)
+    if b_row_shift:
+        if trans_b:
+            raise ValueError("gemm: b_row_shift needs b stored [K, N]")
+        args.b_row_shift = int(b_row_shift)
+    if row_map is not None:
+        args.map_hp, args.map_wp, args.map_h, args.map_w, args.map_pad = (int(v) for v in row_map)
     rc = _lib.lib().rb_gemm(ctypes.byref(args), _lib.stream_ptr())
     _lib.check(rc, "rb_gemm")
     return out

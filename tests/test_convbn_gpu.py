@@ -117,3 +117,47 @@ def test_tiny_resnet_trains_through_the_engine():
     stats = model._traced.rewrite_stats
     assert stats.get("conv2d", 0) >= 16 and stats.get("batch_norm_act", 0) >= 16
     pyrannc.clear()
+
+
+@pytest.mark.parametrize("N,Ci,Co,H,W,k", [(4, 64, 128, 14, 14, 3), (2, 128, 64, 9, 7, 3), (2, 64, 64, 8, 8, 5),
+                                           (3, 192, 320, 28, 28, 3)])
+@pytest.mark.parametrize("main_grad", [False, True])
+def test_conv2d_implicit_gemm_matches_fp32(N, Ci, Co, H, W, k, main_grad):
+    """conv_implicit_gemm: stride-1 "same" convolutions read the zero-padded activation tap by tap inside the
+    GEMM's producer (forward, input gradient) and with a row shift per tap (weight gradient): no im2col matrix."""
+    from rannc_b200.ops import _lib
+    from rannc_b200.ops import functional as RF
+    from rannc_b200.utils.config import set_conf
+
+    set_conf("conv_implicit_gemm", True)
+    set_conf("conv_implicit_max_overhead", 10.0)
+    try:
+        torch.manual_seed(0)
+        p = (k - 1) // 2
+        assert RF._Conv2d._implicit(k, 1, p, Ci, Co, H, W)
+        x = torch.randn(N, Ci, H, W, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+        w = (torch.randn(Co, Ci, k, k, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+        b = torch.randn(Co, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+        if main_grad:
+            w.main_grad = torch.ones(Co, Ci, k, k, device="cuda")
+        y = RF.conv2d(x, w, b, 1, p)
+        xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+        br = b.detach().float().requires_grad_(True)
+        ref = F.conv2d(xr, wr, br, 1, p)
+        assert y.shape == ref.shape
+        _close(y, ref)
+        dy = torch.randn_like(ref)
+        y.backward(dy.to(y.dtype))
+        ref.backward(dy.to(y.dtype).float())
+        torch.cuda.synchronize()
+        assert _lib.read_error() == 0
+        _close(x.grad, xr.grad, 3e-2)
+        if main_grad:
+            assert w.grad is None
+            _close(w.main_grad, wr.grad + 1.0, 3e-2)
+        else:
+            _close(w.grad, wr.grad, 3e-2)
+        _close(b.grad, br.grad, 3e-2)
+    finally:
+        set_conf("conv_implicit_gemm", False)
+        set_conf("conv_implicit_max_overhead", 1.2)
