@@ -107,11 +107,11 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def _plain_bert_module():
-    """The BERT model file is plain ``torch.nn`` code; load it by path so that the eager arm imports nothing
+def _plain_bert_module(fname: str = "bert.py"):
+    """The model files are plain ``torch.nn`` code; load one by path so that the eager arm imports nothing
     else of this library."""
-    spec = importlib.util.spec_from_file_location("_bench_plain_bert", os.path.join(HERE, "rannc_b200", "models",
-                                                                                   "bert.py"))
+    spec = importlib.util.spec_from_file_location("_bench_plain_" + fname[:-3],
+                                                  os.path.join(HERE, "rannc_b200", "models", fname))
     mod = importlib.util.module_from_spec(spec)
     sys.modules[spec.name] = mod
     spec.loader.exec_module(mod)
@@ -157,22 +157,46 @@ def run_eager(args, steps: int, warmup: int, want_e2e: bool):
     dev = torch.device("cuda", local)
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
-    bert = _plain_bert_module()
     torch.manual_seed(1234)
-    cfg = bert.BertConfig(hidden_size=args.hidden, num_hidden_layers=args.layers, num_attention_heads=args.heads,
-                          intermediate_size=4 * args.hidden, max_position_embeddings=max(512, args.seq))
-    model = bert.BertForPreTraining(cfg).to(dev)
-    opt = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0, fused=True)
-    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True) \
-        if world > 1 else model
     lb = args.global_batch // world
     n_sets = 2
     host = []
-    for s in range(n_sets):
-        full = bert.synthetic_batch(cfg, args.global_batch, args.seq, seed=100 + s)
-        host.append(tuple(t[rank * lb:(rank + 1) * lb].contiguous().pin_memory() for t in full))
+    resnet = args.model == "wide_resnet"
+    scaler = None
+    if resnet:
+        # the same wide ResNet-152 on stock PyTorch: channels-last, fp16 autocast with a GradScaler (or bf16),
+        # SGD momentum
+        rn = _plain_bert_module("resnet.py")
+        half = (args.amp_dtype or "fp16") == "fp16"
+        amp_dtype = torch.float16 if half else torch.bfloat16
+        model = rn.ResNetWithLoss(rn.wide_resnet152(width_mult=args.width)).to(dev).to(
+            memory_format=torch.channels_last)
+        opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+        scaler = torch.amp.GradScaler("cuda") if half else None
+        for s in range(n_sets):
+            g = torch.Generator().manual_seed(100 + s)
+            x = torch.randn(lb, 3, args.image, args.image, generator=g).to(amp_dtype).contiguous(
+                memory_format=torch.channels_last).pin_memory()
+            y = torch.randint(0, 1000, (lb,), generator=g).pin_memory()
+            host.append((x, y))
+        default_micro = 32
+    else:
+        bert = _plain_bert_module()
+        amp_dtype = torch.bfloat16
+        cfg = bert.BertConfig(hidden_size=args.hidden, num_hidden_layers=args.layers,
+                              num_attention_heads=args.heads, intermediate_size=4 * args.hidden,
+                              max_position_embeddings=max(512, args.seq))
+        model = bert.BertForPreTraining(cfg).to(dev)
+        opt = torch.optim.Adam(model.parameters(), lr=1e-4, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.0,
+                               fused=True)
+        for s in range(n_sets):
+            full = bert.synthetic_batch(cfg, args.global_batch, args.seq, seed=100 + s)
+            host.append(tuple(t[rank * lb:(rank + 1) * lb].contiguous().pin_memory() for t in full))
+        default_micro = 64
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True) \
+        if world > 1 else model
     dev_sets = [tuple(t.to(dev) for t in hs) for hs in host]
-    micro = [min(lb, args.eager_micro_batch if args.eager_micro_batch > 0 else 64)]
+    micro = [min(lb, args.eager_micro_batch if args.eager_micro_batch > 0 else default_micro)]
 
     def one_step(batch):
         nmb = (lb + micro[0] - 1) // micro[0]
@@ -182,11 +206,16 @@ def run_eager(args, steps: int, warmup: int, want_e2e: bool):
             last = i == nmb - 1
             ctx = net.no_sync() if (world > 1 and not last) else contextlib.nullcontext()
             with ctx:
-                with torch.autocast("cuda", dtype=torch.bfloat16):
+                with torch.autocast("cuda", dtype=amp_dtype):
                     loss = net(*sl)
-                (loss * (sl[0].shape[0] / lb)).backward()
+                part = loss * (sl[0].shape[0] / lb)
+                (scaler.scale(part) if scaler is not None else part).backward()
             total = loss.detach() if total is None else total + loss.detach()
-        opt.step()
+        if scaler is not None:
+            scaler.step(opt)
+            scaler.update()
+        else:
+            opt.step()
         opt.zero_grad(set_to_none=True)
         return total / nmb
 
@@ -259,7 +288,20 @@ def eager_main(args):
     sampler.start()
     r = run_eager(args, args.steps, args.warmup, not args.no_e2e)
     clocks = sampler.stop()
-    if rank == 0:
+    if rank == 0 and args.model == "wide_resnet":
+        print(json.dumps({
+            "metric": "ResNet samples/s (max over ranks)", "value": r["value"], "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": args.amp_dtype or "fp16",
+            "data": "synthetic (N(0,1) images, uniform labels), random-init weights", "impl": "eager",
+            "config": {"model": f"wide ResNet-152 x{args.width:g}", "params": r["params"],
+                       "global_batch": args.global_batch, "image": args.image,
+                       "parallelism": (f"ddp{world}" if world > 1 else "single") + f"_microbatch{r['micro_batch']}",
+                       "optimizer": "torch.optim.SGD(momentum=0.9), autocast + GradScaler, channels-last, cuDNN",
+                       "l2": "per-step working set far exceeds the 126 MB L2; no flush needed"},
+            "clocks": clocks, "e2e": r.get("e2e"), "gpu_launches": 0,
+            "note": "stock PyTorch kernels only (context number, not this library)"}))
+    elif rank == 0:
         print(json.dumps({
             "metric": "BERT samples/s (max over ranks)", "value": r["value"], "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
