@@ -381,6 +381,10 @@ def main():
         os.environ.setdefault("RANNC_PARTITION_NUM", str(args.stages))
     if args.model == "bert26b":
         os.environ.setdefault("RANNC_FORCE_DIST_MATMUL", "true")
+    if args.model == "wide_resnet":
+        # one stage, several micro-batches: each micro-batch's backward right after its forward, so that nothing
+        # has to be recomputed (185.7 against 141.2 samples/s on one GPU)
+        os.environ.setdefault("RANNC_INTERLEAVE_BACKWARD", "true")
 
     import torch
 

@@ -245,6 +245,7 @@ PYBIND11_MODULE(_core, m) {
         .def_readwrite("use_amp_master_params", &PartitioningConf::use_amp_master_params)
         .def_readwrite("enable_zero", &PartitioningConf::enable_zero)
         .def_readwrite("offload_params", &PartitioningConf::offload_params)
+        .def_readwrite("interleave_single_stage", &PartitioningConf::interleave_single_stage)
         .def_readwrite("force_dist_matmul", &PartitioningConf::force_dist_matmul)
         .def_readwrite("opt_param_factor", &PartitioningConf::opt_param_factor)
         .def_readwrite("min_pipeline", &PartitioningConf::min_pipeline)

@@ -983,7 +983,9 @@ bool DPStaging::runOnce(int S, int P, bool ckpt, AllocSolution* sol, std::vector
         ev.e.allreduce_us = calcAllReduceTime(pm_.link(), sg.paramSizeInByte(), repl);
         ev.e.opt_mem = getOptMemSize(sg, conf_, repl);
         ev.e.comm_mem = scaled.commBufSize();
-        ev.e.total_mem = calcGraphMem(scaled, ev.e.profile, conf_, repl, P, stage_ckpt);
+        // a single stage that interleaves forward and backward per micro-batch holds one micro-batch at a time
+        const int P_mem = (conf_.interleave_single_stage && b0 == 0 && b1 == L) ? 1 : P;
+        ev.e.total_mem = calcGraphMem(scaled, ev.e.profile, conf_, repl, P_mem, stage_ckpt);
         ev.ok = conf_.dev_mem <= 0 || ev.e.total_mem < conf_.dev_mem;
         return evals.emplace(key, std::move(ev)).first->second;
     };

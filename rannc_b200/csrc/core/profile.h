@@ -67,6 +67,9 @@ struct PartitioningConf {
     bool checkpointing = false;          // force recompute
     bool checkpointing_no_last = false;
     bool prefer_no_checkpointing = true; // keep activations resident when they fit (180 GB HBM)
+    // a plan of ONE stage runs each micro-batch's backward right after its forward (interleave_backward), so
+    // only one micro-batch's activations are alive whatever the number of micro-batches
+    bool interleave_single_stage = false;
     LinkModel link;
     mp::Value pack() const;
     static PartitioningConf unpack(const mp::Value& v);

@@ -104,6 +104,7 @@ const Def kDefs[] = {
     {"offload_param_window_mb", ConfigItem::INT, "0"},
     {"checkpoint_segments", ConfigItem::INT, "0"},
     {"conv_implicit_gemm", ConfigItem::BOOL, "true"},
+    {"interleave_backward", ConfigItem::BOOL, "false"},
     {"conv_implicit_max_overhead", ConfigItem::FLOAT, "1.2"},
     {"use_named_tensors", ConfigItem::BOOL, "false"},
     {"profiler_cache_size", ConfigItem::INT, "0"},

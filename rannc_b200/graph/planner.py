@@ -141,7 +141,7 @@ def _load_alloc_solution(pconf):
 
 def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: int, global_batch: int,
          dev_total_mem: int, use_amp: bool, enable_zero: bool, offload_params: bool, dep_id: str,
-         load_deployment: Optional[str] = None, subgraph_profiler=None) -> Plan:
+         load_deployment: Optional[str] = None, subgraph_profiler=None, interleave: bool = False) -> Plan:
     """``ir_graph`` must already be scaled to the global batch size.  ``subgraph_profiler``
     (``profiler.SubgraphProfiler``): when given, every block of the coarsened graph is measured once and the
     operator profiles are calibrated to it; with ``measure_subgraphs`` the stage search measures its candidate
@@ -151,6 +151,7 @@ def plan(ir_graph, node_profiles: Dict[str, "_core.NodeProfile"], world_size: in
         dev_total_mem = 180 * 10 ** 9
     dev_mem = device_memory_budget(dev_total_mem)
     pconf = make_partitioning_conf(world_size, global_batch, dev_mem, use_amp, enable_zero, offload_params)
+    pconf.interleave_single_stage = bool(interleave)
 
     load_path = load_deployment or (str(conf("deployment_file")) if bool(conf("load_deployment")) else None)
     if load_path:

@@ -102,6 +102,7 @@ class RaNNCModule:
         self._storage: Optional[ParamStorage] = None
         self._runtime: Optional[PipelineRuntime] = None
         self._traced = None
+        self._interleave = False
         self._plan = None
         self._anchor = None
         self._used_param_names: List[str] = []
@@ -145,7 +146,12 @@ class RaNNCModule:
         # A model without trainable parameters, fed inputs that need no gradient, has nothing to differentiate:
         # its outputs stay plain tensors, nothing is saved for a backward pass, and none is expected on any rank.
         need_grad = torch.is_grad_enabled() and (self._trainable or bool(extra))
-        outs = self._runtime.forward(args, grad_enabled=need_grad)
+        inter = None
+        if need_grad and self._interleave and not extra and not _keep_graph:
+            # the gradient that will arrive at the outputs: 1, or the loss scale under amp.scale_loss
+            inter = float(_amp.get_scaler().loss_scale()) if self.use_amp_master_params else 1.0
+            self._set_split_hook()
+        outs = self._runtime.forward(args, grad_enabled=need_grad, interleave_scale=inter)
         if need_grad:
             outs = list(_DistBackward.apply(weakref.ref(self), self._anchor, len(outs), names, *outs, *extra))
         if trim:
@@ -289,11 +295,18 @@ class RaNNCModule:
         if dev.type == "cuda":
             total_mem = torch.cuda.get_device_properties(dev).total_memory
         dep_bytes = None
+        # interleave_backward: with ONE stage, a micro-batch's backward can run right after its forward, so that
+        # only one micro-batch's activations are alive (the synchronous schedule of the reference keeps or
+        # recomputes all of them).  Needs the upstream gradient before the caller's backward(): possible when every
+        # output is a loss (it is 1, or the loss scale) and no input wants a gradient.
+        self._interleave = bool(conf("interleave_backward")) and not _keep_graph and \
+            all(tm.ir.value(o).is_loss for o in tm.user_outputs) and \
+            not any(isinstance(a, torch.Tensor) and a.requires_grad for a in args)
         if rank == 0:
             logger.info("Partitioning the model for %d device(s), global batch %d ...", world, global_bs)
             self._plan = planner.plan(ir, node_profiles, world, global_bs, total_mem, self.use_amp_master_params,
                                       self.enable_zero, self.offload_params, self.id, self.load_deployment,
-                                      subgraph_profiler=sub_prof)
+                                      subgraph_profiler=sub_prof, interleave=self._interleave)
             if sub_prof is not None:
                 if bool(conf("save_graph_profile")) and sub_prof.count:
                     # the measured blocks / stages go into the same file as the operator profiles
@@ -687,7 +700,7 @@ class RaNNCModule:
                     self._grad_hooks.append(p.register_post_accumulate_grad_hook(fold))
 
     # ------------------------------------------------------------------ backward
-    def _run_backward(self, grads, want_input_grads=()):
+    def _set_split_hook(self):
         red = self._fused_reducer
         if red is not None and red.handles_reduce:
             # the reducer is told which micro-batch's backward is the last one before the optimizer step: during
@@ -696,6 +709,10 @@ class RaNNCModule:
             self._runtime.split_hook = lambda i, n: red.begin_backward(final and i == n - 1)
         else:
             self._runtime.split_hook = None
+
+    def _run_backward(self, grads, want_input_grads=()):
+        red = self._fused_reducer
+        self._set_split_hook()
         try:
             in_grads = self._runtime.backward(grads, want_input_grads)
         finally:

@@ -122,9 +122,18 @@ class PipelineRuntime:
         return comm.redist(t, args, recv_rows, None, row_shape, dtype, self.pending)
 
     # ---------------------------------------------------------------- forward
-    def forward(self, inputs: Sequence[torch.Tensor], grad_enabled: bool = True):
+    def forward(self, inputs: Sequence[torch.Tensor], grad_enabled: bool = True,
+                interleave_scale: Optional[float] = None):
+        """``interleave_scale``: the caller promises that every output is a loss whose backward() will arrive with
+        this upstream gradient (1, or the loss scale).  With a single stage each micro-batch's backward then runs
+        right after its forward, so only one micro-batch's activations are ever alive; ``backward`` later only
+        checks the promise."""
         comm.check_peers()
         P = self.P
+        inter = interleave_scale is not None and grad_enabled and P > 1 and len(self.order) == 1 and \
+            self.order[0] in self.stages
+        self._interleaved = float(interleave_scale) if inter else None
+        self.interleaved_steps = getattr(self, "interleaved_steps", 0) + (1 if inter else 0)
         by_name = dict(zip(self.user_inputs, inputs))
         # cumulative local row offsets of this rank's share of each micro-batch
         local_rows = [self.calc.local_split_size(self.master.index(self.rank), len(self.master), i)
@@ -176,6 +185,19 @@ class PipelineRuntime:
                 self.timers.stop("forward " + sname)
                 _core.trace_end(_core.func_key("forward", sname, i, False))
                 stage_vals[(i, sname)] = outs
+                if inter:
+                    # this micro-batch's backward, now: d(global loss)/d(local loss) x world x upstream gradient
+                    if self.split_hook is not None:
+                        self.split_hook(i, P)
+                    og = {}
+                    for r in self.routes.master_out.get(sname, []):
+                        w = self._loss_weight(ranks, i) * self.world * self._interleaved
+                        og[r.value_name] = torch.full((), w, dtype=torch.float32, device=dev)
+                    _core.trace_begin(_core.func_key("backward", sname, i, True))
+                    self.timers.start("backward " + sname)
+                    st.backward(i, og)
+                    self.timers.stop("backward " + sname)
+                    _core.trace_end(_core.func_key("backward", sname, i, True))
                 if self.show_act:
                     for oname, o in outs.items():
                         self._show("out", oname, i, o)
@@ -249,6 +271,18 @@ class PipelineRuntime:
         (this rank's rows; the same names must be asked for on every rank)."""
         comm.check_peers()
         P = self.P
+        if getattr(self, "_interleaved", None) is not None:
+            # the backward passes ran inside forward(); what is left is to see that the upstream gradient is the
+            # one they were run with
+            want = self._interleaved
+            self._interleaved = None
+            for g in out_grads:
+                if g is not None and abs(float(g) - want) > 1e-6 * max(1.0, abs(want)):
+                    raise RuntimeError(
+                        f"interleave_backward: the loss was differentiated with an upstream gradient of {float(g)} "
+                        f"where {want} was expected (call loss.backward() on the returned loss itself, or through "
+                        f"amp.scale_loss); set interleave_backward=false for anything else")
+            return {}
         input_grads: Dict[str, List[Optional[torch.Tensor]]] = {n: [None] * P for n in want_input_grads}
         offs, _ = self._fwd_state
         gmap = dict(zip(self.user_outputs, out_grads))

@@ -191,6 +191,7 @@ def main():
                             f"{(v.float() - p.detach().float()).abs().max().item()}")
     stages = len(wrapped._dep.fwd_graph_order)
     res = {"ok": ok, "msgs": msgs[:8], "stages": stages,
+           "interleaved": getattr(wrapped._runtime, "interleaved_steps", 0),
            "buckets": max([len(g_.buckets) for g_ in wrapped._storage.groups] or [0]), "pipeline": wrapped._dep.pipeline_num, "sliced": len(wrapped._storage.sliced),
            "alloc": {k: list(v) for k, v in wrapped._dep.allocation.items()}}
     all_res = pyrannc._comm.allgather_obj(res)

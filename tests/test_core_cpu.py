@@ -918,3 +918,21 @@ def test_dimension_names_follow_the_batch_through_the_trace(monkeypatch):
     assert "N" not in tm.dim_names["sum_1"] and "N" not in tm.dim_names["p_lin_weight"]
     tm2 = tracer.trace(M(), (torch.randn(4, 8),), use_kernels=False, name="m")
     assert tm2.dim_names == {}
+
+
+def test_single_stage_plan_with_interleaved_backward_needs_one_micro_batch_of_memory():
+    """interleave_single_stage: the stage search counts ONE micro-batch's activations for a one-stage plan, so a
+    model that the synchronous schedule can only fit with recomputation runs without it in several micro-batches."""
+    g = make_mlp_graph(layers=8, hidden=256, batch=64, with_loss=True)
+    act = 64 * 256 * 4 * 40                                  # activations per operator at the full batch
+    np_ = _profiles(g, act=act)
+    total_act = act * len(g.nodes)
+    conf = _conf(1, 64, int(total_act * 0.4) + g.param_size_in_byte() * 4)
+    pm = _core.ProfileModel(g, np_, conf.link)
+    ml = _core.ml_partition(pm, conf)
+    sol, est, _ = _core.dp_staging(pm, ml, conf)
+    assert sol.checkpointing or len(sol.graphs) > 1, \
+        "the synchronous schedule should not fit this model without recomputation"
+    conf.interleave_single_stage = True
+    sol2, est2, _ = _core.dp_staging(pm, _core.ml_partition(pm, conf), conf)
+    assert len(sol2.graphs) == 1 and not sol2.checkpointing and sol2.pipeline_num >= 4

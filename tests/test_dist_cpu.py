@@ -290,3 +290,19 @@ def test_recomputation_segment_by_segment_matches_stage_recomputation(world, cas
     segment at a time in backward; same dropout masks, same gradients as recomputing the whole stage."""
     res = run_case(world, case, env, timeout=600, worker="stream_worker.py", every_rank=True)
     assert res["info"]["segments"] >= 3
+
+
+@pytest.mark.parametrize("world,case", [
+    (1, {"model": "loss", "batch": 8}),
+    (2, {"model": "loss", "batch": 16, "opt": "adam"}),
+    (2, {"model": "loss", "batch": 16, "amp": True, "zero": True, "opt": "adam", "tol": 1e-1}),
+    (2, {"model": "loss", "batch": 16, "accum": 2}),
+])
+def test_backward_interleaved_with_forward_per_micro_batch(world, case):
+    """interleave_backward: a one-stage plan runs each micro-batch's backward right after its forward (one
+    micro-batch's activations alive instead of all of them); losses, gradients, updates and checkpoints equal
+    eager's on the full batch."""
+    res = run_case(world, case, {"RANNC_INTERLEAVE_BACKWARD": "true", "RANNC_PIPELINE_NUM": "4",
+                                 "RANNC_PARTITION_NUM": "1"})
+    assert res["ranks"][0]["stages"] == 1 and res["ranks"][0]["pipeline"] == 4
+    assert all(r["interleaved"] >= 3 for r in res["ranks"])
