@@ -445,7 +445,8 @@ def main():
             host.append(tuple(t[rank * lb:(rank + 1) * lb].contiguous().pin_memory() for t in full))
     else:
         # wide ResNet-152: bottleneck blocks 3/8/36/3, every convolution x --width, BatchNorm, fp16 mixed
-        # precision with dynamic loss scaling, SGD momentum 0.9, images N(0, 1), labels uniform over 1000 classes
+        # precision (every step checks the gradients for overflow; the loss scale stays 1 unless the caller installs a
+        # dynamic scaler with amp.initialize), SGD momentum 0.9, images N(0, 1), labels uniform over 1000 classes
         from rannc_b200.models.resnet import ResNetWithLoss, wide_resnet152
 
         half = (args.amp_dtype or "fp16") == "fp16"
@@ -579,7 +580,7 @@ def main():
         else:
             mname = f"Wide ResNet-152 (widths x{args.width:g}), {args.image}x{args.image} images"
             data = "synthetic (N(0,1) images, uniform labels over 1000 classes), random-init weights"
-            optname = "SGD momentum 0.9 (fused, fp32 master" + (", dynamic loss scale)" if half else ")")
+            optname = "SGD momentum 0.9 (fused, fp32 master" + (", fp16 overflow check at loss scale 1)" if half else ")")
             dtype = "fp16" if half else "bf16"
         value = args.global_batch * args.steps / (ms / 1e3)
         plan = getattr(wrapped, "_plan", None)
