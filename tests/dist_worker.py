@@ -70,6 +70,24 @@ def main():
                 inputs = tuple(t.clone().requires_grad_(True) if t.is_floating_point() else t for t in inputs)
             out = wrapped(*local)
             rout = ref(*inputs)
+            if case.get("bad_upstream") and out.dim() == 0:
+                # interleave_backward ran the backward passes assuming d(loss) = 1: anything else must be refused
+                try:
+                    (out * 2.0).backward()
+                    ok = False
+                    msgs.append("a scaled loss was accepted although the backward passes had already run")
+                except RuntimeError as e:
+                    if "interleave_backward" not in str(e):
+                        ok = False
+                        msgs.append(f"unexpected error: {e}")
+                res = {"ok": ok, "msgs": msgs[:8], "stages": len(wrapped._dep.fwd_graph_order), "interleaved": 1,
+                       "pipeline": wrapped._dep.pipeline_num}
+                all_res = pyrannc._comm.allgather_obj(res)
+                if rank == 0:
+                    print("RESULT " + json.dumps({"ok": all(r["ok"] for r in all_res), "ranks": all_res}))
+                pyrannc.barrier()
+                pyrannc.clear()
+                sys.exit(0 if all(r["ok"] for r in all_res) else 1)
             if out.dim() == 0:
                 if abs(float(out) - float(rout)) > tol * max(1.0, abs(float(rout))):
                     ok = False

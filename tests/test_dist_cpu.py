@@ -306,3 +306,8 @@ def test_backward_interleaved_with_forward_per_micro_batch(world, case):
                                  "RANNC_PARTITION_NUM": "1"})
     assert res["ranks"][0]["stages"] == 1 and res["ranks"][0]["pipeline"] == 4
     assert all(r["interleaved"] >= 3 for r in res["ranks"])
+
+
+def test_interleaved_backward_refuses_another_upstream_gradient():
+    run_case(1, {"model": "loss", "batch": 8, "bad_upstream": True},
+             {"RANNC_INTERLEAVE_BACKWARD": "true", "RANNC_PIPELINE_NUM": "4", "RANNC_PARTITION_NUM": "1"})
