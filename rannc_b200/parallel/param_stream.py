@@ -303,10 +303,6 @@ class StreamedStage(StageExec):
                                              if isinstance(t, torch.nn.Parameter)}.values())
             self.segments = split_into_segments(gm, params, max(1, total // max(1, segments)), resident=True)
         self.mode: Dict[int, bool] = {}     # micro-batch -> ran segment by segment
-        out_node = next(n for n in gm.graph.nodes if n.op == "output")
-        # a stage output that is a stage input (pass-through) is produced by no segment
-        self._out_nodes = [a.name for a in out_node.args[0]] if isinstance(out_node.args[0], (tuple, list)) \
-            else [out_node.args[0].name]
         self._last_use: Dict[str, int] = {}
         for i, s in enumerate(self.segments):
             for nm in s.inputs:
