@@ -381,9 +381,10 @@ def main():
         os.environ.setdefault("RANNC_PARTITION_NUM", str(args.stages))
     if args.model == "bert26b":
         os.environ.setdefault("RANNC_FORCE_DIST_MATMUL", "true")
-    if args.model == "wide_resnet":
+    if args.model == "wide_resnet" and args.gpus == 1:
         # one stage, several micro-batches: each micro-batch's backward right after its forward, so that nothing
-        # has to be recomputed (185.7 against 141.2 samples/s on one GPU)
+        # has to be recomputed (185.7 against 141.2 samples/s on one GPU).  Measured on one GPU only, hence not
+        # switched on for more (set RANNC_INTERLEAVE_BACKWARD=true to try it there).
         os.environ.setdefault("RANNC_INTERLEAVE_BACKWARD", "true")
 
     import torch
