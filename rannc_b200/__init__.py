@@ -37,6 +37,7 @@ for _w in _core.config_warnings():
 from .parallel import comm as _comm  # noqa: E402
 from .module import (RaNNCModule, delay_grad_allreduce, keep_graph, sync_params_on_init)  # noqa: E402,F401
 from . import amp, tensor_coll, comm_utils, utils  # noqa: E402,F401
+from .tensor_coll import all_gather  # noqa: E402,F401  (re-exported by the reference: pyrannc/__init__.py:30)
 from .dist_param import (DistributeModelParams, store_dist_param, load_dist_param, set_dist_param,  # noqa: E402,F401
                          get_dist_param_range, set_dist_param_dtype, get_dist_param_segment, remove_dist_param,
                          dist_param_registered)
@@ -81,6 +82,17 @@ def _run_dp_dry(path: str, dev_num=None, dev_mem=None):
     """Re-runs only the stage search from a dumped cache, without a GPU (reference: main.cpp:412-421)."""
     with open(path, "rb") as f:
         return _core.run_dp_dry(f.read(), dev_num, dev_mem)
+
+
+def abort_all_processes() -> None:
+    """Ends this process at once with a failure code; the launcher takes the other ranks down (reference:
+    MPI_Abort on the world communicator, src/main.cpp:510-515)."""
+    import os
+    import sys
+
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(1)
 
 
 def show_deployment(path: str, batch_size: int) -> str:

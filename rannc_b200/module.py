@@ -840,6 +840,77 @@ class RaNNCModule:
         shape, dtype = self._param_meta[name]
         return self._storage.get_param_grad(name, shape, dtype, amp_master_param)
 
+    # ---- the reference's lower-level accessors (src/main.cpp:271-402, src/comp/RaNNCModule.cpp:595-664) --------
+    def sync_param(self, name: str) -> torch.Tensor:
+        """Collective: the current value of parameter ``name`` (the 16-bit / working copy) on every rank, on the
+        CPU.  The reference addresses parameters by id; here the name is the key."""
+        return self.get_param(name, False)
+
+    def sync_param_grad(self, name: str) -> torch.Tensor:
+        """Collective: the reduced gradient of parameter ``name`` on every rank, on the CPU."""
+        return self.get_param_grad(name, False)
+
+    def sync_param_zero(self, grad: bool = False) -> None:
+        """Under ZeRO every rank updates slices of the parameters; the reference re-broadcasts the slices here
+        before parameters are read.  The fused and the collective update paths of this runtime both leave every
+        owner with the full 16-bit parameters after each step (the all-gather is part of the step), so there is
+        nothing left to do; gradients are assembled on demand by :meth:`get_param_grad`."""
+        if self.ready:
+            self._storage._ensure_reduced(sticky=False)
+
+    def align_params(self) -> None:
+        """The reference re-aligns its ZeRO buffers after the optimizer was patched; the flat buffers here are
+        laid out aligned at deployment and never move."""
+
+    def get_local_param_range(self, name: str):
+        """(begin, end) in elements, relative to the start of parameter ``name``, of the part whose fp32 master
+        copy and optimizer state this rank keeps (the whole parameter without ZeRO; (0, 0) when this rank holds
+        none of it).  Reference: ParamStorage::getLocalParamRange."""
+        if not self.ready or name not in self._storage.by_name:
+            return (0, 0)
+        g, i = self._storage.by_name[name]
+        lo, _ = g.param_range(i)
+        a, b = g.local_range(i)
+        return (a - lo, b - lo) if b > a else (0, 0)
+
+    def get_local_param_segment(self, name: str) -> Optional[torch.Tensor]:
+        """This rank's part of parameter ``name`` as a flat tensor: the fp32 master values under mixed precision,
+        the parameter's own values otherwise (None when this rank holds none of it)."""
+        if not self.ready or name not in self._storage.by_name:
+            return None
+        g, i = self._storage.by_name[name]
+        a, b = g.local_range(i)
+        if b <= a:
+            return None
+        if g.flat_master is not None:
+            la = g.to_local(a)
+            return g.flat_master[la:la + (b - a)]
+        return g.flat_param[a:b]
+
+    def _sync_orig_params(self, sync_all_ranks: bool = False, sync_grad: bool = False, name_pattern=None) -> None:
+        """Collective: writes the trained values (and, with ``sync_grad``, the reduced gradients) back into the
+        parameters of the wrapped model on rank 0, or on every rank (reference: pyrannc/__init__.py:539-572).  A
+        parameter this rank holds keeps its place in the flat buffer and is already current; one it does not hold
+        gets a tensor of its own."""
+        if not self.ready:
+            return
+        rank = comm.get_rank()
+        held = set(self._used_param_names)
+        for name, p in self.model.named_parameters():
+            if name_pattern is not None and name_pattern not in name:
+                continue
+            v = self.get_param(name, False)
+            gv = self.get_param_grad(name, False) if (sync_grad and p.requires_grad) else None
+            if rank != 0 and not sync_all_ranks:
+                continue
+            with torch.no_grad():
+                if name not in held or p.data.numel() != v.numel():
+                    dev = p.device if p.data.numel() else v.device
+                    p.data = v.to(device=dev, dtype=p.dtype)
+                if gv is not None:
+                    p.grad = gv.to(device=p.device, dtype=p.dtype).view(p.shape)
+        comm.barrier()
+
     def state_dict(self, *args, no_hook: bool = False, sync_all_ranks: bool = True, amp_master_params: bool = True,
                    rank0_only: bool = True, **kwargs):
         """Collective: every rank must call it.  Full CPU tensors under the original names (tied parameters

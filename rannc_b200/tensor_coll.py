@@ -23,6 +23,11 @@ def bcast(t: torch.Tensor, root: int = 0) -> torch.Tensor:
     return t
 
 
+def bcast_tensor(t: torch.Tensor, root: int = 0) -> torch.Tensor:
+    """The reference's name for :func:`bcast` (main.cpp:96-119)."""
+    return bcast(t, root)
+
+
 def all_gather(t: torch.Tensor, buf: torch.Tensor = None) -> torch.Tensor:
     """Concatenation of every rank's ``t`` along a new leading dimension (flattened into ``buf`` when given)."""
     n = comm.get_world_size()

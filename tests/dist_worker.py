@@ -141,6 +141,37 @@ def main():
             if not torch.allclose(v.float(), p.detach().float(), rtol=tol * 10, atol=tol * 10):
                 ok = False
                 msgs.append(f"it {it}: param {n} differs by {(v.float() - p.detach().float()).abs().max().item()}")
+    if case.get("accessors") and has_params:
+        # the reference's lower-level accessors: per-rank segments tile each parameter exactly once over its
+        # owners, sync_param agrees with get_param, _sync_orig_params writes the trained values into the model
+        for n, p in ref.named_parameters():
+            full = wrapped.get_param(n, amp_master_param=True)
+            a, b = wrapped.get_local_param_range(n)
+            seg = wrapped.get_local_param_segment(n)
+            cover = torch.zeros(full.numel())
+            if b > a:
+                if seg is None or seg.numel() != b - a or \
+                        not torch.allclose(seg.detach().float().cpu().view(-1), full.view(-1)[a:b].float(),
+                                           rtol=tol * 10, atol=tol * 10):
+                    ok = False
+                    msgs.append(f"local segment of {n} [{a}, {b}) does not match the parameter")
+                cover[a:b] = 1.0
+            tot = pyrannc._comm.allgather_obj(float(cover.sum()))
+            owners = len(wrapped._storage.param_ranks[n])
+            want_total = full.numel() * (1 if case.get("zero") else owners)
+            if rank == 0 and abs(sum(tot) - want_total) > 0.5:
+                ok = False
+                msgs.append(f"segments of {n} cover {sum(tot)} elements, expected {want_total}")
+            if not torch.equal(wrapped.sync_param(n), wrapped.get_param(n)):
+                ok = False
+                msgs.append(f"sync_param({n}) differs from get_param")
+        wrapped._sync_orig_params(sync_all_ranks=True)
+        for (n, p), (_, q) in zip(ref.named_parameters(), model.named_parameters()):
+            if q.numel() != p.numel() or not torch.allclose(q.detach().float().cpu().view(-1),
+                                                            p.detach().float().view(-1), rtol=tol * 10,
+                                                            atol=tol * 10):
+                ok = False
+                msgs.append(f"_sync_orig_params left {n} different from the trained value")
     # checkpoint round trip
     sd = wrapped.state_dict()
     osd = opt.state_dict(from_global=True) if opt is not None else {"state": {}}

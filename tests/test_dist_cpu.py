@@ -311,3 +311,29 @@ def test_backward_interleaved_with_forward_per_micro_batch(world, case):
 def test_interleaved_backward_refuses_another_upstream_gradient():
     run_case(1, {"model": "loss", "batch": 8, "bad_upstream": True},
              {"RANNC_INTERLEAVE_BACKWARD": "true", "RANNC_PIPELINE_NUM": "4", "RANNC_PARTITION_NUM": "1"})
+
+
+@pytest.mark.parametrize("case,env", [
+    ({"model": "deep", "batch": 8, "accessors": True}, {"RANNC_PARTITION_NUM": "2"}),
+    ({"model": "layernorm", "batch": 8, "amp": True, "zero": True, "opt": "adam", "tol": 1e-1, "accessors": True},
+     {"RANNC_GRAD_BUCKET_MB": "0.0005"}),
+])
+def test_low_level_parameter_accessors(case, env):
+    """get_local_param_range / get_local_param_segment / sync_param / _sync_orig_params
+    (reference: src/main.cpp:271-402, pyrannc/__init__.py:539-572)."""
+    run_case(2, case, env)
+
+
+def test_package_exports_the_reference_names():
+    import rannc_b200 as pyrannc
+
+    for name in ("RaNNCModule", "get_rank", "get_world_size", "barrier", "clear", "delay_grad_allreduce", "keep_graph",
+                 "sync_params_on_init", "recreate_all_communicators", "show_deployment", "_run_dp_dry",
+                 "_dump_events", "all_gather", "patch_optimizer", "abort_all_processes", "store_dist_param",
+                 "load_dist_param", "set_dist_param", "get_dist_param_range", "set_dist_param_dtype"):
+        assert hasattr(pyrannc, name), name
+    for name in ("sync_param", "sync_param_grad", "sync_param_zero", "align_params", "get_local_param_range",
+                 "get_local_param_segment", "_sync_orig_params", "clip_grad_norm", "_calc_grad_norm", "undeploy",
+                 "enable_dropout", "save_deployment", "is_checkpointing_enabled"):
+        assert hasattr(pyrannc.RaNNCModule, name), name
+    assert hasattr(pyrannc.tensor_coll, "bcast_tensor") and hasattr(pyrannc.tensor_coll, "allreduce_tensor")
