@@ -337,3 +337,33 @@ def test_package_exports_the_reference_names():
                  "enable_dropout", "save_deployment", "is_checkpointing_enabled"):
         assert hasattr(pyrannc.RaNNCModule, name), name
     assert hasattr(pyrannc.tensor_coll, "bcast_tensor") and hasattr(pyrannc.tensor_coll, "allreduce_tensor")
+
+
+def test_bert_pretraining_example_saves_and_resumes_across_world_sizes(tmp_path):
+    """examples/bert_pretrain.py: two ranks, two pipeline stages, the model declared in shards, two optimizer
+    groups, clipping; the checkpoint it writes is resumed by a single process (another partitioning)."""
+    ck = tmp_path / "bert.pt"
+    port = _free_port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), RANNC_FORCE_CPU="1", OMP_NUM_THREADS="1", RANNC_LOG_LEVEL="warning",
+                   RANNC_PARTITION_NUM="2")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "examples", "bert_pretrain.py"), "--steps",
+                                       "3", "--dist-params", "--save", str(ck)], env=env, cwd=ROOT,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n----\n".join(o[-2000:] for o in outs)
+    first = [float(ln.split("loss ")[1].split()[0]) for ln in outs[0].splitlines() if ln.startswith("step ")]
+    assert len(first) == 3 and ck.exists()
+    saved_val = [float(ln.split()[-1]) for ln in outs[0].splitlines() if ln.startswith("held-out loss")][0]
+    env = dict(os.environ, RANK="0", WORLD_SIZE="1", RANNC_FORCE_CPU="1", RANNC_LOG_LEVEL="warning",
+               MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "bert_pretrain.py"), "--steps", "2", "--resume",
+                        str(ck)], env=env, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    resumed = [ln for ln in r.stdout.splitlines() if ln.startswith("step ")]
+    assert resumed and resumed[0].startswith("step 3:")
+    # the weights the single process starts from are the ones the two ranks trained: same held-out loss
+    got_val = [float(ln.split()[-1]) for ln in r.stdout.splitlines() if ln.startswith("resumed at step 3")][0]
+    assert abs(got_val - saved_val) < 2e-2 * abs(saved_val), (got_val, saved_val)
