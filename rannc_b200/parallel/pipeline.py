@@ -130,6 +130,9 @@ class PipelineRuntime:
         checks the promise."""
         comm.check_peers()
         P = self.P
+        if getattr(self, "_interleaved", None) is not None:
+            logger.warning("interleave_backward: the previous forward call was not followed by backward(); the "
+                           "gradients it produced are still in the gradient buffers (evaluate under torch.no_grad())")
         inter = interleave_scale is not None and grad_enabled and P > 1 and len(self.order) == 1 and \
             self.order[0] in self.stages
         self._interleaved = float(interleave_scale) if inter else None
