@@ -936,3 +936,24 @@ def test_single_stage_plan_with_interleaved_backward_needs_one_micro_batch_of_me
     conf.interleave_single_stage = True
     sol2, est2, _ = _core.dp_staging(pm, _core.ml_partition(pm, conf), conf)
     assert len(sol2.graphs) == 1 and not sol2.checkpointing and sol2.pipeline_num >= 4
+
+
+def test_bench_reference_arm_reports_unavailable_and_cpu_run_is_refused():
+    """bench.py: the reference arm prints one JSON line saying why the reference cannot run here and exits 0; the
+    library's own arm refuses to produce a number without a CUDA device."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps",
+                        "2", "--warmup", "3"], cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-1000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and len(line["unavailable"]) > 10
+    env = dict(os.environ, RANNC_FORCE_CPU="1", RANK="0", WORLD_SIZE="1", CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--no-baseline", "--layers", "1", "--hidden", "64",
+                        "--heads", "2", "--seq", "16", "--global-batch", "4"], cwd=root, env=env, capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 2 and "CUDA" in r.stderr
